@@ -1,0 +1,146 @@
+"""Compiling and loading the kernel libraries.
+
+Each ``.cu`` file of this folder becomes one shared library for sm_100a, built
+with nvcc at its first use and kept under ``_build/`` beside the sources (or in
+a per-user temporary folder when the source tree cannot be written).  The file
+name carries a hash of the source, of ``common.cuh`` and of the flags, so an
+edited kernel is rebuilt and a stale library is never loaded.  The libraries
+export plain C functions and are loaded with ctypes; they do not link against
+torch.  There is no fallback: if a library cannot be built or loaded, the call
+raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from concurrent.futures import ThreadPoolExecutor
+from typing import Dict, Iterable, List
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-O3", "-lineinfo", "-std=c++17",
+    "--shared", "-Xcompiler", "-fPIC",
+]
+
+# every kernel file of the package; build_all() compiles them all
+SOURCES = ["embed", "norm", "rope_kv", "activation", "gemm_simt", "attention_simt", "sampling"]
+
+
+class KernelBuildError(RuntimeError):
+    pass
+
+
+_libs: Dict[str, ctypes.CDLL] = {}
+_lock = threading.Lock()
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("TRAPETUM_NVCC"),
+                 os.path.join(os.environ.get("CUDA_HOME", ""), "bin", "nvcc") if os.environ.get("CUDA_HOME") else None,
+                 shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.isfile(cand) and os.access(cand, os.X_OK):
+            return cand
+    raise KernelBuildError("nvcc was not found (looked at $TRAPETUM_NVCC, $CUDA_HOME/bin, PATH and "
+                           "/usr/local/cuda/bin); the CUDA kernels cannot be built and there is no fallback")
+
+
+def _build_dir() -> str:
+    d = os.path.join(_HERE, "_build")
+    try:
+        os.makedirs(d, exist_ok=True)
+        probe = os.path.join(d, f".w{os.getpid()}")
+        with open(probe, "w"):
+            pass
+        os.unlink(probe)
+        return d
+    except OSError:
+        d = os.path.join(tempfile.gettempdir(), f"trapetum_b200_build_{os.getuid()}")
+        os.makedirs(d, exist_ok=True)
+        return d
+
+
+def _digest(name: str) -> str:
+    h = hashlib.sha256()
+    for fn in (name + ".cu", "common.cuh"):
+        with open(os.path.join(_HERE, fn), "rb") as f:
+            h.update(f.read())
+    extra = os.path.join(_HERE, name + ".cuh")
+    if os.path.exists(extra):
+        with open(extra, "rb") as f:
+            h.update(f.read())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()[:16]
+
+
+def library_path(name: str) -> str:
+    return os.path.join(_build_dir(), f"tb_{name}-{_digest(name)}.so")
+
+
+def _say(msg: str) -> None:
+    print(f"[trapetum_b200] {msg}", file=sys.stderr, flush=True)
+
+
+def _compile(name: str) -> str:
+    out = library_path(name)
+    if os.path.exists(out):
+        return out
+    src = os.path.join(_HERE, name + ".cu")
+    if not os.path.exists(src):
+        raise KernelBuildError(f"no kernel source {src}")
+    tmp = f"{out}.{os.getpid()}.{threading.get_ident()}.tmp"
+    cmd = [_nvcc()] + NVCC_FLAGS + ["-I", _HERE, "-o", tmp, src]
+    _say(f"compiling {name}.cu for sm_100a ...")
+    t0 = time.time()
+    proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                            cwd=os.path.dirname(out))
+    while True:
+        try:
+            log, _ = proc.communicate(timeout=20)
+            break
+        except subprocess.TimeoutExpired:
+            _say(f"  still compiling {name}.cu ({time.time() - t0:.0f} s)")
+    if proc.returncode != 0:
+        if os.path.exists(tmp):
+            os.unlink(tmp)
+        raise KernelBuildError(f"nvcc failed on {name}.cu:\n{log}")
+    os.replace(tmp, out)
+    _say(f"  built {os.path.basename(out)} in {time.time() - t0:.1f} s")
+    return out
+
+
+def require(names: Iterable[str]) -> None:
+    """Build (in parallel) whatever of ``names`` is not built yet."""
+    todo = [n for n in dict.fromkeys(names) if n not in _libs and not os.path.exists(library_path(n))]
+    if not todo:
+        return
+    with ThreadPoolExecutor(max_workers=min(len(todo), os.cpu_count() or 4)) as ex:
+        list(ex.map(_compile, todo))
+
+
+def load(name: str) -> ctypes.CDLL:
+    with _lock:
+        lib = _libs.get(name)
+        if lib is not None:
+            return lib
+        path = _compile(name)
+        try:
+            lib = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelBuildError(f"cannot load {path}: {e}") from None
+        lib.tb_error.restype = ctypes.c_char_p
+        _libs[name] = lib
+        return lib
+
+
+def build_all() -> List[str]:
+    require(SOURCES)
+    return [library_path(n) for n in SOURCES]

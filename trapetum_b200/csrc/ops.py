@@ -1,0 +1,362 @@
+"""Python faces of the CUDA kernels.
+
+Every function takes CUDA tensors, checks what the kernel relies on (device,
+dtype, contiguity, sizes) and launches on torch's current stream.  There is no
+CPU path and no torch implementation behind these names: a tensor on the CPU,
+or a kernel library that cannot be built, is an error.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+import torch
+
+from . import build
+
+
+class KernelError(RuntimeError):
+    """A kernel refused its arguments or the launch failed."""
+
+
+_CODES = {torch.float32: 0, torch.bfloat16: 1}
+
+PAGE_ROWS = 64          # rows of one cache page
+
+
+def code(dt: torch.dtype) -> int:
+    try:
+        return _CODES[dt]
+    except KeyError:
+        raise KernelError(f"kernels take float32 and bfloat16 tensors, not {dt}") from None
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _cuda(*ts: Optional[torch.Tensor]) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise KernelError("this library computes on the GPU only: got a tensor on " + str(t.device))
+
+
+def _check(lib, status: int, what: str) -> None:
+    if status == 0:
+        return
+    if status < 0:
+        raise KernelError(f"{what}: {lib.tb_error().decode()}")
+    raise KernelError(f"{what}: CUDA error {status} at launch "
+                      f"({torch.cuda.get_device_name() if torch.cuda.is_available() else 'no device'})")
+
+
+def _rows_contig(t: torch.Tensor, what: str) -> None:
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"{what} must be 2-D with contiguous rows, got shape {tuple(t.shape)} strides {t.stride()}")
+
+
+# ---------------------------------------------------------------------------
+def embed(ids: torch.Tensor, table: torch.Tensor, scale: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = float32(table[ids[t]]) * scale."""
+    _cuda(ids, table, out)
+    if ids.dtype != torch.int32 or ids.dim() != 1 or not ids.is_contiguous():
+        raise KernelError("embed: ids must be a contiguous 1-D int32 tensor")
+    if table.dim() != 2 or not table.is_contiguous():
+        raise KernelError("embed: table must be contiguous [vocab, hidden]")
+    V, H = table.shape
+    if out is None:
+        out = torch.empty((ids.numel(), H), dtype=torch.float32, device=ids.device)
+    lib = build.load("embed")
+    _check(lib, lib.tb_embed(_ptr(ids), _ptr(table), c_int(code(table.dtype)), _ptr(out), c_int(ids.numel()),
+                             c_int(H), c_int(V), c_float(scale), _stream()), "embed")
+    return out
+
+
+def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+    """out[i] = x[rows[i]] for a float32 matrix."""
+    _cuda(x, rows)
+    if x.dtype != torch.float32 or x.dim() != 2 or not x.is_contiguous():
+        raise KernelError("gather_rows: x must be contiguous float32 [rows, width]")
+    if rows.dtype != torch.int32 or not rows.is_contiguous():
+        raise KernelError("gather_rows: rows must be contiguous int32")
+    out = torch.empty((rows.numel(), x.shape[1]), dtype=torch.float32, device=x.device)
+    lib = build.load("embed")
+    _check(lib, lib.tb_gather_rows(_ptr(x), _ptr(rows), _ptr(out), c_int(rows.numel()), c_int(x.shape[1]),
+                                   c_int(x.shape[0]), _stream()), "gather_rows")
+    return out
+
+
+# ---------------------------------------------------------------------------
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, offset: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """norm(x) * (offset + w), statistics in 32-bit."""
+    _cuda(x, w)
+    if x.dim() != 2 or not x.is_contiguous() or w.dim() != 1 or w.numel() != x.shape[1] or not w.is_contiguous():
+        raise KernelError(f"rmsnorm: x {tuple(x.shape)} / w {tuple(w.shape)} do not fit")
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    lib = build.load("norm")
+    _check(lib, lib.tb_rmsnorm(_ptr(x), c_int(code(x.dtype)), _ptr(w), c_int(code(w.dtype)), _ptr(out),
+                               c_int(code(out_dtype)), c_int(x.shape[0]), c_int(x.shape[1]), c_float(eps),
+                               c_float(offset), _stream()), "rmsnorm")
+    return out
+
+
+def add_rmsnorm(h: torch.Tensor, a: torch.Tensor, wa: torch.Tensor, eps_a: float, off_a: float,
+                wb: Optional[torch.Tensor] = None, eps_b: float = 0.0, off_b: float = 0.0,
+                out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """h += norm_a(a) in place (h float32); with wb also returns norm_b(h)."""
+    _cuda(h, a, wa, wb)
+    if h.dtype != torch.float32 or h.dim() != 2 or not h.is_contiguous():
+        raise KernelError("add_rmsnorm: the residual stream must be contiguous float32 [rows, width]")
+    if a.shape != h.shape or not a.is_contiguous():
+        raise KernelError(f"add_rmsnorm: branch {tuple(a.shape)} does not fit the stream {tuple(h.shape)}")
+    if wa.numel() != h.shape[1] or (wb is not None and (wb.numel() != h.shape[1] or wb.dtype != wa.dtype)):
+        raise KernelError("add_rmsnorm: norm weights do not fit (both must have the row width and one dtype)")
+    out = None
+    if wb is not None:
+        out = torch.empty(h.shape, dtype=out_dtype, device=h.device)
+    lib = build.load("norm")
+    _check(lib, lib.tb_add_rmsnorm(_ptr(h), _ptr(a), c_int(code(a.dtype)), _ptr(wa), c_float(eps_a), c_float(off_a),
+                                   _ptr(wb), c_float(eps_b), c_float(off_b), c_int(code(wa.dtype)),
+                                   _ptr(out), c_int(code(out_dtype) if out is not None else 0),
+                                   c_int(h.shape[0]), c_int(h.shape[1]), _stream()), "add_rmsnorm")
+    return out
+
+
+def residual_add(h: torch.Tensor, a: torch.Tensor) -> None:
+    _cuda(h, a)
+    if h.dtype != torch.float32 or not h.is_contiguous() or not a.is_contiguous() or a.shape != h.shape:
+        raise KernelError("residual_add: h must be contiguous float32 and a of the same shape")
+    lib = build.load("norm")
+    _check(lib, lib.tb_residual_add(_ptr(h), _ptr(a), c_int(code(a.dtype)), c_longlong(h.numel()), _stream()),
+           "residual_add")
+
+
+# ---------------------------------------------------------------------------
+ACTIVATIONS = {"gelu_tanh": 0, "silu": 1}
+
+
+def gated_act(gu: torch.Tensor, activation: str, out_dtype: torch.dtype) -> torch.Tensor:
+    """act(gu[:, :I]) * gu[:, I:]."""
+    _cuda(gu)
+    if gu.dim() != 2 or not gu.is_contiguous() or gu.shape[1] % 2:
+        raise KernelError("gated_act: input must be contiguous [rows, 2*intermediate]")
+    if activation not in ACTIVATIONS:
+        raise KernelError(f"gated_act: unknown activation '{activation}' (known: {sorted(ACTIVATIONS)})")
+    inter = gu.shape[1] // 2
+    out = torch.empty((gu.shape[0], inter), dtype=out_dtype, device=gu.device)
+    lib = build.load("activation")
+    _check(lib, lib.tb_gated_act(_ptr(gu), c_int(code(gu.dtype)), _ptr(out), c_int(code(out_dtype)),
+                                 c_int(gu.shape[0]), c_int(inter), c_int(ACTIVATIONS[activation]), _stream()),
+           "gated_act")
+    return out
+
+
+# ---------------------------------------------------------------------------
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, softcap: float = 0.0,
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """a[M,K] @ w[N,K]^T with 32-bit FMA (no tensor cores)."""
+    _cuda(a, w, out)
+    _rows_contig(a, "gemm: a")
+    _rows_contig(w, "gemm: w")
+    if a.shape[1] != w.shape[1]:
+        raise KernelError(f"gemm: a is {tuple(a.shape)}, w is {tuple(w.shape)}: inner sizes differ")
+    M, K = a.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    else:
+        _rows_contig(out, "gemm: out")
+    lib = build.load("gemm_simt")
+    _check(lib, lib.tb_gemm_simt(_ptr(a), c_int(code(a.dtype)), _ptr(w), c_int(code(w.dtype)), _ptr(out),
+                                 c_int(code(out.dtype)), c_int(M), c_int(N), c_int(K), c_longlong(a.stride(0)),
+                                 c_longlong(w.stride(0)), c_longlong(out.stride(0)), c_float(softcap or 0.0),
+                                 _stream()), "gemm_simt")
+    return out
+
+
+# ---------------------------------------------------------------------------
+class _RopeKvArgs(ctypes.Structure):
+    _fields_ = [("qkv", c_void_p), ("row_stride", c_longlong),
+                ("q_off", c_int), ("k_off", c_int), ("v_off", c_int),
+                ("n_heads", c_int), ("n_kv_heads", c_int), ("head_dim", c_int), ("rotary_dim", c_int),
+                ("inv_freq", c_void_p), ("positions", c_void_p), ("token_seq", c_void_p), ("len_after", c_void_p),
+                ("k_pool", c_void_p), ("v_pool", c_void_p), ("page_table", c_void_p), ("pt_stride", c_int),
+                ("page_rows", c_int), ("ring_rows", c_int)]
+
+
+def rope_kv(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int,
+            inv_freq: Optional[torch.Tensor], positions: torch.Tensor, token_seq: torch.Tensor,
+            len_after: torch.Tensor, k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
+            page_table: Optional[torch.Tensor], ring_rows: int) -> None:
+    """Rotate q and k of ``qkv`` [T, (n_heads + 2 n_kv_heads) * head_dim] in place and store k, v
+    in the cache line (``k_pool``/``v_pool`` [pages, n_kv_heads, PAGE_ROWS, head_dim])."""
+    _cuda(qkv, inv_freq, positions, token_seq, len_after, k_pool, v_pool, page_table)
+    _rows_contig(qkv, "rope_kv: qkv")
+    T = qkv.shape[0]
+    if qkv.shape[1] != (n_heads + 2 * n_kv_heads) * head_dim:
+        raise KernelError("rope_kv: qkv width does not fit the head counts")
+    for name, t in (("positions", positions), ("token_seq", token_seq)):
+        if t.dtype != torch.int32 or t.numel() != T or not t.is_contiguous():
+            raise KernelError(f"rope_kv: {name} must be contiguous int32 [{T}]")
+    if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.numel() != rotary_dim // 2):
+        raise KernelError("rope_kv: inv_freq must be float32 [rotary_dim/2]")
+    if k_pool is not None:
+        for p in (k_pool, v_pool):
+            if p is None or p.dtype != qkv.dtype or not p.is_contiguous() or tuple(p.shape[1:]) != (n_kv_heads, PAGE_ROWS, head_dim):
+                raise KernelError("rope_kv: cache pools must be contiguous [pages, n_kv_heads, PAGE_ROWS, head_dim] "
+                                  "of the activations' dtype")
+        if page_table is None or page_table.dtype != torch.int32 or page_table.dim() != 2 or page_table.stride(1) != 1:
+            raise KernelError("rope_kv: page_table must be int32 [batch, pages]")
+    a = _RopeKvArgs()
+    a.qkv = qkv.data_ptr(); a.row_stride = qkv.stride(0)
+    a.q_off = 0; a.k_off = n_heads * head_dim; a.v_off = (n_heads + n_kv_heads) * head_dim
+    a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.head_dim = head_dim; a.rotary_dim = rotary_dim
+    a.inv_freq = inv_freq.data_ptr() if inv_freq is not None else None
+    a.positions = positions.data_ptr(); a.token_seq = token_seq.data_ptr(); a.len_after = len_after.data_ptr()
+    a.k_pool = k_pool.data_ptr() if k_pool is not None else None
+    a.v_pool = v_pool.data_ptr() if v_pool is not None else None
+    a.page_table = page_table.data_ptr() if page_table is not None else None
+    a.pt_stride = page_table.stride(0) if page_table is not None else 0
+    a.page_rows = PAGE_ROWS; a.ring_rows = ring_rows
+    lib = build.load("rope_kv")
+    _check(lib, lib.tb_rope_kv(ctypes.byref(a), c_int(code(qkv.dtype)), c_int(T), _stream()), "rope_kv")
+
+
+# ---------------------------------------------------------------------------
+def attn_prefill_simt(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, seq_start: torch.Tensor,
+                      token_seq: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+                      scale: float, softcap: float, window: int) -> torch.Tensor:
+    """Causal attention of packed sequences over their own tokens.  q [T, n_heads*hd] and
+    k, v [T, n_kv_heads*hd] may be column slices of one wider matrix."""
+    _cuda(q, k, v, seq_start, token_seq)
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        _rows_contig(t, "attention: " + name)
+    if k.stride(0) != v.stride(0) or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise KernelError("attention: k and v must share row stride and dtype with q")
+    T = q.shape[0]
+    out = torch.empty((T, n_heads * head_dim), dtype=q.dtype, device=q.device)
+    lib = build.load("attention_simt")
+    _check(lib, lib.tb_attn_prefill_simt(_ptr(q), _ptr(k), _ptr(v), c_longlong(q.stride(0)), c_longlong(k.stride(0)),
+                                         _ptr(seq_start), _ptr(token_seq), _ptr(out), c_int(code(q.dtype)), c_int(T),
+                                         c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_float(scale),
+                                         c_float(softcap or 0.0), c_int(window or 0), _stream()), "attn_prefill_simt")
+    return out
+
+
+class _DecodeArgs(ctypes.Structure):
+    _fields_ = [("q", c_void_p), ("q_stride", c_longlong), ("k_pool", c_void_p), ("v_pool", c_void_p),
+                ("page_table", c_void_p), ("pt_stride", c_int), ("len_after", c_void_p), ("out", c_void_p),
+                ("partial", c_void_p),
+                ("n_heads", c_int), ("n_kv_heads", c_int), ("hd", c_int), ("page_rows", c_int),
+                ("ring_rows", c_int), ("window", c_int), ("n_splits", c_int),
+                ("scale", c_float), ("cap", c_float)]
+
+
+def attn_decode_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
+                     len_after: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
+                     softcap: float, window: int, ring_rows: int, n_splits: int = 1,
+                     scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One query per sequence against the paged cache (the new token's k, v already stored)."""
+    _cuda(q, k_pool, v_pool, page_table, len_after, scratch)
+    _rows_contig(q, "attention: q")
+    B = q.shape[0]
+    if page_table.dtype != torch.int32 or page_table.dim() != 2 or page_table.stride(1) != 1 or page_table.shape[0] < B:
+        raise KernelError("attention: page_table must be int32 [batch, pages]")
+    if len_after.dtype != torch.int32 or len_after.numel() < B:
+        raise KernelError("attention: len_after must be int32 [batch]")
+    out = torch.empty((B, n_heads * head_dim), dtype=q.dtype, device=q.device)
+    need = B * n_heads * n_splits * (head_dim + 2) if n_splits > 1 else 0
+    if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need):
+        scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+    a = _DecodeArgs()
+    a.q = q.data_ptr(); a.q_stride = q.stride(0)
+    a.k_pool = k_pool.data_ptr(); a.v_pool = v_pool.data_ptr()
+    a.page_table = page_table.data_ptr(); a.pt_stride = page_table.stride(0)
+    a.len_after = len_after.data_ptr(); a.out = out.data_ptr()
+    a.partial = scratch.data_ptr() if need else None
+    a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.hd = head_dim; a.page_rows = PAGE_ROWS
+    a.ring_rows = ring_rows; a.window = window or 0; a.n_splits = n_splits
+    a.scale = scale; a.cap = softcap or 0.0
+    lib = build.load("attention_simt")
+    _check(lib, lib.tb_attn_decode_simt(ctypes.byref(a), c_int(code(q.dtype)), c_int(B), _stream()), "attn_decode_simt")
+    return out
+
+
+# ---------------------------------------------------------------------------
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    """Greedy choice per row of float32 logits: int32 ids, the smallest index on a tie."""
+    _cuda(logits)
+    if logits.dtype != torch.float32:
+        raise KernelError("argmax: logits must be float32")
+    _rows_contig(logits, "argmax: logits")
+    rows, V = logits.shape
+    lib = build.load("sampling")
+    lib.tb_argmax_scratch_bytes.restype = c_longlong
+    nbytes = lib.tb_argmax_scratch_bytes(c_int(rows), c_int(V))
+    scratch = torch.empty(max(int(nbytes), 8), dtype=torch.uint8, device=logits.device)
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    _check(lib, lib.tb_argmax(_ptr(logits), c_longlong(logits.stride(0)), c_int(rows), c_int(V), _ptr(out),
+                              _ptr(scratch), _stream()), "argmax")
+    return out
+
+
+class _SampleArgs(ctypes.Structure):
+    _fields_ = [("logits", c_void_p), ("row_stride", c_longlong), ("vocab", c_int),
+                ("temperature", c_void_p), ("top_p", c_void_p), ("penalty", c_void_p), ("draw", c_void_p),
+                ("recent", c_void_p), ("n_recent", c_int), ("out", c_void_p)]
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor, penalty: torch.Tensor,
+           draw: torch.Tensor, recent: Optional[torch.Tensor]) -> torch.Tensor:
+    """Per row: repetition penalty over ``recent`` ids (changes ``logits`` in place), then argmax if
+    the row's temperature is <= 0, else a nucleus draw with the row's ``draw`` in [0,1)."""
+    _cuda(logits, temperature, top_p, penalty, draw, recent)
+    if logits.dtype != torch.float32:
+        raise KernelError("sample: logits must be float32")
+    _rows_contig(logits, "sample: logits")
+    rows, V = logits.shape
+    for name, t in (("temperature", temperature), ("top_p", top_p), ("penalty", penalty), ("draw", draw)):
+        if t.dtype != torch.float32 or t.numel() != rows or not t.is_contiguous():
+            raise KernelError(f"sample: {name} must be contiguous float32 [{rows}]")
+    if recent is not None and (recent.dtype != torch.int32 or recent.dim() != 2 or recent.shape[0] != rows
+                               or not recent.is_contiguous()):
+        raise KernelError("sample: recent must be contiguous int32 [rows, n]")
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    a = _SampleArgs()
+    a.logits = logits.data_ptr(); a.row_stride = logits.stride(0); a.vocab = V
+    a.temperature = temperature.data_ptr(); a.top_p = top_p.data_ptr(); a.penalty = penalty.data_ptr()
+    a.draw = draw.data_ptr()
+    a.recent = recent.data_ptr() if recent is not None else None
+    a.n_recent = recent.shape[1] if recent is not None else 0
+    a.out = out.data_ptr()
+    lib = build.load("sampling")
+    _check(lib, lib.tb_sample(ctypes.byref(a), c_int(rows), _stream()), "sample")
+    return out
+
+
+# ---------------------------------------------------------------------------
+# Choice of kernel per call
+# ---------------------------------------------------------------------------
+def gemm_tc_takes(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the tensor-core GEMM takes these operands."""
+    return False
+
+
+def gemm_tc(a, w, out_dtype, softcap=0.0):
+    raise KernelError("the tensor-core GEMM is not built")
+
+
+def attn_prefill(q, k, v, seq_start, token_seq, n_heads, n_kv_heads, head_dim, scale, softcap, window,
+                 max_seq_len: int) -> torch.Tensor:
+    return attn_prefill_simt(q, k, v, seq_start, token_seq, n_heads, n_kv_heads, head_dim, scale, softcap, window)
+
+
+def attn_decode(q, k_pool, v_pool, page_table, len_after, n_heads, n_kv_heads, head_dim, scale, softcap, window,
+                ring_rows, n_splits: int, max_len_after: int) -> torch.Tensor:
+    return attn_decode_simt(q, k_pool, v_pool, page_table, len_after, n_heads, n_kv_heads, head_dim, scale,
+                            softcap, window, ring_rows, n_splits)

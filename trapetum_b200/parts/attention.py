@@ -1,0 +1,98 @@
+"""Attention as a mixer: grouped-query, causal, optionally windowed and soft-capped.
+
+In the order the reference computes it (runtime/src/lib.rs:4483-4496):
+q, k, v projections without bias; position encoding of q and k; k and v appended
+to the cache; per query ``s = (q.k) * scale``, ``s = cap * tanh(s / cap)`` if a
+cap is set, softmax over the visible keys, weighted sum of v
+(runtime/cuda/codebook_gemv.cu:240-270); output projection.  Query head ``h``
+reads kv head ``h // (num_heads // num_kv_heads)`` (codebook_gemv.cu:244).
+
+Parameters (none is fixed in code): ``hidden_size``, ``num_heads``,
+``num_kv_heads``, ``head_dim``, ``scale``, ``softcap`` (None: off), ``window``
+(None: every earlier token is visible; W: the last W tokens, the query's own
+included), ``position`` (a position-encoding spec) and the four tensor names.
+The reference fixes ``scale = rsqrt(head_dim)`` (codebook_gemv.cu:250) and has
+no window (runtime/src/lib.rs:4455).
+
+The three projections are fused into one matrix when the weights are bound, so
+a step runs one product for q, k and v.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from ..csrc import ops
+from ..weights.loader import TensorSpec
+from .base import KVNeed, Mixer, build_part, register_part
+from .linear import kernel_files as linear_kernels
+from .linear import linear
+
+
+class Attention(Mixer):
+    def __init__(self, params, prefix, rt):
+        super().__init__(params, prefix, rt)
+        p = params
+        self.hidden = int(p["hidden_size"])
+        self.n_heads = int(p["num_heads"])
+        self.n_kv = int(p["num_kv_heads"])
+        self.hd = int(p["head_dim"])
+        self.scale = float(p["scale"])
+        self.softcap = float(p["softcap"]) if p.get("softcap") else 0.0
+        self.window = int(p["window"]) if p.get("window") else None
+        if self.n_heads % self.n_kv:
+            raise ValueError(f"attention: {self.n_heads} heads cannot share {self.n_kv} kv heads")
+        self.position = build_part("position", p["position"], prefix, rt)
+        self.qd = self.n_heads * self.hd
+        self.kvd = self.n_kv * self.hd
+        self.w_qkv: Optional[torch.Tensor] = None
+        self.w_o: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {
+            self._name("q"): TensorSpec((self.qd, self.hidden)),
+            self._name("k"): TensorSpec((self.kvd, self.hidden)),
+            self._name("v"): TensorSpec((self.kvd, self.hidden)),
+            self._name("o"): TensorSpec((self.hidden, self.qd)),
+        }
+
+    def bind(self, tensors) -> None:
+        q, k, v = (tensors[self._name(n)] for n in ("q", "k", "v"))
+        dt = q.dtype if (q.dtype == k.dtype == v.dtype) else torch.float32
+        self.w_qkv = torch.cat([q.to(dt), k.to(dt), v.to(dt)], dim=0).contiguous()
+        self.w_o = tensors[self._name("o")]
+        self.position.bind(tensors)
+
+    def kernel_files(self):
+        return linear_kernels(self.rt.dtype) + self.position.kernel_files() + ("attention_simt",)
+
+    def cache_need(self):
+        return KVNeed(self.n_kv, self.hd, self.window)
+
+    def forward(self, x, ctx, line):
+        dt = self.rt.dtype
+        if line.owner:
+            qkv = linear(x, self.w_qkv, dt)
+            self.position.rotate_and_store(qkv, self.n_heads, self.n_kv, ctx, line, store=True)
+            q = qkv[:, :self.qd]
+            k = qkv[:, self.qd:self.qd + self.kvd]
+            v = qkv[:, self.qd + self.kvd:]
+            if ctx.is_prefill and line.shared:
+                ctx.step_kv[line.entry] = (k, v)      # a later call that reads this cache needs them
+        else:
+            # this call reads another call's cache: only its queries are new
+            q = linear(x, self.w_qkv[:self.qd], dt)
+            self.position.rotate_and_store(q, self.n_heads, 0, ctx, line, store=False)
+            k, v = ctx.step_kv[line.entry] if ctx.is_prefill else (None, None)
+        if ctx.is_prefill:
+            o = ops.attn_prefill(q, k, v, ctx.seq_start, ctx.token_seq, self.n_heads, self.n_kv, self.hd,
+                                 self.scale, self.softcap, self.window or 0, ctx.max_seq_len)
+        else:
+            o = ops.attn_decode(q, line.k, line.v, line.page_table, ctx.len_after, self.n_heads, self.n_kv,
+                                self.hd, self.scale, self.softcap, self.window or 0, line.ring_rows,
+                                ctx.decode_splits, ctx.max_len_after)
+        return linear(o, self.w_o, torch.float32)
+
+
+register_part("mixer", "attention", Attention)

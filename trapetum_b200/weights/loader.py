@@ -1,0 +1,152 @@
+"""Weights by tensor name.
+
+Every part of a model declares the tensors it wants (:class:`TensorSpec`: shape
+and role).  :func:`load_tensors` fetches them from a model folder and reports
+*all* problems at once: names the file lacks, names nobody asked for, and
+shapes that do not fit.  The reference's format is positional and has no such
+check (runtime/src/lib.rs:4564-4604: a short or mismatched file ends in a panic
+inside ``read_exact``).
+
+Storage rules: floating-point tensors stored in 16 bits are kept in bfloat16
+when the engine runs in bfloat16; a tensor stored in 32 bits stays in 32 bits;
+integer tables become int32; the float32 engine up-casts every float tensor to
+float32 (bfloat16 -> float32 is exact: the 16 bits become the upper half of the
+word, as model/export_safetensors.py:38-40 does on the host).
+
+:func:`write_random_model` is the random-weights mode: it writes a model folder
+(config.json and model.safetensors) from a configuration and a seed.
+"""
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import dataclass
+from typing import Dict, Iterable, List, Optional, Tuple
+
+import torch
+
+from .safetensors_io import WeightFileError, open_model_files, write_safetensors
+
+
+class WeightError(RuntimeError):
+    """Missing, unexpected or wrongly shaped tensors; the message lists them all."""
+
+    def __init__(self, folder, missing, unexpected, wrong_shape, wrong_kind=()):
+        self.missing = list(missing)
+        self.unexpected = list(unexpected)
+        self.wrong_shape = list(wrong_shape)
+        self.wrong_kind = list(wrong_kind)
+        lines = [f"weights in {folder} do not fit the model:"]
+        if self.missing:
+            lines.append(f"  missing ({len(self.missing)}): " + ", ".join(self.missing))
+        if self.unexpected:
+            lines.append(f"  unexpected ({len(self.unexpected)}): " + ", ".join(self.unexpected))
+        if self.wrong_shape:
+            lines.append(f"  wrong shape ({len(self.wrong_shape)}): " + ", ".join(
+                f"{n} is {list(got)}, expected {list(want)}" for n, got, want in self.wrong_shape))
+        if self.wrong_kind:
+            lines.append(f"  wrong dtype ({len(self.wrong_kind)}): " + ", ".join(
+                f"{n} is {got}, expected {want}" for n, got, want in self.wrong_kind))
+        super().__init__("\n".join(lines))
+
+
+@dataclass(frozen=True)
+class TensorSpec:
+    """What a part expects of one tensor.
+
+    role: ``"matrix"`` and ``"embedding"`` are drawn N(0, std) in random mode,
+    ``"norm"`` N(0, norm_std); ``"table"`` is an integer table (zeros in random
+    mode).  ``optional`` tensors may be absent (the part then falls back, for
+    instance a tied output head)."""
+    shape: Tuple[int, ...]
+    role: str = "matrix"
+    optional: bool = False
+
+
+def _is_float(dt: torch.dtype) -> bool:
+    return dt in (torch.bfloat16, torch.float16, torch.float32, torch.float64)
+
+
+def storage_dtype(stored: torch.dtype, role: str, engine_dtype: torch.dtype) -> torch.dtype:
+    """The dtype a tensor has on the device, given how the file stores it."""
+    if role == "table":
+        return torch.int32
+    if engine_dtype == torch.float32:
+        return torch.float32
+    if stored in (torch.float32, torch.float64):
+        return torch.float32          # stored in 32 bits: stays so
+    return torch.bfloat16
+
+
+def load_tensors(folder: str, wanted: Dict[str, TensorSpec], engine_dtype: torch.dtype,
+                 device) -> Dict[str, torch.Tensor]:
+    files = open_model_files(folder)
+    missing, unexpected, wrong_shape, wrong_kind = [], [], [], []
+    for name, spec in wanted.items():
+        if name not in files:
+            if not spec.optional:
+                missing.append(name)
+            continue
+        got = files[name].shape(name)
+        if tuple(got) != tuple(spec.shape):
+            wrong_shape.append((name, got, spec.shape))
+        stored = files[name].dtype(name)
+        if spec.role == "table" and _is_float(stored):
+            wrong_kind.append((name, str(stored).replace("torch.", ""), "an integer type"))
+        if spec.role != "table" and not _is_float(stored):
+            wrong_kind.append((name, str(stored).replace("torch.", ""), "a floating-point type"))
+    for name in files:
+        if name not in wanted:
+            unexpected.append(name)
+    if missing or unexpected or wrong_shape or wrong_kind:
+        raise WeightError(folder, sorted(missing), sorted(unexpected), wrong_shape, wrong_kind)
+
+    out: Dict[str, torch.Tensor] = {}
+    for name, spec in wanted.items():
+        if name not in files:
+            continue
+        f = files[name]
+        dt = storage_dtype(f.dtype(name), spec.role, engine_dtype)
+        t = f.tensor(name)
+        # .to() copies out of the memory map; the device copy owns its bytes
+        out[name] = t.to(device=device, dtype=dt, copy=True).contiguous()
+    for f in set(files.values()):
+        f.close()
+    return out
+
+
+def random_tensors(wanted: Dict[str, TensorSpec], seed: int, std: float, norm_std: float,
+                   dtype: torch.dtype = torch.bfloat16, device="cpu",
+                   norm_dtype: Optional[torch.dtype] = None) -> Iterable[Tuple[str, torch.Tensor]]:
+    """Seeded random tensors in the order of ``wanted`` (one generator, drawn in
+    that order, so a folder is reproducible from configuration and seed)."""
+    gen = torch.Generator(device=device)
+    gen.manual_seed(int(seed))
+    for name, spec in wanted.items():
+        if spec.optional:
+            continue
+        if spec.role == "table":
+            yield name, torch.zeros(spec.shape, dtype=torch.int32, device=device)
+            continue
+        s = norm_std if spec.role == "norm" else std
+        t = torch.empty(spec.shape, dtype=torch.float32, device=device)
+        t.normal_(0.0, s, generator=gen)
+        yield name, t.to(norm_dtype if (spec.role == "norm" and norm_dtype is not None) else dtype)
+
+
+def write_random_model(folder: str, config: dict, seed: int, std: float = 0.02, norm_std: float = 0.1,
+                       norm_dtype: Optional[torch.dtype] = None) -> str:
+    """Random-weights mode: make ``folder`` a model folder for ``config``.
+
+    The reference's checks build synthetic models from a fixed seed in the same
+    spirit (runtime/src/bin/model.rs:158-177).  Values are rounded to bfloat16
+    before they are stored, so every reader sees the same numbers."""
+    from ..engine.model import tensor_specs_for_config  # late: avoids an import cycle
+    wanted = tensor_specs_for_config(config)
+    os.makedirs(folder, exist_ok=True)
+    with open(os.path.join(folder, "config.json"), "w", encoding="utf-8") as f:
+        json.dump(config, f, indent=1)
+    write_safetensors(os.path.join(folder, "model.safetensors"),
+                      random_tensors(wanted, seed, std, norm_std, norm_dtype=norm_dtype),
+                      metadata={"format": "pt", "seed": seed})
+    return folder
