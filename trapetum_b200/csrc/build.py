@@ -32,7 +32,7 @@ NVCC_FLAGS = [
 ]
 
 # every kernel file of the package; build_all() compiles them all
-SOURCES = ["embed", "norm", "rope_kv", "activation", "gemm_simt", "attention_simt", "sampling"]
+SOURCES = ["embed", "norm", "rope_kv", "activation", "gemm_simt", "gemm_tc", "attention_simt", "sampling"]
 
 
 class KernelBuildError(RuntimeError):
@@ -41,6 +41,7 @@ class KernelBuildError(RuntimeError):
 
 _libs: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
+_dir_lock = threading.Lock()
 
 
 def _nvcc() -> str:
@@ -53,7 +54,20 @@ def _nvcc() -> str:
                            "/usr/local/cuda/bin); the CUDA kernels cannot be built and there is no fallback")
 
 
+_build_dir_cached = None
+
+
 def _build_dir() -> str:
+    """The folder the libraries live in; decided once per process."""
+    global _build_dir_cached
+    if _build_dir_cached is None:
+        with _dir_lock:
+            if _build_dir_cached is None:
+                _build_dir_cached = _pick_build_dir()
+    return _build_dir_cached
+
+
+def _pick_build_dir() -> str:
     d = os.path.join(_HERE, "_build")
     try:
         os.makedirs(d, exist_ok=True)

@@ -1,0 +1,500 @@
+// C[M,N] = A[M,K] * W[N,K]^T in bfloat16 on the 5th-generation tensor cores.
+//
+// tcgen05.mma (cta_group::1, kind::f16, 128 x BN x 16 per instruction) issued by one
+// thread, operands staged in shared memory by TMA (128-byte swizzle, K-major),
+// accumulators in tensor memory, read back with tcgen05.ld for the epilogue.
+// The reference has no dense tensor-core product: its linears are 4-bit codebook
+// GEMVs (runtime/cuda/codebook_gemv.cu:86-114) with a fixed-order second stage
+// for determinism (:178-184); the same rule holds here (no atomics anywhere).
+//
+// One kernel, two orientations, chosen by the host:
+//   tokens >  128: the 128 lanes of a tile are tokens, its BN columns weight rows
+//   tokens <= 128: swapped, the 128 lanes are weight rows and the BN columns are the
+//                  tokens (BN = 16..128), so a decode step streams every weight
+//                  once through full-height MMA tiles whatever the batch size
+// and optional split-K (small N, large K): each split writes 32-bit partials to
+// scratch and tb_splitk_reduce adds them in split order.
+//
+// Roles per CTA (192 threads): warp 0 issues TMA loads, warp 1 owns tensor memory
+// and issues the MMAs, warps 2..5 are the epilogue (a warp reads the 32 lanes of
+// tensor memory that its index modulo 4 selects).  The kernel is persistent: a
+// CTA walks its share of the work items; two accumulator stages let the epilogue
+// of one item overlap the MMAs of the next.
+//
+// Every wait on an mbarrier is bounded.  A wait that runs out records a code in
+// the error word, and all roles leave their loops, wait (bounded) for TMA loads
+// still in flight, free the tensor memory and return.  tb_gemm_tc_error() reads
+// and clears the word.
+//
+// Sizes: K must be a multiple of 8 elements and A, W 16-byte aligned (TMA strides);
+// anything else is refused and the caller falls back to the FMA kernel.
+#include "common.cuh"
+#include <cuda.h>
+
+TB_EXPORT_ERROR()
+
+#define BM 128
+#define BK 64
+#define UMMA_K 16
+#define WAIT_CYCLES 4000000000LL     /* about two seconds: far beyond any legitimate wait */
+
+__device__ int g_gemm_error = 0;
+
+// ---------------------------------------------------------------------------
+// PTX helpers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait; false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity))
+        if (clock64() - t0 > WAIT_CYCLES) return false;
+    return true;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major tile of rows x 64 bf16 (128 bytes per row),
+// 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3ffff) >> 4);          // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                          // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                          // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                          // 128-byte swizzle
+    return d;
+}
+// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t instr_desc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+// ---------------------------------------------------------------------------
+struct GemmParams {
+    int rows_p, rows_q, K;           // P: the 128-lane operand, Q: the BN-column operand
+    int tiles_p, tiles_q, splits, kb_per_split, kblocks;
+    void* out; long long ld_out;     // C as [tokens, weight rows], row stride ld_out
+    float* partial;                  // [splits][tokens][weight rows] when splits > 1
+    float cap;
+};
+
+template <int BN> struct Cfg {
+    static constexpr int STAGE_BYTES = BM * BK * 2 + BN * BK * 2;
+    static constexpr int STAGES_RAW = (200 * 1024) / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_RAW > 10 ? 10 : STAGES_RAW;
+    static constexpr int ACC_COLS = BN < 32 ? 32 : BN;               // columns of one accumulator stage
+    static constexpr int TMEM_COLS = 2 * ACC_COLS;                   // a power of two >= 32
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
+};
+
+template <int BN, bool SWAP, typename TOut>
+__global__ void __launch_bounds__(192, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, GemmParams p) {
+    using C = Cfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(smem + C::STAGES * C::STAGE_BYTES);
+    uint64_t* full = bars;                       // [STAGES]
+    uint64_t* empty = bars + C::STAGES;          // [STAGES]
+    uint64_t* acc_full = bars + 2 * C::STAGES;   // [2]
+    uint64_t* acc_empty = acc_full + 2;          // [2]
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int n_items = p.tiles_p * p.tiles_q * p.splits;
+    // item -> (tile_q, tile_p, split): the tiles that share a Q tile (prefill: a weight
+    // tile; swapped: the tokens) run side by side
+    auto decode = [&](int item, int& tp, int& tq, int& sp) {
+        sp = item % p.splits; item /= p.splits;
+        tp = item % p.tiles_p; tq = item / p.tiles_p;
+    };
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+                int tp, tq, sp; decode(item, tp, tq, sp);
+                const int kb0 = sp * p.kb_per_split, kb1 = min(p.kblocks, kb0 + p.kb_per_split);
+                for (int kb = kb0; kb < kb1; kb++, it++) {
+                    const int s = it % C::STAGES; const uint32_t ph = (it / C::STAGES) & 1;
+                    if (*abort_flag || !mbar_wait(&empty[s], ph ^ 1)) { ok = false; break; }
+                    uint8_t* sa = smem + s * C::STAGE_BYTES;
+                    mbar_expect_tx(&full[s], C::STAGE_BYTES);
+                    tma_load_2d(sa, &map_p, &full[s], kb * BK, tp * BM);
+                    tma_load_2d(sa + BM * BK * 2, &map_q, &full[s], kb * BK, tq * BN);
+                }
+            }
+            if (!ok) {
+                if (!*abort_flag) { atomicExch(&g_gemm_error, 1); *abort_flag = 1; }
+                // loads already issued still land in this CTA's shared memory: wait for them
+                for (uint32_t back = 1; back <= (uint32_t)C::STAGES && back <= it; back++) {
+                    const uint32_t j = it - back;
+                    mbar_wait(&full[j % C::STAGES], (j / C::STAGES) & 1);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc(BN);
+            uint32_t it = 0, tile_it = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, tile_it++) {
+                int tp, tq, sp; decode(item, tp, tq, sp);
+                const int kb0 = sp * p.kb_per_split, kb1 = min(p.kblocks, kb0 + p.kb_per_split);
+                const int a = tile_it & 1; const uint32_t aph = (tile_it >> 1) & 1;
+                if (*abort_flag || !mbar_wait(&acc_empty[a], aph ^ 1)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_addr = tmem_base + a * C::ACC_COLS;
+                for (int kb = kb0; kb < kb1; kb++, it++) {
+                    const int s = it % C::STAGES; const uint32_t ph = (it / C::STAGES) & 1;
+                    if (*abort_flag || !mbar_wait(&full[s], ph)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + s * C::STAGE_BYTES);
+                    const uint32_t sb = sa + BM * BK * 2;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; k++) {
+                        umma_bf16(d_addr, smem_desc(sa + k * UMMA_K * 2), smem_desc(sb + k * UMMA_K * 2), idesc,
+                                  (kb > kb0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&empty[s]);            // frees the stage once these MMAs have read it
+                }
+                if (ok) umma_commit(&acc_full[a]);     // the accumulator is complete
+            }
+            if (!ok && !*abort_flag) { atomicExch(&g_gemm_error, 2); *abort_flag = 1; }
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5 ----------------
+        const int quarter = warp & 3;                  // the TMEM lanes this warp may read
+        uint32_t tile_it = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, tile_it++) {
+            int tp, tq, sp; decode(item, tp, tq, sp);
+            const int a = tile_it & 1; const uint32_t aph = (tile_it >> 1) & 1;
+            // the decision must be the same in every lane: tcgen05.ld is a warp-wide instruction
+            const bool mine = !*abort_flag && mbar_wait(&acc_full[a], aph);
+            if (!__all_sync(0xffffffffu, mine)) { ok = false; break; }
+            tc_fence_after();
+            const int prow = tp * BM + quarter * 32 + lane;            // row of P this thread holds
+            const uint32_t t_addr = tmem_base + a * C::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+            constexpr int CH = BN >= 32 ? 32 : 16;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += CH) {
+                uint32_t r[CH];
+                if (CH == 32) tmem_ld32(t_addr + c0, r); else tmem_ld16(t_addr + c0, r);
+                tmem_ld_wait();
+                const int q0 = tq * BN + c0;                           // first row of Q in this chunk
+                if (!SWAP) {
+                    // tokens on lanes (prow), weight rows on columns (q0 + j): a thread writes a row segment
+                    if (prow < p.rows_p) {
+                        if (p.splits > 1) {
+                            float* dst = p.partial + ((size_t)sp * p.rows_p + prow) * p.rows_q + q0;
+#pragma unroll
+                            for (int j = 0; j < CH; j++) if (q0 + j < p.rows_q) dst[j] = __uint_as_float(r[j]);
+                        } else {
+                            TOut* dst = (TOut*)p.out + (size_t)prow * p.ld_out + q0;
+                            const bool vec = (q0 + CH <= p.rows_q) && ((((uintptr_t)dst) & 15) == 0);
+                            if (vec && sizeof(TOut) == 2) {
+#pragma unroll
+                                for (int j = 0; j < CH; j += 8) {
+                                    uint32_t w[4];
+#pragma unroll
+                                    for (int e = 0; e < 4; e++) {
+                                        float v0 = __uint_as_float(r[j + 2 * e]), v1 = __uint_as_float(r[j + 2 * e + 1]);
+                                        if (p.cap > 0.f) { v0 = softcap_f(v0, p.cap); v1 = softcap_f(v1, p.cap); }
+                                        __nv_bfloat162 h2 = __floats2bfloat162_rn(v0, v1);
+                                        w[e] = *(uint32_t*)&h2;
+                                    }
+                                    *(uint4*)((bf16*)dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
+                                }
+                            } else if (vec) {
+#pragma unroll
+                                for (int j = 0; j < CH; j += 4) {
+                                    float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                           __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                                    if (p.cap > 0.f) { v.x = softcap_f(v.x, p.cap); v.y = softcap_f(v.y, p.cap);
+                                                       v.z = softcap_f(v.z, p.cap); v.w = softcap_f(v.w, p.cap); }
+                                    *(float4*)((float*)dst + j) = v;
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < CH; j++) if (q0 + j < p.rows_q) {
+                                    float v = __uint_as_float(r[j]);
+                                    if (p.cap > 0.f) v = softcap_f(v, p.cap);
+                                    dst[j] = from_f<TOut>(v);
+                                }
+                            }
+                        }
+                    }
+                } else {
+                    // weight rows on lanes (prow), tokens on columns (q0 + j): lanes write neighbours
+                    if (prow < p.rows_p) {
+#pragma unroll
+                        for (int j = 0; j < CH; j++) {
+                            const int tok = q0 + j;
+                            if (tok >= p.rows_q) break;
+                            float v = __uint_as_float(r[j]);
+                            if (p.splits > 1) {
+                                p.partial[((size_t)sp * p.rows_q + tok) * p.rows_p + prow] = v;
+                            } else {
+                                if (p.cap > 0.f) v = softcap_f(v, p.cap);
+                                ((TOut*)p.out)[(size_t)tok * p.ld_out + prow] = from_f<TOut>(v);
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[a]);
+        }
+        if (!ok && !*abort_flag && lane == 0) { atomicExch(&g_gemm_error, 3); *abort_flag = 1; }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
+}
+
+// partial[splits][rows][cols] summed in split order, then cap and conversion.
+template <typename TOut>
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, TOut* __restrict__ out, int rows, int cols,
+                                     long long ld_out, int splits, float cap) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t n = (size_t)rows * cols;
+    if (i >= n) return;
+    float s = 0.f;
+    for (int k = 0; k < splits; k++) s += partial[(size_t)k * n + i];
+    if (cap > 0.f) s = softcap_f(s, cap);
+    out[(i / cols) * ld_out + (i % cols)] = from_f<TOut>(s);
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// rows x K bf16 matrix with row stride ld (elements); box = box_rows x 64 elements, 128-byte swizzle.
+static int make_map(CUtensorMap* m, const void* base, long long rows, long long K, long long ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return tb_refuse("gemm_tc: the driver does not provide cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return tb_refuse("gemm_tc: cuTensorMapEncodeTiled failed with %d", (int)r);
+    return 0;
+}
+
+static int g_sms = 0;
+
+template <int BN, bool SWAP, typename TOut>
+static int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmParams& p, cudaStream_t stream) {
+    using C = Cfg<BN>;
+    static bool attr_set = false;
+    auto kern = gemm_tc_kernel<BN, SWAP, TOut>;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    const int items = p.tiles_p * p.tiles_q * p.splits;
+    const int grid = items < g_sms ? items : g_sms;
+    kern<<<grid, 192, C::SMEM, stream>>>(mp, mq, p);
+    return tb_launch_status();
+}
+
+extern "C" int tb_gemm_tc_takes(const void* A, const void* W, int M, int N, int K, long long lda, long long ldw) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if (K % 8 || lda % 8 || ldw % 8) return 0;
+    if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return 0;
+    return 1;
+}
+
+extern "C" long long tb_gemm_tc_scratch_floats(int M, int N, int splits) {
+    return splits > 1 ? (long long)splits * M * N : 0;
+}
+
+// How many K splits a small-token product should use so that about one CTA per SM streams weights.
+extern "C" int tb_gemm_tc_splits(int M, int N, int K, int sms) {
+    if (M > BM) return 1;
+    const int tiles = (N + BM - 1) / BM;
+    const int kblocks = (K + BK - 1) / BK;
+    if (tiles * 2 > sms) return 1;
+    int s = sms / tiles;
+    if (s > kblocks / 2) s = kblocks / 2;          // at least two k-blocks per split
+    if (s > 16) s = 16;
+    if (s < 1) s = 1;
+    const int per = (kblocks + s - 1) / s;
+    return (kblocks + per - 1) / per;              // every split non-empty
+}
+
+extern "C" int tb_gemm_tc(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K,
+                          long long lda, long long ldw, long long ldc, float softcap, int splits, float* scratch,
+                          cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (!tb_gemm_tc_takes(A, W, M, N, K, lda, ldw))
+        return tb_refuse("gemm_tc: needs K, lda, ldw multiples of 8 and 16-byte aligned operands "
+                         "(M=%d N=%d K=%d lda=%lld ldw=%lld)", M, N, K, lda, ldw);
+    if (c_dtype != TB_F32 && c_dtype != TB_BF16) return tb_refuse("gemm_tc: unknown output dtype %d", c_dtype);
+    if (!g_sms) {
+        int dev = 0; cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev);
+        if (g_sms <= 0) g_sms = 148;
+    }
+    const int kblocks = (K + BK - 1) / BK;
+    if (splits < 1) splits = 1;
+    if (splits > kblocks) splits = kblocks;
+    int per = (kblocks + splits - 1) / splits;
+    splits = (kblocks + per - 1) / per;
+    if (splits > 1 && scratch == nullptr) return tb_refuse("gemm_tc: split-K needs scratch");
+
+    const bool swap = M <= BM;
+    int bn;
+    if (swap) bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+    else bn = N >= 256 ? 256 : 128;
+
+    GemmParams p;
+    p.K = K; p.kblocks = kblocks; p.splits = splits; p.kb_per_split = per;
+    p.out = C; p.ld_out = ldc; p.partial = scratch; p.cap = splits > 1 ? 0.f : softcap;
+    CUtensorMap mp, mq;
+    if (swap) {
+        p.rows_p = N; p.rows_q = M;
+        if (make_map(&mp, W, N, K, ldw, BM) || make_map(&mq, A, M, K, lda, bn)) return -1;
+    } else {
+        p.rows_p = M; p.rows_q = N;
+        if (make_map(&mp, A, M, K, lda, BM) || make_map(&mq, W, N, K, ldw, bn)) return -1;
+    }
+    p.tiles_p = (p.rows_p + BM - 1) / BM;
+    p.tiles_q = (p.rows_q + bn - 1) / bn;
+
+    int st;
+#define GO(BN_, SW_) (c_dtype == TB_BF16 ? launch<BN_, SW_, bf16>(mp, mq, p, stream) : launch<BN_, SW_, float>(mp, mq, p, stream))
+    if (swap) {
+        switch (bn) {
+        case 16: st = GO(16, true); break;
+        case 32: st = GO(32, true); break;
+        case 64: st = GO(64, true); break;
+        default: st = GO(128, true); break;
+        }
+    } else {
+        st = bn == 256 ? GO(256, false) : GO(128, false);
+    }
+#undef GO
+    if (st) return st;
+    if (splits > 1) {
+        const size_t n = (size_t)M * N;
+        const unsigned blocks = (unsigned)((n + 255) / 256);
+        if (c_dtype == TB_BF16)
+            splitk_reduce_kernel<bf16><<<blocks, 256, 0, stream>>>(scratch, (bf16*)C, M, N, ldc, splits, softcap);
+        else
+            splitk_reduce_kernel<float><<<blocks, 256, 0, stream>>>(scratch, (float*)C, M, N, ldc, splits, softcap);
+        st = tb_launch_status();
+    }
+    return st;
+}
+
+// Reads and clears the error word (0 = no wait ran out).  Synchronises the device.
+extern "C" int tb_gemm_tc_error() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_gemm_error, sizeof(int)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int));
+    return v;
+}

@@ -342,13 +342,58 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor,
 # ---------------------------------------------------------------------------
 # Choice of kernel per call
 # ---------------------------------------------------------------------------
+_SMS = {}
+
+
+def sm_count(device=None) -> int:
+    idx = torch.cuda.current_device() if device is None else (torch.device(device).index or 0)
+    if idx not in _SMS:
+        _SMS[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _SMS[idx]
+
+
 def gemm_tc_takes(a: torch.Tensor, w: torch.Tensor) -> bool:
-    """Whether the tensor-core GEMM takes these operands."""
-    return False
+    """Whether the tensor-core GEMM takes these operands (bfloat16, K and row strides multiples
+    of 8 elements, 16-byte aligned); otherwise the FMA kernel computes the product."""
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or a.dim() != 2 or w.dim() != 2:
+        return False
+    if a.stride(1) != 1 or w.stride(1) != 1 or a.shape[1] != w.shape[1]:
+        return False
+    K = a.shape[1]
+    return (K % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def gemm_tc(a, w, out_dtype, softcap=0.0):
-    raise KernelError("the tensor-core GEMM is not built")
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, softcap: float = 0.0,
+            splits: Optional[int] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """a[M,K] @ w[N,K]^T in bfloat16 on tcgen05 tensor cores with 32-bit accumulation.
+    ``splits`` None: the library picks the K split (more than 1 only for few tokens and few weight rows)."""
+    _cuda(a, w, out)
+    if not gemm_tc_takes(a, w):
+        raise KernelError(f"gemm_tc does not take a {tuple(a.shape)}/{a.stride()} {a.dtype}, "
+                          f"w {tuple(w.shape)}/{w.stride()} {w.dtype}")
+    M, K = a.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    else:
+        _rows_contig(out, "gemm: out")
+    lib = build.load("gemm_tc")
+    if splits is None:
+        splits = lib.tb_gemm_tc_splits(c_int(M), c_int(N), c_int(K), c_int(sm_count(a.device)))
+    scratch = None
+    if splits > 1:
+        scratch = torch.empty(splits * M * N, dtype=torch.float32, device=a.device)
+    _check(lib, lib.tb_gemm_tc(_ptr(a), _ptr(w), _ptr(out), c_int(code(out.dtype)), c_int(M), c_int(N), c_int(K),
+                               c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
+                               c_float(softcap or 0.0), c_int(splits), _ptr(scratch), _stream()), "gemm_tc")
+    return out
+
+
+def gemm_tc_error() -> int:
+    """Reads and clears the tensor-core GEMM's error word (synchronises): 0, or the role whose
+    bounded wait ran out (1 loader, 2 MMA issuer, 3 epilogue)."""
+    return int(build.load("gemm_tc").tb_gemm_tc_error())
 
 
 def attn_prefill(q, k, v, seq_start, token_seq, n_heads, n_kv_heads, head_dim, scale, softcap, window,

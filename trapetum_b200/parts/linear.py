@@ -22,4 +22,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, softcap: Op
 
 
 def kernel_files(dtype: torch.dtype):
-    return ("gemm_simt", "gemm_tc") if dtype == torch.bfloat16 else ("gemm_simt",)
+    from ..csrc import build
+    if dtype == torch.bfloat16 and "gemm_tc" in build.SOURCES:
+        return ("gemm_simt", "gemm_tc")
+    return ("gemm_simt",)
