@@ -1,0 +1,86 @@
+"""Shared pieces of the tests: the tiny configurations, model folders made in a temporary
+place, and the error measures."""
+import json
+import os
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+for p in (ROOT, os.path.dirname(os.path.abspath(__file__))):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on the GPU box)")
+
+
+def _cfg(**kw):
+    base = {"architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2", "hidden_activation": "gelu_pytorch_tanh",
+            "tie_word_embeddings": True, "max_position_embeddings": 8192}
+    base.update(kw)
+    return base
+
+
+# Two tiny configurations that differ in every size and option, plus a third for what both share.
+TINY_A = _cfg(num_hidden_layers=2, hidden_size=64, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+              intermediate_size=128, vocab_size=256, rope_theta=10000.0, sliding_window=8, query_pre_attn_scalar=16,
+              attn_logit_softcapping=50.0, final_logit_softcapping=30.0, rms_norm_eps=1e-6)
+TINY_B = _cfg(num_hidden_layers=3, hidden_size=96, num_attention_heads=6, num_key_value_heads=1, head_dim=32,
+              intermediate_size=160, vocab_size=384, rope_theta=1000.0, sliding_window=16, query_pre_attn_scalar=32,
+              attn_logit_softcapping=None, final_logit_softcapping=15.0, rms_norm_eps=1e-5)
+# query_pre_attn_scalar != head_dim, no final cap, as many kv heads as heads, a window that never bites
+# a short prompt but does bite a long one, one layer more than B, a vocabulary and widths that are no
+# power of two and not multiples of 8 (so the bfloat16 path must take its FMA fallback for some products).
+TINY_C = _cfg(num_hidden_layers=4, hidden_size=72, num_attention_heads=3, num_key_value_heads=3, head_dim=48,
+              intermediate_size=100, vocab_size=301, rope_theta=50000.0, sliding_window=70, query_pre_attn_scalar=24,
+              attn_logit_softcapping=20.0, final_logit_softcapping=None, rms_norm_eps=1e-4)
+
+TINY = {"A": (TINY_A, 0, 0.02, 0.1), "B": (TINY_B, 1, 0.03, 0.2), "C": (TINY_C, 5, 0.05, 0.3)}
+
+# Tolerances on logits against the plain implementation (relative L2 over a position's logits,
+# the reference's measure: runtime/src/bin/model.rs:131-139).
+TOL = {"float32": 1e-5, "bfloat16": 2e-2}
+
+
+def rel_l2(got: torch.Tensor, want: torch.Tensor) -> float:
+    got, want = got.double().cpu(), want.double().cpu()
+    return float((got - want).norm() / want.norm().clamp_min(1e-30))
+
+
+def sharpen(folder: str, factor: float = 8.0) -> None:
+    """Scale the query and key projections so that attention is peaked: with weights of
+    N(0, 0.02) every softmax is nearly flat and a wrong key would barely move the logits."""
+    from safetensors.torch import load_file, save_file
+    path = os.path.join(folder, "model.safetensors")
+    w = load_file(path)
+    for k in list(w):
+        if k.endswith("q_proj.weight") or k.endswith("k_proj.weight"):
+            w[k] = (w[k].float() * factor).to(w[k].dtype)
+    save_file(w, path)
+
+
+@pytest.fixture(scope="session")
+def model_folders(tmp_path_factory):
+    """name -> folder with config.json and model.safetensors (random weights, sharpened attention)."""
+    import trapetum_b200 as tb
+    out = {}
+    for name, (cfg, seed, std, nstd) in TINY.items():
+        d = str(tmp_path_factory.mktemp("tiny" + name))
+        tb.write_random_model(d, cfg, seed, std, nstd)
+        sharpen(d)
+        out[name] = d
+    return out
+
+
+@pytest.fixture(scope="session")
+def plain_models(model_folders):
+    import plain_gemma2 as plain
+    return {name: plain.load_folder(d) for name, d in model_folders.items()}
+
+
+def make_prompts(vocab: int, lengths, seed: int):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lengths]

@@ -1,0 +1,388 @@
+"""Each CUDA kernel alone against a plain float32 torch formula, at sizes the engine's tiny
+models do not use (odd widths, head sizes in steps of 16, group sizes, long rows)."""
+import math
+
+import pytest
+import torch
+
+import plain_gemma2 as plain
+
+pytestmark = pytest.mark.gpu
+
+DT = [torch.float32, torch.bfloat16]
+PAGE = 64
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from trapetum_b200.csrc import ops as o
+    assert torch.cuda.is_available(), "these tests need a GPU"
+    return o
+
+
+def tol(dt):
+    return 2e-6 if dt == torch.float32 else 1e-2
+
+
+def close(got, want, dt, scale=1.0):
+    got, want = got.float().cpu(), want.float().cpu()
+    err = float((got - want).abs().max())
+    ref = float(want.abs().max()) + 1e-6
+    assert err <= tol(dt) * scale * max(ref, 1.0), f"max abs err {err} (ref max {ref})"
+
+
+def rnd(*shape, dt=torch.float32, s=1.0, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, device="cuda", generator=g) * s).to(dt)
+
+
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("V,H", [(50, 24), (301, 1000), (1024, 2304)])
+def test_embed(ops, dt, V, H):
+    table = rnd(V, H, dt=dt)
+    ids = torch.tensor([0, V - 1, 3, 3, V // 2], dtype=torch.int32, device="cuda")
+    out = ops.embed(ids, table, 7.5)
+    assert out.dtype == torch.float32
+    assert torch.equal(out, table.float()[ids.long()] * 7.5)
+    bad = ops.embed(torch.tensor([V, -1], dtype=torch.int32, device="cuda"), table, 1.0)
+    assert torch.isnan(bad).all()                     # an id outside the table cannot pass for a result
+
+
+def test_gather_rows(ops):
+    x = rnd(37, 131)
+    rows = torch.tensor([36, 0, 5, 5], dtype=torch.int32, device="cuda")
+    assert torch.equal(ops.gather_rows(x, rows), x[rows.long()])
+
+
+@pytest.mark.parametrize("xdt", DT)
+@pytest.mark.parametrize("wdt", DT)
+@pytest.mark.parametrize("odt", DT)
+@pytest.mark.parametrize("rows,width,eps,off", [(3, 17, 1e-6, 1.0), (5, 2304, 1e-5, 1.0), (2, 5000, 1e-3, 0.0)])
+def test_rmsnorm(ops, xdt, wdt, odt, rows, width, eps, off):
+    x, w = rnd(rows, width, dt=xdt, s=3.0), rnd(width, dt=wdt, s=0.3)
+    got = ops.rmsnorm(x, w, eps, off, odt)
+    xf, wf = x.float(), w.float()
+    want = xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + eps) * (off + wf)
+    close(got, want, odt)
+
+
+@pytest.mark.parametrize("adt", DT)
+@pytest.mark.parametrize("odt", DT)
+@pytest.mark.parametrize("rows,width", [(4, 72), (3, 2304), (1, 4099)])
+def test_add_rmsnorm(ops, adt, odt, rows, width):
+    h0, a = rnd(rows, width, s=2.0), rnd(rows, width, dt=adt, s=5.0, seed=1)
+    wa, wb = rnd(width, dt=odt, s=0.2, seed=2), rnd(width, dt=odt, s=0.2, seed=3)
+    af = a.float()
+    add = af * torch.rsqrt((af * af).mean(-1, keepdim=True) + 1e-6) * (1.0 + wa.float())
+    h = h0.clone()
+    assert ops.add_rmsnorm(h, a, wa, 1e-6, 1.0) is None
+    close(h, h0 + add, torch.float32, 2.0)
+    h = h0.clone()
+    x = ops.add_rmsnorm(h, a, wa, 1e-6, 1.0, wb, 1e-5, 0.0, odt)
+    hn = h0 + add
+    close(h, hn, torch.float32, 2.0)
+    close(x, hn * torch.rsqrt((hn * hn).mean(-1, keepdim=True) + 1e-5) * wb.float(), odt, 2.0)
+    h = h0.clone()
+    ops.residual_add(h, a)
+    close(h, h0 + af, torch.float32)
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("act", ["gelu_tanh", "silu"])
+def test_gated_act(ops, dt, act):
+    gu = rnd(5, 2 * 333, dt=dt, s=2.0)
+    g, u = gu.float()[:, :333], gu.float()[:, 333:]
+    want = (plain.gelu_tanh(g) if act == "gelu_tanh" else g * torch.sigmoid(g)) * u
+    close(ops.gated_act(gu, act, dt), want, dt)
+
+
+@pytest.mark.parametrize("adt,wdt,odt", [(torch.float32, torch.float32, torch.float32),
+                                         (torch.bfloat16, torch.bfloat16, torch.bfloat16),
+                                         (torch.bfloat16, torch.float32, torch.float32),
+                                         (torch.bfloat16, torch.bfloat16, torch.float32)])
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (7, 301, 100), (65, 130, 77), (200, 64, 1030)])
+def test_gemm_simt(ops, adt, wdt, odt, M, N, K):
+    a, w = rnd(M, K, dt=adt, s=0.5), rnd(N, K, dt=wdt, s=0.5, seed=1)
+    want = a.double() @ w.double().T
+    close(ops.gemm_simt(a, w, odt), want, odt, scale=math.sqrt(K))
+    close(ops.gemm_simt(a, w, torch.float32, softcap=3.0), 3.0 * torch.tanh(want / 3.0), torch.float32, scale=4.0)
+
+
+def test_gemm_simt_row_does_not_depend_on_the_batch(ops):
+    a, w = rnd(50, 333), rnd(97, 333, seed=1)
+    full = ops.gemm_simt(a, w, torch.float32)
+    one = ops.gemm_simt(a[17:18].contiguous(), w, torch.float32)
+    assert torch.equal(full[17:18], one)
+
+
+@pytest.mark.parametrize("odt", DT)
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (3, 40, 72), (16, 384, 96), (17, 130, 64), (64, 2304, 2048),
+                                   (100, 512, 520), (128, 256, 64), (129, 256, 64), (300, 520, 200),
+                                   (1000, 301 * 8, 1032), (2048, 1024, 2304)])
+def test_gemm_tc(ops, odt, M, N, K):
+    a, w = rnd(M, K, dt=torch.bfloat16, s=0.5), rnd(N, K, dt=torch.bfloat16, s=0.5, seed=1)
+    assert ops.gemm_tc_takes(a, w)
+    want = a.double() @ w.double().T
+    got = ops.gemm_tc(a, w, odt)
+    torch.cuda.synchronize()
+    assert ops.gemm_tc_error() == 0
+    if odt == torch.float32:
+        assert float((got.double() - want).norm() / want.norm()) < 2e-5
+    else:
+        assert float((got.double() - want).norm() / want.norm()) < 4e-3
+
+
+@pytest.mark.parametrize("M,N,K,splits", [(8, 2304, 2048, 8), (64, 640, 9216, 5), (1, 136, 1024, 16), (33, 100 * 8, 520, 3)])
+def test_gemm_tc_split_k(ops, M, N, K, splits):
+    a, w = rnd(M, K, dt=torch.bfloat16, s=0.5), rnd(N, K, dt=torch.bfloat16, s=0.5, seed=1)
+    want = a.double() @ w.double().T
+    got = ops.gemm_tc(a, w, torch.float32, 0.0, splits)
+    again = ops.gemm_tc(a, w, torch.float32, 0.0, splits)
+    assert torch.equal(got, again)                                  # fixed summation order
+    assert float((got.double() - want).norm() / want.norm()) < 2e-5
+    capped = ops.gemm_tc(a, w, torch.float32, 5.0, splits)
+    assert float((capped.double() - 5 * torch.tanh(want / 5)).abs().max()) < 1e-4
+    assert ops.gemm_tc_error() == 0
+
+
+def test_gemm_tc_views_and_refusals(ops):
+    big = rnd(40, 3 * 256, dt=torch.bfloat16, s=0.5)
+    w = rnd(96, 256, dt=torch.bfloat16, s=0.5, seed=1)
+    a = big[:, 256:512]                                              # a column slice: row stride 768
+    got = ops.gemm_tc(a, w, torch.float32)
+    assert float((got.double() - a.double() @ w.double().T).abs().max()) < 1e-3
+    assert not ops.gemm_tc_takes(rnd(4, 100, dt=torch.bfloat16), rnd(8, 100, dt=torch.bfloat16))   # K % 8
+    assert not ops.gemm_tc_takes(rnd(4, 64), rnd(8, 64))                                         # float32
+    with pytest.raises(ops.KernelError, match="does not take"):
+        ops.gemm_tc(rnd(4, 100, dt=torch.bfloat16), rnd(8, 100, dt=torch.bfloat16), torch.float32)
+
+
+def test_gemm_tc_token_rows_do_not_depend_on_the_batch(ops):
+    """The same token row gives the same bits alone (swapped tiles) and among 40 rows."""
+    a, w = rnd(40, 512, dt=torch.bfloat16, s=0.5), rnd(384, 512, dt=torch.bfloat16, s=0.5, seed=1)
+    full = ops.gemm_tc(a, w, torch.float32, splits=1)
+    one = ops.gemm_tc(a[7:8].contiguous(), w, torch.float32, splits=1)
+    assert torch.equal(full[7:8], one)
+
+
+# ---------------------------------------------------------------------------
+def paged(k, v, lens, ring_rows, n_pages, seed=0):
+    """Scatter dense per-sequence k, v ([len, nkv, hd] each) into scrambled pages; untouched rows are NaN."""
+    nkv, hd = k[0].shape[1:]
+    dt = k[0].dtype
+    kp = torch.full((n_pages, nkv, PAGE, hd), float("nan"), dtype=dt, device="cuda")
+    vp = torch.full((n_pages, nkv, PAGE, hd), float("nan"), dtype=dt, device="cuda")
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(seed)).tolist()
+    width = max((min(n, ring_rows) if ring_rows else n) + PAGE - 1 for n in lens) // PAGE
+    table = torch.zeros(len(lens), width, dtype=torch.int32)
+    for b, n in enumerate(lens):
+        rows = min(n, ring_rows) if ring_rows else n
+        for pg in range((rows + PAGE - 1) // PAGE):
+            table[b, pg] = perm.pop()
+        for p in range(max(0, n - ring_rows) if ring_rows else 0, n):
+            r = p % ring_rows if ring_rows else p
+            page = int(table[b, r // PAGE])
+            kp[page, :, r % PAGE, :] = k[b][p]
+            vp[page, :, r % PAGE, :] = v[b][p]
+    return kp, vp, table.cuda()
+
+
+def ref_attention_one(q, k, v, scale, cap, window):
+    """q [nh, hd] at position len-1 against k, v [len, nkv, hd] -> [nh, hd] (float64)."""
+    n, nkv, hd = k.shape
+    nh = q.shape[0]
+    out = torch.zeros(nh, hd, dtype=torch.float64)
+    lo = max(0, n - window) if window else 0
+    for h in range(nh):
+        kh = h // (nh // nkv)
+        s = (k[lo:, kh].double() @ q[h].double()) * scale
+        if cap:
+            s = cap * torch.tanh(s / cap)
+        p = torch.softmax(s, 0)
+        out[h] = p @ v[lo:, kh].double()
+    return out
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("nh,nkv,hd,cap,window,splits", [
+    (4, 2, 16, 50.0, 0, 1), (6, 1, 32, 0.0, 40, 3), (3, 3, 48, 20.0, 70, 2), (8, 4, 256, 50.0, 0, 4),
+    (5, 5, 80, 0.0, 128, 7), (8, 2, 128, 30.0, 100, 1)])
+def test_attn_decode(ops, dt, nh, nkv, hd, cap, window, splits):
+    lens = [1, 37, 64, 65, 200, 333]
+    ring = ((window + PAGE - 1) // PAGE) * PAGE if window else 0
+    ks = [rnd(n, nkv, hd, dt=dt, seed=i).cpu() for i, n in enumerate(lens)]
+    vs = [rnd(n, nkv, hd, dt=dt, seed=10 + i).cpu() for i, n in enumerate(lens)]
+    q = rnd(len(lens), nh * hd, dt=dt, seed=99)
+    kp, vp, table = paged([k.cuda() for k in ks], [v.cuda() for v in vs], lens, ring, 64, seed=hd)
+    la = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    scale = 0.37 / math.sqrt(hd)
+    got = ops.attn_decode_simt(q, kp, vp, table, la, nh, nkv, hd, scale, cap, window, ring, splits)
+    assert torch.isfinite(got.float()).all(), "a row outside the sequence's own keys was read"
+    for b, n in enumerate(lens):
+        want = ref_attention_one(q[b].view(nh, hd).cpu(), ks[b], vs[b], scale, cap, window)
+        close(got[b].view(nh, hd), want, dt, 2.0)
+
+
+@pytest.mark.parametrize("dt", DT)
+def test_attn_decode_far_key_and_window_edge(ops, dt):
+    """One key is made to stand out.  Among hundreds it must win the softmax; one step outside the
+    window it must be invisible; on the window's first row it must be seen."""
+    nh, nkv, hd, n, W = 2, 1, 32, 500, 128
+    ring = 128
+    for marked, sees in ((3, "full only"), (n - W - 1, "full only"), (n - W, "both"), (n - 1, "both")):
+        k = rnd(n, nkv, hd, dt=dt, s=0.1, seed=marked)
+        v = rnd(n, nkv, hd, dt=dt, s=1.0, seed=marked + 1)
+        q = rnd(1, nh * hd, dt=dt, s=0.1, seed=7)
+        k[marked, 0] = (q.view(nh, hd)[0].float() * 400).to(dt)        # q0 . k_marked is huge
+        la = torch.tensor([n], dtype=torch.int32, device="cuda")
+        for window, rr in ((0, 0), (W, ring)):
+            kp, vp, table = paged([k], [v], [n], rr, 16, seed=1)
+            got = ops.attn_decode_simt(q, kp, vp, table, la, nh, nkv, hd, 1.0, 0.0, window, rr, 3).view(nh, hd)
+            visible = window == 0 or sees == "both"
+            hit = float((got[0].float() - v[marked, 0].float()).abs().max()) < 2e-2
+            assert hit == visible, f"key {marked}, window {window}: expected visible={visible}"
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("nh,nkv,hd,cap,window", [(4, 2, 16, 50.0, 8), (6, 1, 32, 0.0, 16), (3, 3, 48, 20.0, 0),
+                                                  (2, 1, 256, 50.0, 50), (4, 4, 112, 0.0, 0)])
+def test_attn_prefill(ops, dt, nh, nkv, hd, cap, window):
+    lens = [1, 70, 9, 33]
+    T = sum(lens)
+    qkv = rnd(T, (nh + 2 * nkv) * hd, dt=dt, s=0.7)
+    q, k, v = qkv[:, :nh * hd], qkv[:, nh * hd:(nh + nkv) * hd], qkv[:, (nh + nkv) * hd:]
+    starts = [0]
+    for n in lens:
+        starts.append(starts[-1] + n)
+    seq_start = torch.tensor(starts, dtype=torch.int32, device="cuda")
+    token_seq = torch.repeat_interleave(torch.arange(len(lens), dtype=torch.int32), torch.tensor(lens)).cuda()
+    scale = 1.0 / math.sqrt(hd)
+    got = ops.attn_prefill_simt(q, k, v, seq_start, token_seq, nh, nkv, hd, scale, cap, window)
+    for b, n in enumerate(lens):
+        s = slice(starts[b], starts[b + 1])
+        want = plain.attention(q[s].float().cpu().view(n, nh, hd), k[s].float().cpu().view(n, nkv, hd),
+                               v[s].float().cpu().view(n, nkv, hd), scale, cap or None, window or None)
+        close(got[s].view(n, nh, hd), want, dt, 2.0)
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("hd,rot,ring,theta", [(16, 16, 0, 1e4), (48, 48, 128, 5e4), (256, 256, 64, 1e4), (32, 16, 0, 1e3), (64, 0, 0, 1.0)])
+def test_rope_kv(ops, dt, hd, rot, ring, theta):
+    nh, nkv = 3, 2
+    lens_before, new = [0, 0, 0], [5, 150, 70]                      # a first step
+    for lens_before, new in (([0, 0, 0], [5, 150, 70]), ([5, 150, 70], [1, 1, 1])):
+        B, T = len(new), sum(new)
+        qkv = rnd(T, (nh + 2 * nkv) * hd, dt=dt, seed=T)
+        orig = qkv.clone()
+        pos = torch.cat([torch.arange(b, b + n) for b, n in zip(lens_before, new)]).int().cuda()
+        tseq = torch.repeat_interleave(torch.arange(B), torch.tensor(new)).int().cuda()
+        after = [b + n for b, n in zip(lens_before, new)]
+        la = torch.tensor(after, dtype=torch.int32, device="cuda")
+        n_pages = 16
+        kp = torch.full((n_pages, nkv, PAGE, hd), float("nan"), dtype=dt, device="cuda")
+        vp = torch.full_like(kp, float("nan"))
+        width = max(((min(a, ring) if ring else a) + PAGE - 1) // PAGE for a in after)
+        table = torch.zeros(B, width, dtype=torch.int32)
+        perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(3)).tolist()
+        for b, a in enumerate(after):
+            for pg in range(((min(a, ring) if ring else a) + PAGE - 1) // PAGE):
+                table[b, pg] = perm.pop()
+        table = table.cuda()
+        inv = (1.0 / (torch.tensor(theta) ** (torch.arange(0, rot, 2).float() / rot))).cuda() if rot else None
+        ops.rope_kv(qkv, nh, nkv, hd, rot, inv, pos, tseq, la, kp, vp, table, ring)
+        o = orig.float().cpu().view(T, nh + 2 * nkv, hd)
+        want = o.clone()
+        if rot:
+            want[:, :nh + nkv, :rot] = plain.rope(o[:, :nh + nkv, :rot], pos.cpu(), theta)
+        got = qkv.float().cpu().view(T, nh + 2 * nkv, hd)
+        close(got, want, dt, 2.0)
+        assert torch.equal(got[:, nh + nkv:], o[:, nh + nkv:])       # v is not rotated
+        # every token that must be in the cache is there, at its row, and nothing else was written
+        written = 0
+        for t in range(T):
+            b, p = int(tseq[t]), int(pos[t])
+            if ring and p < after[b] - ring:
+                continue
+            r = p % ring if ring else p
+            page = int(table[b, r // PAGE])
+            assert torch.equal(kp[page, :, r % PAGE].float().cpu(), got[t, nh:nh + nkv])
+            assert torch.equal(vp[page, :, r % PAGE].float().cpu(), got[t, nh + nkv:])
+            written += 1
+        assert int((~torch.isnan(kp.float()[:, 0, :, 0])).sum()) == written
+
+
+# ---------------------------------------------------------------------------
+def test_argmax_ties_and_rows(ops):
+    V = 256000
+    x = rnd(5, V)
+    x[0, 1234] = x[0, 200000] = 50.0            # a tie: the smaller index wins
+    x[1, V - 1] = 60.0
+    x[2, 0] = 60.0
+    x[3, :] = -1.0                              # all equal
+    x[4, 8191] = x[4, 8192] = 70.0              # a tie across the border of two stage-one chunks
+    got = ops.argmax(x).cpu().tolist()
+    assert got == [1234, V - 1, 0, 0, 8191]
+    assert ops.argmax(rnd(3, 301)).cpu().tolist() == rnd(3, 301).argmax(-1).cpu().tolist()
+
+
+def _args(rows, temperature, top_p, penalty, draws):
+    f = lambda v: torch.full((rows,), float(v), device="cuda") if not isinstance(v, torch.Tensor) else v.cuda().float()
+    return f(temperature), f(top_p), f(penalty), f(draws)
+
+
+def test_sample_greedy_and_penalty(ops):
+    V = 1000
+    x = rnd(4, V)
+    x[:, 10] = 9.0; x[:, 20] = 8.0
+    recent = torch.full((4, 128), -1, dtype=torch.int32, device="cuda")
+    recent[1, :3] = torch.tensor([10, 10, 5], dtype=torch.int32)        # 10 twice: penalised once
+    recent[2, 0] = 20
+    x[3, 10] = -0.5; x[3, 20] = -0.6; x[3, 30] = -0.55
+    x[3, :] = torch.minimum(x[3, :], torch.tensor(-0.5, device="cuda"))
+    recent[3, 0] = 10
+    before = x.clone()
+    t, p, pen, u = _args(4, 0.0, 0.95, 1.2, 0.5)
+    got = ops.sample(x, t, p, pen, u, recent).cpu().tolist()
+    want = [plain.greedy(plain.repetition_penalty(before[i].cpu(), recent[i].cpu().tolist(), 1.2)) for i in range(4)]
+    assert got == want and got[0] == 10 and got[1] == 20 and got[2] == 10
+    assert float(x[1, 10]) == pytest.approx(9.0 / 1.2) and float(x[1, 5]) == pytest.approx(
+        float(before[1, 5]) / 1.2 if before[1, 5] > 0 else float(before[1, 5]) * 1.2)
+
+
+@pytest.mark.parametrize("V", [301, 256000])
+@pytest.mark.parametrize("temperature,top_p", [(1.0, 1.0), (0.7, 0.95), (1.5, 0.5), (0.3, 0.9)])
+def test_sample_draws_follow_the_inverse_cdf(ops, V, temperature, top_p):
+    rows = 32
+    x = rnd(rows, V, s=2.0, seed=V)
+    u = torch.linspace(0.001, 0.999, rows)
+    t, p, pen, ud = _args(rows, temperature, top_p, 1.0, u)
+    got = ops.sample(x.clone(), t, p, pen, ud, None).cpu().tolist()
+    for i in range(rows):
+        probs = plain.nucleus(x[i].cpu(), temperature, top_p)          # float64, renormalised over the nucleus
+        cdf = torch.cumsum(probs, 0)
+        tok = got[i]
+        assert probs[tok] > 0, "a token outside the nucleus was drawn"
+        lo = float(cdf[tok] - probs[tok])
+        assert lo - 1e-4 <= float(u[i]) <= float(cdf[tok]) + 1e-4
+
+
+def test_sample_mixed_rows(ops):
+    x = rnd(3, 500, s=3.0)
+    t = torch.tensor([0.0, 1.0, 0.0]); p = torch.tensor([1.0, 1.0, 1.0])
+    got = ops.sample(x.clone(), t.cuda(), p.cuda(), torch.ones(3).cuda(), torch.tensor([0.3, 0.3, 0.3]).cuda(), None)
+    assert got[0] == x[0].argmax() and got[2] == x[2].argmax()
+
+
+def test_refusals(ops):
+    with pytest.raises(ops.KernelError, match="GPU only"):
+        ops.rmsnorm(torch.zeros(2, 4), torch.zeros(4), 1e-6, 1.0, torch.float32)
+    with pytest.raises(ops.KernelError, match="heads"):
+        ops.attn_prefill_simt(rnd(2, 48), rnd(2, 32), rnd(2, 32), torch.zeros(2, dtype=torch.int32, device="cuda"),
+                              torch.zeros(2, dtype=torch.int32, device="cuda"), 3, 2, 16, 1.0, 0.0, 0)
+    with pytest.raises(ops.KernelError, match="512"):
+        ops.attn_prefill_simt(rnd(2, 1024), rnd(2, 1024), rnd(2, 1024), torch.zeros(2, dtype=torch.int32, device="cuda"),
+                              torch.zeros(2, dtype=torch.int32, device="cuda"), 1, 1, 1024, 1.0, 0.0, 0)
+    with pytest.raises(ops.KernelError, match="float32 and bfloat16"):
+        ops.rmsnorm(torch.zeros(2, 4, device="cuda", dtype=torch.float16), torch.zeros(4, device="cuda"), 1e-6, 1.0,
+                    torch.float32)

@@ -1,0 +1,304 @@
+"""The parts of a layer, each alone against the plain implementation; and the generality of the
+arrangement: a schedule that names a layer twice and shares a cache, and a toy mixer with a state of
+its own that is registered, built and stepped without touching the library."""
+import math
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+import plain_gemma2 as plain
+from conftest import TINY_A, TINY_B, TINY_C, TOL, make_prompts, rel_l2, sharpen
+
+pytestmark = pytest.mark.gpu
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def _rt(dt):
+    from trapetum_b200.parts import Runtime
+    return Runtime(dt, torch.device("cuda:0"))
+
+
+def _ctx(lens_before, new, slots=None):
+    from trapetum_b200.engine.step import StepContext
+    B, T = len(new), sum(new)
+    starts = [0]
+    for n in new:
+        starts.append(starts[-1] + n)
+    dev = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")
+    after = [b + n for b, n in zip(lens_before, new)]
+    return StepContext(is_prefill=all(b == 0 for b in lens_before), n_tokens=T, batch=B,
+                       positions=dev([p for b, n in zip(lens_before, new) for p in range(b, b + n)]),
+                       token_seq=dev([i for i, n in enumerate(new) for _ in range(n)]), seq_start=dev(starts),
+                       len_after=dev(after), slot_ids=dev(slots or list(range(B))), slots=slots or list(range(B)),
+                       seq_lens=list(new), max_seq_len=max(new), max_len_after=max(after))
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+def test_norm_part_and_stream(dt):
+    from trapetum_b200.config import PartSpec
+    from trapetum_b200.parts import ResidualStream, build_part
+    H = 200
+    mk = lambda n, eps, uo: build_part("norm", PartSpec("rmsnorm", {"size": H, "eps": eps, "unit_offset": uo, "weight": n}),
+                                       "p.", _rt(dt))
+    n1, n2, n3 = mk("a", 1e-6, True), mk("b", 1e-5, True), mk("c", 1e-6, False)
+    assert list(n1.tensor_specs()) == ["p.a"] and n1.tensor_specs()["p.a"].shape == (H,)
+    w = {f"p.{k}": (torch.randn(H, device="cuda") * 0.3).to(dt) for k in "abc"}
+    for n in (n1, n2, n3):
+        n.bind(w)
+    h0 = torch.randn(7, H, device="cuda")
+    a = (torch.randn(7, H, device="cuda") * 4).to(dt)
+    b = (torch.randn(7, H, device="cuda") * 4).to(dt)
+    st = ResidualStream(h0.clone())
+    x1 = st.normed(n1, dt)
+    st.add_normed(a, n2)
+    x2 = st.normed(n3, dt)                      # the addition and the next norm run as one kernel
+    st.add(b)
+    hf = st.value()
+    pw = {k: v.float().cpu() for k, v in w.items()}
+    ph = h0.cpu()
+    assert rel_l2(x1, plain.rmsnorm(ph, pw["p.a"], 1e-6)) < (1e-6 if dt == torch.float32 else 5e-3)
+    ph = ph + plain.rmsnorm(a.float().cpu(), pw["p.b"], 1e-5)
+    want3 = ph * torch.rsqrt((ph * ph).mean(-1, keepdim=True) + 1e-6) * pw["p.c"]
+    assert rel_l2(x2, want3) < (1e-6 if dt == torch.float32 else 5e-3)
+    assert rel_l2(hf, ph + b.float().cpu()) < 1e-6
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+def test_feed_forward_part(dt):
+    from trapetum_b200.config import PartSpec
+    from trapetum_b200.parts import build_part
+    H, I = 136, 392
+    ff = build_part("feed_forward", PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": I, "activation": "gelu_tanh",
+                                                           "gate": "g", "up": "u", "down": "d"}), "L.", _rt(dt))
+    specs = ff.tensor_specs()
+    assert specs["L.g"].shape == (I, H) and specs["L.d"].shape == (H, I)
+    w = {"L.g": torch.randn(I, H) * 0.1, "L.u": torch.randn(I, H) * 0.1, "L.d": torch.randn(H, I) * 0.1}
+    w = {k: v.bfloat16() for k, v in w.items()}
+    ff.bind({k: v.to("cuda", dt) for k, v in w.items()})
+    x = torch.randn(150, H).bfloat16()
+    got = ff.forward(x.to("cuda", dt), None)
+    assert got.dtype == torch.float32
+    want = plain.feed_forward(x.float(), w["L.g"].float(), w["L.u"].float(), w["L.d"].float())
+    assert rel_l2(got, want) < (1e-5 if dt == torch.float32 else 1e-2)
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("cfg", [TINY_A, TINY_B, TINY_C])
+def test_attention_part_prefill_then_decode(dt, cfg):
+    """The attention mixer with its rope and its cache line, outside any model: a first step of two
+    unequal sequences, then single tokens, against whole-sequence attention."""
+    from trapetum_b200.cache import Cache
+    from trapetum_b200.config import load_config
+    from trapetum_b200.parts import build_part
+    _, spec = load_config(cfg)
+    layer = spec.layers[0]                                       # a sliding layer
+    att = build_part("mixer", layer.mixer, layer.prefix, _rt(dt))
+    H = cfg["hidden_size"]
+    w = {n: (torch.randn(s.shape) * 0.15).bfloat16() for n, s in att.tensor_specs().items()}
+    att.bind({k: v.to("cuda", dt) for k, v in w.items()})
+    cache = Cache({0: att.cache_need()}, {}, 64 * 8, dt, "cuda")
+    lens = [cfg["sliding_window"] + 5, 3]
+    extra = 6
+    xs = [torch.randn(n + extra, H).bfloat16() for n in lens]
+    pw = {k: v.float() for k, v in w.items()}
+    pcfg = dict(cfg)
+    want = [plain.attention_block(x.float(), pw, layer.prefix, pcfg, cfg["sliding_window"])[0] for x in xs]
+    slots = [cache.claim(), cache.claim()]
+    cache.grow({s: n for s, n in zip(slots, lens)})
+
+    def table(max_len):
+        width = cache.table_width(0, max_len)
+        t = torch.zeros(2, width, dtype=torch.int32)
+        for i, s in enumerate(slots):
+            pg = cache.pages(s, 0)
+            t[i, :len(pg)] = torch.tensor(pg, dtype=torch.int32)
+        cache.groups[0].table = t.cuda()
+    table(max(lens))
+    ctx = _ctx([0, 0], lens)
+    x = torch.cat([xs[0][:lens[0]], xs[1][:lens[1]]]).to("cuda", dt)
+    got = att.forward(x, ctx, cache.view(0, 0))
+    t = 1e-5 if dt == torch.float32 else 1.5e-2
+    assert rel_l2(got[:lens[0]], want[0][:lens[0]]) < t and rel_l2(got[lens[0]:], want[1][:lens[1]]) < t
+    for step in range(extra):
+        before = [n + step for n in lens]
+        cache.grow({s: 1 for s in slots})
+        table(max(before) + 1)
+        ctx = _ctx(before, [1, 1])
+        x = torch.stack([xs[0][before[0]], xs[1][before[1]]]).to("cuda", dt)
+        got = att.forward(x, ctx, cache.view(0, 0))
+        assert rel_l2(got[0], want[0][before[0]]) < t and rel_l2(got[1], want[1][before[1]]) < t
+
+
+# ---------------------------------------------------------------------------
+# A schedule that names a layer twice and lets a call read another call's cache
+# ---------------------------------------------------------------------------
+LOOPED = [(0, None), (1, None), (0, None), (1, 1)]
+
+
+def _register_looped():
+    from trapetum_b200.config import Gemma2Config, ModelSpec, ScheduleEntry, register_architecture
+    from trapetum_b200.models.gemma2 import gemma2_spec
+
+    def spec(cfg):
+        s = gemma2_spec(cfg)
+        return ModelSpec(**{**s.__dict__, "architecture": "TestLoopedGemma2",
+                            "schedule": tuple(ScheduleEntry(l, c) for l, c in LOOPED)})
+    register_architecture("TestLoopedGemma2", Gemma2Config, spec)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_schedule_repeats_a_layer_and_shares_a_cache(tmp_path, dtype):
+    import trapetum_b200 as tb
+    _register_looped()
+    cfg = dict(TINY_A, architectures=["TestLoopedGemma2"])
+    d = str(tmp_path / "looped")
+    tb.write_random_model(d, cfg, 3, 0.05, 0.2)
+    sharpen(d, 4.0)
+    pc, pw = plain.load_folder(d)
+    model = tb.load_model(d, dtype)
+    eng = tb.Engine(model, 64 * 8)
+    assert len(eng.cache.entry_group) == 3                         # entries 0, 1, 2 own lines; entry 3 reads entry 1's
+    prompts = make_prompts(256, [30, 12], seed=8)
+    truth = [plain.forward(pc, pw, p, schedule=LOOPED) for p in prompts]
+    s = eng.start(2)
+    cut = [18, 5]
+    first = eng.step(s, [p[:c] for p, c in zip(prompts, cut)], [list(range(c)) for c in cut])
+    assert max(rel_l2(first[i], truth[0][i]) for i in range(18)) <= TOL[dtype]
+    assert max(rel_l2(first[18 + i], truth[1][i]) for i in range(5)) <= TOL[dtype]
+    for t in range(7):
+        out = eng.step(s, [[prompts[0][18 + t]], [prompts[1][5 + t]]])
+        assert rel_l2(out[0], truth[0][18 + t]) <= TOL[dtype] and rel_l2(out[1], truth[1][5 + t]) <= TOL[dtype]
+    eng.release(s)
+
+
+# ---------------------------------------------------------------------------
+# A toy mixer with a state of its own, defined here
+# ---------------------------------------------------------------------------
+def _register_toy():
+    from trapetum_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, register_architecture
+    from trapetum_b200.config.base import _get
+    from trapetum_b200.parts import Mixer, StateNeed, register_part
+    from trapetum_b200.weights import TensorSpec
+
+    class RunningMean(Mixer):
+        """y_t = W * mean(x_0..x_t): its state is the running sum and the count, kept per sequence in
+        the cache's state area.  Plain torch on the device: a toy, not a product kernel."""
+
+        def __init__(self, params, prefix, rt):
+            super().__init__(params, prefix, rt)
+            self.h = params["hidden_size"]
+
+        def tensor_specs(self):
+            return {self._name("weight"): TensorSpec((self.h, self.h))}
+
+        def bind(self, tensors):
+            self.w = tensors[self._name("weight")].float()
+
+        def cache_need(self):
+            return StateNeed((self.h + 1,))
+
+        def forward(self, x, ctx, state):
+            x = x.float()
+            out = torch.empty_like(x)
+            start = 0
+            for slot, n in zip(ctx.slots, ctx.seq_lens):
+                st = state.data[slot]
+                cs = torch.cumsum(x[start:start + n], 0) + st[:self.h]
+                cnt = st[self.h] + torch.arange(1, n + 1, device=x.device, dtype=torch.float32)
+                out[start:start + n] = cs / cnt[:, None]
+                st[:self.h] = cs[-1]
+                st[self.h] = cnt[-1]
+                start += n
+            return out @ self.w.T
+
+    register_part("mixer", "test_running_mean", RunningMean)
+
+    @dataclass(frozen=True)
+    class ToyConfig:
+        layers: int
+        hidden: int
+        inter: int
+        vocab: int
+        eps: float
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(_get(d, "toy_layers", int), _get(d, "toy_hidden", int), _get(d, "toy_inter", int),
+                       _get(d, "toy_vocab", int), _get(d, "toy_eps", float))
+
+    def spec(c):
+        norm = lambda n: PartSpec("rmsnorm", {"size": c.hidden, "eps": c.eps, "unit_offset": False, "weight": n})
+        layers = tuple(LayerSpec(
+            block=PartSpec("pre_norm", {"pre_mixer_norm": norm("n1.weight"), "pre_ffn_norm": norm("n2.weight")}),
+            mixer=PartSpec("test_running_mean", {"hidden_size": c.hidden, "weight": "mix.weight"}),
+            feed_forward=PartSpec("gated_mlp", {"hidden_size": c.hidden, "intermediate_size": c.inter, "activation": "silu",
+                                                "gate": "g.weight", "up": "u.weight", "down": "d.weight"}),
+            prefix=f"blocks.{i}.") for i in range(c.layers))
+        return ModelSpec(architecture="TestToyLM", hidden_size=c.hidden, vocab_size=c.vocab,
+                         embedding=PartSpec("embedding", {"vocab_size": c.vocab, "hidden_size": c.hidden, "scale": 1.0,
+                                                          "weight": "emb.weight"}),
+                         layers=layers, schedule=tuple(ScheduleEntry(i) for i in range(c.layers)),
+                         final_norm=norm("out_norm.weight"),
+                         head=PartSpec("linear_head", {"vocab_size": c.vocab, "hidden_size": c.hidden, "softcap": None,
+                                                       "weight": "head.weight", "tied_to": None}),
+                         max_positions=512)
+    register_architecture("TestToyLM", ToyConfig, spec)
+
+
+def _toy_plain(cfg, w, ids):
+    """The toy model, whole sequence, plain torch on the CPU."""
+    H, eps = cfg["toy_hidden"], cfg["toy_eps"]
+    norm = lambda x, g: x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * g
+    h = w["emb.weight"][torch.tensor(ids)]
+    for i in range(cfg["toy_layers"]):
+        p = f"blocks.{i}."
+        x = norm(h, w[p + "n1.weight"])
+        mean = torch.cumsum(x, 0) / torch.arange(1, len(ids) + 1)[:, None]
+        h = h + mean @ w[p + "mix.weight"].T
+        x = norm(h, w[p + "n2.weight"])
+        g = x @ w[p + "g.weight"].T
+        h = h + ((g * torch.sigmoid(g)) * (x @ w[p + "u.weight"].T)) @ w[p + "d.weight"].T
+    return norm(h, w["out_norm.weight"]) @ w["head.weight"].T
+
+
+def test_a_toy_mixer_with_its_own_state_is_registered_built_and_stepped(tmp_path):
+    import trapetum_b200 as tb
+    _register_toy()
+    cfg = {"architectures": ["TestToyLM"], "toy_layers": 2, "toy_hidden": 40, "toy_inter": 56, "toy_vocab": 90,
+           "toy_eps": 1e-5}
+    d = str(tmp_path / "toy")
+    tb.write_random_model(d, cfg, 9, 0.2, 0.3)
+    pw = plain.load_folder(d)[1]
+    for k in pw:
+        if "n1" in k or "n2" in k or "out_norm" in k:
+            pw[k] = pw[k]                                          # plain (not 1+w) norms, as the spec says
+    model = tb.load_model(d, "float32")
+    eng = tb.Engine(model, 64 * 4, max_slots=4)
+    assert eng.cache.groups == [] and sorted(eng.cache.states) == [0, 1]       # no keys or values: state only
+    prompts = make_prompts(90, [21, 8, 13], seed=1)
+    truth = [_toy_plain(cfg, pw, p) for p in prompts]
+    for round_ in range(2):                                        # the second round reuses slots: state must restart
+        s = eng.start(3)
+        cut = [10, 8 - 3, 1]
+        first = eng.step(s, [p[:c] for p, c in zip(prompts, cut)], [list(range(c)) for c in cut])
+        o = 0
+        for r in range(3):
+            assert max(rel_l2(first[o + i], truth[r][i]) for i in range(cut[r])) < 1e-5
+            o += cut[r]
+        live = list(range(3))
+        t = 0
+        while live:
+            for r in [r for r in live if cut[r] + t >= len(prompts[r])]:
+                eng.release([s[r]]); live.remove(r)
+            if not live:
+                break
+            out = eng.step([s[r] for r in live], [[prompts[r][cut[r] + t]] for r in live])
+            for i, r in enumerate(live):
+                assert rel_l2(out[i], truth[r][cut[r] + t]) < 1e-5
+            t += 1
+    out = tb.generate(eng, [prompts[0][:4]], max_tokens=5, stop_ids=[])
+    ids = list(prompts[0][:4])
+    for tok in out[0]:
+        assert tok == int(_toy_plain(cfg, pw, ids)[-1].argmax())
+        ids.append(tok)
