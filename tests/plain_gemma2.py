@@ -47,6 +47,15 @@ def layer_is_sliding(cfg: dict, i: int) -> bool:
 # ----------------------------------------------------------------------------
 # Parts
 # ----------------------------------------------------------------------------
+def _same(x):
+    return x
+
+
+def to_bf16(x: torch.Tensor) -> torch.Tensor:
+    """Round to bfloat16 and back: what a 16-bit activation buffer does to its contents."""
+    return x.to(torch.bfloat16).to(x.dtype)
+
+
 def embed(ids: Sequence[int], table: torch.Tensor, hidden: int) -> torch.Tensor:
     """h[t] = E[id_t] * sqrt(hidden)   (model/export_gemma.py:59-61; runtime/src/lib.rs:4554-4555)."""
     return table[torch.tensor(list(ids), dtype=torch.long)] * math.sqrt(hidden)
@@ -102,49 +111,50 @@ def gelu_tanh(g: torch.Tensor) -> torch.Tensor:
     return 0.5 * g * (1.0 + torch.tanh(0.7978845608 * (g + 0.044715 * g * g * g)))
 
 
-def feed_forward(x: torch.Tensor, wg: torch.Tensor, wu: torch.Tensor, wd: torch.Tensor) -> torch.Tensor:
+def feed_forward(x: torch.Tensor, wg: torch.Tensor, wu: torch.Tensor, wd: torch.Tensor, rnd=_same) -> torch.Tensor:
     """down(gelu_tanh(gate(x)) * up(x))   (runtime/src/lib.rs:4511-4516)."""
-    return (gelu_tanh(x @ wg.T) * (x @ wu.T)) @ wd.T
+    return rnd(gelu_tanh(rnd(x @ wg.T)) * rnd(x @ wu.T)) @ wd.T
 
 
 def attention_block(x: torch.Tensor, w: Dict[str, torch.Tensor], prefix: str, cfg: dict, window: Optional[int],
-                    kv_from: Optional[Tuple[torch.Tensor, torch.Tensor]] = None):
+                    kv_from: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, rnd=_same):
     """Projections without bias, rope on q and k, attention, output projection
-    (runtime/src/lib.rs:4483-4496).  Returns (output, (k_rot, v))."""
+    (runtime/src/lib.rs:4483-4496).  Returns (output, (k_rot, v)).  ``rnd`` is applied wherever a
+    16-bit engine stores an activation (identity for the oracle; see :func:`forward`)."""
     T = x.shape[0]
     nh, nkv, hd = cfg["num_attention_heads"], cfg.get("num_key_value_heads", cfg["num_attention_heads"]), cfg["head_dim"]
     pos = torch.arange(T)
     theta = float(cfg.get("rope_theta", 10000.0))
-    q = rope((x @ w[prefix + "self_attn.q_proj.weight"].T).view(T, nh, hd), pos, theta)
+    q = rnd(rope(rnd(x @ w[prefix + "self_attn.q_proj.weight"].T).view(T, nh, hd), pos, theta))
     if kv_from is None:
-        k = rope((x @ w[prefix + "self_attn.k_proj.weight"].T).view(T, nkv, hd), pos, theta)
-        v = (x @ w[prefix + "self_attn.v_proj.weight"].T).view(T, nkv, hd)
+        k = rnd(rope(rnd(x @ w[prefix + "self_attn.k_proj.weight"].T).view(T, nkv, hd), pos, theta))
+        v = rnd(x @ w[prefix + "self_attn.v_proj.weight"].T).view(T, nkv, hd)
     else:
         k, v = kv_from
     scale = float(cfg.get("query_pre_attn_scalar", hd)) ** -0.5
     cap = cfg.get("attn_logit_softcapping") or None
-    o = attention(q, k, v, scale, cap, window)
+    o = rnd(attention(q, k, v, scale, cap, window))
     return o.reshape(T, nh * hd) @ w[prefix + "self_attn.o_proj.weight"].T, (k, v)
 
 
-def decoder_layer(h: torch.Tensor, w: Dict[str, torch.Tensor], i: int, cfg: dict, kv_from=None):
+def decoder_layer(h: torch.Tensor, w: Dict[str, torch.Tensor], i: int, cfg: dict, kv_from=None, rnd=_same):
     """h += post_attn_norm(attn(input_norm(h))); h += post_ff_norm(mlp(pre_ff_norm(h)))
     (runtime/src/lib.rs:4527-4540)."""
     p = f"model.layers.{i}."
     eps = float(cfg.get("rms_norm_eps", 1e-6))
     window = cfg["sliding_window"] if layer_is_sliding(cfg, i) else None
-    a, kv = attention_block(rmsnorm(h, w[p + "input_layernorm.weight"], eps), w, p, cfg, window, kv_from)
+    a, kv = attention_block(rnd(rmsnorm(h, w[p + "input_layernorm.weight"], eps)), w, p, cfg, window, kv_from, rnd)
     h = h + rmsnorm(a, w[p + "post_attention_layernorm.weight"], eps)
-    m = feed_forward(rmsnorm(h, w[p + "pre_feedforward_layernorm.weight"], eps),
-                     w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    m = feed_forward(rnd(rmsnorm(h, w[p + "pre_feedforward_layernorm.weight"], eps)),
+                     w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"], rnd)
     h = h + rmsnorm(m, w[p + "post_feedforward_layernorm.weight"], eps)
     return h, kv
 
 
-def head(h: torch.Tensor, w: Dict[str, torch.Tensor], cfg: dict) -> torch.Tensor:
+def head(h: torch.Tensor, w: Dict[str, torch.Tensor], cfg: dict, rnd=_same) -> torch.Tensor:
     """logits = final_norm(h) E^T (tied, unscaled), then cap*tanh(logits/cap)
     (runtime/src/lib.rs:4557-4560; model/export_gemma.py:73)."""
-    x = rmsnorm(h, w["model.norm.weight"], float(cfg.get("rms_norm_eps", 1e-6)))
+    x = rnd(rmsnorm(h, w["model.norm.weight"], float(cfg.get("rms_norm_eps", 1e-6))))
     E = w.get("lm_head.weight", w["model.embed_tokens.weight"])
     logits = x @ E.T
     cap = cfg.get("final_logit_softcapping") or None
@@ -154,18 +164,23 @@ def head(h: torch.Tensor, w: Dict[str, torch.Tensor], cfg: dict) -> torch.Tensor
 
 
 def forward(cfg: dict, w: Dict[str, torch.Tensor], ids: Sequence[int],
-            schedule: Optional[List[Tuple[int, Optional[int]]]] = None) -> torch.Tensor:
+            schedule: Optional[List[Tuple[int, Optional[int]]]] = None, rnd=_same) -> torch.Tensor:
     """Logits [T, vocab] of one whole sequence.  ``schedule``: (layer, entry whose keys and values
-    this call reads, or None) per call; by default every layer once, in order."""
+    this call reads, or None) per call; by default every layer once, in order.
+
+    ``rnd=to_bf16`` rounds every activation that a 16-bit engine stores between two kernels (normed
+    inputs, q/k/v before and after rope, attention output, gate, up and their product) while the
+    residual stream, all sums and the logits stay 32-bit.  Its distance from the exact run measures
+    what 16-bit storage alone costs on a given model; the tests size the bfloat16 budget with it."""
     h = embed(ids, w["model.embed_tokens.weight"], cfg["hidden_size"])
     if schedule is None:
         schedule = [(i, None) for i in range(cfg["num_hidden_layers"])]
     kvs = {}
     for e, (layer, cache_of) in enumerate(schedule):
-        h, kv = decoder_layer(h, w, layer, cfg, None if cache_of is None else kvs[cache_of])
+        h, kv = decoder_layer(h, w, layer, cfg, None if cache_of is None else kvs[cache_of], rnd)
         if cache_of is None:
             kvs[e] = kv
-    return head(h, w, cfg)
+    return head(h, w, cfg, rnd)
 
 
 # ----------------------------------------------------------------------------

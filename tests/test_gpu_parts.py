@@ -8,7 +8,7 @@ import pytest
 import torch
 
 import plain_gemma2 as plain
-from conftest import TINY_A, TINY_B, TINY_C, TOL, make_prompts, rel_l2, sharpen
+from conftest import TINY_A, TINY_B, TINY_C, TOL, bf16_budget, make_prompts, rel_l2, sharpen
 
 pytestmark = pytest.mark.gpu
 DTYPES = [torch.float32, torch.bfloat16]
@@ -154,21 +154,22 @@ def test_schedule_repeats_a_layer_and_shares_a_cache(tmp_path, dtype):
     cfg = dict(TINY_A, architectures=["TestLoopedGemma2"])
     d = str(tmp_path / "looped")
     tb.write_random_model(d, cfg, 3, 0.05, 0.2)
-    sharpen(d, 4.0)
+    sharpen(d, 3.0)
     pc, pw = plain.load_folder(d)
     model = tb.load_model(d, dtype)
     eng = tb.Engine(model, 64 * 8)
     assert len(eng.cache.entry_group) == 3                         # entries 0, 1, 2 own lines; entry 3 reads entry 1's
     prompts = make_prompts(256, [30, 12], seed=8)
     truth = [plain.forward(pc, pw, p, schedule=LOOPED) for p in prompts]
+    tol = TOL[dtype] if dtype == "float32" else bf16_budget(pc, pw, prompts, LOOPED)
     s = eng.start(2)
     cut = [18, 5]
     first = eng.step(s, [p[:c] for p, c in zip(prompts, cut)], [list(range(c)) for c in cut])
-    assert max(rel_l2(first[i], truth[0][i]) for i in range(18)) <= TOL[dtype]
-    assert max(rel_l2(first[18 + i], truth[1][i]) for i in range(5)) <= TOL[dtype]
+    assert max(rel_l2(first[i], truth[0][i]) for i in range(18)) <= tol
+    assert max(rel_l2(first[18 + i], truth[1][i]) for i in range(5)) <= tol
     for t in range(7):
         out = eng.step(s, [[prompts[0][18 + t]], [prompts[1][5 + t]]])
-        assert rel_l2(out[0], truth[0][18 + t]) <= TOL[dtype] and rel_l2(out[1], truth[1][5 + t]) <= TOL[dtype]
+        assert rel_l2(out[0], truth[0][18 + t]) <= tol and rel_l2(out[1], truth[1][5 + t]) <= tol
     eng.release(s)
 
 
