@@ -79,7 +79,7 @@ class FakeEngine:
             self.cache.release(s)
             del self.sums[s]
 
-    def step(self, slots, tokens, want=None):
+    def step(self, slots, tokens, want=None, borrow=False):
         first = all(self.cache.length(s) == 0 for s in slots)
         assert first or all(len(t) == 1 and self.cache.length(s) > 0 for s, t in zip(slots, tokens))
         self.cache.grow({s: len(t) for s, t in zip(slots, tokens)})

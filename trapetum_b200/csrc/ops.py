@@ -46,8 +46,23 @@ def _cuda(*ts: Optional[torch.Tensor]) -> None:
             raise KernelError("this library computes on the GPU only: got a tensor on " + str(t.device))
 
 
-def _check(lib, status: int, what: str) -> None:
+_launches = 0
+
+
+def launches() -> int:
+    """How many kernel launches this process has made through this module (graph replays count their kernels)."""
+    return _launches
+
+
+def count_launches(n: int) -> None:
+    global _launches
+    _launches += n
+
+
+def _check(lib, status: int, what: str, kernels: int = 1) -> None:
+    global _launches
     if status == 0:
+        _launches += kernels
         return
     if status < 0:
         raise KernelError(f"{what}: {lib.tb_error().decode()}")

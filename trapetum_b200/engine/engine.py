@@ -20,6 +20,7 @@ import numpy as np
 import torch
 
 from ..cache import Cache
+from ..csrc import ops
 from .model import Model
 from .step import StepContext, StepError, StepInputs, classify
 
@@ -46,7 +47,7 @@ def decode_splits(batch: int, n_heads: int, max_len: int, sms: int) -> int:
 
 
 class Engine:
-    def __init__(self, model: Model, max_tokens: int, max_slots: Optional[int] = None):
+    def __init__(self, model: Model, max_tokens: int, max_slots: Optional[int] = None, use_graphs: bool = True):
         self.model = model
         self.rt = model.rt
         needs, readers = model.cache_needs()
@@ -54,6 +55,12 @@ class Engine:
         self.vocab_size = model.vocab_size
         self._inputs = StepInputs(self.rt.device)
         self._heads = max([getattr(b.mixer, "n_heads", 1) for b in model.blocks] or [1])
+        # CUDA graphs for decode steps: only if every part says that its launches depend on nothing
+        # that lives on the host (a part that reads ctx.slots in Python, for one, does not qualify)
+        self.use_graphs = use_graphs and self.rt.device.type == "cuda"
+        self._graph_safe = all(getattr(p, "graph_safe", False) for b in model.blocks for p in (b, b.mixer, b.feed_forward))
+        self._decode: Dict[tuple, "_DecodeShape"] = {}
+        self._graph_pool = torch.cuda.graph_pool_handle() if self.use_graphs and self._graph_safe else None
 
     # -- sequences ----------------------------------------------------------------
     def start(self, n: int) -> List[int]:
@@ -74,8 +81,11 @@ class Engine:
 
     # -- the step -------------------------------------------------------------------
     def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],
-             want: Optional[Sequence[Sequence[int]]] = None) -> Optional[torch.Tensor]:
-        """Run one step; returns float32 logits [wanted, vocab] on the device (None if nothing is wanted)."""
+             want: Optional[Sequence[Sequence[int]]] = None, borrow: bool = False) -> Optional[torch.Tensor]:
+        """Run one step; returns float32 logits [wanted, vocab] on the device (None if nothing is wanted).
+
+        ``borrow=True`` lets the result alias a buffer that the next step overwrites (the generation
+        loop consumes the logits at once and saves the copy)."""
         slots = list(slots)
         is_prefill = classify(self.cache, slots, tokens)
         B = len(slots)
@@ -97,6 +107,8 @@ class Engine:
         before = [self.cache.length(s) for s in slots]
         self.cache.grow({s: n for s, n in zip(slots, lens)})          # raises CacheFull before anything ran
         after = [b + n for b, n in zip(before, lens)]
+        if not is_prefill and self.use_graphs and self._graph_safe:
+            return self._decode_step(slots, tokens, want, before, after, borrow)
 
         T = sum(lens)
         starts = np.zeros(B + 1, dtype=np.int32)
@@ -112,12 +124,7 @@ class Engine:
         }
         max_after = max(after)
         for gi, g in enumerate(self.cache.groups):
-            width = self.cache.table_width(gi, max_after)
-            tab = np.zeros((B, width), dtype=np.int32)
-            for i, s in enumerate(slots):
-                pg = self.cache.pages(s, gi)
-                tab[i, :len(pg)] = pg
-            arrays[f"table{gi}"] = tab
+            arrays[f"table{gi}"] = self._table(gi, slots, self.cache.table_width(gi, max_after))
         dev = self._inputs.upload(arrays)
         for gi, g in enumerate(self.cache.groups):
             g.table = dev[f"table{gi}"]
@@ -135,3 +142,102 @@ class Engine:
             return None
         all_rows = n_want == T and bool((arrays["want"] == np.arange(T)).all())
         return self.model.forward(dev["ids"], ctx, self.cache, None if all_rows else dev["want"])
+
+    def _table(self, gi: int, slots: Sequence[int], width: int) -> np.ndarray:
+        tab = np.zeros((len(slots), width), dtype=np.int32)
+        for i, s in enumerate(slots):
+            pg = self.cache.pages(s, gi)
+            tab[i, :len(pg)] = pg
+        return tab
+
+    # -- one token per sequence, as a CUDA graph ---------------------------------------
+    def _decode_step(self, slots, tokens, want, before, after, borrow):
+        """A decode step's launches do not depend on the tokens, the positions or the pages, only on
+        the batch size and on the number of key splits: the inputs live in buffers of a fixed layout,
+        the first step of a shape runs eagerly (it also sets up every kernel), the second is captured
+        into a CUDA graph, and from then on a step is one copy of the inputs and one graph launch."""
+        B = len(slots)
+        max_after = max(after)
+        splits = decode_splits(B, self._heads, max_after, _sm_count(self.rt.device))
+        key = (B, splits)
+        dg = self._decode.get(key)
+        if dg is None:
+            dg = self._decode[key] = _DecodeShape(B, splits, self)
+        dg.fill(self, slots, [t[0] for t in tokens], before, after)
+        for gi, g in enumerate(self.cache.groups):
+            g.table = dg.dev[f"table{gi}"]
+        dg.hits += 1
+        if dg.graph is None and dg.hits >= 2:
+            ctx = dg.context(slots, max_after)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                dg.logits = self.model.forward(dg.dev["ids"], ctx, self.cache, None)
+            dg.graph = graph
+        if dg.graph is not None:
+            dg.graph.replay()
+            logits = dg.logits
+            ops.count_launches(dg.n_kernels)
+        else:
+            n0 = ops.launches()
+            logits = self.model.forward(dg.dev["ids"], dg.context(slots, max_after), self.cache, None)
+            dg.n_kernels = ops.launches() - n0
+        rows = [i for i, w in enumerate(want) for _ in w]
+        if not rows:
+            return None
+        if rows == list(range(B)):
+            return logits if (borrow or dg.graph is None) else logits.clone()
+        return ops.gather_rows(logits, torch.tensor(rows, dtype=torch.int32, device=self.rt.device))
+
+
+class _DecodeShape:
+    """The fixed-layout inputs, and later the graph, of decode steps of one batch size and split count."""
+
+    def __init__(self, B: int, splits: int, engine: "Engine"):
+        self.B, self.splits = B, splits
+        self.graph = None
+        self.logits = None
+        self.hits = 0
+        self.n_kernels = 0
+        cache = engine.cache
+        cap = min(engine.model.spec.max_positions, cache.max_tokens)
+        self.widths = [cache.table_width(gi, cap) for gi in range(len(cache.groups))]
+        names = [("ids", (B,)), ("positions", (B,)), ("token_seq", (B,)), ("seq_start", (B + 1,)),
+                 ("len_after", (B,)), ("slot_ids", (B,))] + [(f"table{gi}", (B, w)) for gi, w in enumerate(self.widths)]
+        off, self.layout = 0, {}
+        for name, shape in names:
+            n = int(np.prod(shape))
+            self.layout[name] = (off, shape)
+            off += (n + 3) & ~3
+        dev = engine.rt.device
+        self.host = torch.zeros(off, dtype=torch.int32).pin_memory()
+        self.buf = torch.zeros(off, dtype=torch.int32, device=dev)
+        self.hv = {name: self.host.numpy()[o:o + int(np.prod(shape))].reshape(shape) for name, (o, shape) in self.layout.items()}
+        self.dev = {name: self.buf[o:o + int(np.prod(shape))].view(shape) for name, (o, shape) in self.layout.items()}
+        self.hv["token_seq"][:] = np.arange(B)
+        self.hv["seq_start"][:] = np.arange(B + 1)
+        self.copied = None
+        self.h2d_bytes = off * 4
+
+    def fill(self, engine, slots, toks, before, after) -> None:
+        if self.copied is not None:
+            self.copied.synchronize()              # the last copy has left the host buffer
+        hv = self.hv
+        hv["ids"][:] = toks
+        hv["positions"][:] = before
+        hv["len_after"][:] = after
+        hv["slot_ids"][:] = slots
+        for gi, w in enumerate(self.widths):
+            t = hv[f"table{gi}"]
+            for i, s in enumerate(slots):
+                pg = engine.cache.pages(s, gi)
+                t[i, :len(pg)] = pg
+        self.buf.copy_(self.host, non_blocking=True)
+        self.copied = torch.cuda.Event()
+        self.copied.record()
+
+    def context(self, slots, max_after) -> StepContext:
+        d = self.dev
+        return StepContext(is_prefill=False, n_tokens=self.B, batch=self.B, positions=d["positions"],
+                           token_seq=d["token_seq"], seq_start=d["seq_start"], len_after=d["len_after"],
+                           slot_ids=d["slot_ids"], slots=list(slots), seq_lens=[1] * self.B, max_seq_len=1,
+                           max_len_after=max_after, decode_splits=self.splits)

@@ -107,7 +107,7 @@ def generate(model_or_engine, prompts: Sequence[Sequence[int]], max_tokens: int 
         try:
             for q in live:
                 sampler.begin(q.request, prompts[q.request])
-            logits = engine.step([q.slot for q in live], [prompts[q.request] for q in live])
+            logits = engine.step([q.slot for q in live], [prompts[q.request] for q in live], borrow=True)
             for q in live:
                 q.length = len(prompts[q.request])
             while live:
@@ -127,7 +127,7 @@ def generate(model_or_engine, prompts: Sequence[Sequence[int]], max_tokens: int 
                         engine.release([q.slot])
                 live = nxt
                 if live:
-                    logits = engine.step([q.slot for q in live], [[q.new[-1]] for q in live])
+                    logits = engine.step([q.slot for q in live], [[q.new[-1]] for q in live], borrow=True)
                     for q in live:
                         q.length += 1
         except BaseException:

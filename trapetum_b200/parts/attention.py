@@ -31,6 +31,7 @@ from .linear import linear
 
 
 class Attention(Mixer):
+    graph_safe = True          # every launch depends on device data only
     def __init__(self, params, prefix, rt):
         super().__init__(params, prefix, rt)
         p = params

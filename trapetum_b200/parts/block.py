@@ -22,6 +22,7 @@ from .base import Block, build_part, register_part
 
 
 class _NormedBlock(Block):
+    graph_safe = True          # every launch depends on device data only
     NORMS = ()
 
     def __init__(self, params, prefix, rt, mixer, feed_forward):

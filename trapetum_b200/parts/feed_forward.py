@@ -19,6 +19,7 @@ from .linear import linear
 
 
 class GatedMLP(FeedForward):
+    graph_safe = True          # every launch depends on device data only
     def __init__(self, params, prefix, rt):
         super().__init__(params, prefix, rt)
         self.hidden = int(params["hidden_size"])
