@@ -204,10 +204,19 @@ def ref_attention_one(q, k, v, scale, cap, window):
     return out
 
 
+def decode_impls(ops, dt, nh, nkv, hd):
+    """The generic kernel always; the bulk-copy kernel too where it takes the shape."""
+    impls = [ops.attn_decode_simt]
+    if ops.attn_decode_takes(dt, nh, nkv, hd):
+        impls.append(ops.attn_decode_tma)
+    return impls
+
+
 @pytest.mark.parametrize("dt", DT)
 @pytest.mark.parametrize("nh,nkv,hd,cap,window,splits", [
     (4, 2, 16, 50.0, 0, 1), (6, 1, 32, 0.0, 40, 3), (3, 3, 48, 20.0, 70, 2), (8, 4, 256, 50.0, 0, 4),
-    (5, 5, 80, 0.0, 128, 7), (8, 2, 128, 30.0, 100, 1)])
+    (5, 5, 80, 0.0, 128, 7), (8, 2, 128, 30.0, 100, 1), (8, 1, 64, 10.0, 0, 2), (4, 4, 32, 0.0, 64, 5),
+    (16, 2, 256, 50.0, 200, 3), (2, 1, 128, 0.0, 0, 9), (8, 8, 64, 0.0, 300, 1)])
 def test_attn_decode(ops, dt, nh, nkv, hd, cap, window, splits):
     lens = [1, 37, 64, 65, 200, 333]
     ring = ((window + PAGE - 1) // PAGE) * PAGE if window else 0
@@ -217,11 +226,14 @@ def test_attn_decode(ops, dt, nh, nkv, hd, cap, window, splits):
     kp, vp, table = paged([k.cuda() for k in ks], [v.cuda() for v in vs], lens, ring, 64, seed=hd)
     la = torch.tensor(lens, dtype=torch.int32, device="cuda")
     scale = 0.37 / math.sqrt(hd)
-    got = ops.attn_decode_simt(q, kp, vp, table, la, nh, nkv, hd, scale, cap, window, ring, splits)
-    assert torch.isfinite(got.float()).all(), "a row outside the sequence's own keys was read"
-    for b, n in enumerate(lens):
-        want = ref_attention_one(q[b].view(nh, hd).cpu(), ks[b], vs[b], scale, cap, window)
-        close(got[b].view(nh, hd), want, dt, 2.0)
+    for impl in decode_impls(ops, dt, nh, nkv, hd):
+        got = impl(q, kp, vp, table, la, nh, nkv, hd, scale, cap, window, ring, splits)
+        assert torch.isfinite(got.float()).all(), f"{impl.__name__}: a row outside the sequence's own keys was read"
+        for b, n in enumerate(lens):
+            want = ref_attention_one(q[b].view(nh, hd).cpu(), ks[b], vs[b], scale, cap, window)
+            close(got[b].view(nh, hd), want, dt, 2.0)
+    torch.cuda.synchronize()
+    assert ops.attn_decode_error() == 0
 
 
 @pytest.mark.parametrize("dt", DT)
@@ -238,10 +250,11 @@ def test_attn_decode_far_key_and_window_edge(ops, dt):
         la = torch.tensor([n], dtype=torch.int32, device="cuda")
         for window, rr in ((0, 0), (W, ring)):
             kp, vp, table = paged([k], [v], [n], rr, 16, seed=1)
-            got = ops.attn_decode_simt(q, kp, vp, table, la, nh, nkv, hd, 1.0, 0.0, window, rr, 3).view(nh, hd)
-            visible = window == 0 or sees == "both"
-            hit = float((got[0].float() - v[marked, 0].float()).abs().max()) < 2e-2
-            assert hit == visible, f"key {marked}, window {window}: expected visible={visible}"
+            for impl in decode_impls(ops, dt, nh, nkv, hd):
+                got = impl(q, kp, vp, table, la, nh, nkv, hd, 1.0, 0.0, window, rr, 3).view(nh, hd)
+                visible = window == 0 or sees == "both"
+                hit = float((got[0].float() - v[marked, 0].float()).abs().max()) < 2e-2
+                assert hit == visible, f"{impl.__name__}: key {marked}, window {window}: expected visible={visible}"
 
 
 @pytest.mark.parametrize("dt", DT)

@@ -1,0 +1,404 @@
+// Decode attention over the paged cache at memory speed (bfloat16).
+//
+// One query token per sequence; its keys and values are the sequence's pages in the
+// cache.  Same formula as the reference's attn_k (runtime/cuda/codebook_gemv.cu:240-270:
+// s = q.k * scale, optional cap*tanh(s/cap), softmax, sum of p*v), but where that
+// kernel runs one block per head with a block-wide tree reduction per key and a
+// single-thread softmax, here
+//   * a CTA owns (sequence, kv head, split of the page range) and serves all query
+//     heads of the group from one read of K and V;
+//   * pages (64 keys x head_dim, contiguous in the pool) are brought into shared
+//     memory by bulk copies of the TMA unit, several pages ahead, tracked by mbarriers;
+//   * each of the 8 warps takes 8 keys of a page; a key's head_dim is spread over
+//     head_dim/8 lanes (16 bytes each); partial dot products are reduced with a
+//     butterfly that leaves one (key, head) score per lane, so cap, exp and the
+//     running softmax are computed once per score;
+//   * all math is 32-bit; splits write (max, sum, o) partials that a second kernel
+//     folds in split order (no atomics).
+// Rows of a page beyond the sequence's keys (or outside the window) are never used,
+// not even multiplied by zero: stale or uninitialised rows cannot leak.
+//
+// Takes head_dim in {32, 64, 128, 256} and group sizes 1, 2, 4, 8; other shapes are
+// refused and the caller uses the generic kernel.
+#include "common.cuh"
+#include "async.cuh"
+
+TB_EXPORT_ERROR()
+
+#define PAGE 64
+#define NWARP 8
+#define KPW (PAGE / NWARP)          // keys of a page per warp
+
+__device__ int g_attn_error = 0;
+
+struct DecodeArgs {
+    const void* q; long long q_stride;
+    const void* k_pool; const void* v_pool;
+    const int* page_table; int pt_stride;
+    const int* len_after;
+    void* out;
+    float* partial;
+    int n_heads, n_kv_heads, hd, page_rows, ring_rows, window, n_splits;
+    float scale, cap;
+};
+
+template <int HD> struct DCfg {
+    static constexpr int PAGE_BYTES = PAGE * HD * 2;                 // one page of K (or V) for one kv head
+    static constexpr int STAGE_BYTES = 2 * PAGE_BYTES;
+    static constexpr int STAGES_RAW = (192 * 1024) / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_RAW > 6 ? 6 : STAGES_RAW;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 128;
+};
+
+__device__ __forceinline__ void bf16x8_to_f32(const uint4& w, float* f) {
+    const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        f[2 * i] = __uint_as_float(u[i] << 16);
+        f[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+    }
+}
+
+template <int HD, int G>
+__global__ void __launch_bounds__(NWARP * 32, 1) attn_decode_kernel(DecodeArgs a) {
+    using C = DCfg<HD>;
+    constexpr int LPK = HD / 8;                    // lanes per key
+    constexpr int KP = 32 / LPK;                   // keys per pass of a warp
+    constexpr int NP = KPW / KP;                   // passes per page
+    constexpr int N = NP * G;                      // scores a lane group produces per page
+    constexpr int NF = N > LPK ? N / LPK : 1;      // scores a lane holds after the butterfly
+    constexpr int SPREAD = N > LPK ? 1 : LPK / N;  // lanes that hold the same score
+    static_assert(KP <= KPW && NP >= 1, "head_dim too small for this kernel");
+
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t* full = (uint64_t*)(smem + C::STAGES * C::STAGE_BYTES);
+    __shared__ int s_abort;
+
+    const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane % LPK, kg = lane / LPK;
+
+    const int len = a.len_after[b];
+    const int lo = (a.window > 0 && len > a.window) ? len - a.window : 0;
+    // the rows of this sequence in "row space": positions, or ring rows
+    int first_page, n_pages;
+    if (a.ring_rows > 0) { first_page = 0; n_pages = (min(len, a.ring_rows) + PAGE - 1) / PAGE; }
+    else { first_page = lo / PAGE; n_pages = (len - 1) / PAGE - first_page + 1; }
+    const int per = (n_pages + a.n_splits - 1) / a.n_splits;
+    const int pg_beg = first_page + split * per;
+    const int pg_end = min(first_page + n_pages, pg_beg + per);
+    const int n = max(0, pg_end - pg_beg);
+    const int* pt = a.page_table + (size_t)b * a.pt_stride;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; s++) mbar_init(&full[s], 1);
+        s_abort = 0;
+        mbar_init_fence();
+    }
+    __syncthreads();
+
+    auto issue = [&](int i) {
+        const int s = i % C::STAGES;
+        const int page = pt[pg_beg + i];
+        const size_t off = ((size_t)page * a.n_kv_heads + kvh) * PAGE * HD;
+        uint8_t* dst = smem + s * C::STAGE_BYTES;
+        mbar_expect_tx(&full[s], C::STAGE_BYTES);
+        bulk_load(dst, (const bf16*)a.k_pool + off, C::PAGE_BYTES, &full[s]);
+        bulk_load(dst + C::PAGE_BYTES, (const bf16*)a.v_pool + off, C::PAGE_BYTES, &full[s]);
+    };
+    if (threadIdx.x == 0)
+        for (int i = 0; i < n && i < C::STAGES; i++) issue(i);
+
+    // this lane's slice of the queries, already multiplied by the scale
+    float q[G][8];
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        const bf16* qp = (const bf16*)a.q + (size_t)b * a.q_stride + (size_t)(kvh * G + g) * HD + sub * 8;
+        float f[8];
+        bf16x8_to_f32(*(const uint4*)qp, f);
+#pragma unroll
+        for (int e = 0; e < 8; e++) q[g][e] = f[e] * a.scale;
+    }
+
+    float m[G], o[G][8], l_lane[NF];
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        m[g] = -INFINITY;
+#pragma unroll
+        for (int e = 0; e < 8; e++) o[g][e] = 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < NF; j++) l_lane[j] = 0.f;
+
+    int consumed = 0;
+    for (int i = 0; i < n; i++) {
+        const int s = i % C::STAGES;
+        const bool got = mbar_wait(&full[s], (i / C::STAGES) & 1);
+        if (!__syncthreads_and(got)) { if (threadIdx.x == 0) s_abort = 1; break; }
+        consumed = i + 1;
+        const uint8_t* ks = smem + s * C::STAGE_BYTES;
+        const uint8_t* vs = ks + C::PAGE_BYTES;
+        const int row0 = (pg_beg + i) * PAGE + warp * KPW;           // first row of this warp's keys
+
+        // ---- partial dot products: vals[pass * G + g] over this lane's 8 dims
+        float vals[N];
+#pragma unroll
+        for (int p = 0; p < NP; p++) {
+            const int kk = warp * KPW + p * KP + kg;
+            float kf[8];
+            bf16x8_to_f32(*(const uint4*)(ks + (size_t)kk * HD * 2 + sub * 16), kf);
+#pragma unroll
+            for (int g = 0; g < G; g++) {
+                float d = 0.f;
+#pragma unroll
+                for (int e = 0; e < 8; e++) d = fmaf(q[g][e], kf[e], d);
+                vals[p * G + g] = d;
+            }
+        }
+        // ---- butterfly over the LPK lanes of a key: halves the values a lane holds at each step
+        {
+            int cnt = N;
+#pragma unroll
+            for (int off = LPK / 2; off >= 1; off >>= 1) {
+                if (cnt > 1) {
+                    cnt >>= 1;
+                    const bool upper = (lane & off) != 0;
+#pragma unroll
+                    for (int j = 0; j < N / 2; j++) {
+                        if (j < cnt) {
+                            const float send = upper ? vals[j] : vals[j + cnt];
+                            const float keep = upper ? vals[j + cnt] : vals[j];
+                            vals[j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+                        }
+                    }
+                } else {
+                    vals[0] += __shfl_xor_sync(0xffffffffu, vals[0], off);
+                }
+            }
+        }
+        // lane now holds NF scores: original index idx_j = (N > LPK) ? sub * NF + j : sub / SPREAD
+        float sc[NF];
+        int gh[NF];
+        float pmax[G];
+#pragma unroll
+        for (int g = 0; g < G; g++) pmax[g] = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < NF; j++) {
+            const int idx = (N > LPK) ? sub * NF + j : sub / SPREAD;
+            const int p = idx / G, g = idx % G;
+            gh[j] = g;
+            const int R = row0 + p * KP + kg;                       // row of this score's key
+            bool valid;
+            if (a.ring_rows > 0) {
+                valid = R < min(len, a.ring_rows);
+                if (valid) { const int pos = R + a.ring_rows * ((len - 1 - R) / a.ring_rows); valid = pos >= lo; }
+            } else {
+                valid = R >= lo && R < len;
+            }
+            float v = vals[j];
+            if (a.cap > 0.f) v = softcap_f(v, a.cap);
+            sc[j] = valid ? v : -INFINITY;
+#pragma unroll
+            for (int gg = 0; gg < G; gg++) if (gg == g) pmax[gg] = fmaxf(pmax[gg], sc[j]);
+        }
+#pragma unroll
+        for (int g = 0; g < G; g++) pmax[g] = warp_max(pmax[g]);
+        // ---- running softmax: one correction per page
+        float corr[G];
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+            const float mn = fmaxf(m[g], pmax[g]);
+            corr[g] = (mn == -INFINITY || m[g] == -INFINITY) ? 0.f : __expf(m[g] - mn);
+            m[g] = mn;
+#pragma unroll
+            for (int e = 0; e < 8; e++) o[g][e] *= corr[g];
+        }
+        float pr[NF];
+#pragma unroll
+        for (int j = 0; j < NF; j++) {
+            float mg = -INFINITY, cg = 0.f;
+#pragma unroll
+            for (int g = 0; g < G; g++) if (g == gh[j]) { mg = m[g]; cg = corr[g]; }
+            pr[j] = (sc[j] == -INFINITY) ? 0.f : __expf(sc[j] - mg);
+            l_lane[j] = l_lane[j] * cg + ((lane % SPREAD) == 0 ? pr[j] : 0.f);   // count each score once
+        }
+        // ---- o += p * v: fetch each (pass, head) probability from the lane that holds it
+#pragma unroll
+        for (int p = 0; p < NP; p++) {
+            const int kk = warp * KPW + p * KP + kg;
+            float pv[G];
+            bool any = false;
+#pragma unroll
+            for (int g = 0; g < G; g++) {
+                const int idx = p * G + g;
+                const int src_sub = (N > LPK) ? idx / NF : idx * SPREAD;
+                float val = 0.f;
+#pragma unroll
+                for (int j = 0; j < NF; j++) {
+                    const float t = __shfl_sync(0xffffffffu, pr[j], kg * LPK + src_sub);
+                    if ((N > LPK ? idx % NF : 0) == j) val = t;
+                }
+                pv[g] = val;
+                any |= val != 0.f;
+            }
+            if (any) {                                              // rows that are not keys are never read
+                float vf[8];
+                bf16x8_to_f32(*(const uint4*)(vs + (size_t)kk * HD * 2 + sub * 16), vf);
+#pragma unroll
+                for (int g = 0; g < G; g++)
+                    if (pv[g] != 0.f) {
+#pragma unroll
+                        for (int e = 0; e < 8; e++) o[g][e] = fmaf(pv[g], vf[e], o[g][e]);
+                    }
+            }
+        }
+        __syncthreads();                                            // everyone is done with stage s
+        if (threadIdx.x == 0 && i + C::STAGES < n) issue(i + C::STAGES);
+    }
+
+    if (s_abort) {
+        // a wait ran out: record it, and let copies that were issued land before the CTA ends
+        if (threadIdx.x == 0) {
+            atomicExch(&g_attn_error, 1);
+            const int issued = min(n, consumed + C::STAGES);
+            for (int i = consumed; i < issued; i++) mbar_wait(&full[i % C::STAGES], (i / C::STAGES) & 1);
+        }
+        __syncthreads();
+        return;
+    }
+
+    // ---- fold the key groups of a warp, then the warps
+#pragma unroll
+    for (int off = LPK; off < 32; off <<= 1)
+#pragma unroll
+        for (int g = 0; g < G; g++)
+#pragma unroll
+            for (int e = 0; e < 8; e++) o[g][e] += __shfl_xor_sync(0xffffffffu, o[g][e], off);
+    float lsum[G];
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        float t = 0.f;
+#pragma unroll
+        for (int j = 0; j < NF; j++) if ((((N > LPK) ? sub * NF + j : sub / SPREAD) % G) == g) t += l_lane[j];
+        lsum[g] = warp_sum(t);
+    }
+    __syncthreads();                                                // the stages are free: reuse them
+    float* red = (float*)smem;                                      // [NWARP][G][HD + 2]
+    if (kg == 0) {
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+            float* r = red + ((size_t)warp * G + g) * (HD + 2);
+#pragma unroll
+            for (int e = 0; e < 8; e++) r[sub * 8 + e] = o[g][e];
+            if (sub == 0) { r[HD] = m[g]; r[HD + 1] = lsum[g]; }
+        }
+    }
+    __syncthreads();
+    for (int t = threadIdx.x; t < G * HD; t += blockDim.x) {
+        const int g = t / HD, d = t % HD;
+        float M = -INFINITY;
+        for (int w = 0; w < NWARP; w++) M = fmaxf(M, red[((size_t)w * G + g) * (HD + 2) + HD]);
+        float L = 0.f, acc = 0.f;
+        for (int w = 0; w < NWARP; w++) {
+            const float* r = red + ((size_t)w * G + g) * (HD + 2);
+            if (r[HD] != -INFINITY) { const float f = __expf(r[HD] - M); L += r[HD + 1] * f; acc += r[d] * f; }
+        }
+        const int h = kvh * G + g;
+        if (a.n_splits == 1) {
+            ((bf16*)a.out)[((size_t)b * a.n_heads + h) * HD + d] = __float2bfloat16_rn(acc / L);
+        } else {
+            float* p = a.partial + (((size_t)b * a.n_heads + h) * a.n_splits + split) * (HD + 2);
+            p[d] = acc;
+            if (d == 0) { p[HD] = M; p[HD + 1] = L; }
+        }
+    }
+}
+
+// out[b,h,:] = sum_s e^(m_s - M) o_s / sum_s e^(m_s - M) l_s, splits in ascending order.
+__global__ void attn_combine_kernel(const float* __restrict__ partial, bf16* __restrict__ out, int n_splits, int hd) {
+    const size_t bh = blockIdx.x;
+    const float* p = partial + bh * n_splits * (hd + 2);
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; s++) M = fmaxf(M, p[(size_t)s * (hd + 2) + hd]);
+    float L = 0.f;
+    for (int s = 0; s < n_splits; s++) {
+        const float ms = p[(size_t)s * (hd + 2) + hd];
+        if (ms != -INFINITY) L += p[(size_t)s * (hd + 2) + hd + 1] * __expf(ms - M);
+    }
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float o = 0.f;
+        for (int s = 0; s < n_splits; s++) {
+            const float ms = p[(size_t)s * (hd + 2) + hd];
+            if (ms != -INFINITY) o += p[(size_t)s * (hd + 2) + d] * __expf(ms - M);
+        }
+        out[bh * hd + d] = __float2bfloat16_rn(o / L);
+    }
+}
+
+template <int HD, int G>
+static int launch(const DecodeArgs& a, int batch, cudaStream_t stream) {
+    using C = DCfg<HD>;
+    static bool attr_set = false;
+    auto kern = attn_decode_kernel<HD, G>;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    dim3 grid(batch, a.n_kv_heads, a.n_splits);
+    kern<<<grid, NWARP * 32, C::SMEM, stream>>>(a);
+    return tb_launch_status();
+}
+
+extern "C" int tb_attn_decode_takes(int dtype, int n_heads, int n_kv_heads, int hd) {
+    if (dtype != TB_BF16 || n_kv_heads <= 0 || n_heads % n_kv_heads) return 0;
+    const int g = n_heads / n_kv_heads;
+    if (!(hd == 32 || hd == 64 || hd == 128 || hd == 256)) return 0;
+    if (!(g == 1 || g == 2 || g == 4 || g == 8)) return 0;
+    return 1;
+}
+
+extern "C" int tb_attn_decode(const DecodeArgs* args, int dtype, int batch, cudaStream_t stream) {
+    if (batch <= 0) return 0;
+    DecodeArgs a = *args;
+    if (!tb_attn_decode_takes(dtype, a.n_heads, a.n_kv_heads, a.hd))
+        return tb_refuse("attn_decode: takes bfloat16, head_dim 32/64/128/256 and 1/2/4/8 heads per kv head "
+                         "(got dtype %d, %d heads, %d kv heads, head_dim %d)", dtype, a.n_heads, a.n_kv_heads, a.hd);
+    if (a.page_rows != PAGE) return tb_refuse("attn_decode: pages of %d rows, this kernel is built for %d", a.page_rows, PAGE);
+    if (a.n_splits < 1 || a.n_splits > 65535 || a.n_kv_heads > 65535) return tb_refuse("attn_decode: n_splits=%d", a.n_splits);
+    if (a.n_splits > 1 && a.partial == nullptr) return tb_refuse("attn_decode: splits need scratch");
+    if (a.ring_rows > 0 && (a.ring_rows % PAGE || a.window <= 0 || a.window > a.ring_rows))
+        return tb_refuse("attn_decode: a ring of %d rows cannot hold a window of %d", a.ring_rows, a.window);
+    if (((uintptr_t)a.q & 15) || (a.q_stride % 8) || ((uintptr_t)a.k_pool & 15) || ((uintptr_t)a.v_pool & 15))
+        return tb_refuse("attn_decode: q rows and the pools must be 16-byte aligned");
+    const int g = a.n_heads / a.n_kv_heads;
+    int st = -1;
+#define GO(HD_)                                                          \
+    switch (g) {                                                         \
+    case 1: st = launch<HD_, 1>(a, batch, stream); break;                \
+    case 2: st = launch<HD_, 2>(a, batch, stream); break;                \
+    case 4: st = launch<HD_, 4>(a, batch, stream); break;                \
+    default: st = launch<HD_, 8>(a, batch, stream); break;               \
+    }
+    switch (a.hd) {
+    case 32: GO(32); break;
+    case 64: GO(64); break;
+    case 128: GO(128); break;
+    default: GO(256); break;
+    }
+#undef GO
+    if (st) return st;
+    if (a.n_splits > 1) {
+        attn_combine_kernel<<<(unsigned)batch * a.n_heads, 128, 0, stream>>>(a.partial, (bf16*)a.out, a.n_splits, a.hd);
+        st = tb_launch_status();
+    }
+    return st;
+}
+
+// Reads and clears the error word (1: a bounded wait on a page copy ran out).  Synchronises.
+extern "C" int tb_attn_decode_error() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_attn_error, sizeof(int)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_attn_error, &zero, sizeof(int));
+    return v;
+}

@@ -3,7 +3,7 @@
 Each ``.cu`` file of this folder becomes one shared library for sm_100a, built
 with nvcc at its first use and kept under ``_build/`` beside the sources (or in
 a per-user temporary folder when the source tree cannot be written).  The file
-name carries a hash of the source, of ``common.cuh`` and of the flags, so an
+name carries a hash of the source, of the shared headers and of the flags, so an
 edited kernel is rebuilt and a stale library is never loaded.  The libraries
 export plain C functions and are loaded with ctypes; they do not link against
 torch.  There is no fallback: if a library cannot be built or loaded, the call
@@ -32,7 +32,7 @@ NVCC_FLAGS = [
 ]
 
 # every kernel file of the package; build_all() compiles them all
-SOURCES = ["embed", "norm", "rope_kv", "activation", "gemm_simt", "gemm_tc", "attention_simt", "sampling"]
+SOURCES = ["embed", "norm", "rope_kv", "activation", "gemm_simt", "gemm_tc", "attention_simt", "attention_decode", "sampling"]
 
 
 class KernelBuildError(RuntimeError):
@@ -84,12 +84,9 @@ def _pick_build_dir() -> str:
 
 def _digest(name: str) -> str:
     h = hashlib.sha256()
-    for fn in (name + ".cu", "common.cuh"):
+    headers = sorted(fn for fn in os.listdir(_HERE) if fn.endswith(".cuh"))
+    for fn in [name + ".cu"] + headers:
         with open(os.path.join(_HERE, fn), "rb") as f:
-            h.update(f.read())
-    extra = os.path.join(_HERE, name + ".cuh")
-    if os.path.exists(extra):
-        with open(extra, "rb") as f:
             h.update(f.read())
     h.update(" ".join(NVCC_FLAGS).encode())
     return h.hexdigest()[:16]

@@ -416,7 +416,58 @@ def attn_prefill(q, k, v, seq_start, token_seq, n_heads, n_kv_heads, head_dim, s
     return attn_prefill_simt(q, k, v, seq_start, token_seq, n_heads, n_kv_heads, head_dim, scale, softcap, window)
 
 
+def attn_decode_takes(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int) -> bool:
+    """Whether the bulk-copy decode kernel takes this shape (bfloat16, head_dim 32/64/128/256, 1/2/4/8
+    query heads per kv head); other shapes run on the generic kernel."""
+    if dtype != torch.bfloat16 or n_kv_heads <= 0 or n_heads % n_kv_heads:
+        return False
+    return head_dim in (32, 64, 128, 256) and (n_heads // n_kv_heads) in (1, 2, 4, 8)
+
+
+def attn_decode_tma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
+                    len_after: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
+                    softcap: float, window: int, ring_rows: int, n_splits: int = 1) -> torch.Tensor:
+    """Decode attention with pages staged in shared memory by bulk copies (see attention_decode.cu)."""
+    _cuda(q, k_pool, v_pool, page_table, len_after)
+    _rows_contig(q, "attention: q")
+    B = q.shape[0]
+    if not attn_decode_takes(q.dtype, n_heads, n_kv_heads, head_dim):
+        raise KernelError(f"attn_decode_tma does not take {q.dtype}, {n_heads}/{n_kv_heads} heads, head_dim {head_dim}")
+    if page_table.dtype != torch.int32 or page_table.dim() != 2 or page_table.stride(1) != 1 or page_table.shape[0] < B:
+        raise KernelError("attention: page_table must be int32 [batch, pages]")
+    if len_after.dtype != torch.int32 or len_after.numel() < B:
+        raise KernelError("attention: len_after must be int32 [batch]")
+    if tuple(k_pool.shape[1:]) != (n_kv_heads, PAGE_ROWS, head_dim) or k_pool.shape != v_pool.shape \
+            or not k_pool.is_contiguous() or not v_pool.is_contiguous() or k_pool.dtype != q.dtype:
+        raise KernelError("attention: pools must be contiguous [pages, n_kv_heads, PAGE_ROWS, head_dim] of q's dtype")
+    out = torch.empty((B, n_heads * head_dim), dtype=q.dtype, device=q.device)
+    scratch = None
+    if n_splits > 1:
+        scratch = torch.empty(B * n_heads * n_splits * (head_dim + 2), dtype=torch.float32, device=q.device)
+    a = _DecodeArgs()
+    a.q = q.data_ptr(); a.q_stride = q.stride(0)
+    a.k_pool = k_pool.data_ptr(); a.v_pool = v_pool.data_ptr()
+    a.page_table = page_table.data_ptr(); a.pt_stride = page_table.stride(0)
+    a.len_after = len_after.data_ptr(); a.out = out.data_ptr()
+    a.partial = scratch.data_ptr() if scratch is not None else None
+    a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.hd = head_dim; a.page_rows = PAGE_ROWS
+    a.ring_rows = ring_rows; a.window = window or 0; a.n_splits = n_splits
+    a.scale = scale; a.cap = softcap or 0.0
+    lib = build.load("attention_decode")
+    _check(lib, lib.tb_attn_decode(ctypes.byref(a), c_int(code(q.dtype)), c_int(B), _stream()), "attn_decode",
+           2 if n_splits > 1 else 1)
+    return out
+
+
+def attn_decode_error() -> int:
+    """Reads and clears the decode attention's error word (synchronises); 0 = no wait ran out."""
+    return int(build.load("attention_decode").tb_attn_decode_error())
+
+
 def attn_decode(q, k_pool, v_pool, page_table, len_after, n_heads, n_kv_heads, head_dim, scale, softcap, window,
                 ring_rows, n_splits: int, max_len_after: int) -> torch.Tensor:
+    if attn_decode_takes(q.dtype, n_heads, n_kv_heads, head_dim):
+        return attn_decode_tma(q, k_pool, v_pool, page_table, len_after, n_heads, n_kv_heads, head_dim, scale,
+                               softcap, window, ring_rows, n_splits)
     return attn_decode_simt(q, k_pool, v_pool, page_table, len_after, n_heads, n_kv_heads, head_dim, scale,
                             softcap, window, ring_rows, n_splits)

@@ -34,15 +34,16 @@ def _sm_count(device) -> int:
     return _SM_COUNT[idx]
 
 
-def decode_splits(batch: int, n_heads: int, max_len: int, sms: int) -> int:
-    """In how many pieces a decode step cuts each sequence's keys, so that the attention
-    kernel fills the GPU when batch * heads alone does not.  Depends on the longest
-    context only through a power-of-two bucket, so the choice is stable while a batch grows."""
+def decode_splits(batch: int, n_kv_heads: int, max_len: int, sms: int) -> int:
+    """In how many pieces a decode step cuts each sequence's keys, so that the attention kernel
+    (one CTA per sequence, kv head and piece) fills the GPU when batch * kv heads alone does not.
+    A piece keeps at least four pages (256 keys).  The longest context enters only through a
+    power-of-two bucket, so the choice is stable while a batch grows."""
     bucket = 256
     while bucket < max_len:
         bucket *= 2
-    by_len = max(1, bucket // 256)                    # at least 256 keys per piece
-    by_fill = max(1, (2 * sms + batch * n_heads - 1) // (batch * n_heads))
+    by_len = max(1, bucket // 256)
+    by_fill = max(1, (sms + batch * n_kv_heads - 1) // (batch * n_kv_heads))
     return int(min(by_len, by_fill, 64))
 
 
@@ -54,7 +55,7 @@ class Engine:
         self.cache = Cache(needs, readers, max_tokens, self.rt.dtype, self.rt.device, max_slots)
         self.vocab_size = model.vocab_size
         self._inputs = StepInputs(self.rt.device)
-        self._heads = max([getattr(b.mixer, "n_heads", 1) for b in model.blocks] or [1])
+        self._heads = max([getattr(b.mixer, "n_kv", 1) for b in model.blocks] or [1])
         # CUDA graphs for decode steps: only if every part says that its launches depend on nothing
         # that lives on the host (a part that reads ctx.slots in Python, for one, does not qualify)
         self.use_graphs = use_graphs and self.rt.device.type == "cuda"

@@ -66,7 +66,8 @@ class Attention(Mixer):
         self.position.bind(tensors)
 
     def kernel_files(self):
-        return linear_kernels(self.rt.dtype) + self.position.kernel_files() + ("attention_simt",)
+        fast = ("attention_decode",) if ops.attn_decode_takes(self.rt.dtype, self.n_heads, self.n_kv, self.hd) else ()
+        return linear_kernels(self.rt.dtype) + self.position.kernel_files() + ("attention_simt",) + fast
 
     def cache_need(self):
         return KVNeed(self.n_kv, self.hd, self.window)
