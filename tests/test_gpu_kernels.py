@@ -259,9 +259,10 @@ def test_attn_decode_far_key_and_window_edge(ops, dt):
 
 @pytest.mark.parametrize("dt", DT)
 @pytest.mark.parametrize("nh,nkv,hd,cap,window", [(4, 2, 16, 50.0, 8), (6, 1, 32, 0.0, 16), (3, 3, 48, 20.0, 0),
-                                                  (2, 1, 256, 50.0, 50), (4, 4, 112, 0.0, 0)])
+                                                  (2, 1, 256, 50.0, 50), (4, 4, 112, 0.0, 0), (4, 2, 64, 0.0, 64),
+                                                  (2, 2, 128, 30.0, 65), (8, 4, 256, 50.0, 0)])
 def test_attn_prefill(ops, dt, nh, nkv, hd, cap, window):
-    lens = [1, 70, 9, 33]
+    lens = [1, 70, 9, 33, 200, 64, 129]
     T = sum(lens)
     qkv = rnd(T, (nh + 2 * nkv) * hd, dt=dt, s=0.7)
     q, k, v = qkv[:, :nh * hd], qkv[:, nh * hd:(nh + nkv) * hd], qkv[:, (nh + nkv) * hd:]
@@ -271,12 +272,40 @@ def test_attn_prefill(ops, dt, nh, nkv, hd, cap, window):
     seq_start = torch.tensor(starts, dtype=torch.int32, device="cuda")
     token_seq = torch.repeat_interleave(torch.arange(len(lens), dtype=torch.int32), torch.tensor(lens)).cuda()
     scale = 1.0 / math.sqrt(hd)
-    got = ops.attn_prefill_simt(q, k, v, seq_start, token_seq, nh, nkv, hd, scale, cap, window)
+    impls = [lambda: ops.attn_prefill_simt(q, k, v, seq_start, token_seq, nh, nkv, hd, scale, cap, window)]
+    if ops.attn_prefill_takes(dt, hd) and hd in (16, 32, 48, 64, 128, 256):
+        impls.append(lambda: ops.attn_prefill_mma(q, k, v, seq_start, nh, nkv, hd, scale, cap, window, max(lens)))
+    wants = []
     for b, n in enumerate(lens):
         s = slice(starts[b], starts[b + 1])
-        want = plain.attention(q[s].float().cpu().view(n, nh, hd), k[s].float().cpu().view(n, nkv, hd),
-                               v[s].float().cpu().view(n, nkv, hd), scale, cap or None, window or None)
-        close(got[s].view(n, nh, hd), want, dt, 2.0)
+        wants.append(plain.attention(q[s].float().cpu().view(n, nh, hd), k[s].float().cpu().view(n, nkv, hd),
+                                     v[s].float().cpu().view(n, nkv, hd), scale, cap or None, window or None))
+    for impl in impls:
+        got = impl()
+        for b, n in enumerate(lens):
+            close(got[starts[b]:starts[b + 1]].view(n, nh, hd), wants[b], dt, 2.0)
+
+
+def test_attn_prefill_far_key_and_window_edge(ops):
+    """A key made to stand out is seen from far away without a window, and exactly up to the window's
+    edge with one; on tensor cores and on the generic kernel alike."""
+    nh, nkv, hd, n, W = 2, 1, 64, 300, 100
+    qkv = rnd(n, (nh + 2 * nkv) * hd, dt=torch.bfloat16, s=0.1)
+    q, k, v = qkv[:, :nh * hd], qkv[:, nh * hd:(nh + nkv) * hd], qkv[:, (nh + nkv) * hd:]
+    marked = 37
+    k[marked] = (q[250, :hd].float() * 300).to(torch.bfloat16)          # query 250, head 0 loves key 37
+    for i in (marked + W - 1, marked + W, 250):
+        q[i, :hd] = q[250, :hd]
+    seq_start = torch.tensor([0, n], dtype=torch.int32, device="cuda")
+    token_seq = torch.zeros(n, dtype=torch.int32, device="cuda")
+    for window in (0, W):
+        for got in (ops.attn_prefill_simt(q, k, v, seq_start, token_seq, nh, nkv, hd, 1.0, 0.0, window),
+                    ops.attn_prefill_mma(q, k, v, seq_start, nh, nkv, hd, 1.0, 0.0, window, n)):
+            got = got.view(n, nh, hd).float()
+            hit = lambda i: float((got[i, 0] - v[marked].float()).abs().max()) < 3e-2
+            assert hit(marked + W - 1)                                  # the window's last row that still sees it
+            assert hit(marked + W) == (window == 0)                     # one further: only without a window
+            assert hit(250) == (window == 0)
 
 
 @pytest.mark.parametrize("dt", DT)

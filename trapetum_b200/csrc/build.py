@@ -31,8 +31,10 @@ NVCC_FLAGS = [
     "--shared", "-Xcompiler", "-fPIC",
 ]
 
-# every kernel file of the package; build_all() compiles them all
-SOURCES = ["embed", "norm", "rope_kv", "activation", "gemm_simt", "gemm_tc", "attention_simt", "attention_decode", "sampling"]
+# every kernel file of the package; build_all() compiles them all.  A name of the form
+# "file@MACRO=value" is the file compiled with -DMACRO=value (one library per value).
+SOURCES = ["embed", "norm", "rope_kv", "activation", "gemm_simt", "gemm_tc", "attention_simt", "attention_decode", "sampling"] + \
+    [f"attention_prefill@TB_HD={hd}" for hd in (16, 32, 48, 64, 128, 256)]
 
 
 class KernelBuildError(RuntimeError):
@@ -82,8 +84,18 @@ def _pick_build_dir() -> str:
         return d
 
 
+def _split(name: str):
+    """"file@MACRO=value" -> (file, ["-DMACRO=value"], "file_MACROvalue")."""
+    if "@" not in name:
+        return name, [], name
+    base, macro = name.split("@", 1)
+    return base, ["-D" + macro], base + "_" + macro.replace("=", "")
+
+
 def _digest(name: str) -> str:
+    name, defines, _ = _split(name)
     h = hashlib.sha256()
+    h.update(" ".join(defines).encode())
     headers = sorted(fn for fn in os.listdir(_HERE) if fn.endswith(".cuh"))
     for fn in [name + ".cu"] + headers:
         with open(os.path.join(_HERE, fn), "rb") as f:
@@ -93,7 +105,7 @@ def _digest(name: str) -> str:
 
 
 def library_path(name: str) -> str:
-    return os.path.join(_build_dir(), f"tb_{name}-{_digest(name)}.so")
+    return os.path.join(_build_dir(), f"tb_{_split(name)[2]}-{_digest(name)}.so")
 
 
 def _say(msg: str) -> None:
@@ -104,12 +116,13 @@ def _compile(name: str) -> str:
     out = library_path(name)
     if os.path.exists(out):
         return out
-    src = os.path.join(_HERE, name + ".cu")
+    base, defines, _ = _split(name)
+    src = os.path.join(_HERE, base + ".cu")
     if not os.path.exists(src):
         raise KernelBuildError(f"no kernel source {src}")
     tmp = f"{out}.{os.getpid()}.{threading.get_ident()}.tmp"
-    cmd = [_nvcc()] + NVCC_FLAGS + ["-I", _HERE, "-o", tmp, src]
-    _say(f"compiling {name}.cu for sm_100a ...")
+    cmd = [_nvcc()] + NVCC_FLAGS + defines + ["-I", _HERE, "-o", tmp, src]
+    _say(f"compiling {base}.cu {' '.join(defines)} for sm_100a ...")
     t0 = time.time()
     proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
                             cwd=os.path.dirname(out))
@@ -118,11 +131,11 @@ def _compile(name: str) -> str:
             log, _ = proc.communicate(timeout=20)
             break
         except subprocess.TimeoutExpired:
-            _say(f"  still compiling {name}.cu ({time.time() - t0:.0f} s)")
+            _say(f"  still compiling {base}.cu ({time.time() - t0:.0f} s)")
     if proc.returncode != 0:
         if os.path.exists(tmp):
             os.unlink(tmp)
-        raise KernelBuildError(f"nvcc failed on {name}.cu:\n{log}")
+        raise KernelBuildError(f"nvcc failed on {base}.cu {' '.join(defines)}:\n{log}")
     os.replace(tmp, out)
     _say(f"  built {os.path.basename(out)} in {time.time() - t0:.1f} s")
     return out

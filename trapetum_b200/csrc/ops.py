@@ -411,8 +411,44 @@ def gemm_tc_error() -> int:
     return int(build.load("gemm_tc").tb_gemm_tc_error())
 
 
+def attn_prefill_takes(dtype: torch.dtype, head_dim: int) -> bool:
+    """Whether the tensor-core prefill kernel takes this shape (bfloat16, head_dim a multiple of 16 up to 256)."""
+    return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256
+
+
+def attn_prefill_lib(head_dim: int) -> str:
+    return f"attention_prefill@TB_HD={head_dim}"
+
+
+def attn_prefill_mma(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, seq_start: torch.Tensor, n_heads: int,
+                     n_kv_heads: int, head_dim: int, scale: float, softcap: float, window: int,
+                     max_seq_len: int) -> torch.Tensor:
+    """Causal attention of packed sequences on tensor cores (see attention_prefill.cu); ``max_seq_len`` is the
+    longest sequence of the batch (it sizes the grid)."""
+    _cuda(q, k, v, seq_start)
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        _rows_contig(t, "attention: " + name)
+    if not attn_prefill_takes(q.dtype, head_dim) or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise KernelError(f"attn_prefill_mma does not take {q.dtype} with head_dim {head_dim}")
+    if k.stride(0) != v.stride(0):
+        raise KernelError("attention: k and v must share their row stride")
+    if seq_start.dtype != torch.int32 or not seq_start.is_contiguous() or seq_start.numel() < 2:
+        raise KernelError("attention: seq_start must be contiguous int32 [batch + 1]")
+    T = q.shape[0]
+    B = seq_start.numel() - 1
+    out = torch.empty((T, n_heads * head_dim), dtype=q.dtype, device=q.device)
+    lib = build.load(attn_prefill_lib(head_dim))
+    _check(lib, lib.tb_attn_prefill_mma(_ptr(q), _ptr(k), _ptr(v), c_longlong(q.stride(0)), c_longlong(k.stride(0)),
+                                        _ptr(seq_start), _ptr(out), c_int(B), c_int(max_seq_len), c_int(n_heads),
+                                        c_int(n_kv_heads), c_int(head_dim), c_float(scale), c_float(softcap or 0.0),
+                                        c_int(window or 0), _stream()), "attn_prefill_mma")
+    return out
+
+
 def attn_prefill(q, k, v, seq_start, token_seq, n_heads, n_kv_heads, head_dim, scale, softcap, window,
                  max_seq_len: int) -> torch.Tensor:
+    if attn_prefill_takes(q.dtype, head_dim):
+        return attn_prefill_mma(q, k, v, seq_start, n_heads, n_kv_heads, head_dim, scale, softcap, window, max_seq_len)
     return attn_prefill_simt(q, k, v, seq_start, token_seq, n_heads, n_kv_heads, head_dim, scale, softcap, window)
 
 

@@ -67,6 +67,8 @@ class Attention(Mixer):
 
     def kernel_files(self):
         fast = ("attention_decode",) if ops.attn_decode_takes(self.rt.dtype, self.n_heads, self.n_kv, self.hd) else ()
+        if ops.attn_prefill_takes(self.rt.dtype, self.hd):
+            fast += (ops.attn_prefill_lib(self.hd),)
         return linear_kernels(self.rt.dtype) + self.position.kernel_files() + ("attention_simt",) + fast
 
     def cache_need(self):
