@@ -402,3 +402,56 @@ extern "C" int tb_attn_decode_error() {
     if (v) cudaMemcpyToSymbol(g_attn_error, &zero, sizeof(int));
     return v;
 }
+
+// ---------------------------------------------------------------------------
+// An entry point that allocates nothing (declared in attention_decode_noalloc.h; it has no
+// counterpart in the reference).
+//
+// tb_attn_decode wants its split partials in scratch memory that the caller allocates.  Some
+// callers cannot do that: a C program or another runtime's plugin that was handed a fixed slice
+// of device memory at start-up and may not call cudaMalloc afterwards, or a latency-critical
+// loop for which cudaMalloc's device-wide synchronisation is unacceptable.  For them the
+// partials live in the array below, which is part of this library's image: every GPU that loads
+// the library holds these 4 MiB until the process exits.
+//
+// In host code `g_noalloc_scratch` is only a stand-in for the symbol, not a device address;
+// handing it to a kernel would fault or, where the GPU can reach host memory, quietly use the
+// wrong bytes.  The device address is looked up once per device with cudaGetSymbolAddress while
+// that device is current, and that pointer is what the kernel receives.
+#include "attention_decode_noalloc.h"
+#include <mutex>
+
+static __device__ __align__(256) float g_noalloc_scratch[TB_ATTN_DECODE_NOALLOC_MAX_FLOATS];
+
+#define NOALLOC_MAX_DEVICES 64
+static float* g_noalloc_ptr[NOALLOC_MAX_DEVICES];          // device address of the array, per device
+static std::mutex g_noalloc_mutex;
+
+extern "C" int tb_attn_decode_noalloc(const DecodeArgs* args, int dtype, int batch, cudaStream_t stream) {
+    if (batch <= 0) return 0;
+    DecodeArgs a = *args;
+    const long long need = a.n_splits > 1 ? (long long)batch * a.n_heads * a.n_splits * (a.hd + 2) : 0;
+    if (need > (long long)TB_ATTN_DECODE_NOALLOC_MAX_FLOATS)
+        return tb_refuse("attn_decode_noalloc: batch %d x %d heads x %d splits x (head_dim %d + 2) = %lld floats of "
+                         "partials, the built-in scratch holds %lld; use fewer splits or tb_attn_decode with "
+                         "scratch of your own", batch, a.n_heads, a.n_splits, a.hd, need,
+                         (long long)TB_ATTN_DECODE_NOALLOC_MAX_FLOATS);
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return tb_refuse("attn_decode_noalloc: device index %d", dev);
+    float* ptr;
+    {
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        if (g_noalloc_ptr[dev] == nullptr) {
+            // set-up, once per device, with that device current
+            void* p = nullptr;
+            e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+            if (e != cudaSuccess) return (int)e;
+            g_noalloc_ptr[dev] = (float*)p;
+        }
+        ptr = g_noalloc_ptr[dev];
+    }
+    a.partial = need ? ptr : nullptr;
+    return tb_attn_decode(&a, dtype, batch, stream);
+}
