@@ -206,9 +206,14 @@ def ref_attention_one(q, k, v, scale, cap, window):
 
 def decode_impls(ops, dt, nh, nkv, hd):
     """The generic kernel always; the bulk-copy kernel too where it takes the shape."""
+    import functools
     impls = [ops.attn_decode_simt]
     if ops.attn_decode_takes(dt, nh, nkv, hd):
         impls.append(ops.attn_decode_tma)
+        if nh // nkv in (1, 2, 4, 8):
+            lanes = functools.partial(ops.attn_decode_tma, variant="lanes")
+            lanes.__name__ = "attn_decode_lanes"
+            impls.append(lanes)
     return impls
 
 
@@ -216,7 +221,8 @@ def decode_impls(ops, dt, nh, nkv, hd):
 @pytest.mark.parametrize("nh,nkv,hd,cap,window,splits", [
     (4, 2, 16, 50.0, 0, 1), (6, 1, 32, 0.0, 40, 3), (3, 3, 48, 20.0, 70, 2), (8, 4, 256, 50.0, 0, 4),
     (5, 5, 80, 0.0, 128, 7), (8, 2, 128, 30.0, 100, 1), (8, 1, 64, 10.0, 0, 2), (4, 4, 32, 0.0, 64, 5),
-    (16, 2, 256, 50.0, 200, 3), (2, 1, 128, 0.0, 0, 9), (8, 8, 64, 0.0, 300, 1)])
+    (16, 2, 256, 50.0, 200, 3), (2, 1, 128, 0.0, 0, 9), (8, 8, 64, 0.0, 300, 1), (6, 2, 64, 25.0, 90, 2),
+    (5, 1, 128, 0.0, 0, 3), (14, 2, 256, 50.0, 0, 2)])
 def test_attn_decode(ops, dt, nh, nkv, hd, cap, window, splits):
     lens = [1, 37, 64, 65, 200, 333]
     ring = ((window + PAGE - 1) // PAGE) * PAGE if window else 0

@@ -31,7 +31,7 @@ def _ctx(lens_before, new, slots=None):
                        positions=dev([p for b, n in zip(lens_before, new) for p in range(b, b + n)]),
                        token_seq=dev([i for i, n in enumerate(new) for _ in range(n)]), seq_start=dev(starts),
                        len_after=dev(after), slot_ids=dev(slots or list(range(B))), slots=slots or list(range(B)),
-                       seq_lens=list(new), max_seq_len=max(new), max_len_after=max(after))
+                       seq_lens=list(new), max_seq_len=max(new), max_len_after=max(after), len_bucket=256)
 
 
 @pytest.mark.parametrize("dt", DTYPES)

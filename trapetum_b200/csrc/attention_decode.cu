@@ -18,10 +18,13 @@
 // Rows of a page beyond the sequence's keys (or outside the window) are never used,
 // not even multiplied by zero: stale or uninitialised rows cannot leak.
 //
-// Takes head_dim in {32, 64, 128, 256} and group sizes 1, 2, 4, 8; other shapes are
-// refused and the caller uses the generic kernel.
+// Takes head_dim in {32, 64, 128, 256} and up to 8 query heads per kv head; other shapes are
+// refused and the caller uses the generic kernel.  Two variants share the staging: the scalar
+// one described above (tb_attn_decode_lanes) and the tensor-core one further down (tb_attn_decode,
+// the product path).
 #include "common.cuh"
 #include "async.cuh"
+#include <cuda.h>
 
 TB_EXPORT_ERROR()
 
@@ -314,6 +317,296 @@ __global__ void __launch_bounds__(NWARP * 32, 1) attn_decode_kernel(DecodeArgs a
     }
 }
 
+// ---------------------------------------------------------------------------
+// Tensor-core variant: the group's query heads are the first rows of a 16-row MMA tile.
+//
+// Q.K^T and P.V run as mma.sync m16n8k16 (bfloat16 operands, 32-bit accumulators): per page of
+// 64 keys a warp issues 64 MMAs instead of some 600 scalar instructions, so the kernel's time
+// is the time of its page copies.  A page arrives as head_dim/64 tiled TMA copies of 64 keys x
+// 64 dims with the 128-byte swizzle (8 KB each), the layout in which every ldmatrix is
+// conflict-free; a dense copy would put all rows of a page on the same banks.  Each of the
+// 4 warps owns 16 keys of a page for both products and keeps its own running softmax; the warps
+// are folded at the end.  Rows of a page that are not keys of the sequence get their scores
+// masked and their V rows zeroed in shared memory before use.
+// ---------------------------------------------------------------------------
+#define MW 4                                       // warps per CTA
+template <int HD> struct MCfg {
+    static constexpr int BOXES = HD / 64;                            // 64-dim column boxes per page
+    static constexpr int BOX_BYTES = PAGE * 128;                     // 64 keys x 128 bytes, swizzled
+    static constexpr int TILE_BYTES = BOXES * BOX_BYTES;             // one page of K (or V)
+    static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+    static constexpr int STAGES_RAW = (192 * 1024) / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_RAW > 6 ? 6 : STAGES_RAW;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /* alignment */ + 128;
+};
+// byte offset of (key row r, 16-byte chunk c of the head dim) inside a swizzled page
+__device__ __forceinline__ int sw_off(int r, int c) {
+    return (c >> 3) * (PAGE * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+}
+__device__ __forceinline__ void tma_load_box(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+// D += A B with rows 8..15 of A all zero (a1 = a3 = 0): only the group's heads occupy rows
+__device__ __forceinline__ void mma_rows8(float* d, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    const uint32_t z = 0u;
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(z), "r"(a2), "r"(z), "r"(b0), "r"(b1));
+}
+
+template <int HD>
+__global__ void __launch_bounds__(MW * 32, 1)
+attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, DecodeArgs a) {
+    using C = MCfg<HD>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(smem + C::STAGES * C::STAGE_BYTES);
+    __shared__ int s_abort;
+
+    const int G = a.n_heads / a.n_kv_heads;                         // 1..8 query heads on rows 0..G-1
+    const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+
+    const int len = a.len_after[b];
+    const int lo = (a.window > 0 && len > a.window) ? len - a.window : 0;
+    int first_page, n_pages;
+    if (a.ring_rows > 0) { first_page = 0; n_pages = (min(len, a.ring_rows) + PAGE - 1) / PAGE; }
+    else { first_page = lo / PAGE; n_pages = (len - 1) / PAGE - first_page + 1; }
+    const int per = (n_pages + a.n_splits - 1) / a.n_splits;
+    const int pg_beg = first_page + split * per;
+    const int pg_end = min(first_page + n_pages, pg_beg + per);
+    const int n = max(0, pg_end - pg_beg);
+    const int* pt = a.page_table + (size_t)b * a.pt_stride;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; s++) mbar_init(&full[s], 1);
+        s_abort = 0;
+        mbar_init_fence();
+    }
+    __syncthreads();
+
+    // one thread issues the copies of a page: head_dim/64 boxes of K and as many of V
+    auto issue = [&](int i) {
+        const int s = i % C::STAGES;
+        const int page = pt[pg_beg + i];
+        const int row = (page * a.n_kv_heads + kvh) * PAGE;          // row of the pool seen as [rows, head_dim]
+        uint8_t* dst = smem + s * C::STAGE_BYTES;
+        mbar_expect_tx(&full[s], C::STAGE_BYTES);
+#pragma unroll
+        for (int bx = 0; bx < C::BOXES; bx++) {
+            tma_load_box(dst + bx * C::BOX_BYTES, &map_k, &full[s], bx * 64, row);
+            tma_load_box(dst + C::TILE_BYTES + bx * C::BOX_BYTES, &map_v, &full[s], bx * 64, row);
+        }
+    };
+    if (threadIdx.x == 0)
+        for (int i = 0; i < n && i < C::STAGES; i++) issue(i);
+
+    // A fragments of Q: a0 = Q[g][16 ks + 2t, +1], a2 = Q[g][16 ks + 8 + 2t, +1]; rows >= G are zero
+    uint32_t qa[HD / 16][2];
+    {
+        const bf16* qp = (const bf16*)a.q + (size_t)b * a.q_stride + (size_t)(kvh * G + g) * HD;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ks++) {
+            qa[ks][0] = (g < G) ? *(const uint32_t*)(qp + ks * 16 + 2 * t) : 0u;
+            qa[ks][1] = (g < G) ? *(const uint32_t*)(qp + ks * 16 + 8 + 2 * t) : 0u;
+        }
+    }
+    float o[HD / 8][4];
+#pragma unroll
+    for (int d = 0; d < HD / 8; d++) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
+    float m_run = -INFINITY, l_run = 0.f;                           // of row g (meaningful for g < G)
+
+    int consumed = 0;
+    for (int i = 0; i < n; i++) {
+        const int s = i % C::STAGES;
+        const bool got = mbar_wait(&full[s], (i / C::STAGES) & 1);
+        if (!__syncthreads_and(got)) { if (threadIdx.x == 0) s_abort = 1; break; }
+        consumed = i + 1;
+        uint8_t* k_s = smem + s * C::STAGE_BYTES;
+        uint8_t* v_s = k_s + C::TILE_BYTES;
+        const int key0 = warp * 16;                                  // this warp's keys within the page
+        const int row0 = (pg_beg + i) * PAGE + key0;
+
+        // ---- which of this warp's 16 rows are keys of the sequence
+        auto is_key = [&](int R) -> bool {
+            if (a.ring_rows > 0) {
+                if (R >= min(len, a.ring_rows)) return false;
+                const int pos = R + a.ring_rows * ((len - 1 - R) / a.ring_rows);
+                return pos >= lo;
+            }
+            return R >= lo && R < len;
+        };
+        const bool first_ok = is_key(row0), last_ok = is_key(row0 + 15);
+        bool all_ok = first_ok && last_ok;
+        if (a.ring_rows > 0 && all_ok) {                             // a ring's keys need not be contiguous
+            for (int r = 1; r < 15; r++) all_ok = all_ok && is_key(row0 + r);
+        }
+        if (!all_ok) {
+            // zero the V rows that are not keys: p is 0 there, but 0 * NaN would still poison o
+            for (int r = 0; r < 16; r++) {
+                if (!is_key(row0 + r)) {
+                    for (int c = lane; c < HD / 8; c += 32)
+                        *(uint4*)(v_s + sw_off(key0 + r, c)) = make_uint4(0, 0, 0, 0);
+                }
+            }
+            // these rows were written by ordinary stores; the stage is later refilled by bulk copies
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+        }
+
+        // ---- S = Q K^T: 16 rows x 16 keys (two n-tiles)
+        float sc[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++) { sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f; }
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ks++) {
+            uint32_t b0, b1, b2, b3;
+            ldsm_x4(smem_u32(k_s + sw_off(key0 + (lane >> 4) * 8 + (lane & 7), ks * 2 + ((lane >> 3) & 1))), b0, b1, b2, b3);
+            mma_rows8(sc[0], qa[ks][0], qa[ks][1], b0, b1);
+            mma_rows8(sc[1], qa[ks][0], qa[ks][1], b2, b3);
+        }
+        // ---- scale, cap, mask; row g lives in sc[nt][0..1] of the quad's four lanes
+        float mx = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                float v = sc[nt][e] * a.scale;
+                if (a.cap > 0.f) v = softcap_f(v, a.cap);
+                const bool ok = all_ok || is_key(row0 + nt * 8 + 2 * t + e);
+                v = ok ? v : -INFINITY;
+                sc[nt][e] = v;
+                mx = fmaxf(mx, v);
+            }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float mn = fmaxf(m_run, mx);
+        const float msafe = (mn == -INFINITY) ? 0.f : mn;
+        const float corr = (m_run == -INFINITY) ? 0.f : __expf(m_run - msafe);
+        m_run = mn;
+        float p[2][2];
+        float ps = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+            for (int e = 0; e < 2; e++) { p[nt][e] = __expf(sc[nt][e] - msafe); ps += p[nt][e]; }
+        l_run = l_run * corr + ps;
+#pragma unroll
+        for (int d = 0; d < HD / 8; d++) { o[d][0] *= corr; o[d][1] *= corr; }
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(p[0][0], p[0][1]), h1 = __floats2bfloat162_rn(p[1][0], p[1][1]);
+        const uint32_t pa0 = (g < G) ? *(uint32_t*)&h0 : 0u, pa2 = (g < G) ? *(uint32_t*)&h1 : 0u;
+        // ---- O += P V over this warp's 16 keys
+#pragma unroll
+        for (int d = 0; d < HD / 8; d += 2) {
+            uint32_t b0, b1, b2, b3;
+            ldsm_x4_t(smem_u32(v_s + sw_off(key0 + ((lane >> 3) & 1) * 8 + (lane & 7), d + (lane >> 4))), b0, b1, b2, b3);
+            mma_rows8(o[d], pa0, pa2, b0, b1);
+            mma_rows8(o[d + 1], pa0, pa2, b2, b3);
+        }
+        __syncthreads();                                            // everyone is done with stage s
+        if (threadIdx.x == 0 && i + C::STAGES < n) issue(i + C::STAGES);
+    }
+
+    if (s_abort) {
+        if (threadIdx.x == 0) {
+            atomicExch(&g_attn_error, 1);
+            const int issued = min(n, consumed + C::STAGES);
+            for (int i = consumed; i < issued; i++) mbar_wait(&full[i % C::STAGES], (i / C::STAGES) & 1);
+        }
+        __syncthreads();
+        return;
+    }
+
+    // ---- fold the four warps: row sums over the quad first
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    __syncthreads();
+    float* red = (float*)smem;                                      // [MW][G][HD + 2]
+    if (g < G) {
+        float* r = red + ((size_t)warp * G + g) * (HD + 2);
+#pragma unroll
+        for (int d = 0; d < HD / 8; d++) { r[d * 8 + 2 * t] = o[d][0]; r[d * 8 + 2 * t + 1] = o[d][1]; }
+        if (t == 0) { r[HD] = m_run; r[HD + 1] = l_run; }
+    }
+    __syncthreads();
+    for (int x = threadIdx.x; x < G * HD; x += blockDim.x) {
+        const int gg = x / HD, d = x % HD;
+        float M = -INFINITY;
+        for (int w = 0; w < MW; w++) M = fmaxf(M, red[((size_t)w * G + gg) * (HD + 2) + HD]);
+        float L = 0.f, acc = 0.f;
+        for (int w = 0; w < MW; w++) {
+            const float* r = red + ((size_t)w * G + gg) * (HD + 2);
+            if (r[HD] != -INFINITY) { const float f = __expf(r[HD] - M); L += r[HD + 1] * f; acc += r[d] * f; }
+        }
+        const int h = kvh * G + gg;
+        if (a.n_splits == 1) {
+            ((bf16*)a.out)[((size_t)b * a.n_heads + h) * HD + d] = __float2bfloat16_rn(acc / L);
+        } else {
+            float* pp = a.partial + (((size_t)b * a.n_heads + h) * a.n_splits + split) * (HD + 2);
+            pp[d] = acc;
+            if (d == 0) { pp[HD] = M; pp[HD + 1] = L; }
+        }
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+// A cache pool seen as a matrix [rows = pages * kv_heads * 64, head_dim]; box = 64 rows x 64 dims.
+static int pool_map(CUtensorMap* m, const void* pool, long long rows, int hd) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return tb_refuse("attn_decode: the driver does not provide cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+    cuuint32_t box[2] = {64, PAGE};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)pool, dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return tb_refuse("attn_decode: cuTensorMapEncodeTiled failed with %d", (int)r);
+    return 0;
+}
+
+template <int HD>
+static int launch_mma(const DecodeArgs& a, int batch, long long pool_rows, cudaStream_t stream) {
+    using C = MCfg<HD>;
+    static bool attr_set = false;
+    auto kern = attn_decode_mma_kernel<HD>;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    CUtensorMap mk, mv;
+    if (pool_map(&mk, a.k_pool, pool_rows, HD) || pool_map(&mv, a.v_pool, pool_rows, HD)) return -1;
+    dim3 grid(batch, a.n_kv_heads, a.n_splits);
+    kern<<<grid, MW * 32, C::SMEM, stream>>>(mk, mv, a);
+    return tb_launch_status();
+}
+
 // out[b,h,:] = sum_s e^(m_s - M) o_s / sum_s e^(m_s - M) l_s, splits in ascending order.
 __global__ void attn_combine_kernel(const float* __restrict__ partial, bf16* __restrict__ out, int n_splits, int hd) {
     const size_t bh = blockIdx.x;
@@ -354,15 +647,27 @@ extern "C" int tb_attn_decode_takes(int dtype, int n_heads, int n_kv_heads, int 
     if (dtype != TB_BF16 || n_kv_heads <= 0 || n_heads % n_kv_heads) return 0;
     const int g = n_heads / n_kv_heads;
     if (!(hd == 32 || hd == 64 || hd == 128 || hd == 256)) return 0;
-    if (!(g == 1 || g == 2 || g == 4 || g == 8)) return 0;
+    if (g < 1 || g > 8) return 0;
+    if (hd == 32 && !(g == 1 || g == 2 || g == 4 || g == 8)) return 0;
     return 1;
 }
 
+static int run_decode(const DecodeArgs* args, int dtype, int batch, bool tensor_cores, cudaStream_t stream);
+
+// The product path: tensor-core variant.
 extern "C" int tb_attn_decode(const DecodeArgs* args, int dtype, int batch, cudaStream_t stream) {
+    return run_decode(args, dtype, batch, true, stream);
+}
+// The scalar variant (one lane group per key), kept for comparison in tests and measurements.
+extern "C" int tb_attn_decode_lanes(const DecodeArgs* args, int dtype, int batch, cudaStream_t stream) {
+    return run_decode(args, dtype, batch, false, stream);
+}
+
+static int run_decode(const DecodeArgs* args, int dtype, int batch, bool tensor_cores, cudaStream_t stream) {
     if (batch <= 0) return 0;
     DecodeArgs a = *args;
     if (!tb_attn_decode_takes(dtype, a.n_heads, a.n_kv_heads, a.hd))
-        return tb_refuse("attn_decode: takes bfloat16, head_dim 32/64/128/256 and 1/2/4/8 heads per kv head "
+        return tb_refuse("attn_decode: takes bfloat16, head_dim 32/64/128/256 and 1 to 8 heads per kv head "
                          "(got dtype %d, %d heads, %d kv heads, head_dim %d)", dtype, a.n_heads, a.n_kv_heads, a.hd);
     if (a.page_rows != PAGE) return tb_refuse("attn_decode: pages of %d rows, this kernel is built for %d", a.page_rows, PAGE);
     if (a.n_splits < 1 || a.n_splits > 65535 || a.n_kv_heads > 65535) return tb_refuse("attn_decode: n_splits=%d", a.n_splits);
@@ -373,6 +678,18 @@ extern "C" int tb_attn_decode(const DecodeArgs* args, int dtype, int batch, cuda
         return tb_refuse("attn_decode: q rows and the pools must be 16-byte aligned");
     const int g = a.n_heads / a.n_kv_heads;
     int st = -1;
+    if (a.hd < 64) tensor_cores = false;            // a 64-byte row has no 128-byte swizzled box
+    if (tensor_cores) {
+        // the map's row count only bounds the copy engine's address check; pages come from the table
+        const long long rows = 0x7fffff00LL;
+        switch (a.hd) {
+        case 64: st = launch_mma<64>(a, batch, rows, stream); break;
+        case 128: st = launch_mma<128>(a, batch, rows, stream); break;
+        default: st = launch_mma<256>(a, batch, rows, stream); break;
+        }
+    } else {
+    if (!(g == 1 || g == 2 || g == 4 || g == 8))
+        return tb_refuse("attn_decode_lanes: %d heads per kv head (takes 1, 2, 4 or 8)", g);
 #define GO(HD_)                                                          \
     switch (g) {                                                         \
     case 1: st = launch<HD_, 1>(a, batch, stream); break;                \
@@ -387,6 +704,7 @@ extern "C" int tb_attn_decode(const DecodeArgs* args, int dtype, int batch, cuda
     default: GO(256); break;
     }
 #undef GO
+    }
     if (st) return st;
     if (a.n_splits > 1) {
         attn_combine_kernel<<<(unsigned)batch * a.n_heads, 128, 0, stream>>>(a.partial, (bf16*)a.out, a.n_splits, a.hd);

@@ -453,17 +453,20 @@ def attn_prefill(q, k, v, seq_start, token_seq, n_heads, n_kv_heads, head_dim, s
 
 
 def attn_decode_takes(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int) -> bool:
-    """Whether the bulk-copy decode kernel takes this shape (bfloat16, head_dim 32/64/128/256, 1/2/4/8
+    """Whether the bulk-copy decode kernel takes this shape (bfloat16, head_dim 32/64/128/256, up to 8
     query heads per kv head); other shapes run on the generic kernel."""
     if dtype != torch.bfloat16 or n_kv_heads <= 0 or n_heads % n_kv_heads:
         return False
-    return head_dim in (32, 64, 128, 256) and (n_heads // n_kv_heads) in (1, 2, 4, 8)
+    g = n_heads // n_kv_heads
+    return (head_dim in (64, 128, 256) and 1 <= g <= 8) or (head_dim == 32 and g in (1, 2, 4, 8))
 
 
 def attn_decode_tma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
                     len_after: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
-                    softcap: float, window: int, ring_rows: int, n_splits: int = 1) -> torch.Tensor:
-    """Decode attention with pages staged in shared memory by bulk copies (see attention_decode.cu)."""
+                    softcap: float, window: int, ring_rows: int, n_splits: int = 1,
+                    variant: str = "mma") -> torch.Tensor:
+    """Decode attention with pages staged in shared memory by bulk copies (see attention_decode.cu).
+    ``variant``: "mma" (tensor cores, the product path) or "lanes" (scalar, kept for comparison)."""
     _cuda(q, k_pool, v_pool, page_table, len_after)
     _rows_contig(q, "attention: q")
     B = q.shape[0]
@@ -490,7 +493,8 @@ def attn_decode_tma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     a.ring_rows = ring_rows; a.window = window or 0; a.n_splits = n_splits
     a.scale = scale; a.cap = softcap or 0.0
     lib = build.load("attention_decode")
-    _check(lib, lib.tb_attn_decode(ctypes.byref(a), c_int(code(q.dtype)), c_int(B), _stream()), "attn_decode",
+    fn = lib.tb_attn_decode if variant == "mma" else lib.tb_attn_decode_lanes
+    _check(lib, fn(ctypes.byref(a), c_int(code(q.dtype)), c_int(B), _stream()), "attn_decode",
            2 if n_splits > 1 else 1)
     return out
 
@@ -500,10 +504,38 @@ def attn_decode_error() -> int:
     return int(build.load("attention_decode").tb_attn_decode_error())
 
 
+def choose_decode_splits(batch: int, n_kv_heads: int, pages: int, sms: int) -> int:
+    """In how many pieces decode attention cuts a sequence's pages.  A CTA serves one (sequence, kv head,
+    piece); all CTAs of a launch are about equally long, so the launch takes ceil(CTAs / SMs) rounds.
+    Among the piece counts that keep at least 8 pages per piece, take the one that wastes least of the
+    last round (ties: fewer pieces)."""
+    items = max(1, batch * n_kv_heads)
+    best, best_eff = 1, 0.0
+    for s in range(1, max(1, pages // 8) + 1):
+        if s > 64:
+            break
+        ctas = items * s
+        eff = ctas / (((ctas + sms - 1) // sms) * sms)
+        # a piece that is too short pays its start-up (about two pages' worth) too often
+        per = (pages + s - 1) // s
+        eff *= per / (per + 2.0)
+        if eff > best_eff + 1e-9:
+            best, best_eff = s, eff
+    return best
+
+
 def attn_decode(q, k_pool, v_pool, page_table, len_after, n_heads, n_kv_heads, head_dim, scale, softcap, window,
-                ring_rows, n_splits: int, max_len_after: int) -> torch.Tensor:
+                ring_rows, len_bucket: int) -> torch.Tensor:
+    """Decode attention, kernel and split count chosen here.  ``len_bucket``: an upper bound of the longest
+    context of the batch (the engine passes a power of two so that the choice is stable across steps)."""
+    rows = min(len_bucket, ring_rows) if ring_rows else len_bucket
+    pages = max(1, (rows + PAGE_ROWS - 1) // PAGE_ROWS)
+    splits = choose_decode_splits(q.shape[0], n_kv_heads, pages, sm_count(q.device))
     if attn_decode_takes(q.dtype, n_heads, n_kv_heads, head_dim):
+        g = n_heads // n_kv_heads
+        # one lane group per key is the faster variant for small groups; tensor cores pay off above
+        variant = "lanes" if (g <= 2 or head_dim < 64) else "mma"
         return attn_decode_tma(q, k_pool, v_pool, page_table, len_after, n_heads, n_kv_heads, head_dim, scale,
-                               softcap, window, ring_rows, n_splits)
+                               softcap, window, ring_rows, splits, variant)
     return attn_decode_simt(q, k_pool, v_pool, page_table, len_after, n_heads, n_kv_heads, head_dim, scale,
-                            softcap, window, ring_rows, n_splits)
+                            softcap, window, ring_rows, splits)

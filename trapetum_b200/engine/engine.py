@@ -34,17 +34,14 @@ def _sm_count(device) -> int:
     return _SM_COUNT[idx]
 
 
-def decode_splits(batch: int, n_kv_heads: int, max_len: int, sms: int) -> int:
-    """In how many pieces a decode step cuts each sequence's keys, so that the attention kernel
-    (one CTA per sequence, kv head and piece) fills the GPU when batch * kv heads alone does not.
-    A piece keeps at least four pages (256 keys).  The longest context enters only through a
-    power-of-two bucket, so the choice is stable while a batch grows."""
-    bucket = 256
-    while bucket < max_len:
-        bucket *= 2
-    by_len = max(1, bucket // 256)
-    by_fill = max(1, (sms + batch * n_kv_heads - 1) // (batch * n_kv_heads))
-    return int(min(by_len, by_fill, 64))
+def len_bucket(max_len: int) -> int:
+    """The smallest power of two (at least 256) that is not below ``max_len``.  Launch shapes of a decode
+    step (how attention cuts the keys) depend on the longest context only through this bucket, so they stay
+    the same for many steps and a captured graph stays valid."""
+    b = 256
+    while b < max_len:
+        b *= 2
+    return b
 
 
 class Engine:
@@ -55,7 +52,6 @@ class Engine:
         self.cache = Cache(needs, readers, max_tokens, self.rt.dtype, self.rt.device, max_slots)
         self.vocab_size = model.vocab_size
         self._inputs = StepInputs(self.rt.device)
-        self._heads = max([getattr(b.mixer, "n_kv", 1) for b in model.blocks] or [1])
         # CUDA graphs for decode steps: only if every part says that its launches depend on nothing
         # that lives on the host (a part that reads ctx.slots in Python, for one, does not qualify)
         self.use_graphs = use_graphs and self.rt.device.type == "cuda"
@@ -133,9 +129,7 @@ class Engine:
         ctx = StepContext(is_prefill=is_prefill, n_tokens=T, batch=B, positions=dev["positions"],
                           token_seq=dev["token_seq"], seq_start=dev["seq_start"], len_after=dev["len_after"],
                           slot_ids=dev["slot_ids"], slots=slots, seq_lens=lens, max_seq_len=max(lens),
-                          max_len_after=max_after,
-                          decode_splits=1 if is_prefill else decode_splits(B, self._heads, max_after,
-                                                                           _sm_count(self.rt.device)))
+                          max_len_after=max_after, len_bucket=len_bucket(max_after))
         n_want = arrays["want"].size
         if n_want == 0:
             # nothing is asked for: the layers still run (they fill the cache), the head does not
@@ -154,16 +148,16 @@ class Engine:
     # -- one token per sequence, as a CUDA graph ---------------------------------------
     def _decode_step(self, slots, tokens, want, before, after, borrow):
         """A decode step's launches do not depend on the tokens, the positions or the pages, only on
-        the batch size and on the number of key splits: the inputs live in buffers of a fixed layout,
+        the batch size and on the bucket of the longest context: the inputs live in buffers of a fixed layout,
         the first step of a shape runs eagerly (it also sets up every kernel), the second is captured
         into a CUDA graph, and from then on a step is one copy of the inputs and one graph launch."""
         B = len(slots)
         max_after = max(after)
-        splits = decode_splits(B, self._heads, max_after, _sm_count(self.rt.device))
-        key = (B, splits)
+        bucket = len_bucket(max_after)
+        key = (B, bucket)
         dg = self._decode.get(key)
         if dg is None:
-            dg = self._decode[key] = _DecodeShape(B, splits, self)
+            dg = self._decode[key] = _DecodeShape(B, bucket, self)
         dg.fill(self, slots, [t[0] for t in tokens], before, after)
         for gi, g in enumerate(self.cache.groups):
             g.table = dg.dev[f"table{gi}"]
@@ -191,10 +185,10 @@ class Engine:
 
 
 class _DecodeShape:
-    """The fixed-layout inputs, and later the graph, of decode steps of one batch size and split count."""
+    """The fixed-layout inputs, and later the graph, of decode steps of one batch size and length bucket."""
 
-    def __init__(self, B: int, splits: int, engine: "Engine"):
-        self.B, self.splits = B, splits
+    def __init__(self, B: int, bucket: int, engine: "Engine"):
+        self.B, self.bucket = B, bucket
         self.graph = None
         self.logits = None
         self.hits = 0
@@ -241,4 +235,4 @@ class _DecodeShape:
         return StepContext(is_prefill=False, n_tokens=self.B, batch=self.B, positions=d["positions"],
                            token_seq=d["token_seq"], seq_start=d["seq_start"], len_after=d["len_after"],
                            slot_ids=d["slot_ids"], slots=list(slots), seq_lens=[1] * self.B, max_seq_len=1,
-                           max_len_after=max_after, decode_splits=self.splits)
+                           max_len_after=max_after, len_bucket=self.bucket)

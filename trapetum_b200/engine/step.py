@@ -39,7 +39,7 @@ class StepContext:
     seq_lens: List[int]              # tokens this step brings, per sequence (host)
     max_seq_len: int                 # the longest of them
     max_len_after: int
-    decode_splits: int = 1
+    len_bucket: int = 0              # a power of two >= max_len_after: what launch shapes may depend on
     step_kv: Dict[int, tuple] = field(default_factory=dict)   # prefill: entry -> (k, v) of this step
 
 

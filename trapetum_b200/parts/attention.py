@@ -94,8 +94,7 @@ class Attention(Mixer):
                                  self.scale, self.softcap, self.window or 0, ctx.max_seq_len)
         else:
             o = ops.attn_decode(q, line.k, line.v, line.page_table, ctx.len_after, self.n_heads, self.n_kv,
-                                self.hd, self.scale, self.softcap, self.window or 0, line.ring_rows,
-                                ctx.decode_splits, ctx.max_len_after)
+                                self.hd, self.scale, self.softcap, self.window or 0, line.ring_rows, ctx.len_bucket)
         return linear(o, self.w_o, torch.float32)
 
 
