@@ -88,6 +88,21 @@ def test_add_rmsnorm(ops, adt, odt, rows, width):
     close(h, h0 + af, torch.float32)
 
 
+@pytest.mark.parametrize("rows,width,splits", [(8, 2304, 8), (3, 72, 2), (1, 12000, 5)])
+def test_add_rmsnorm_from_partial_sums(ops, rows, width, splits):
+    part = rnd(splits, rows, width, s=2.0)
+    h0 = rnd(rows, width, seed=5)
+    wa, wb = rnd(width, dt=torch.bfloat16, s=0.2, seed=2), rnd(width, dt=torch.bfloat16, s=0.2, seed=3)
+    a = part[0].clone()
+    for s_ in range(1, splits):
+        a += part[s_]                                                # the kernel adds in split order too
+    h1, h2 = h0.clone(), h0.clone()
+    x1 = ops.add_rmsnorm(h1, a, wa, 1e-6, 1.0, wb, 1e-6, 1.0, torch.bfloat16)
+    x2 = ops.add_rmsnorm(h2, part, wa, 1e-6, 1.0, wb, 1e-6, 1.0, torch.bfloat16)
+    assert torch.equal(h1, h2) and torch.equal(x1, x2)
+    assert torch.equal(ops.sum_partials(part), a)
+
+
 @pytest.mark.parametrize("dt", DT)
 @pytest.mark.parametrize("act", ["gelu_tanh", "silu"])
 def test_gated_act(ops, dt, act):
@@ -338,7 +353,16 @@ def test_rope_kv(ops, dt, hd, rot, ring, theta):
                 table[b, pg] = perm.pop()
         table = table.cuda()
         inv = (1.0 / (torch.tensor(theta) ** (torch.arange(0, rot, 2).float() / rot))).cuda() if rot else None
+        if dt == torch.bfloat16 and T <= 16:
+            # the same values as three partial sums: the kernel adds them, rotates in 32-bit, rounds once
+            part = torch.stack([orig.float() * 0.5, orig.float() * 0.25, orig.float() * 0.25])
+            dst = torch.full_like(qkv, float("nan"))
+            kp2, vp2 = kp.clone(), vp.clone()
+            ops.rope_kv(dst, nh, nkv, hd, rot, inv, pos, tseq, la, kp2, vp2, table, ring, partial=part)
         ops.rope_kv(qkv, nh, nkv, hd, rot, inv, pos, tseq, la, kp, vp, table, ring)
+        if dt == torch.bfloat16 and T <= 16:
+            assert torch.equal(dst, qkv) and torch.equal(torch.nan_to_num(kp2.float()), torch.nan_to_num(kp.float())) \
+                and torch.equal(torch.nan_to_num(vp2.float()), torch.nan_to_num(vp.float()))
         o = orig.float().cpu().view(T, nh + 2 * nkv, hd)
         want = o.clone()
         if rot:

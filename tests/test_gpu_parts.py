@@ -14,6 +14,11 @@ pytestmark = pytest.mark.gpu
 DTYPES = [torch.float32, torch.bfloat16]
 
 
+def _whole(y):
+    """A part may return [splits, tokens, hidden] partial sums; their sum is the result."""
+    return y.sum(0) if y.dim() == 3 else y
+
+
 def _rt(dt):
     from trapetum_b200.parts import Runtime
     return Runtime(dt, torch.device("cuda:0"))
@@ -79,6 +84,7 @@ def test_feed_forward_part(dt):
     x = torch.randn(150, H).bfloat16()
     got = ff.forward(x.to("cuda", dt), None)
     assert got.dtype == torch.float32
+    got = _whole(got)
     want = plain.feed_forward(x.float(), w["L.g"].float(), w["L.u"].float(), w["L.d"].float())
     assert rel_l2(got, want) < (1e-5 if dt == torch.float32 else 1e-2)
 
@@ -117,7 +123,7 @@ def test_attention_part_prefill_then_decode(dt, cfg):
     table(max(lens))
     ctx = _ctx([0, 0], lens)
     x = torch.cat([xs[0][:lens[0]], xs[1][:lens[1]]]).to("cuda", dt)
-    got = att.forward(x, ctx, cache.view(0, 0))
+    got = _whole(att.forward(x, ctx, cache.view(0, 0)))
     t = 1e-5 if dt == torch.float32 else 1.5e-2
     assert rel_l2(got[:lens[0]], want[0][:lens[0]]) < t and rel_l2(got[lens[0]:], want[1][:lens[1]]) < t
     for step in range(extra):
@@ -126,7 +132,7 @@ def test_attention_part_prefill_then_decode(dt, cfg):
         table(max(before) + 1)
         ctx = _ctx(before, [1, 1])
         x = torch.stack([xs[0][before[0]], xs[1][before[1]]]).to("cuda", dt)
-        got = att.forward(x, ctx, cache.view(0, 0))
+        got = _whole(att.forward(x, ctx, cache.view(0, 0)))
         assert rel_l2(got[0], want[0][before[0]]) < t and rel_l2(got[1], want[1][before[1]]) < t
 
 

@@ -18,6 +18,8 @@ __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g));
 
 template <typename TI, typename TO, int ACT>
 __global__ void gated_act_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int inter) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t row = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= inter) return;
@@ -36,8 +38,8 @@ extern "C" int tb_gated_act(const void* gu, int in_dtype, void* out, int out_dty
     if (grid.y > 65535) return tb_refuse("gated_act: intermediate size %d is too wide", inter);
 #define LAUNCH(TI, TO)                                                                         \
     do {                                                                                       \
-        if (act == ACT_GELU_TANH) gated_act_kernel<TI, TO, ACT_GELU_TANH><<<grid, 256, 0, stream>>>((const TI*)gu, (TO*)out, inter); \
-        else gated_act_kernel<TI, TO, ACT_SILU><<<grid, 256, 0, stream>>>((const TI*)gu, (TO*)out, inter);                       \
+        if (act == ACT_GELU_TANH) tb_launch(gated_act_kernel<TI, TO, ACT_GELU_TANH>, dim3(grid), dim3(256), 0, stream, (const TI*)gu, (TO*)out, inter); \
+        else tb_launch(gated_act_kernel<TI, TO, ACT_SILU>, dim3(grid), dim3(256), 0, stream, (const TI*)gu, (TO*)out, inter);                       \
     } while (0)
     if (in_dtype == TB_F32 && out_dtype == TB_F32) LAUNCH(float, float);
     else if (in_dtype == TB_F32 && out_dtype == TB_BF16) LAUNCH(float, bf16);

@@ -64,6 +64,7 @@ __device__ __forceinline__ void bf16x8_to_f32(const uint4& w, float* f) {
 
 template <int HD, int G>
 __global__ void __launch_bounds__(NWARP * 32, 1) attn_decode_kernel(DecodeArgs a) {
+    pdl_launch_dependents();
     using C = DCfg<HD>;
     constexpr int LPK = HD / 8;                    // lanes per key
     constexpr int KP = 32 / LPK;                   // keys per pass of a warp
@@ -109,6 +110,7 @@ __global__ void __launch_bounds__(NWARP * 32, 1) attn_decode_kernel(DecodeArgs a
         bulk_load(dst, (const bf16*)a.k_pool + off, C::PAGE_BYTES, &full[s]);
         bulk_load(dst + C::PAGE_BYTES, (const bf16*)a.v_pool + off, C::PAGE_BYTES, &full[s]);
     };
+    pdl_wait();                                     // the cache rows of this step and q come from earlier kernels
     if (threadIdx.x == 0)
         for (int i = 0; i < n && i < C::STAGES; i++) issue(i);
 
@@ -368,6 +370,7 @@ __device__ __forceinline__ void mma_rows8(float* d, uint32_t a0, uint32_t a2, ui
 template <int HD>
 __global__ void __launch_bounds__(MW * 32, 1)
 attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, DecodeArgs a) {
+    pdl_launch_dependents();
     using C = MCfg<HD>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -410,6 +413,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             tma_load_box(dst + C::TILE_BYTES + bx * C::BOX_BYTES, &map_v, &full[s], bx * 64, row);
         }
     };
+    pdl_wait();                                     // the cache rows of this step and q come from earlier kernels
     if (threadIdx.x == 0)
         for (int i = 0; i < n && i < C::STAGES; i++) issue(i);
 
@@ -603,12 +607,14 @@ static int launch_mma(const DecodeArgs& a, int batch, long long pool_rows, cudaS
     CUtensorMap mk, mv;
     if (pool_map(&mk, a.k_pool, pool_rows, HD) || pool_map(&mv, a.v_pool, pool_rows, HD)) return -1;
     dim3 grid(batch, a.n_kv_heads, a.n_splits);
-    kern<<<grid, MW * 32, C::SMEM, stream>>>(mk, mv, a);
+    tb_launch(kern, dim3(grid), dim3(MW * 32), C::SMEM, stream, mk, mv, a);
     return tb_launch_status();
 }
 
 // out[b,h,:] = sum_s e^(m_s - M) o_s / sum_s e^(m_s - M) l_s, splits in ascending order.
 __global__ void attn_combine_kernel(const float* __restrict__ partial, bf16* __restrict__ out, int n_splits, int hd) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t bh = blockIdx.x;
     const float* p = partial + bh * n_splits * (hd + 2);
     float M = -INFINITY;
@@ -639,7 +645,7 @@ static int launch(const DecodeArgs& a, int batch, cudaStream_t stream) {
         attr_set = true;
     }
     dim3 grid(batch, a.n_kv_heads, a.n_splits);
-    kern<<<grid, NWARP * 32, C::SMEM, stream>>>(a);
+    tb_launch(kern, dim3(grid), dim3(NWARP * 32), C::SMEM, stream, a);
     return tb_launch_status();
 }
 
@@ -707,7 +713,7 @@ static int run_decode(const DecodeArgs* args, int dtype, int batch, bool tensor_
     }
     if (st) return st;
     if (a.n_splits > 1) {
-        attn_combine_kernel<<<(unsigned)batch * a.n_heads, 128, 0, stream>>>(a.partial, (bf16*)a.out, a.n_splits, a.hd);
+        tb_launch(attn_combine_kernel, dim3((unsigned)batch * a.n_heads), dim3(128), 0, stream, a.partial, (bf16*)a.out, a.n_splits, a.hd);
         st = tb_launch_status();
     }
     return st;

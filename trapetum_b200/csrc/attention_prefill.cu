@@ -93,6 +93,8 @@ __device__ __forceinline__ void load_tile(uint8_t* dst, const bf16* src, long lo
 }
 
 __global__ void __launch_bounds__(NWARPS * 32) attn_prefill_mma_kernel(PrefillArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* sQ = smem;                                   // [BM][PITCH]
     uint8_t* sK = sQ + BM * PITCH;                        // [2][BN][PITCH]
@@ -261,6 +263,6 @@ extern "C" int tb_attn_prefill_mma(const void* q, const void* k, const void* v, 
         attr_set = true;
     }
     dim3 grid((max_seq_len + BM - 1) / BM, n_heads, batch);
-    attn_prefill_mma_kernel<<<grid, NWARPS * 32, SMEM, stream>>>(a);
+    tb_launch(attn_prefill_mma_kernel, dim3(grid), dim3(NWARPS * 32), SMEM, stream, a);
     return tb_launch_status();
 }

@@ -82,6 +82,8 @@ __global__ void attn_prefill_simt_kernel(const T* __restrict__ q, const T* __res
                                          const int* __restrict__ seq_start, const int* __restrict__ token_seq,
                                          T* __restrict__ out, int n_tokens, int n_heads, int n_kv_heads, int hd,
                                          float scale, float cap, int window) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
@@ -130,6 +132,8 @@ struct DecodeArgs {
 
 template <typename T, int NC>
 __global__ void attn_decode_simt_kernel(DecodeArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float smem[];
     const int b = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
@@ -199,6 +203,8 @@ __global__ void attn_decode_simt_kernel(DecodeArgs a) {
 template <typename T>
 __global__ void attn_combine_kernel(const float* __restrict__ partial, T* __restrict__ out,
                                     int n_splits, int hd) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t bh = blockIdx.x;
     const float* p = partial + bh * n_splits * (hd + 2);
     float M = -INFINITY;
@@ -254,7 +260,7 @@ extern "C" int tb_attn_prefill_simt(const void* q, const void* k, const void* v,
     const size_t smem = (size_t)warps * hd * sizeof(float);
     const int nc = pick_nc(hd);
     TB_DISPATCH_1(dtype, T, DISPATCH_NC(nc,
-        attn_prefill_simt_kernel<T, NC><<<blocks, warps * 32, smem, stream>>>(
+        tb_launch(attn_prefill_simt_kernel<T, NC>, dim3(blocks), dim3(warps * 32), smem, stream, 
             (const T*)q, (const T*)k, (const T*)v, q_stride, kv_stride, seq_start, token_seq, (T*)out,
             n_tokens, n_heads, n_kv_heads, hd, scale, cap, window)));
     return tb_launch_status();
@@ -281,13 +287,13 @@ extern "C" int tb_attn_decode_simt(const DecodeArgs* args, int dtype, int batch,
     dim3 grid(batch, a.n_heads, a.n_splits);
     const int nc = pick_nc(hd);
     TB_DISPATCH_1(dtype, T, DISPATCH_NC(nc,
-        attn_decode_simt_kernel<T, NC><<<grid, warps * 32, smem, stream>>>(a)));
+        tb_launch(attn_decode_simt_kernel<T, NC>, dim3(grid), dim3(warps * 32), smem, stream, a)));
     int st = tb_launch_status();
     if (st) return st;
     if (a.n_splits > 1) {
         const unsigned rows = (unsigned)batch * a.n_heads;
         TB_DISPATCH_1(dtype, T,
-            attn_combine_kernel<T><<<rows, 128, 0, stream>>>(a.partial, (T*)a.out, a.n_splits, hd));
+            tb_launch(attn_combine_kernel<T>, dim3(rows), dim3(128), 0, stream, a.partial, (T*)a.out, a.n_splits, hd));
         st = tb_launch_status();
     }
     return st;

@@ -29,6 +29,28 @@ static int tb_refuse(const char* fmt, ...) {
 
 static inline int tb_launch_status() { return (int)cudaGetLastError(); }
 
+// Programmatic dependent launch.  Every kernel of this library is launched with the attribute that
+// lets it start while the kernel before it in the stream is still draining, begins with
+// pdl_launch_dependents() (so that its own successor may be scheduled early too) and calls pdl_wait()
+// before it first touches memory that an earlier kernel wrote or still reads.  pdl_wait() returns when
+// the preceding kernel has completed and its writes are visible, so the order of effects is that of
+// ordinary stream order; what overlaps is launch latency, block scheduling and whatever a kernel does
+// before its wait (barrier set-up, tensor-memory allocation, loads of weights).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline void tb_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);       // the status is read with tb_launch_status()
+}
+
 typedef __nv_bfloat16 bf16;
 
 template <typename T> __device__ __forceinline__ float to_f(T v);

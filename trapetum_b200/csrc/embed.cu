@@ -12,6 +12,8 @@ TB_EXPORT_ERROR()
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
                              float* __restrict__ out, int hidden, int vocab, float scale) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * hidden;
@@ -29,13 +31,15 @@ extern "C" int tb_embed(const int* ids, const void* table, int table_dtype, floa
     if (hidden <= 0 || vocab <= 0) return tb_refuse("embed: hidden=%d vocab=%d", hidden, vocab);
     const int threads = hidden >= 1024 ? 256 : 128;
     TB_DISPATCH_1(table_dtype, TW,
-        embed_kernel<TW><<<n_tokens, threads, 0, stream>>>(ids, (const TW*)table, out, hidden, vocab, scale));
+        tb_launch(embed_kernel<TW>, dim3(n_tokens), dim3(threads), 0, stream, ids, (const TW*)table, out, hidden, vocab, scale));
     return tb_launch_status();
 }
 
 // out[i, :] = in[rows[i], :]; an index outside [0, n_rows) yields NaN.
 __global__ void gather_rows_kernel(const float* __restrict__ in, const int* __restrict__ rows,
                                    float* __restrict__ out, int width, int n_rows) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int i = blockIdx.x;
     const int r = rows[i];
     float* o = out + (size_t)i * width;
@@ -50,6 +54,6 @@ __global__ void gather_rows_kernel(const float* __restrict__ in, const int* __re
 extern "C" int tb_gather_rows(const float* in, const int* rows, float* out, int n_out, int width,
                               int n_rows, cudaStream_t stream) {
     if (n_out <= 0) return 0;
-    gather_rows_kernel<<<n_out, 256, 0, stream>>>(in, rows, out, width, n_rows);
+    tb_launch(gather_rows_kernel, dim3(n_out), dim3(256), 0, stream, in, rows, out, width, n_rows);
     return tb_launch_status();
 }

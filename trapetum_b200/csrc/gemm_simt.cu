@@ -21,6 +21,8 @@ template <typename TA, typename TW, typename TC>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restrict__ C,
                  int M, int N, int K, long long lda, long long ldw, long long ldc, float cap) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -79,7 +81,7 @@ extern "C" int tb_gemm_simt(const void* A, int a_dtype, const void* W, int w_dty
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (grid.y > 65535) return tb_refuse("gemm: M=%d is too many rows for one call", M);
     const int key = (a_dtype << 2) | (w_dtype << 1) | c_dtype;
-#define LAUNCH(TA, TW, TC) gemm_simt_kernel<TA, TW, TC><<<grid, 256, 0, stream>>>( \
+#define LAUNCH(TA, TW, TC) tb_launch(gemm_simt_kernel<TA, TW, TC>, dim3(grid), dim3(256), 0, stream,  \
         (const TA*)A, (const TW*)W, (TC*)C, M, N, K, lda, ldw, ldc, softcap)
     switch (key) {
     case 0: LAUNCH(float, float, float); break;

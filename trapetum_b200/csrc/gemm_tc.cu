@@ -125,6 +125,7 @@ template <int BN> struct Cfg {
 template <int BN, bool SWAP, typename TOut>
 __global__ void __launch_bounds__(192, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, GemmParams p) {
+    pdl_launch_dependents();
     using C = Cfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -162,17 +163,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             uint32_t it = 0;
-            bool ok = true;
+            bool ok = true, waited = false;
+            // the tile that holds weights: the 128-lane operand when swapped, else the BN-column one
+            const CUtensorMap* wmap = SWAP ? &map_p : &map_q;
+            const CUtensorMap* amap = SWAP ? &map_q : &map_p;
+            constexpr int W_OFF = SWAP ? 0 : BM * BK * 2, A_OFF = SWAP ? BM * BK * 2 : 0;
             for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
                 int tp, tq, sp; decode(item, tp, tq, sp);
                 const int kb0 = sp * p.kb_per_split, kb1 = min(p.kblocks, kb0 + p.kb_per_split);
-                for (int kb = kb0; kb < kb1; kb++, it++) {
+                const int w_row = SWAP ? tp * BM : tq * BN, a_row = SWAP ? tq * BN : tp * BM;
+                int kb = kb0;
+                if (!waited) {
+                    // Weights do not depend on the kernel before this one: start streaming them into the
+                    // (still empty) stages at once, and only then wait for that kernel, whose output is
+                    // the activation operand.
+                    const int pre = min(kb1 - kb0, C::STAGES);
+                    for (int j = 0; j < pre; j++) {
+                        mbar_expect_tx(&full[j], C::STAGE_BYTES);
+                        tma_load_2d(smem + j * C::STAGE_BYTES + W_OFF, wmap, &full[j], (kb0 + j) * BK, w_row);
+                    }
+                    pdl_wait();
+                    waited = true;
+                    for (int j = 0; j < pre; j++)
+                        tma_load_2d(smem + j * C::STAGE_BYTES + A_OFF, amap, &full[j], (kb0 + j) * BK, a_row);
+                    it = pre; kb = kb0 + pre;
+                }
+                for (; kb < kb1; kb++, it++) {
                     const int s = it % C::STAGES; const uint32_t ph = (it / C::STAGES) & 1;
                     if (*abort_flag || !mbar_wait(&empty[s], ph ^ 1)) { ok = false; break; }
-                    uint8_t* sa = smem + s * C::STAGE_BYTES;
+                    uint8_t* st = smem + s * C::STAGE_BYTES;
                     mbar_expect_tx(&full[s], C::STAGE_BYTES);
-                    tma_load_2d(sa, &map_p, &full[s], kb * BK, tp * BM);
-                    tma_load_2d(sa + BM * BK * 2, &map_q, &full[s], kb * BK, tq * BN);
+                    tma_load_2d(st + W_OFF, wmap, &full[s], kb * BK, w_row);
+                    tma_load_2d(st + A_OFF, amap, &full[s], kb * BK, a_row);
                 }
             }
             if (!ok) {
@@ -217,6 +239,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     } else {
         // ---------------- epilogue: warps 2..5 ----------------
         const int quarter = warp & 3;                  // the TMEM lanes this warp may read
+        pdl_wait();                                    // the output may still be read by the kernel before
         uint32_t tile_it = 0;
         bool ok = true;
         for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, tile_it++) {
@@ -312,6 +335,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
 template <typename TOut>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, TOut* __restrict__ out, int rows, int cols,
                                      long long ld_out, int splits, float cap) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t n = (size_t)rows * cols;
     if (i >= n) return;
@@ -369,7 +394,7 @@ static int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmParams
     }
     const int items = p.tiles_p * p.tiles_q * p.splits;
     const int grid = items < g_sms ? items : g_sms;
-    kern<<<grid, 192, C::SMEM, stream>>>(mp, mq, p);
+    tb_launch(kern, dim3(grid), dim3(192), C::SMEM, stream, mp, mq, p);
     return tb_launch_status();
 }
 
@@ -398,9 +423,19 @@ extern "C" int tb_gemm_tc_splits(int M, int N, int K, int sms) {
     return (kblocks + per - 1) / per;              // every split non-empty
 }
 
+// The split count a call really uses: every split gets the same number of k-blocks and none is empty.
+extern "C" int tb_gemm_tc_effective_splits(int K, int splits) {
+    const int kblocks = (K + BK - 1) / BK;
+    if (splits < 1) splits = 1;
+    if (splits > kblocks) splits = kblocks;
+    const int per = (kblocks + splits - 1) / splits;
+    return (kblocks + per - 1) / per;
+}
+
+// reduce = 0 with splits > 1: leave the partial sums in `scratch` ([splits][M][N]) for the consumer to add.
 extern "C" int tb_gemm_tc(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K,
                           long long lda, long long ldw, long long ldc, float softcap, int splits, float* scratch,
-                          cudaStream_t stream) {
+                          int reduce, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (!tb_gemm_tc_takes(A, W, M, N, K, lda, ldw))
         return tb_refuse("gemm_tc: needs K, lda, ldw multiples of 8 and 16-byte aligned operands "
@@ -451,16 +486,26 @@ extern "C" int tb_gemm_tc(const void* A, const void* W, void* C, int c_dtype, in
     }
 #undef GO
     if (st) return st;
-    if (splits > 1) {
+    if (splits > 1 && reduce) {
         const size_t n = (size_t)M * N;
         const unsigned blocks = (unsigned)((n + 255) / 256);
         if (c_dtype == TB_BF16)
-            splitk_reduce_kernel<bf16><<<blocks, 256, 0, stream>>>(scratch, (bf16*)C, M, N, ldc, splits, softcap);
+            tb_launch(splitk_reduce_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, scratch, (bf16*)C, M, N, ldc, splits, softcap);
         else
-            splitk_reduce_kernel<float><<<blocks, 256, 0, stream>>>(scratch, (float*)C, M, N, ldc, splits, softcap);
+            tb_launch(splitk_reduce_kernel<float>, dim3(blocks), dim3(256), 0, stream, scratch, (float*)C, M, N, ldc, splits, softcap);
         st = tb_launch_status();
     }
     return st;
+}
+
+// out[rows][cols] = sum over splits, in order, of partial[s][rows][cols] (32-bit).
+extern "C" int tb_sum_partials(const float* partial, float* out, int rows, int cols, int splits, cudaStream_t stream) {
+    const size_t n = (size_t)rows * cols;
+    if (n == 0) return 0;
+    if (splits < 1) return tb_refuse("sum_partials: splits=%d", splits);
+    tb_launch(splitk_reduce_kernel<float>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream,
+              partial, out, rows, cols, (long long)cols, splits, 0.f);
+    return tb_launch_status();
 }
 
 // Reads and clears the error word (0 = no wait ran out).  Synchronises the device.

@@ -10,7 +10,8 @@
 // does `h += norm_a(a); x = norm_b(h)` in one pass over the row:
 //
 //   tb_rmsnorm      out = norm(x)
-//   tb_add_rmsnorm  h (32-bit, in place) += norm_a(a);  then, if asked, out = norm_b(h)
+//   tb_add_rmsnorm  h (32-bit, in place) += norm_a(a);  then, if asked, out = norm_b(h);
+//                   a may be given as split-K partial sums, added here in split order
 //
 // Any row width works (loops are strided by the block size).
 #include "common.cuh"
@@ -20,6 +21,8 @@ TB_EXPORT_ERROR()
 template <typename TX, typename TW, typename TO>
 __global__ void rmsnorm_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
                                int width, float eps, float offset) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float red[33];
     const size_t base = (size_t)blockIdx.x * width;
     float ss = 0.f;
@@ -30,30 +33,47 @@ __global__ void rmsnorm_kernel(const TX* __restrict__ x, const TW* __restrict__ 
         out[base + i] = from_f<TO>(to_f<TX>(x[base + i]) * r * (offset + to_f<TW>(w[i])));
 }
 
-// h += norm_a(a); optionally out = norm_b(h).  A thread re-reads only elements
-// of h that it wrote itself, so no fence is needed between the passes.
+// h += norm_a(a); optionally out = norm_b(h).  `a` may come as n_splits partial sums (32-bit, the
+// split-K output of a matrix product, [n_splits][rows][width]); they are added in split order here,
+// which saves the separate reduction pass.  The row of `a` is kept in shared memory between the two
+// passes over it when it fits (row_cache != 0); a thread re-reads only elements that it wrote itself.
 template <typename TA, typename TW, typename TO>
-__global__ void add_rmsnorm_kernel(float* __restrict__ h, const TA* __restrict__ a,
+__global__ void add_rmsnorm_kernel(float* __restrict__ h, const TA* __restrict__ a, int n_splits, long long split_stride,
                                    const TW* __restrict__ wa, float eps_a, float off_a,
                                    const TW* __restrict__ wb, float eps_b, float off_b,
-                                   TO* __restrict__ out, int width) {
+                                   TO* __restrict__ out, int width, int row_cache) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float row[];
     __shared__ float red[33];
     const size_t base = (size_t)blockIdx.x * width;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) { float v = to_f<TA>(a[base + i]); ss += v * v; }
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = to_f<TA>(a[base + i]);
+        for (int s = 1; s < n_splits; s++) v += to_f<TA>(a[(size_t)s * split_stride + base + i]);
+        if (row_cache) row[i] = v;
+        ss += v * v;
+    }
     ss = block_sum(ss, red);
     const float ra = rsqrtf(ss / (float)width + eps_a);
     float s2 = 0.f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        float v = h[base + i] + to_f<TA>(a[base + i]) * ra * (off_a + to_f<TW>(wa[i]));
+        float av;
+        if (row_cache) av = row[i];
+        else {
+            av = to_f<TA>(a[base + i]);
+            for (int s = 1; s < n_splits; s++) av += to_f<TA>(a[(size_t)s * split_stride + base + i]);
+        }
+        const float v = h[base + i] + av * ra * (off_a + to_f<TW>(wa[i]));
         h[base + i] = v;
+        if (row_cache) row[i] = v;
         s2 += v * v;
     }
     if (out == nullptr) return;
     s2 = block_sum(s2, red);
     const float rb = rsqrtf(s2 / (float)width + eps_b);
     for (int i = threadIdx.x; i < width; i += blockDim.x)
-        out[base + i] = from_f<TO>(h[base + i] * rb * (off_b + to_f<TW>(wb[i])));
+        out[base + i] = from_f<TO>((row_cache ? row[i] : h[base + i]) * rb * (off_b + to_f<TW>(wb[i])));
 }
 
 static int norm_threads(int width) {
@@ -87,12 +107,12 @@ extern "C" int tb_rmsnorm(const void* x, int x_dtype, const void* w, int w_dtype
     if (!code_ok(x_dtype) || !code_ok(w_dtype) || !code_ok(out_dtype))
         return tb_refuse("rmsnorm: unknown dtype codes %d %d %d", x_dtype, w_dtype, out_dtype);
     DISPATCH3(x_dtype, w_dtype, out_dtype,
-        rmsnorm_kernel<TX, TW, TO><<<rows, norm_threads(width), 0, stream>>>(
+        tb_launch(rmsnorm_kernel<TX, TW, TO>, dim3(rows), dim3(norm_threads(width)), 0, stream, 
             (const TX*)x, (const TW*)w, (TO*)out, width, eps, offset));
     return tb_launch_status();
 }
 
-extern "C" int tb_add_rmsnorm(float* h, const void* a, int a_dtype,
+extern "C" int tb_add_rmsnorm(float* h, const void* a, int a_dtype, int n_splits, long long split_stride,
                               const void* wa, float eps_a, float off_a,
                               const void* wb, float eps_b, float off_b, int w_dtype,
                               void* out, int out_dtype, int rows, int width, cudaStream_t stream) {
@@ -101,9 +121,13 @@ extern "C" int tb_add_rmsnorm(float* h, const void* a, int a_dtype,
     if (!code_ok(a_dtype) || !code_ok(w_dtype) || !code_ok(out_dtype))
         return tb_refuse("add_rmsnorm: unknown dtype codes %d %d %d", a_dtype, w_dtype, out_dtype);
     if (out != nullptr && wb == nullptr) return tb_refuse("add_rmsnorm: an output needs the second norm's weight");
+    if (n_splits < 1) return tb_refuse("add_rmsnorm: n_splits=%d", n_splits);
+    const int row_cache = (size_t)width * sizeof(float) <= 40 * 1024;
+    const size_t smem = row_cache ? (size_t)width * sizeof(float) : 0;
     DISPATCH3(a_dtype, w_dtype, out_dtype,
-        add_rmsnorm_kernel<TX, TW, TO><<<rows, norm_threads(width), 0, stream>>>(
-            h, (const TX*)a, (const TW*)wa, eps_a, off_a, (const TW*)wb, eps_b, off_b, (TO*)out, width));
+        tb_launch(add_rmsnorm_kernel<TX, TW, TO>, dim3(rows), dim3(norm_threads(width)), smem, stream,
+            h, (const TX*)a, n_splits, split_stride, (const TW*)wa, eps_a, off_a, (const TW*)wb, eps_b, off_b,
+            (TO*)out, width, row_cache));
     return tb_launch_status();
 }
 
@@ -111,6 +135,8 @@ extern "C" int tb_add_rmsnorm(float* h, const void* a, int a_dtype,
 // that have no norm on the branch output.
 template <typename TA>
 __global__ void add_kernel(float* __restrict__ h, const TA* __restrict__ a, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) h[i] += to_f<TA>(a[i]);
 }
@@ -118,6 +144,6 @@ __global__ void add_kernel(float* __restrict__ h, const TA* __restrict__ a, size
 extern "C" int tb_residual_add(float* h, const void* a, int a_dtype, long long n, cudaStream_t stream) {
     if (n <= 0) return 0;
     const unsigned blocks = (unsigned)((n + 255) / 256);
-    TB_DISPATCH_1(a_dtype, TA, add_kernel<TA><<<blocks, 256, 0, stream>>>(h, (const TA*)a, (size_t)n));
+    TB_DISPATCH_1(a_dtype, TA, tb_launch(add_kernel<TA>, dim3(blocks), dim3(256), 0, stream, h, (const TA*)a, (size_t)n));
     return tb_launch_status();
 }

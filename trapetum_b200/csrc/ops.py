@@ -123,11 +123,19 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, offset: float, out_dty
 def add_rmsnorm(h: torch.Tensor, a: torch.Tensor, wa: torch.Tensor, eps_a: float, off_a: float,
                 wb: Optional[torch.Tensor] = None, eps_b: float = 0.0, off_b: float = 0.0,
                 out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
-    """h += norm_a(a) in place (h float32); with wb also returns norm_b(h)."""
+    """h += norm_a(a) in place (h float32); with wb also returns norm_b(h).  ``a`` is [rows, width], or
+    [splits, rows, width] partial sums (float32) that are added in split order on the way."""
     _cuda(h, a, wa, wb)
     if h.dtype != torch.float32 or h.dim() != 2 or not h.is_contiguous():
         raise KernelError("add_rmsnorm: the residual stream must be contiguous float32 [rows, width]")
-    if a.shape != h.shape or not a.is_contiguous():
+    n_splits, split_stride = 1, 0
+    if a.dim() == 3:
+        if a.dtype != torch.float32:
+            raise KernelError("add_rmsnorm: partial sums must be float32")
+        n_splits, split_stride = a.shape[0], a.stride(0)
+        if tuple(a.shape[1:]) != tuple(h.shape) or a.stride(1) != h.shape[1] or a.stride(2) != 1:
+            raise KernelError(f"add_rmsnorm: partial sums {tuple(a.shape)} do not fit the stream {tuple(h.shape)}")
+    elif a.shape != h.shape or not a.is_contiguous():
         raise KernelError(f"add_rmsnorm: branch {tuple(a.shape)} does not fit the stream {tuple(h.shape)}")
     if wa.numel() != h.shape[1] or (wb is not None and (wb.numel() != h.shape[1] or wb.dtype != wa.dtype)):
         raise KernelError("add_rmsnorm: norm weights do not fit (both must have the row width and one dtype)")
@@ -135,7 +143,8 @@ def add_rmsnorm(h: torch.Tensor, a: torch.Tensor, wa: torch.Tensor, eps_a: float
     if wb is not None:
         out = torch.empty(h.shape, dtype=out_dtype, device=h.device)
     lib = build.load("norm")
-    _check(lib, lib.tb_add_rmsnorm(_ptr(h), _ptr(a), c_int(code(a.dtype)), _ptr(wa), c_float(eps_a), c_float(off_a),
+    _check(lib, lib.tb_add_rmsnorm(_ptr(h), _ptr(a), c_int(code(a.dtype)), c_int(n_splits), c_longlong(split_stride),
+                                   _ptr(wa), c_float(eps_a), c_float(off_a),
                                    _ptr(wb), c_float(eps_b), c_float(off_b), c_int(code(wa.dtype)),
                                    _ptr(out), c_int(code(out_dtype) if out is not None else 0),
                                    c_int(h.shape[0]), c_int(h.shape[1]), _stream()), "add_rmsnorm")
@@ -143,7 +152,10 @@ def add_rmsnorm(h: torch.Tensor, a: torch.Tensor, wa: torch.Tensor, eps_a: float
 
 
 def residual_add(h: torch.Tensor, a: torch.Tensor) -> None:
+    """h += a (a may be [splits, rows, width] partial sums: they are added one after the other)."""
     _cuda(h, a)
+    if a.dim() == 3:
+        a = sum_partials(a.contiguous())
     if h.dtype != torch.float32 or not h.is_contiguous() or not a.is_contiguous() or a.shape != h.shape:
         raise KernelError("residual_add: h must be contiguous float32 and a of the same shape")
     lib = build.load("norm")
@@ -201,16 +213,23 @@ class _RopeKvArgs(ctypes.Structure):
                 ("n_heads", c_int), ("n_kv_heads", c_int), ("head_dim", c_int), ("rotary_dim", c_int),
                 ("inv_freq", c_void_p), ("positions", c_void_p), ("token_seq", c_void_p), ("len_after", c_void_p),
                 ("k_pool", c_void_p), ("v_pool", c_void_p), ("page_table", c_void_p), ("pt_stride", c_int),
-                ("page_rows", c_int), ("ring_rows", c_int)]
+                ("page_rows", c_int), ("ring_rows", c_int),
+                ("partial", c_void_p), ("n_splits", c_int), ("split_stride", c_longlong),
+                ("partial_row_stride", c_longlong)]
 
 
 def rope_kv(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int,
             inv_freq: Optional[torch.Tensor], positions: torch.Tensor, token_seq: torch.Tensor,
             len_after: torch.Tensor, k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
-            page_table: Optional[torch.Tensor], ring_rows: int) -> None:
+            page_table: Optional[torch.Tensor], ring_rows: int, partial: Optional[torch.Tensor] = None) -> None:
     """Rotate q and k of ``qkv`` [T, (n_heads + 2 n_kv_heads) * head_dim] in place and store k, v
-    in the cache line (``k_pool``/``v_pool`` [pages, n_kv_heads, PAGE_ROWS, head_dim])."""
-    _cuda(qkv, inv_freq, positions, token_seq, len_after, k_pool, v_pool, page_table)
+    in the cache line (``k_pool``/``v_pool`` [pages, n_kv_heads, PAGE_ROWS, head_dim]).  With ``partial``
+    ([splits, T, width] float32 partial sums of the q/k/v product) the values are taken from their sum
+    and ``qkv`` is only written."""
+    _cuda(qkv, inv_freq, positions, token_seq, len_after, k_pool, v_pool, page_table, partial)
+    if partial is not None and (partial.dtype != torch.float32 or partial.dim() != 3 or partial.shape[1:] != qkv.shape
+                                or partial.stride(2) != 1):
+        raise KernelError("rope_kv: partial sums must be float32 [splits, tokens, width] matching qkv")
     _rows_contig(qkv, "rope_kv: qkv")
     T = qkv.shape[0]
     if qkv.shape[1] != (n_heads + 2 * n_kv_heads) * head_dim:
@@ -238,6 +257,10 @@ def rope_kv(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, rot
     a.page_table = page_table.data_ptr() if page_table is not None else None
     a.pt_stride = page_table.stride(0) if page_table is not None else 0
     a.page_rows = PAGE_ROWS; a.ring_rows = ring_rows
+    a.partial = partial.data_ptr() if partial is not None else None
+    a.n_splits = partial.shape[0] if partial is not None else 0
+    a.split_stride = partial.stride(0) if partial is not None else 0
+    a.partial_row_stride = partial.stride(1) if partial is not None else 0
     lib = build.load("rope_kv")
     _check(lib, lib.tb_rope_kv(ctypes.byref(a), c_int(code(qkv.dtype)), c_int(T), _stream()), "rope_kv")
 
@@ -380,28 +403,59 @@ def gemm_tc_takes(a: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, softcap: float = 0.0,
-            splits: Optional[int] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+            splits: Optional[int] = None, out: Optional[torch.Tensor] = None, partials: bool = False) -> torch.Tensor:
     """a[M,K] @ w[N,K]^T in bfloat16 on tcgen05 tensor cores with 32-bit accumulation.
-    ``splits`` None: the library picks the K split (more than 1 only for few tokens and few weight rows)."""
+    ``splits`` None: the library picks the K split (more than 1 only for few tokens and few weight rows).
+    ``partials=True`` returns float32 [splits, M, N] whose sum over the first axis, taken in order, is the
+    product: a consumer that reads the product once anyway adds them on the way and saves a pass."""
     _cuda(a, w, out)
     if not gemm_tc_takes(a, w):
         raise KernelError(f"gemm_tc does not take a {tuple(a.shape)}/{a.stride()} {a.dtype}, "
                           f"w {tuple(w.shape)}/{w.stride()} {w.dtype}")
     M, K = a.shape
     N = w.shape[0]
+    lib = build.load("gemm_tc")
+    if splits is None:
+        splits = lib.tb_gemm_tc_splits(c_int(M), c_int(N), c_int(K), c_int(sm_count(a.device)))
+    splits = int(lib.tb_gemm_tc_effective_splits(c_int(K), c_int(splits)))
+    if partials:
+        if softcap:
+            raise KernelError("gemm_tc: a soft cap cannot be applied to partial sums")
+        part = torch.empty((splits, M, N), dtype=torch.float32, device=a.device)
+        if splits == 1:
+            _check(lib, lib.tb_gemm_tc(_ptr(a), _ptr(w), _ptr(part), c_int(0), c_int(M), c_int(N), c_int(K),
+                                       c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(N),
+                                       c_float(0.0), c_int(1), _ptr(None), c_int(1), _stream()), "gemm_tc")
+        else:
+            _check(lib, lib.tb_gemm_tc(_ptr(a), _ptr(w), _ptr(None), c_int(0), c_int(M), c_int(N), c_int(K),
+                                       c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(N),
+                                       c_float(0.0), c_int(splits), _ptr(part), c_int(0), _stream()), "gemm_tc")
+        return part
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
     else:
         _rows_contig(out, "gemm: out")
-    lib = build.load("gemm_tc")
-    if splits is None:
-        splits = lib.tb_gemm_tc_splits(c_int(M), c_int(N), c_int(K), c_int(sm_count(a.device)))
     scratch = None
     if splits > 1:
         scratch = torch.empty(splits * M * N, dtype=torch.float32, device=a.device)
     _check(lib, lib.tb_gemm_tc(_ptr(a), _ptr(w), _ptr(out), c_int(code(out.dtype)), c_int(M), c_int(N), c_int(K),
                                c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
-                               c_float(softcap or 0.0), c_int(splits), _ptr(scratch), _stream()), "gemm_tc")
+                               c_float(softcap or 0.0), c_int(splits), _ptr(scratch), c_int(1), _stream()), "gemm_tc",
+           2 if splits > 1 else 1)
+    return out
+
+
+def sum_partials(part: torch.Tensor) -> torch.Tensor:
+    """[splits, rows, cols] float32 partial sums -> their sum, added in split order."""
+    _cuda(part)
+    if part.dtype != torch.float32 or part.dim() != 3 or not part.is_contiguous():
+        raise KernelError("sum_partials: wants contiguous float32 [splits, rows, cols]")
+    S, R, Cc = part.shape
+    if S == 1:
+        return part[0]
+    out = torch.empty((R, Cc), dtype=torch.float32, device=part.device)
+    lib = build.load("gemm_tc")
+    _check(lib, lib.tb_sum_partials(_ptr(part), _ptr(out), c_int(R), c_int(Cc), c_int(S), _stream()), "sum_partials")
     return out
 
 

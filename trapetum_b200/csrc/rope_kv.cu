@@ -13,6 +13,9 @@
 //   page = page_table[seq, row / page_rows]
 //   K[page, kv_head, row % page_rows, :] = k_rot      (V likewise, unrotated)
 //
+// The input may also be the split-K partial sums of the q/k/v product (32-bit): they are added in
+// split order, rotated in 32-bit and rounded once.
+//
 // In a ring (a layer that only ever reads the last `window` keys) a prompt longer
 // than the ring maps several tokens to one row; only tokens with
 // pos >= len_after - ring_rows are written, so the newest one wins without a race.
@@ -31,10 +34,14 @@ struct RopeKvArgs {
     void* k_pool; void* v_pool;               // this cache line: [n_pages][n_kv][page_rows][head_dim]; null: no write
     const int* page_table; int pt_stride;     // [B, pt_stride]
     int page_rows; int ring_rows;
+    const float* partial; int n_splits; long long split_stride, partial_row_stride;   // if set: the row's values are the sum over
+                                                                  // splits of partial[s][t][col]; qkv is written
 };
 
 template <typename T>
 __global__ void rope_kv_kernel(RopeKvArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int hs = blockIdx.y;                      // head slot: q heads, then k heads, then v heads
     const int hd = a.head_dim, half = a.rotary_dim >> 1;
@@ -43,8 +50,17 @@ __global__ void rope_kv_kernel(RopeKvArgs a) {
     const bool is_q = hs < a.n_heads;
     const bool is_k = !is_q && hs < a.n_heads + a.n_kv_heads;
     const int kvh = is_q ? 0 : (is_k ? hs - a.n_heads : hs - a.n_heads - a.n_kv_heads);
-    T* x = is_q ? row + a.q_off + (size_t)hs * hd
-                : (is_k ? row + a.k_off + (size_t)kvh * hd : row + a.v_off + (size_t)kvh * hd);
+    const int col0 = is_q ? a.q_off + hs * hd : (is_k ? a.k_off + kvh * hd : a.v_off + kvh * hd);
+    T* x = row + col0;
+    // value of element i of this head: from the matrix itself, or summed from split-K partials (in split order)
+    auto val = [&](int i) -> float {
+        if (a.partial == nullptr) return to_f<T>(x[i]);
+        const float* p = a.partial + (size_t)t * a.partial_row_stride + col0 + i;
+        float v = p[0];
+        for (int s = 1; s < a.n_splits; s++) v += p[(size_t)s * a.split_stride];
+        return v;
+    };
+    const bool from_partial = a.partial != nullptr;
 
     T* dst = nullptr;
     if (!is_q && a.k_pool != nullptr) {
@@ -63,7 +79,11 @@ __global__ void rope_kv_kernel(RopeKvArgs a) {
     }
 
     if (!is_q && !is_k) {                            // v: copy only
-        if (dst) for (int i = threadIdx.x; i < hd; i += blockDim.x) dst[i] = x[i];
+        for (int i = threadIdx.x; i < hd; i += blockDim.x) {
+            const T y = from_partial ? from_f<T>(val(i)) : x[i];
+            if (from_partial) x[i] = y;
+            if (dst) dst[i] = y;
+        }
         return;
     }
     const bool rotate = a.inv_freq != nullptr;
@@ -73,12 +93,14 @@ __global__ void rope_kv_kernel(RopeKvArgs a) {
             const float ang = (float)pos * a.inv_freq[i];
             float s, c;
             sincosf(ang, &s, &c);
-            const float x0 = to_f<T>(x[i]), x1 = to_f<T>(x[i + half]);
+            const float x0 = val(i), x1 = val(i + half);
             const T y0 = from_f<T>(x0 * c - x1 * s), y1 = from_f<T>(x1 * c + x0 * s);
             x[i] = y0; x[i + half] = y1;
             if (dst) { dst[i] = y0; dst[i + half] = y1; }
         } else if (!rotate || i >= 2 * half) {
-            if (dst) dst[i] = x[i];
+            const T y = from_partial ? from_f<T>(val(i)) : x[i];
+            if (from_partial) x[i] = y;
+            if (dst) dst[i] = y;
         }
     }
 }
@@ -97,6 +119,6 @@ extern "C" int tb_rope_kv(const RopeKvArgs* args, int dtype, int n_tokens, cudaS
     int threads = 32;
     while (threads < 256 && threads < a.head_dim / 2) threads <<= 1;
     dim3 grid(n_tokens, slots);
-    TB_DISPATCH_1(dtype, T, rope_kv_kernel<T><<<grid, threads, 0, stream>>>(a));
+    TB_DISPATCH_1(dtype, T, tb_launch(rope_kv_kernel<T>, dim3(grid), dim3(threads), 0, stream, a));
     return tb_launch_status();
 }

@@ -57,6 +57,8 @@ __device__ __forceinline__ ValIdx block_best(ValIdx x, ValIdx* red /* 32 */) {
 
 __global__ void argmax_stage1_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
                                      float* __restrict__ pval, int* __restrict__ pidx, int n_chunks) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ ValIdx red[32];
     const int row = blockIdx.y, chunk = blockIdx.x;
     const float* x = logits + (size_t)row * row_stride;
@@ -69,6 +71,8 @@ __global__ void argmax_stage1_kernel(const float* __restrict__ logits, long long
 
 __global__ void argmax_stage2_kernel(const float* __restrict__ pval, const int* __restrict__ pidx,
                                      int n_chunks, int* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ ValIdx red[32];
     const int row = blockIdx.x;
     ValIdx b; b.v = -INFINITY; b.i = 0x7fffffff;
@@ -94,8 +98,8 @@ extern "C" int tb_argmax(const float* logits, long long row_stride, int rows, in
     float* pval = (float*)scratch;
     int* pidx = (int*)(pval + (size_t)rows * n_chunks);
     dim3 grid(n_chunks, rows);
-    argmax_stage1_kernel<<<grid, 256, 0, stream>>>(logits, row_stride, vocab, pval, pidx, n_chunks);
-    argmax_stage2_kernel<<<rows, 128, 0, stream>>>(pval, pidx, n_chunks, out);
+    tb_launch(argmax_stage1_kernel, dim3(grid), dim3(256), 0, stream, logits, row_stride, vocab, pval, pidx, n_chunks);
+    tb_launch(argmax_stage2_kernel, dim3(rows), dim3(128), 0, stream, pval, pidx, n_chunks, out);
     return tb_launch_status();
 }
 
@@ -123,6 +127,8 @@ struct SampleArgs {
 };
 
 __global__ void __launch_bounds__(1024) sample_kernel(SampleArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float red[33];
     __shared__ ValIdx redvi[32];
     __shared__ float scan[1024];
@@ -220,6 +226,6 @@ extern "C" int tb_sample(const SampleArgs* args, int rows, cudaStream_t stream) 
     SampleArgs a = *args;
     if (a.vocab <= 0) return tb_refuse("sample: vocab=%d", a.vocab);
     if (a.draw == nullptr) return tb_refuse("sample: the draws are missing");
-    sample_kernel<<<rows, 1024, 0, stream>>>(a);
+    tb_launch(sample_kernel, dim3(rows), dim3(1024), 0, stream, a);
     return tb_launch_status();
 }

@@ -27,7 +27,7 @@ from ..csrc import ops
 from ..weights.loader import TensorSpec
 from .base import KVNeed, Mixer, build_part, register_part
 from .linear import kernel_files as linear_kernels
-from .linear import linear
+from .linear import linear, linear_partials
 
 
 class Attention(Mixer):
@@ -77,8 +77,14 @@ class Attention(Mixer):
     def forward(self, x, ctx, line):
         dt = self.rt.dtype
         if line.owner:
-            qkv = linear(x, self.w_qkv, dt)
-            self.position.rotate_and_store(qkv, self.n_heads, self.n_kv, ctx, line, store=True)
+            if dt == torch.bfloat16 and x.shape[0] <= 128 and ops.gemm_tc_takes(x, self.w_qkv):
+                # few tokens: the product comes as split-K partial sums, which the rotation kernel adds up
+                part = ops.gemm_tc(x, self.w_qkv, torch.float32, partials=True)
+                qkv = torch.empty(part.shape[1:], dtype=dt, device=x.device)
+                self.position.rotate_and_store(qkv, self.n_heads, self.n_kv, ctx, line, store=True, partial=part)
+            else:
+                qkv = linear(x, self.w_qkv, dt)
+                self.position.rotate_and_store(qkv, self.n_heads, self.n_kv, ctx, line, store=True)
             q = qkv[:, :self.qd]
             k = qkv[:, self.qd:self.qd + self.kvd]
             v = qkv[:, self.qd + self.kvd:]
@@ -95,7 +101,7 @@ class Attention(Mixer):
         else:
             o = ops.attn_decode(q, line.k, line.v, line.page_table, ctx.len_after, self.n_heads, self.n_kv,
                                 self.hd, self.scale, self.softcap, self.window or 0, line.ring_rows, ctx.len_bucket)
-        return linear(o, self.w_o, torch.float32)
+        return linear_partials(o, self.w_o)
 
 
 register_part("mixer", "attention", Attention)

@@ -95,7 +95,9 @@ class Norm(Part):
         """``h += self(a)`` in place; if ``then`` is given, also return ``then(h)``.
         The default composes the two; a norm may fuse them."""
         from ..csrc import ops
-        ops.residual_add(h, self.apply(a, torch.float32))
+        if a.dim() == 3:                              # split-K partial sums: add them up first
+            a = ops.sum_partials(a.contiguous())
+        ops.residual_add(h, self.apply(a.contiguous(), torch.float32))
         return then.apply(h, out_dtype) if then is not None else None
 
 
@@ -112,7 +114,8 @@ class Mixer(Part):
         """``x`` [tokens, hidden] in the compute dtype; ``ctx`` the step's
         :class:`~trapetum_b200.engine.step.StepContext`; ``cache`` this call's view
         of the cache (:class:`~trapetum_b200.cache.kv.KVLineView`, a state tensor
-        view, or None).  Returns [tokens, hidden]."""
+        view, or None).  Returns [tokens, hidden], or [splits, tokens, hidden] float32 partial
+        sums whose sum over the first axis is the result (the residual stream adds them)."""
         raise NotImplementedError
 
 

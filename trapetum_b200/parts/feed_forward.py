@@ -15,7 +15,7 @@ from ..csrc import ops
 from ..weights.loader import TensorSpec
 from .base import FeedForward, register_part
 from .linear import kernel_files as linear_kernels
-from .linear import linear
+from .linear import linear, linear_partials
 
 
 class GatedMLP(FeedForward):
@@ -49,7 +49,7 @@ class GatedMLP(FeedForward):
     def forward(self, x, ctx):
         gu = linear(x, self.w_gu, self.rt.dtype)
         act = ops.gated_act(gu, self.activation, self.rt.dtype)
-        return linear(act, self.w_down, torch.float32)
+        return linear_partials(act, self.w_down)
 
 
 register_part("feed_forward", "gated_mlp", GatedMLP)

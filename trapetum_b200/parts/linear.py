@@ -21,6 +21,14 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, softcap: Op
     return ops.gemm_simt(x, w, out_dtype, cap)
 
 
+def linear_partials(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """The product as 32-bit partial sums [splits, T, N] (splits may be 1): for outputs that go straight into
+    a kernel that reads them once (the residual sum with its norm), which then adds the splits itself."""
+    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and ops.gemm_tc_takes(x, w):
+        return ops.gemm_tc(x, w, torch.float32, partials=True)
+    return ops.gemm_simt(x, w, torch.float32)[None]
+
+
 def kernel_files(dtype: torch.dtype):
     from ..csrc import build
     if dtype == torch.bfloat16 and "gemm_tc" in build.SOURCES:

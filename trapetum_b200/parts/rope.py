@@ -36,13 +36,14 @@ class Rope(PositionEncoding):
     def kernel_files(self):
         return ("rope_kv",)
 
-    def rotate_and_store(self, qkv, n_heads, n_kv_heads, ctx, line, store: bool) -> None:
+    def rotate_and_store(self, qkv, n_heads, n_kv_heads, ctx, line, store: bool, partial=None) -> None:
         """Rotate q and k inside ``qkv`` at the step's positions; with ``store`` also
-        write k and v into the cache line."""
+        write k and v into the cache line.  ``partial``: split-K partial sums of the projection
+        ([splits, tokens, width] float32) to take the values from; ``qkv`` is then only written."""
         ops.rope_kv(qkv, n_heads, n_kv_heads, self.head_dim, self.rotary_dim, self.inv_freq,
                     ctx.positions, ctx.token_seq, ctx.len_after,
                     line.k if store else None, line.v if store else None,
-                    line.page_table if store else None, line.ring_rows if store else 0)
+                    line.page_table if store else None, line.ring_rows if store else 0, partial)
 
 
 class NoPosition(PositionEncoding):
@@ -55,10 +56,11 @@ class NoPosition(PositionEncoding):
     def kernel_files(self):
         return ("rope_kv",)
 
-    def rotate_and_store(self, qkv, n_heads, n_kv_heads, ctx, line, store: bool) -> None:
-        if store:
+    def rotate_and_store(self, qkv, n_heads, n_kv_heads, ctx, line, store: bool, partial=None) -> None:
+        if store or partial is not None:
             ops.rope_kv(qkv, n_heads, n_kv_heads, self.head_dim, 0, None, ctx.positions, ctx.token_seq,
-                        ctx.len_after, line.k, line.v, line.page_table, line.ring_rows)
+                        ctx.len_after, line.k if store else None, line.v if store else None,
+                        line.page_table if store else None, line.ring_rows if store else 0, partial)
 
 
 register_part("position", "rope", Rope)
