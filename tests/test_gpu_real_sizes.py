@@ -1,0 +1,65 @@
+"""The kernels at the layer sizes of Gemma-2-2B (head_dim 256, 8 heads over 4 kv heads, hidden 2304,
+intermediate 9216, vocabulary 256000), two layers, random weights: the engine in bfloat16 and in true
+32-bit against the plain implementation.  The tiny models never reach the tensor-core tile sizes, the
+split-K paths or the 256-wide heads that the real sizes use."""
+import pytest
+import torch
+
+import plain_gemma2 as plain
+from conftest import TOL, bf16_budget, make_prompts, rel_l2, sharpen
+
+pytestmark = pytest.mark.gpu
+
+CFG = {
+    "architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2", "num_hidden_layers": 2, "hidden_size": 2304,
+    "num_attention_heads": 8, "num_key_value_heads": 4, "head_dim": 256, "intermediate_size": 9216,
+    "vocab_size": 256000, "rope_theta": 10000.0, "sliding_window": 96, "query_pre_attn_scalar": 256,
+    "attn_logit_softcapping": 50.0, "final_logit_softcapping": 30.0, "rms_norm_eps": 1e-6,
+    "hidden_activation": "gelu_pytorch_tanh", "tie_word_embeddings": True, "max_position_embeddings": 8192,
+}
+
+
+@pytest.fixture(scope="module")
+def folder(tmp_path_factory):
+    import trapetum_b200 as tb
+    d = str(tmp_path_factory.mktemp("real_sizes"))
+    tb.write_random_model(d, CFG, seed=2, std=0.02, norm_std=0.1)
+    sharpen(d, 2.0)
+    return d
+
+
+@pytest.fixture(scope="module")
+def truth(folder):
+    cfg, w = plain.load_folder(folder)
+    prompts = make_prompts(CFG["vocab_size"], [150, 37, 220], seed=4)
+    return cfg, w, prompts, [plain.forward(cfg, w, p) for p in prompts]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_logits_at_real_layer_sizes(folder, truth, dtype):
+    import trapetum_b200 as tb
+    from trapetum_b200.csrc import ops
+    cfg, w, prompts, want = truth
+    tol = TOL["float32"] if dtype == "float32" else bf16_budget(cfg, w, prompts[:1])
+    model = tb.load_model(folder, dtype)
+    eng = tb.Engine(model, max_tokens=64 * 12)
+    for g in eng.cache.groups:
+        g.k.fill_(float("nan")); g.v.fill_(float("nan"))
+    # a first step of three unequal prompts (their last 20 tokens held back), then one token each
+    cut = [len(p) - 20 for p in prompts]
+    s = eng.start(3)
+    got = [[] for _ in prompts]
+    first = eng.step(s, [p[:c] for p, c in zip(prompts, cut)], [[0, c // 2, c - 1] for c in cut])
+    for r, c in enumerate(cut):
+        for k, i in enumerate([0, c // 2, c - 1]):
+            e = rel_l2(first[3 * r + k], want[r][i])
+            assert e <= tol, f"{dtype}: prompt {r} position {i}: {e:.3e} > {tol:.1e}"
+    for t in range(20):
+        out = eng.step(s, [[p[c + t]] for p, c in zip(prompts, cut)])
+        assert torch.isfinite(out).all()
+        for r, c in enumerate(cut):
+            e = rel_l2(out[r], want[r][c + t])
+            assert e <= tol, f"{dtype}: request {r} decoded token {t}: {e:.3e} > {tol:.1e}"
+    eng.release(s)
+    torch.cuda.synchronize()
+    assert ops.gemm_tc_error() == 0 and ops.attn_decode_error() == 0

@@ -113,9 +113,13 @@ struct GemmParams {
     float cap;
 };
 
-template <int BN> struct Cfg {
+// Shared-memory budget: the token-major orientation (prefill) takes what an SM has; the swapped one
+// (decode) takes under half, so that the CTAs of the next product can already sit on the SM and stream
+// their weights while this one drains (see pdl_wait in the producer).
+template <int BN, bool SWAP> struct Cfg {
     static constexpr int STAGE_BYTES = BM * BK * 2 + BN * BK * 2;
-    static constexpr int STAGES_RAW = (200 * 1024) / STAGE_BYTES;
+    static constexpr int BUDGET = SWAP && BN <= 64 ? 104 * 1024 : 200 * 1024;
+    static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 10 ? 10 : STAGES_RAW;
     static constexpr int ACC_COLS = BN < 32 ? 32 : BN;               // columns of one accumulator stage
     static constexpr int TMEM_COLS = 2 * ACC_COLS;                   // a power of two >= 32
@@ -126,7 +130,7 @@ template <int BN, bool SWAP, typename TOut>
 __global__ void __launch_bounds__(192, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, GemmParams p) {
     pdl_launch_dependents();
-    using C = Cfg<BN>;
+    using C = Cfg<BN, SWAP>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(smem + C::STAGES * C::STAGE_BYTES);
@@ -384,7 +388,7 @@ static int g_sms = 0;
 
 template <int BN, bool SWAP, typename TOut>
 static int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmParams& p, cudaStream_t stream) {
-    using C = Cfg<BN>;
+    using C = Cfg<BN, SWAP>;
     static bool attr_set = false;
     auto kern = gemm_tc_kernel<BN, SWAP, TOut>;
     if (!attr_set) {
