@@ -161,6 +161,21 @@ def test_gemm_tc_split_k(ops, M, N, K, splits):
     assert ops.gemm_tc_error() == 0
 
 
+@pytest.mark.parametrize("act", ["gelu_tanh", "silu"])
+@pytest.mark.parametrize("M,I,K", [(1, 160, 96), (8, 9216, 2304), (40, 128, 64), (64, 1024, 512), (128, 176, 72),
+                                   (129, 160, 96), (700, 1296, 520), (2048, 2048, 256)])
+def test_gemm_tc_gated_epilogue(ops, act, M, I, K):
+    """act(x Wg^T) * (x Wu^T) in the product's epilogue, swapped tiles (few tokens) and token-major ones."""
+    x = rnd(M, K, dt=torch.bfloat16, s=1.0)
+    wg, wu = rnd(I, K, dt=torch.bfloat16, s=0.1, seed=1), rnd(I, K, dt=torch.bfloat16, s=0.1, seed=2)
+    g, u = x.double() @ wg.double().T, x.double() @ wu.double().T
+    want = (plain.gelu_tanh(g) if act == "gelu_tanh" else g * torch.sigmoid(g)) * u
+    got = ops.gemm_tc(x, ops.interleave_gate_up(wg, wu), torch.bfloat16, gated_act=act)
+    assert got.shape == (M, I) and got.dtype == torch.bfloat16
+    assert float((got.double() - want).norm() / want.norm()) < 4e-3
+    assert ops.gemm_tc_error() == 0
+
+
 def test_gemm_tc_views_and_refusals(ops):
     big = rnd(40, 3 * 256, dt=torch.bfloat16, s=0.5)
     w = rnd(96, 256, dt=torch.bfloat16, s=0.5, seed=1)

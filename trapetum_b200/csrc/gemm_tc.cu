@@ -111,14 +111,26 @@ struct GemmParams {
     void* out; long long ld_out;     // C as [tokens, weight rows], row stride ld_out
     float* partial;                  // [splits][tokens][weight rows] when splits > 1
     float cap;
+    int act;                         // gated epilogue: 0 gelu_tanh, 1 silu (only with GATED kernels)
 };
 
-// Shared-memory budget: the token-major orientation (prefill) takes what an SM has; the swapped one
-// (decode) takes under half, so that the CTAs of the next product can already sit on the SM and stream
-// their weights while this one drains (see pdl_wait in the producer).
+// Gated epilogue.  The weight rows are interleaved in blocks of 16: [gate 0..15 | up 0..15 | gate 16..31 | ...],
+// so that a gate and its up value always meet in one epilogue thread (token-major tiles: columns j and j + 16
+// of a 32-column chunk) or in one warp (swapped tiles: lanes l and l + 16).  The output has half the width:
+// out[token][16 b + j] = act(gate) * up, computed on the 32-bit accumulators
+// (the reference's gelu_mul_k does this as a kernel of its own, runtime/cuda/codebook_gemv.cu:531-537).
+__device__ __forceinline__ float gated(float g, float u, int act) {
+    const float a = act == 0 ? 0.5f * g * (1.0f + tanhf(0.7978845608f * (g + 0.044715f * g * g * g)))
+                             : g / (1.0f + expf(-g));
+    return a * u;
+}
+
+// Shared-memory budget: as many stages as an SM holds.  (Half of it, so that the next product's CTAs could
+// already sit on the SM and stream weights while this one drains, was measured slower: bytes in flight
+// per SM matter more than the overlap.)
 template <int BN, bool SWAP> struct Cfg {
     static constexpr int STAGE_BYTES = BM * BK * 2 + BN * BK * 2;
-    static constexpr int BUDGET = SWAP && BN <= 64 ? 104 * 1024 : 200 * 1024;
+    static constexpr int BUDGET = 200 * 1024;
     static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 10 ? 10 : STAGES_RAW;
     static constexpr int ACC_COLS = BN < 32 ? 32 : BN;               // columns of one accumulator stage
@@ -126,7 +138,7 @@ template <int BN, bool SWAP> struct Cfg {
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
 };
 
-template <int BN, bool SWAP, typename TOut>
+template <int BN, bool SWAP, typename TOut, bool GATED>
 __global__ void __launch_bounds__(192, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, GemmParams p) {
     pdl_launch_dependents();
@@ -262,7 +274,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 if (CH == 32) tmem_ld32(t_addr + c0, r); else tmem_ld16(t_addr + c0, r);
                 tmem_ld_wait();
                 const int q0 = tq * BN + c0;                           // first row of Q in this chunk
-                if (!SWAP) {
+                if (GATED && !SWAP) {
+                    // 32 columns = 16 gates then their 16 ups: 16 outputs at column q0 / 2
+                    if (prow < p.rows_p && q0 < p.rows_q) {
+                        bf16* dst = (bf16*)p.out + (size_t)prow * p.ld_out + (q0 >> 1);
+                        uint32_t w[8];
+#pragma unroll
+                        for (int j = 0; j < 16; j += 2) {
+                            const float v0 = gated(__uint_as_float(r[j]), __uint_as_float(r[j + 16]), p.act);
+                            const float v1 = gated(__uint_as_float(r[j + 1]), __uint_as_float(r[j + 17]), p.act);
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(v0, v1);
+                            w[j >> 1] = *(uint32_t*)&h2;
+                        }
+                        if ((((uintptr_t)dst) & 15) == 0) {
+                            *(uint4*)dst = make_uint4(w[0], w[1], w[2], w[3]);
+                            *(uint4*)(dst + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 8; j++) *(uint32_t*)(dst + 2 * j) = w[j];
+                        }
+                    }
+                } else if (GATED && SWAP) {
+                    // lanes 0..15 hold gates, lanes 16..31 the ups of the same 16 features
+#pragma unroll
+                    for (int j = 0; j < CH; j++) {
+                        const float mine = __uint_as_float(r[j]);
+                        const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
+                        const int tok = q0 + j;
+                        if (lane < 16 && tok < p.rows_q && prow < p.rows_p)
+                            ((bf16*)p.out)[(size_t)tok * p.ld_out + ((prow >> 5) << 4) + lane] =
+                                __float2bfloat16_rn(gated(mine, other, p.act));
+                    }
+                } else if (!SWAP) {
                     // tokens on lanes (prow), weight rows on columns (q0 + j): a thread writes a row segment
                     if (prow < p.rows_p) {
                         if (p.splits > 1) {
@@ -386,11 +429,11 @@ static int make_map(CUtensorMap* m, const void* base, long long rows, long long 
 
 static int g_sms = 0;
 
-template <int BN, bool SWAP, typename TOut>
+template <int BN, bool SWAP, typename TOut, bool GATED = false>
 static int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmParams& p, cudaStream_t stream) {
     using C = Cfg<BN, SWAP>;
     static bool attr_set = false;
-    auto kern = gemm_tc_kernel<BN, SWAP, TOut>;
+    auto kern = gemm_tc_kernel<BN, SWAP, TOut, GATED>;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
         if (e != cudaSuccess) return (int)e;
@@ -439,7 +482,7 @@ extern "C" int tb_gemm_tc_effective_splits(int K, int splits) {
 // reduce = 0 with splits > 1: leave the partial sums in `scratch` ([splits][M][N]) for the consumer to add.
 extern "C" int tb_gemm_tc(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K,
                           long long lda, long long ldw, long long ldc, float softcap, int splits, float* scratch,
-                          int reduce, cudaStream_t stream) {
+                          int reduce, int gated_act, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (!tb_gemm_tc_takes(A, W, M, N, K, lda, ldw))
         return tb_refuse("gemm_tc: needs K, lda, ldw multiples of 8 and 16-byte aligned operands "
@@ -456,6 +499,14 @@ extern "C" int tb_gemm_tc(const void* A, const void* W, void* C, int c_dtype, in
     int per = (kblocks + splits - 1) / splits;
     splits = (kblocks + per - 1) / per;
     if (splits > 1 && scratch == nullptr) return tb_refuse("gemm_tc: split-K needs scratch");
+    const bool gated = gated_act >= 0;
+    if (gated) {
+        if (gated_act > 1) return tb_refuse("gemm_tc: unknown gated activation %d", gated_act);
+        if (N % 32) return tb_refuse("gemm_tc: the gated epilogue needs a multiple of 32 weight rows, got %d", N);
+        if (c_dtype != TB_BF16) return tb_refuse("gemm_tc: the gated epilogue writes bfloat16");
+        if (softcap > 0.f) return tb_refuse("gemm_tc: the gated epilogue takes no soft cap");
+        splits = 1; per = kblocks;                   // the activation is not linear: no partial sums
+    }
 
     const bool swap = M <= BM;
     int bn;
@@ -465,6 +516,7 @@ extern "C" int tb_gemm_tc(const void* A, const void* W, void* C, int c_dtype, in
     GemmParams p;
     p.K = K; p.kblocks = kblocks; p.splits = splits; p.kb_per_split = per;
     p.out = C; p.ld_out = ldc; p.partial = scratch; p.cap = splits > 1 ? 0.f : softcap;
+    p.act = gated ? gated_act : 0;
     CUtensorMap mp, mq;
     if (swap) {
         p.rows_p = N; p.rows_q = M;
@@ -478,7 +530,12 @@ extern "C" int tb_gemm_tc(const void* A, const void* W, void* C, int c_dtype, in
 
     int st;
 #define GO(BN_, SW_) (c_dtype == TB_BF16 ? launch<BN_, SW_, bf16>(mp, mq, p, stream) : launch<BN_, SW_, float>(mp, mq, p, stream))
-    if (swap) {
+    if (gated) {
+#define GG(BN_, SW_) launch<BN_, SW_, bf16, true>(mp, mq, p, stream)
+        if (swap) st = bn == 16 ? GG(16, true) : bn == 32 ? GG(32, true) : bn == 64 ? GG(64, true) : GG(128, true);
+        else st = bn == 256 ? GG(256, false) : GG(128, false);
+#undef GG
+    } else if (swap) {
         switch (bn) {
         case 16: st = GO(16, true); break;
         case 32: st = GO(32, true); break;

@@ -18,7 +18,51 @@
 
 TB_EXPORT_ERROR()
 
-template <typename TX, typename TW, typename TO>
+// Four consecutive elements at a time (one 16-byte or 8-byte access) when the row width allows.
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ void load(const float* p, float* f) {
+        const float4 v = *(const float4*)p; f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float* f) { *(float4*)p = make_float4(f[0], f[1], f[2], f[3]); }
+};
+template <> struct Vec4<bf16> {
+    static __device__ __forceinline__ void load(const bf16* p, float* f) {
+        const uint2 v = *(const uint2*)p;
+        f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u);
+        f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xffff0000u);
+    }
+    static __device__ __forceinline__ void store(bf16* p, const float* f) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+        *(uint2*)p = make_uint2(*(uint32_t*)&a, *(uint32_t*)&b);
+    }
+};
+
+// Element(s) at `p` summed over n_splits partial sums, in split order.  The loads of up to four splits are
+// issued before the first addition, so their latencies overlap instead of forming a chain.
+template <typename TA, int VEC>
+__device__ __forceinline__ void load_sum(const TA* p, int n_splits, long long split_stride, float* v) {
+    if (VEC == 4) Vec4<TA>::load(p, v); else v[0] = to_f<TA>(p[0]);
+    for (int s = 1; s < n_splits; s += 4) {
+        float t[4][VEC];
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            if (s + k < n_splits) {
+                if (VEC == 4) Vec4<TA>::load(p + (size_t)(s + k) * split_stride, t[k]);
+                else t[k][0] = to_f<TA>(p[(size_t)(s + k) * split_stride]);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+            if (s + k < n_splits) {
+#pragma unroll
+                for (int e = 0; e < VEC; e++) v[e] += t[k][e];
+            }
+    }
+}
+
+// VEC = 4: width % 4 == 0 and all rows 16-byte aligned; VEC = 1: anything.
+template <typename TX, typename TW, typename TO, int VEC>
 __global__ void rmsnorm_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
                                int width, float eps, float offset) {
     pdl_launch_dependents();
@@ -26,61 +70,94 @@ __global__ void rmsnorm_kernel(const TX* __restrict__ x, const TW* __restrict__ 
     __shared__ float red[33];
     const size_t base = (size_t)blockIdx.x * width;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) { float v = to_f<TX>(x[base + i]); ss += v * v; }
+    if (VEC == 4) {
+        for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+            float v[4]; Vec4<TX>::load(x + base + i, v);
+            ss += v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+        }
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) { float v = to_f<TX>(x[base + i]); ss += v * v; }
+    }
     ss = block_sum(ss, red);
     const float r = rsqrtf(ss / (float)width + eps);
-    for (int i = threadIdx.x; i < width; i += blockDim.x)
-        out[base + i] = from_f<TO>(to_f<TX>(x[base + i]) * r * (offset + to_f<TW>(w[i])));
+    if (VEC == 4) {
+        for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+            float v[4], g[4]; Vec4<TX>::load(x + base + i, v); Vec4<TW>::load(w + i, g);
+#pragma unroll
+            for (int e = 0; e < 4; e++) v[e] = v[e] * r * (offset + g[e]);
+            Vec4<TO>::store(out + base + i, v);
+        }
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x)
+            out[base + i] = from_f<TO>(to_f<TX>(x[base + i]) * r * (offset + to_f<TW>(w[i])));
+    }
 }
 
 // h += norm_a(a); optionally out = norm_b(h).  `a` may come as n_splits partial sums (32-bit, the
 // split-K output of a matrix product, [n_splits][rows][width]); they are added in split order here,
 // which saves the separate reduction pass.  The row of `a` is kept in shared memory between the two
 // passes over it when it fits (row_cache != 0); a thread re-reads only elements that it wrote itself.
-template <typename TA, typename TW, typename TO>
+template <typename TA, typename TW, typename TO, int VEC>
 __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TA* __restrict__ a, int n_splits, long long split_stride,
                                    const TW* __restrict__ wa, float eps_a, float off_a,
                                    const TW* __restrict__ wb, float eps_b, float off_b,
                                    TO* __restrict__ out, int width, int row_cache) {
     pdl_launch_dependents();
     pdl_wait();
-    extern __shared__ float row[];
+    extern __shared__ __align__(16) float row[];
     __shared__ float red[33];
     const size_t base = (size_t)blockIdx.x * width;
+    const int step = blockDim.x * VEC;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        float v = to_f<TA>(a[base + i]);
-        for (int s = 1; s < n_splits; s++) v += to_f<TA>(a[(size_t)s * split_stride + base + i]);
-        if (row_cache) row[i] = v;
-        ss += v * v;
+    for (int i = threadIdx.x * VEC; i < width; i += step) {
+        float v[VEC];
+        load_sum<TA, VEC>(a + base + i, n_splits, split_stride, v);
+#pragma unroll
+        for (int e = 0; e < VEC; e++) { if (row_cache) row[i + e] = v[e]; ss += v[e] * v[e]; }
     }
     ss = block_sum(ss, red);
     const float ra = rsqrtf(ss / (float)width + eps_a);
     float s2 = 0.f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        float av;
-        if (row_cache) av = row[i];
-        else {
-            av = to_f<TA>(a[base + i]);
-            for (int s = 1; s < n_splits; s++) av += to_f<TA>(a[(size_t)s * split_stride + base + i]);
+    for (int i = threadIdx.x * VEC; i < width; i += step) {
+        float av[VEC], hv[VEC], g[VEC];
+        if (row_cache) {
+#pragma unroll
+            for (int e = 0; e < VEC; e++) av[e] = row[i + e];
+        } else {
+            load_sum<TA, VEC>(a + base + i, n_splits, split_stride, av);
         }
-        const float v = h[base + i] + av * ra * (off_a + to_f<TW>(wa[i]));
-        h[base + i] = v;
-        if (row_cache) row[i] = v;
-        s2 += v * v;
+        if (VEC == 4) { Vec4<float>::load(h + base + i, hv); Vec4<TW>::load(wa + i, g); }
+        else { hv[0] = h[base + i]; g[0] = to_f<TW>(wa[i]); }
+#pragma unroll
+        for (int e = 0; e < VEC; e++) {
+            hv[e] = hv[e] + av[e] * ra * (off_a + g[e]);
+            if (row_cache) row[i + e] = hv[e];
+            s2 += hv[e] * hv[e];
+        }
+        if (VEC == 4) Vec4<float>::store(h + base + i, hv); else h[base + i] = hv[0];
     }
     if (out == nullptr) return;
     s2 = block_sum(s2, red);
     const float rb = rsqrtf(s2 / (float)width + eps_b);
-    for (int i = threadIdx.x; i < width; i += blockDim.x)
-        out[base + i] = from_f<TO>((row_cache ? row[i] : h[base + i]) * rb * (off_b + to_f<TW>(wb[i])));
+    for (int i = threadIdx.x * VEC; i < width; i += step) {
+        float hv[VEC], g[VEC];
+        if (row_cache) {
+#pragma unroll
+            for (int e = 0; e < VEC; e++) hv[e] = row[i + e];
+        } else if (VEC == 4) Vec4<float>::load(h + base + i, hv);
+        else hv[0] = h[base + i];
+        if (VEC == 4) Vec4<TW>::load(wb + i, g); else g[0] = to_f<TW>(wb[i]);
+#pragma unroll
+        for (int e = 0; e < VEC; e++) hv[e] = hv[e] * rb * (off_b + g[e]);
+        if (VEC == 4) Vec4<TO>::store(out + base + i, hv); else out[base + i] = from_f<TO>(hv[0]);
+    }
 }
 
-static int norm_threads(int width) {
-    int t = 64;
-    while (t < 1024 && t * 4 < width) t <<= 1;
-    return t;
+static int norm_threads(int width, int vec) {
+    int t = ((width + vec - 1) / vec + 31) / 32 * 32;      // one access per thread and pass, if a block holds it
+    return t < 64 ? 64 : (t > 1024 ? 1024 : t);
 }
+static bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 
 #define DISPATCH3(cx, cw, co, ...)                                                         \
     do {                                                                                   \
@@ -106,9 +183,15 @@ extern "C" int tb_rmsnorm(const void* x, int x_dtype, const void* w, int w_dtype
     if (width <= 0) return tb_refuse("rmsnorm: width=%d", width);
     if (!code_ok(x_dtype) || !code_ok(w_dtype) || !code_ok(out_dtype))
         return tb_refuse("rmsnorm: unknown dtype codes %d %d %d", x_dtype, w_dtype, out_dtype);
-    DISPATCH3(x_dtype, w_dtype, out_dtype,
-        tb_launch(rmsnorm_kernel<TX, TW, TO>, dim3(rows), dim3(norm_threads(width)), 0, stream, 
-            (const TX*)x, (const TW*)w, (TO*)out, width, eps, offset));
+    const bool vec = width % 4 == 0 && aligned16(x) && aligned16(w) && aligned16(out);
+    if (vec)
+        DISPATCH3(x_dtype, w_dtype, out_dtype,
+            tb_launch(rmsnorm_kernel<TX, TW, TO, 4>, dim3(rows), dim3(norm_threads(width, 4)), 0, stream,
+                (const TX*)x, (const TW*)w, (TO*)out, width, eps, offset));
+    else
+        DISPATCH3(x_dtype, w_dtype, out_dtype,
+            tb_launch(rmsnorm_kernel<TX, TW, TO, 1>, dim3(rows), dim3(norm_threads(width, 1)), 0, stream,
+                (const TX*)x, (const TW*)w, (TO*)out, width, eps, offset));
     return tb_launch_status();
 }
 
@@ -124,10 +207,18 @@ extern "C" int tb_add_rmsnorm(float* h, const void* a, int a_dtype, int n_splits
     if (n_splits < 1) return tb_refuse("add_rmsnorm: n_splits=%d", n_splits);
     const int row_cache = (size_t)width * sizeof(float) <= 40 * 1024;
     const size_t smem = row_cache ? (size_t)width * sizeof(float) : 0;
-    DISPATCH3(a_dtype, w_dtype, out_dtype,
-        tb_launch(add_rmsnorm_kernel<TX, TW, TO>, dim3(rows), dim3(norm_threads(width)), smem, stream,
-            h, (const TX*)a, n_splits, split_stride, (const TW*)wa, eps_a, off_a, (const TW*)wb, eps_b, off_b,
-            (TO*)out, width, row_cache));
+    const bool vec = width % 4 == 0 && split_stride % 4 == 0 && aligned16(h) && aligned16(a) && aligned16(wa) &&
+                     aligned16(wb) && aligned16(out);
+    if (vec)
+        DISPATCH3(a_dtype, w_dtype, out_dtype,
+            tb_launch(add_rmsnorm_kernel<TX, TW, TO, 4>, dim3(rows), dim3(norm_threads(width, 4)), smem, stream,
+                h, (const TX*)a, n_splits, split_stride, (const TW*)wa, eps_a, off_a, (const TW*)wb, eps_b, off_b,
+                (TO*)out, width, row_cache));
+    else
+        DISPATCH3(a_dtype, w_dtype, out_dtype,
+            tb_launch(add_rmsnorm_kernel<TX, TW, TO, 1>, dim3(rows), dim3(norm_threads(width, 1)), smem, stream,
+                h, (const TX*)a, n_splits, split_stride, (const TW*)wa, eps_a, off_a, (const TW*)wb, eps_b, off_b,
+                (TO*)out, width, row_cache));
     return tb_launch_status();
 }
 

@@ -403,11 +403,15 @@ def gemm_tc_takes(a: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, softcap: float = 0.0,
-            splits: Optional[int] = None, out: Optional[torch.Tensor] = None, partials: bool = False) -> torch.Tensor:
+            splits: Optional[int] = None, out: Optional[torch.Tensor] = None, partials: bool = False,
+            gated_act: Optional[str] = None) -> torch.Tensor:
     """a[M,K] @ w[N,K]^T in bfloat16 on tcgen05 tensor cores with 32-bit accumulation.
     ``splits`` None: the library picks the K split (more than 1 only for few tokens and few weight rows).
     ``partials=True`` returns float32 [splits, M, N] whose sum over the first axis, taken in order, is the
-    product: a consumer that reads the product once anyway adds them on the way and saves a pass."""
+    product: a consumer that reads the product once anyway adds them on the way and saves a pass.
+    ``gated_act`` ("gelu_tanh" or "silu"): ``w`` holds gate and up rows interleaved in blocks of 16
+    (see :func:`interleave_gate_up`); the result is bfloat16 [M, N/2] = act(gate) * up, taken on the
+    32-bit accumulators in the epilogue."""
     _cuda(a, w, out)
     if not gemm_tc_takes(a, w):
         raise KernelError(f"gemm_tc does not take a {tuple(a.shape)}/{a.stride()} {a.dtype}, "
@@ -418,6 +422,17 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, softcap: f
     if splits is None:
         splits = lib.tb_gemm_tc_splits(c_int(M), c_int(N), c_int(K), c_int(sm_count(a.device)))
     splits = int(lib.tb_gemm_tc_effective_splits(c_int(K), c_int(splits)))
+    if gated_act is not None:
+        if gated_act not in ACTIVATIONS:
+            raise KernelError(f"gemm_tc: unknown activation '{gated_act}' (known: {sorted(ACTIVATIONS)})")
+        if N % 32 or partials or softcap:
+            raise KernelError("gemm_tc: the gated epilogue needs a multiple of 32 weight rows, no partials, no cap")
+        out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=a.device)
+        _check(lib, lib.tb_gemm_tc(_ptr(a), _ptr(w), _ptr(out), c_int(1), c_int(M), c_int(N), c_int(K),
+                                   c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
+                                   c_float(0.0), c_int(1), _ptr(None), c_int(1), c_int(ACTIVATIONS[gated_act]),
+                                   _stream()), "gemm_tc")
+        return out
     if partials:
         if softcap:
             raise KernelError("gemm_tc: a soft cap cannot be applied to partial sums")
@@ -425,11 +440,11 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, softcap: f
         if splits == 1:
             _check(lib, lib.tb_gemm_tc(_ptr(a), _ptr(w), _ptr(part), c_int(0), c_int(M), c_int(N), c_int(K),
                                        c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(N),
-                                       c_float(0.0), c_int(1), _ptr(None), c_int(1), _stream()), "gemm_tc")
+                                       c_float(0.0), c_int(1), _ptr(None), c_int(1), c_int(-1), _stream()), "gemm_tc")
         else:
             _check(lib, lib.tb_gemm_tc(_ptr(a), _ptr(w), _ptr(None), c_int(0), c_int(M), c_int(N), c_int(K),
                                        c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(N),
-                                       c_float(0.0), c_int(splits), _ptr(part), c_int(0), _stream()), "gemm_tc")
+                                       c_float(0.0), c_int(splits), _ptr(part), c_int(0), c_int(-1), _stream()), "gemm_tc")
         return part
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
@@ -440,9 +455,19 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, softcap: f
         scratch = torch.empty(splits * M * N, dtype=torch.float32, device=a.device)
     _check(lib, lib.tb_gemm_tc(_ptr(a), _ptr(w), _ptr(out), c_int(code(out.dtype)), c_int(M), c_int(N), c_int(K),
                                c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
-                               c_float(softcap or 0.0), c_int(splits), _ptr(scratch), c_int(1), _stream()), "gemm_tc",
+                               c_float(softcap or 0.0), c_int(splits), _ptr(scratch), c_int(1), c_int(-1), _stream()), "gemm_tc",
            2 if splits > 1 else 1)
     return out
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[I, K] gate and up matrices -> [2I, K] with rows in blocks of 16: gate 0..15, up 0..15, gate 16..31, ...
+    (the layout the gated epilogue of :func:`gemm_tc` expects; I must be a multiple of 16).  Run once, when
+    the weights are bound."""
+    I, K = gate.shape
+    if up.shape != gate.shape or I % 16:
+        raise KernelError("interleave_gate_up: gate and up must be [I, K] with I a multiple of 16")
+    return torch.stack([gate.view(I // 16, 16, K), up.view(I // 16, 16, K)], dim=1).reshape(2 * I, K).contiguous()
 
 
 def sum_partials(part: torch.Tensor) -> torch.Tensor:

@@ -38,69 +38,95 @@ struct RopeKvArgs {
                                                                   // splits of partial[s][t][col]; qkv is written
 };
 
+// One CTA per token (several when tokens are few).  threadIdx.x walks the rotary pairs two at a time (4-byte accesses for bfloat16),
+// threadIdx.y strides over the head slots (q heads, then k heads, then v heads), so the sine and cosine of
+// a pair are computed once per thread and reused for every head it visits.
 template <typename T>
 __global__ void rope_kv_kernel(RopeKvArgs a) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
-    const int hs = blockIdx.y;                      // head slot: q heads, then k heads, then v heads
     const int hd = a.head_dim, half = a.rotary_dim >> 1;
     T* row = (T*)a.qkv + (size_t)t * a.row_stride;
     const int pos = a.positions[t];
-    const bool is_q = hs < a.n_heads;
-    const bool is_k = !is_q && hs < a.n_heads + a.n_kv_heads;
-    const int kvh = is_q ? 0 : (is_k ? hs - a.n_heads : hs - a.n_heads - a.n_kv_heads);
-    const int col0 = is_q ? a.q_off + hs * hd : (is_k ? a.k_off + kvh * hd : a.v_off + kvh * hd);
-    T* x = row + col0;
-    // value of element i of this head: from the matrix itself, or summed from split-K partials (in split order)
-    auto val = [&](int i) -> float {
-        if (a.partial == nullptr) return to_f<T>(x[i]);
-        const float* p = a.partial + (size_t)t * a.partial_row_stride + col0 + i;
-        float v = p[0];
-        for (int s = 1; s < a.n_splits; s++) v += p[(size_t)s * a.split_stride];
-        return v;
-    };
+    const bool rotate = a.inv_freq != nullptr && half > 0;
     const bool from_partial = a.partial != nullptr;
+    const float* prow = from_partial ? a.partial + (size_t)t * a.partial_row_stride : nullptr;
 
-    T* dst = nullptr;
-    if (!is_q && a.k_pool != nullptr) {
+    // where this token's k and v go in the cache (if anywhere)
+    size_t cache_off = 0;
+    bool store = false;
+    if (a.k_pool != nullptr) {
         const int b = a.token_seq[t];
-        bool keep = true;
+        store = true;
         int r = pos;
         if (a.ring_rows > 0) {
-            keep = pos >= a.len_after[b] - a.ring_rows;
+            store = pos >= a.len_after[b] - a.ring_rows;
             r = pos % a.ring_rows;
         }
-        if (keep) {
+        if (store) {
             const int page = a.page_table[(size_t)b * a.pt_stride + r / a.page_rows];
-            T* pool = (T*)(is_k ? a.k_pool : a.v_pool);
-            dst = pool + (((size_t)page * a.n_kv_heads + kvh) * a.page_rows + (r % a.page_rows)) * hd;
+            cache_off = ((size_t)page * a.n_kv_heads * a.page_rows + (r % a.page_rows)) * hd;
         }
     }
+    auto val = [&](int col) -> float {               // element `col` of the token's row
+        if (!from_partial) return to_f<T>(row[col]);
+        float v = prow[col];
+        for (int s = 1; s < a.n_splits; s += 4) {    // loads of four splits at a time, then added in order
+            float t4[4];
+#pragma unroll
+            for (int k = 0; k < 4; k++) t4[k] = (s + k < a.n_splits) ? prow[(size_t)(s + k) * a.split_stride + col] : 0.f;
+#pragma unroll
+            for (int k = 0; k < 4; k++) if (s + k < a.n_splits) v += t4[k];
+        }
+        return v;
+    };
 
-    if (!is_q && !is_k) {                            // v: copy only
-        for (int i = threadIdx.x; i < hd; i += blockDim.x) {
-            const T y = from_partial ? from_f<T>(val(i)) : x[i];
-            if (from_partial) x[i] = y;
-            if (dst) dst[i] = y;
-        }
-        return;
+    const int i0 = threadIdx.x * 2;                  // this thread's pairs: i0 and i0 + 1
+    float sn[2] = {0.f, 0.f}, cs[2] = {1.f, 1.f};
+    if (rotate) {
+#pragma unroll
+        for (int e = 0; e < 2; e++)
+            if (i0 + e < half) sincosf((float)pos * a.inv_freq[i0 + e], &sn[e], &cs[e]);
     }
-    const bool rotate = a.inv_freq != nullptr;
-    for (int i = threadIdx.x; i < hd; i += blockDim.x) {
-        // each thread owns a pair (i, i+half) for i < half, or a pass-through dim
-        if (rotate && i < half) {
-            const float ang = (float)pos * a.inv_freq[i];
-            float s, c;
-            sincosf(ang, &s, &c);
-            const float x0 = val(i), x1 = val(i + half);
-            const T y0 = from_f<T>(x0 * c - x1 * s), y1 = from_f<T>(x1 * c + x0 * s);
-            x[i] = y0; x[i + half] = y1;
-            if (dst) { dst[i] = y0; dst[i + half] = y1; }
-        } else if (!rotate || i >= 2 * half) {
-            const T y = from_partial ? from_f<T>(val(i)) : x[i];
-            if (from_partial) x[i] = y;
-            if (dst) dst[i] = y;
+    const int slots = a.n_heads + 2 * a.n_kv_heads;
+    for (int hs = blockIdx.y * blockDim.y + threadIdx.y; hs < slots; hs += gridDim.y * blockDim.y) {
+        const bool is_q = hs < a.n_heads;
+        const bool is_k = !is_q && hs < a.n_heads + a.n_kv_heads;
+        const int kvh = is_q ? 0 : (is_k ? hs - a.n_heads : hs - a.n_heads - a.n_kv_heads);
+        const int col0 = is_q ? a.q_off + hs * hd : (is_k ? a.k_off + kvh * hd : a.v_off + kvh * hd);
+        T* x = row + col0;
+        T* dst = nullptr;
+        if (!is_q && store)
+            dst = (T*)(is_k ? a.k_pool : a.v_pool) + cache_off + (size_t)kvh * a.page_rows * hd;
+        if ((is_q || is_k) && rotate) {
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const int i = i0 + e;
+                if (i < half) {
+                    const float x0 = val(col0 + i), x1 = val(col0 + i + half);
+                    const T y0 = from_f<T>(x0 * cs[e] - x1 * sn[e]), y1 = from_f<T>(x1 * cs[e] + x0 * sn[e]);
+                    x[i] = y0; x[i + half] = y1;
+                    if (dst) { dst[i] = y0; dst[i + half] = y1; }
+                }
+            }
+            // dims beyond the rotary part pass through
+            for (int i = 2 * half + i0; i < hd; i += blockDim.x * 2)
+#pragma unroll
+                for (int e = 0; e < 2; e++) if (i + e < hd) {
+                    const T y = from_partial ? from_f<T>(val(col0 + i + e)) : x[i + e];
+                    if (from_partial) x[i + e] = y;
+                    if (dst) dst[i + e] = y;
+                }
+        } else if (dst != nullptr || from_partial) {
+            // v heads, or no rotation at all: copy (and round, when the source is partial sums)
+            for (int i = i0; i < hd; i += blockDim.x * 2)
+#pragma unroll
+                for (int e = 0; e < 2; e++) if (i + e < hd) {
+                    const T y = from_partial ? from_f<T>(val(col0 + i + e)) : x[i + e];
+                    if (from_partial) x[i + e] = y;
+                    if (dst) dst[i + e] = y;
+                }
         }
     }
 }
@@ -116,9 +142,15 @@ extern "C" int tb_rope_kv(const RopeKvArgs* args, int dtype, int n_tokens, cudaS
     if (a.ring_rows > 0 && a.ring_rows % a.page_rows != 0)
         return tb_refuse("rope: ring_rows=%d must be a multiple of page_rows=%d", a.ring_rows, a.page_rows);
     const int slots = a.n_heads + 2 * a.n_kv_heads;
-    int threads = 32;
-    while (threads < 256 && threads < a.head_dim / 2) threads <<= 1;
-    dim3 grid(n_tokens, slots);
-    TB_DISPATCH_1(dtype, T, tb_launch(rope_kv_kernel<T>, dim3(grid), dim3(threads), 0, stream, a));
+    int tx = 16;                                     // threads over pairs (two pairs each)
+    while (tx < 128 && tx * 4 < a.head_dim) tx <<= 1;
+    int ty = 1;                                      // threads over head slots
+    while (ty * 2 <= slots && tx * ty * 2 <= 256) ty <<= 1;
+    // few tokens (decode): spread the head slots over several CTAs per token; many tokens: one CTA each,
+    // so that the sines and cosines are computed once per token
+    int gy = 1;
+    if (n_tokens < 128) gy = (slots + ty - 1) / ty;
+    if (gy > 65535) gy = 65535;
+    TB_DISPATCH_1(dtype, T, tb_launch(rope_kv_kernel<T>, dim3(n_tokens, gy), dim3(tx, ty), 0, stream, a));
     return tb_launch_status();
 }

@@ -40,13 +40,26 @@ class GatedMLP(FeedForward):
     def bind(self, tensors) -> None:
         g, u = tensors[self._name("gate")], tensors[self._name("up")]
         dt = g.dtype if g.dtype == u.dtype else torch.float32
-        self.w_gu = torch.cat([g.to(dt), u.to(dt)], dim=0).contiguous()
+        # With bfloat16 weights of tensor-core sizes the activation runs in the product's epilogue; the gate
+        # and up rows are then interleaved in blocks of 16.  Otherwise: [gate; up] and a kernel of its own.
+        self.fused = (dt == torch.bfloat16 and self.rt.dtype == torch.bfloat16 and self.inter % 16 == 0
+                      and self.hidden % 8 == 0)
+        if self.fused:
+            self.w_gu = ops.interleave_gate_up(g, u)
+        else:
+            self.w_gu = torch.cat([g.to(dt), u.to(dt)], dim=0).contiguous()
         self.w_down = tensors[self._name("down")]
 
     def kernel_files(self):
         return linear_kernels(self.rt.dtype) + ("activation",)
 
     def forward(self, x, ctx):
+        if self.fused and ops.gemm_tc_takes(x, self.w_gu):
+            act = ops.gemm_tc(x, self.w_gu, self.rt.dtype, gated_act=self.activation)
+            return linear_partials(act, self.w_down)
+        if self.fused:
+            raise RuntimeError("gated_mlp: the interleaved weights need the tensor-core product, which does not take "
+                               f"an input of shape {tuple(x.shape)} with strides {x.stride()}")
         gu = linear(x, self.w_gu, self.rt.dtype)
         act = ops.gated_act(gu, self.activation, self.rt.dtype)
         return linear_partials(act, self.w_down)
