@@ -432,6 +432,23 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     for (int d = 0; d < HD / 8; d++) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
     float m_run = -INFINITY, l_run = 0.f;                           // of row g (meaningful for g < G)
 
+    // Which rows (in row space) are keys.  Without a ring, or before the ring has wrapped: lo <= R < len.
+    // Once it has wrapped (len >= ring_rows) every row holds a token; too old are the ring_rows - window rows
+    // that follow the newest one, a single circular run that starts at old_beg.
+    const bool wrapped = a.ring_rows > 0 && len >= a.ring_rows;
+    const int newest = wrapped ? (len - 1) % a.ring_rows : 0;
+    const int n_old = wrapped ? a.ring_rows - a.window : 0;
+    const int old_beg = wrapped ? (newest + 1 == a.ring_rows ? 0 : newest + 1) : 0;
+    const bool no_invalid = wrapped && n_old == 0;                  // a full ring whose every row is in the window
+    auto is_key = [&](int R) -> bool {
+        if (wrapped) {
+            int d = R - old_beg;                                    // distance past the start of the old run
+            if (d < 0) d += a.ring_rows;
+            return d >= n_old;
+        }
+        return R >= lo && R < len;
+    };
+
     int consumed = 0;
     for (int i = 0; i < n; i++) {
         const int s = i % C::STAGES;
@@ -444,18 +461,12 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         const int row0 = (pg_beg + i) * PAGE + key0;
 
         // ---- which of this warp's 16 rows are keys of the sequence
-        auto is_key = [&](int R) -> bool {
-            if (a.ring_rows > 0) {
-                if (R >= min(len, a.ring_rows)) return false;
-                const int pos = R + a.ring_rows * ((len - 1 - R) / a.ring_rows);
-                return pos >= lo;
-            }
-            return R >= lo && R < len;
-        };
-        const bool first_ok = is_key(row0), last_ok = is_key(row0 + 15);
-        bool all_ok = first_ok && last_ok;
-        if (a.ring_rows > 0 && all_ok) {                             // a ring's keys need not be contiguous
-            for (int r = 1; r < 15; r++) all_ok = all_ok && is_key(row0 + r);
+        bool all_ok;
+        if (no_invalid) all_ok = true;
+        else {
+            all_ok = is_key(row0) && is_key(row0 + 15);
+            // in a ring the rows that are too old form one circular run; it may lie inside these 16 rows
+            if (wrapped && all_ok) all_ok = !(old_beg > row0 && old_beg <= row0 + 15);
         }
         if (!all_ok) {
             // zero the V rows that are not keys: p is 0 there, but 0 * NaN would still poison o
@@ -471,16 +482,20 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         }
 
         // ---- S = Q K^T: 16 rows x 16 keys (two n-tiles)
-        float sc[2][4];
+        float sc[2][4], sc2[2][4];                                   // two chains per n-tile: even and odd k-steps
 #pragma unroll
-        for (int nt = 0; nt < 2; nt++) { sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f; }
+        for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) { sc[nt][e] = 0.f; sc2[nt][e] = 0.f; }
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ks++) {
             uint32_t b0, b1, b2, b3;
             ldsm_x4(smem_u32(k_s + sw_off(key0 + (lane >> 4) * 8 + (lane & 7), ks * 2 + ((lane >> 3) & 1))), b0, b1, b2, b3);
-            mma_rows8(sc[0], qa[ks][0], qa[ks][1], b0, b1);
-            mma_rows8(sc[1], qa[ks][0], qa[ks][1], b2, b3);
+            if (ks & 1) { mma_rows8(sc2[0], qa[ks][0], qa[ks][1], b0, b1); mma_rows8(sc2[1], qa[ks][0], qa[ks][1], b2, b3); }
+            else { mma_rows8(sc[0], qa[ks][0], qa[ks][1], b0, b1); mma_rows8(sc[1], qa[ks][0], qa[ks][1], b2, b3); }
         }
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++) { sc[nt][0] += sc2[nt][0]; sc[nt][1] += sc2[nt][1]; }
         // ---- scale, cap, mask; row g lives in sc[nt][0..1] of the quad's four lanes
         float mx = -INFINITY;
 #pragma unroll

@@ -595,9 +595,9 @@ def choose_decode_splits(batch: int, n_kv_heads: int, pages: int, sms: int) -> i
             break
         ctas = items * s
         eff = ctas / (((ctas + sms - 1) // sms) * sms)
-        # a piece that is too short pays its start-up (about two pages' worth) too often
+        # a piece pays its start-up and its share of the final fold: about four pages' worth (measured)
         per = (pages + s - 1) // s
-        eff *= per / (per + 2.0)
+        eff *= per / (per + 4.0)
         if eff > best_eff + 1e-9:
             best, best_eff = s, eff
     return best
