@@ -26,7 +26,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# Layer sizes of Gemma-2-2B (BASELINE.json, configs[2]); weights are random (seed 2).
+# Layer sizes of Gemma-2-2B; weights are random (seed 2).
 GEMMA2_2B = {
     "architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2",
     "num_hidden_layers": 26, "hidden_size": 2304, "num_attention_heads": 8, "num_key_value_heads": 4,
