@@ -311,6 +311,8 @@ def test_attn_prefill(ops, dt, nh, nkv, hd, cap, window):
     impls = [lambda: ops.attn_prefill_simt(q, k, v, seq_start, token_seq, nh, nkv, hd, scale, cap, window)]
     if ops.attn_prefill_takes(dt, hd) and hd in (16, 32, 48, 64, 128, 256):
         impls.append(lambda: ops.attn_prefill_mma(q, k, v, seq_start, nh, nkv, hd, scale, cap, window, max(lens)))
+    if ops.attn_prefill_tc_takes(dt, hd):
+        impls.append(lambda: ops.attn_prefill_tc(q, k, v, seq_start, lens, nh, nkv, hd, scale, cap, window))
     wants = []
     for b, n in enumerate(lens):
         s = slice(starts[b], starts[b + 1])
@@ -320,6 +322,39 @@ def test_attn_prefill(ops, dt, nh, nkv, hd, cap, window):
         got = impl()
         for b, n in enumerate(lens):
             close(got[starts[b]:starts[b + 1]].view(n, nh, hd), wants[b], dt, 2.0)
+    if ops.attn_prefill_tc_takes(dt, hd):
+        torch.cuda.synchronize()
+        assert ops.attn_prefill_tc_error(hd) == 0
+
+
+@pytest.mark.parametrize("nh,nkv,hd,cap,window,lens", [(8, 4, 256, 50.0, 0, [1000]), (8, 4, 256, 50.0, 300, [700, 64, 129]),
+                                                       (4, 1, 128, 0.0, 0, [513, 1]), (2, 2, 64, 20.0, 100, [400, 333])])
+def test_attn_prefill_tc_long(ops, nh, nkv, hd, cap, window, lens):
+    """Long sequences: many key blocks, the lazy rescaling of O, the window's trailing edge, and query
+    tiles whose rows belong to the next sequence of the packed batch."""
+    T = sum(lens)
+    qkv = rnd(T, (nh + 2 * nkv) * hd, dt=torch.bfloat16, s=1.0)
+    # make the scores grow along each sequence, so that the running maximum keeps moving
+    ramp = torch.cat([torch.linspace(0.2, 2.0, n) for n in lens]).cuda().bfloat16()
+    qkv[:, nh * hd:(nh + nkv) * hd] *= ramp[:, None]
+    q, k, v = qkv[:, :nh * hd], qkv[:, nh * hd:(nh + nkv) * hd], qkv[:, (nh + nkv) * hd:]
+    starts = [0]
+    for n in lens:
+        starts.append(starts[-1] + n)
+    seq_start = torch.tensor(starts, dtype=torch.int32, device="cuda")
+    scale = 1.0 / math.sqrt(hd)
+    got = ops.attn_prefill_tc(q, k, v, seq_start, lens, nh, nkv, hd, scale, cap, window)
+    ref = ops.attn_prefill_mma(q, k, v, seq_start, nh, nkv, hd, scale, cap, window, max(lens))
+    torch.cuda.synchronize()
+    assert ops.attn_prefill_tc_error(hd) == 0
+    assert torch.isfinite(got.float()).all()
+    for b, n in enumerate(lens):
+        s = slice(starts[b], starts[b + 1])
+        sub = slice(0, n) if n <= 400 else slice(n - 200, n)
+        want = plain.attention(q[s].float().cpu().view(n, nh, hd), k[s].float().cpu().view(n, nkv, hd),
+                               v[s].float().cpu().view(n, nkv, hd), scale, cap or None, window or None)
+        close(got[s].view(n, nh, hd)[sub], want[sub], torch.bfloat16, 2.0)
+        close(ref[s].view(n, nh, hd)[sub], want[sub], torch.bfloat16, 2.0)
 
 
 def test_attn_prefill_far_key_and_window_edge(ops):
@@ -336,7 +371,8 @@ def test_attn_prefill_far_key_and_window_edge(ops):
     token_seq = torch.zeros(n, dtype=torch.int32, device="cuda")
     for window in (0, W):
         for got in (ops.attn_prefill_simt(q, k, v, seq_start, token_seq, nh, nkv, hd, 1.0, 0.0, window),
-                    ops.attn_prefill_mma(q, k, v, seq_start, nh, nkv, hd, 1.0, 0.0, window, n)):
+                    ops.attn_prefill_mma(q, k, v, seq_start, nh, nkv, hd, 1.0, 0.0, window, n),
+                    ops.attn_prefill_tc(q, k, v, seq_start, [n], nh, nkv, hd, 1.0, 0.0, window)):
             got = got.view(n, nh, hd).float()
             hit = lambda i: float((got[i, 0] - v[marked].float()).abs().max()) < 3e-2
             assert hit(marked + W - 1)                                  # the window's last row that still sees it

@@ -1,0 +1,437 @@
+// Prefill attention on the 5th-generation tensor cores (tcgen05, bfloat16): causal, packed sequences
+// of unequal length, optional sliding window and tanh soft cap, grouped-query heads.
+//
+// Same formula as attention_prefill.cu (and as the reference's one-query attn_k,
+// runtime/cuda/codebook_gemv.cu:240-270); what differs is where the work runs:
+//   * one CTA = 128 queries of one head of one sequence; S = Q K^T and O += P V are tcgen05.mma
+//     (128 x 64 x 16 and 128 x head_dim x 16) issued by one thread, with S and O in tensor memory;
+//   * tensor memory's lanes are the query rows, so a row's running maximum, exponentials and row sum
+//     stay with the row's threads: no shuffles across a warp;
+//   * Q, K and the transposed V tiles arrive by tiled TMA (128-byte swizzle); P is written to shared
+//     memory in the same swizzled K-major layout and is the A operand of the second product;
+//   * the exponent's reference maximum is only raised when a block's maximum exceeds it by 2^8
+//     ("lazy rescaling"): then the thread scales its O row in tensor memory; otherwise O is left
+//     alone and p may reach 256, which bfloat16 and the 32-bit accumulators hold without loss;
+//   * warp 0 loads, warp 1 issues MMAs, warps 2..9 are the softmax (two threads per row, 32 keys of a
+//     block each; the row maximum crosses between them through shared memory); S and P are double-buffered so
+//     that the tensor cores run block j+1's Q K^T while block j's softmax is computed.
+// V is needed as [dim][key] (keys contiguous) for the second product; tb_transpose_v makes that copy
+// per sequence, each sequence starting at a multiple of 64 keys so that every TMA copy is aligned.
+//
+// All waits are bounded (async.cuh); a wait that runs out records an error word.
+// Compiled once per head size (-DTB_HD = 64, 128 or 256).
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+TB_EXPORT_ERROR()
+
+#ifndef TB_HD
+#define TB_HD 256
+#endif
+constexpr int HD = TB_HD;
+static_assert(HD == 64 || HD == 128 || HD == 256, "head_dim 64, 128 or 256");
+#define BM 128
+#define BN 64
+constexpr int QBOXES = HD / 64;                       // 64-dim boxes along the head dim
+constexpr int Q_BYTES = QBOXES * BM * 128;            // 128 rows x head_dim
+constexpr int K_BYTES = QBOXES * BN * 128;            // 64 keys x head_dim
+constexpr int VT_BYTES = HD * 128;                    // head_dim rows x 64 keys
+constexpr int P_BYTES = BM * 128;                     // 128 rows x 64 keys
+constexpr int TILE_BYTES = Q_BYTES + 2 * K_BYTES + 2 * VT_BYTES + 2 * P_BYTES;
+constexpr int ROWX_BYTES = 2 * 2 * BM * 4;         // the softmax threads' exchange
+constexpr int USED_BYTES = TILE_BYTES + ROWX_BYTES + 256;
+constexpr int SMEM_BYTES = USED_BYTES + 512;       // head_dim 256 uses all but 256 bytes of an SM's shared memory
+static_assert(SMEM_BYTES <= 232448, "does not fit an SM's shared memory");
+constexpr int TMEM_COLS = (2 * BN + HD) <= 256 ? 256 : 512;
+constexpr float RESCALE_AT = 8.f;                     // in log2 units
+
+__device__ int g_attn_tc_error = 0;
+
+struct PrefillTcArgs {
+    const int* seq_start;          // [B + 1] rows of the packed q/k matrices
+    const int* vt_start;           // [B + 1] key columns of the transposed v (multiples of 64)
+    bf16* out;                     // [T, n_heads * HD]
+    int n_heads, n_kv_heads, window;
+    float scale, cap;
+};
+
+__device__ __forceinline__ float ex2f(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float rcpf(float x) { float y; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+
+__global__ void __launch_bounds__(320, 1)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_vt, PrefillTcArgs a) {
+    pdl_launch_dependents();
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    if (smem + USED_BYTES > smem_raw + SMEM_BYTES) {                 // the base was less aligned than assumed
+        if (threadIdx.x == 0) atomicExch(&g_attn_tc_error, 4);
+        return;
+    }
+    uint8_t* sQ = smem;
+    uint8_t* sK = sQ + Q_BYTES;                       // [2][K_BYTES]
+    uint8_t* sVT = sK + 2 * K_BYTES;                  // [2][VT_BYTES]
+    uint8_t* sP = sVT + 2 * VT_BYTES;                 // [2][P_BYTES]
+    float (*row_x)[2][BM] = (float (*)[2][BM])(sP + 2 * P_BYTES);   // [block parity][half][row]
+    uint64_t* bars = (uint64_t*)(sP + 2 * P_BYTES + ROWX_BYTES);
+    uint64_t* q_full = bars;                          // 1
+    uint64_t* k_full = bars + 1;                      // [2]
+    uint64_t* k_empty = bars + 3;                     // [2]
+    uint64_t* v_full = bars + 5;                      // [2]
+    uint64_t* v_empty = bars + 7;                     // [2]  (also: P buffer free)
+    uint64_t* s_full = bars + 9;                      // [2]
+    uint64_t* s_empty = bars + 11;                    // [2]
+    uint64_t* p_full = bars + 13;                     // [2]
+    uint64_t* x_bar = bars + 15;                      // 1: the softmax warps' exchange, one phase per block
+    uint32_t* tmem_slot = (uint32_t*)(bars + 16);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int s0 = a.seq_start[b], len = a.seq_start[b + 1] - s0;
+    const int qb = (int)gridDim.x - 1 - (int)blockIdx.x;             // longest blocks first
+    const int m0 = qb * BM;
+    if (m0 >= len) return;                                           // uniform for the CTA
+    const int kvh = h / (a.n_heads / a.n_kv_heads);
+    const int vt0 = a.vt_start[b];
+
+    // key blocks this query block can see
+    const int i_last = min(len, m0 + BM) - 1;
+    const int j_lo = (a.window > 0) ? max(0, m0 - a.window + 1) : 0;
+    const int nb_lo = j_lo / BN, nb_hi = i_last / BN + 1;
+    const int nblocks = nb_hi - nb_lo;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < 2; s++) {
+            mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+            mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 8); mbar_init(&p_full[s], 8);
+        }
+        mbar_init(x_bar, 8);
+        *abort_flag = 0;
+        mbar_init_fence();
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_s = tmem_base;                               // [2][BN] columns
+    const uint32_t tmem_o = tmem_base + 2 * BN;                      // HD columns
+
+    if (warp == 0) {
+        // ---------------- loads ----------------
+        if (lane == 0) {
+            pdl_wait();
+            bool ok = true;
+            mbar_expect_tx(q_full, Q_BYTES);
+            for (int c = 0; c < QBOXES; c++) tma_load_2d(sQ + c * BM * 128, &map_q, q_full, h * HD + c * 64, s0 + m0);
+            for (int j = 0; j < nblocks && ok; j++) {
+                const int s = j & 1; const uint32_t ph = (j >> 1) & 1;
+                const int key0 = (nb_lo + j) * BN;
+                if (*abort_flag || !mbar_wait(&k_empty[s], ph ^ 1)) { ok = false; break; }
+                mbar_expect_tx(&k_full[s], K_BYTES);
+                for (int c = 0; c < QBOXES; c++)
+                    tma_load_2d(sK + s * K_BYTES + c * BN * 128, &map_k, &k_full[s], kvh * HD + c * 64, s0 + key0);
+                if (*abort_flag || !mbar_wait(&v_empty[s], ph ^ 1)) { ok = false; break; }
+                mbar_expect_tx(&v_full[s], VT_BYTES);
+                tma_load_2d(sVT + s * VT_BYTES, &map_vt, &v_full[s], vt0 + key0, kvh * HD);
+            }
+            if (!ok && !*abort_flag) { atomicExch(&g_attn_tc_error, 1); *abort_flag = 1; }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issue ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = instr_desc(BN), idesc_o = instr_desc(HD);
+            bool ok = mbar_wait(q_full, 0);
+            tc_fence_after();
+            const uint32_t q_addr = smem_u32(sQ);
+            auto issue_qk = [&](int j) -> bool {
+                const int s = j & 1; const uint32_t ph = (j >> 1) & 1;
+                if (*abort_flag || !mbar_wait(&k_full[s], ph) || !mbar_wait(&s_empty[s], ph ^ 1)) return false;
+                tc_fence_after();
+                const uint32_t k_addr = smem_u32(sK + s * K_BYTES);
+#pragma unroll
+                for (int ks = 0; ks < HD / UMMA_K; ks++) {
+                    const uint32_t off_q = (ks >> 2) * (BM * 128) + (ks & 3) * 32;
+                    const uint32_t off_k = (ks >> 2) * (BN * 128) + (ks & 3) * 32;
+                    umma_bf16(tmem_s + s * BN, smem_desc(q_addr + off_q), smem_desc(k_addr + off_k), idesc_s, ks > 0 ? 1u : 0u);
+                }
+                umma_commit(&k_empty[s]);             // K tile may be overwritten once these have run
+                umma_commit(&s_full[s]);              // and S is ready for the softmax
+                return true;
+            };
+            auto issue_pv = [&](int j) -> bool {
+                const int s = j & 1; const uint32_t ph = (j >> 1) & 1;
+                if (*abort_flag || !mbar_wait(&v_full[s], ph) || !mbar_wait(&p_full[s], ph)) return false;
+                tc_fence_after();
+                const uint32_t p_addr = smem_u32(sP + s * P_BYTES), v_addr = smem_u32(sVT + s * VT_BYTES);
+#pragma unroll
+                for (int ks = 0; ks < BN / UMMA_K; ks++)
+                    umma_bf16(tmem_o, smem_desc(p_addr + ks * 32), smem_desc(v_addr + ks * 32), idesc_o,
+                              (j > 0 || ks > 0) ? 1u : 0u);
+                umma_commit(&v_empty[s]);             // V^T tile and P buffer are free again; O holds blocks 0..j
+                return true;
+            };
+            if (ok) ok = issue_qk(0);
+            for (int j = 0; j < nblocks && ok; j++) {
+                if (j + 1 < nblocks) ok = issue_qk(j + 1);       // the next block's scores overlap this block's softmax
+                if (ok) ok = issue_pv(j);
+            }
+            if (!ok && !*abort_flag) { atomicExch(&g_attn_tc_error, 2); *abort_flag = 1; }
+        }
+    } else {
+        // ---------------- softmax: two threads per query row, 32 of the block's 64 keys each ----------------
+        const int sw = warp - 2;                                     // 0..7
+        const int quarter = warp & 3;                                // the TMEM lanes this warp may touch
+        const int half = sw >> 2;                                    // which 32 columns of S (and which half of O)
+        const int r = quarter * 32 + lane;                           // row of the tile = TMEM lane
+        const int i = m0 + r;                                        // position of the query in its sequence
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        const float LOG2E = 1.4426950408889634f;
+        const float sc2 = a.scale * LOG2E;                           // scores in log2 units
+        const float cap2 = a.cap * LOG2E;
+        const float cap_k = a.cap > 0.f ? 2.f * a.scale / a.cap * LOG2E : 0.f;
+        float m_ref = -INFINITY, l_sum = 0.f;                        // l_sum: this thread's half of the row sum
+        bool ok = true;
+        pdl_wait();
+        for (int j = 0; j < nblocks; j++) {
+            const int s = j & 1; const uint32_t ph = (j >> 1) & 1;
+            const bool got = !*abort_flag && mbar_wait(&s_full[s], ph);
+            if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+            tc_fence_after();
+            uint32_t raw[32];
+            tmem_ld32(tmem_s + s * BN + lane_addr + half * 32, raw);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_empty[s]);                 // this warp has read its part of S
+            // scale, cap, mask; values in log2 units
+            const int key0 = (nb_lo + j) * BN + half * 32;
+            const bool edge = (key0 + 31 > m0) || (key0 + 32 > len) || (a.window > 0 && (m0 + BM - 1) - key0 >= a.window);
+            float v[32];
+            float mx = -INFINITY;
+            if (a.cap > 0.f) {
+                // cap * tanh(x * scale / cap) = cap - 2 cap / (e^(2 x scale / cap) + 1), in log2 units; 2^(+big) is
+                // inf and its reciprocal 0, 2^(-big) is 0: both ends come out right without a clamp
+#pragma unroll
+                for (int c = 0; c < 32; c++)
+                    v[c] = fmaf(-2.f * cap2, rcpf(ex2f(__uint_as_float(raw[c]) * cap_k) + 1.f), cap2);
+            } else {
+#pragma unroll
+                for (int c = 0; c < 32; c++) v[c] = __uint_as_float(raw[c]) * sc2;
+            }
+            if (edge) {
+#pragma unroll
+                for (int c = 0; c < 32; c++) {
+                    const int jj = key0 + c;
+                    if (!(jj <= i && jj < len && (a.window <= 0 || i - jj < a.window))) v[c] = -INFINITY;
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < 32; c += 4)
+                mx = fmaxf(mx, fmaxf(fmaxf(v[c], v[c + 1]), fmaxf(v[c + 2], v[c + 3])));
+            // the row's maximum over both halves (a bounded mbarrier wait, not bar.sync: no wait here may hang)
+            row_x[j & 1][half][r] = mx;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(x_bar);
+            const bool met = mbar_wait(x_bar, j & 1);
+            if (!__all_sync(0xffffffffu, met)) { ok = false; break; }
+            mx = fmaxf(mx, row_x[j & 1][half ^ 1][r]);
+            // lazy rescaling: raise the reference only when the block's maximum is far above it
+            float factor = 1.f;
+            bool raise = mx > m_ref + RESCALE_AT;
+            if (m_ref == -INFINITY) raise = mx != -INFINITY;         // first block with a visible key
+            if (raise) {
+                factor = (m_ref == -INFINITY) ? 0.f : ex2f(m_ref - mx);
+                m_ref = mx;
+            }
+            const float mr = (m_ref == -INFINITY) ? 0.f : m_ref;
+            uint32_t pk[16];
+            float ls0 = 0.f, ls1 = 0.f;
+#pragma unroll
+            for (int c = 0; c < 32; c += 2) {
+                const float p0 = ex2f(v[c] - mr), p1 = ex2f(v[c + 1] - mr);
+                ls0 += p0; ls1 += p1;
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+                pk[c >> 1] = *(uint32_t*)&h2;
+            }
+            l_sum = l_sum * factor + (ls0 + ls1);
+            // O holds blocks before j: scale this row if its reference moved (not for the first block: the
+            // second product starts O from zero).  Each of the row's two threads scales half of the columns.
+            const bool need = raise && j > 0;
+            if (__any_sync(0xffffffffu, need)) {
+                // every MMA into O must have completed: block j-1's second product signals v_empty of its slot
+                // (block j-3's has for certain, since S of block j is there, so the parity is unambiguous)
+                const bool done = mbar_wait(&v_empty[(j - 1) & 1], ((j - 1) >> 1) & 1);
+                if (!__all_sync(0xffffffffu, done)) { ok = false; break; }
+                tc_fence_after();
+#pragma unroll 1
+                for (int c0 = half * (HD / 2); c0 < (half + 1) * (HD / 2); c0 += 32) {
+                    uint32_t ov[32];
+                    tmem_ld32(tmem_o + lane_addr + c0, ov);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 32; e++) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * factor);
+                    tmem_st32(tmem_o + lane_addr + c0, ov);
+                }
+                tmem_st_wait();
+            }
+            // P into shared memory (free once the second product of block j-2 has run)
+            const bool freep = mbar_wait(&v_empty[s], ph ^ 1);
+            if (!__all_sync(0xffffffffu, freep)) { ok = false; break; }
+            uint8_t* prow = sP + s * P_BYTES + r * 128;
+#pragma unroll
+            for (int c = 0; c < 4; c++)
+                *(uint4*)(prow + (((half * 4 + c) ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // visible to the tensor core's reads
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_full[s]);
+        }
+        if (ok) {
+            // ---- the last product has to land, then O / l goes out
+            const bool done = mbar_wait(&v_empty[(nblocks - 1) & 1], ((nblocks - 1) >> 1) & 1);
+            ok = __all_sync(0xffffffffu, done);
+        }
+        if (ok) {
+            // the two halves of the row sum meet
+            row_x[nblocks & 1][half][r] = l_sum;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(x_bar);
+            const bool met = mbar_wait(x_bar, nblocks & 1);
+            ok = __all_sync(0xffffffffu, met);
+        }
+        if (ok) {
+            tc_fence_after();
+            const float inv = 1.f / (l_sum + row_x[nblocks & 1][half ^ 1][r]);
+            bf16* orow = a.out + ((size_t)(s0 + i) * a.n_heads + h) * HD;
+#pragma unroll 1
+            for (int c0 = half * (HD / 2); c0 < (half + 1) * (HD / 2); c0 += 32) {
+                uint32_t ov[32];
+                tmem_ld32(tmem_o + lane_addr + c0, ov);
+                tmem_ld_wait();
+                if (i < len) {
+#pragma unroll
+                    for (int e = 0; e < 32; e += 8) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int k = 0; k < 4; k++) {
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(ov[e + 2 * k]) * inv,
+                                                                      __uint_as_float(ov[e + 2 * k + 1]) * inv);
+                            w[k] = *(uint32_t*)&h2;
+                        }
+                        *(uint4*)(orow + c0 + e) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+        }
+        if (!ok && !*abort_flag && lane == 0) { atomicExch(&g_attn_tc_error, 3); *abort_flag = 1; }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// v [T, kv_stride] (token rows) -> vt [n_kv_heads * HD, vt_cols]: sequence b's keys at columns
+// vt_start[b] .. vt_start[b] + len_b, zero up to the next multiple of 64.
+__global__ void transpose_v_kernel(const bf16* __restrict__ v, long long kv_stride, bf16* __restrict__ vt, long long vt_cols,
+                                   const int* __restrict__ seq_start, const int* __restrict__ vt_start, int width) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ bf16 tile[32][33];
+    const int b = blockIdx.z;
+    const int s0 = seq_start[b], len = seq_start[b + 1] - s0;
+    const int c0 = vt_start[b], cols = vt_start[b + 1] - c0;          // padded key count of this sequence
+    const int k0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
+    if (k0 >= cols) return;
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int key = k0 + r, d = d0 + threadIdx.x;
+        tile[r][threadIdx.x] = (key < len && d < width) ? v[(size_t)(s0 + key) * kv_stride + d] : __float2bfloat16(0.f);
+    }
+    __syncthreads();
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int d = d0 + r, key = k0 + threadIdx.x;
+        if (d < width && key < cols) vt[(size_t)d * vt_cols + c0 + key] = tile[threadIdx.x][r];
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+static int make_map(CUtensorMap* m, const void* base, long long rows, long long cols, long long ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return tb_refuse("attn_prefill_tc: the driver does not provide cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return tb_refuse("attn_prefill_tc: cuTensorMapEncodeTiled failed with %d", (int)r);
+    return 0;
+}
+
+extern "C" int tb_attn_prefill_tc_head_dim() { return HD; }
+
+// vt: scratch of n_kv_heads * HD rows x vt_cols columns (bfloat16), vt_cols a multiple of 64 that holds every
+// sequence rounded up to 64 keys; vt_start [batch + 1] on the device, multiples of 64.
+extern "C" int tb_attn_prefill_tc(const void* q, const void* k, const void* v, long long q_stride, long long kv_stride,
+                                  const int* seq_start, const int* vt_start, void* vt, long long vt_cols, void* out,
+                                  int n_tokens, int batch, int max_seq_len, int n_heads, int n_kv_heads, int hd,
+                                  float scale, float cap, int window, cudaStream_t stream) {
+    if (batch <= 0 || max_seq_len <= 0) return 0;
+    if (hd != HD) return tb_refuse("attn_prefill_tc: this library is built for head_dim %d, got %d", HD, hd);
+    if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads)
+        return tb_refuse("attn_prefill_tc: %d heads cannot share %d kv heads", n_heads, n_kv_heads);
+    if (((uintptr_t)q & 15) || ((uintptr_t)k & 15) || ((uintptr_t)v & 15) || ((uintptr_t)vt & 15) || (q_stride % 8) ||
+        (kv_stride % 8) || (vt_cols % 64))
+        return tb_refuse("attn_prefill_tc: q, k, v rows must be 16-byte aligned and vt_cols a multiple of 64");
+    if (n_heads > 65535 || batch > 65535) return tb_refuse("attn_prefill_tc: %d heads x %d sequences exceed one launch", n_heads, batch);
+    const int kvw = n_kv_heads * HD;
+    {
+        dim3 grid((unsigned)((max_seq_len + 63) / 64 * 2), (kvw + 31) / 32, batch);
+        tb_launch(transpose_v_kernel, grid, dim3(32, 8), 0, stream, (const bf16*)v, kv_stride, (bf16*)vt, vt_cols,
+                  seq_start, vt_start, kvw);
+        int st = tb_launch_status();
+        if (st) return st;
+    }
+    CUtensorMap mq, mk, mvt;
+    if (make_map(&mq, q, n_tokens, (long long)n_heads * HD, q_stride, BM) ||
+        make_map(&mk, k, n_tokens, kvw, kv_stride, BN) ||
+        make_map(&mvt, vt, kvw, vt_cols, vt_cols, HD))
+        return -1;
+    PrefillTcArgs a;
+    a.seq_start = seq_start; a.vt_start = vt_start; a.out = (bf16*)out;
+    a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.window = window; a.scale = scale; a.cap = cap;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    dim3 grid((max_seq_len + BM - 1) / BM, n_heads, batch);
+    tb_launch(attn_prefill_tc_kernel, grid, dim3(320), SMEM_BYTES, stream, mq, mk, mvt, a);
+    return tb_launch_status();
+}
+
+extern "C" int tb_attn_prefill_tc_error() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_attn_tc_error, sizeof(int)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_attn_tc_error, &zero, sizeof(int));
+    return v;
+}

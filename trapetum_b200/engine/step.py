@@ -41,6 +41,7 @@ class StepContext:
     max_len_after: int
     len_bucket: int = 0              # a power of two >= max_len_after: what launch shapes may depend on
     step_kv: Dict[int, tuple] = field(default_factory=dict)   # prefill: entry -> (k, v) of this step
+    memo: Dict[str, object] = field(default_factory=dict)     # small per-step values that kernels share across layers
 
 
 def _align4(n: int) -> int:

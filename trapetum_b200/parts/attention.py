@@ -67,7 +67,9 @@ class Attention(Mixer):
 
     def kernel_files(self):
         fast = ("attention_decode",) if ops.attn_decode_takes(self.rt.dtype, self.n_heads, self.n_kv, self.hd) else ()
-        if ops.attn_prefill_takes(self.rt.dtype, self.hd):
+        if ops.attn_prefill_tc_takes(self.rt.dtype, self.hd):
+            fast += (ops.attn_prefill_tc_lib(self.hd),)
+        elif ops.attn_prefill_takes(self.rt.dtype, self.hd):
             fast += (ops.attn_prefill_lib(self.hd),)
         return linear_kernels(self.rt.dtype) + self.position.kernel_files() + ("attention_simt",) + fast
 
@@ -97,7 +99,7 @@ class Attention(Mixer):
             k, v = ctx.step_kv[line.entry] if ctx.is_prefill else (None, None)
         if ctx.is_prefill:
             o = ops.attn_prefill(q, k, v, ctx.seq_start, ctx.token_seq, self.n_heads, self.n_kv, self.hd,
-                                 self.scale, self.softcap, self.window or 0, ctx.max_seq_len)
+                                 self.scale, self.softcap, self.window or 0, ctx.max_seq_len, ctx.seq_lens, ctx.memo)
         else:
             o = ops.attn_decode(q, line.k, line.v, line.page_table, ctx.len_after, self.n_heads, self.n_kv,
                                 self.hd, self.scale, self.softcap, self.window or 0, line.ring_rows, ctx.len_bucket)
