@@ -88,6 +88,23 @@ def test_add_rmsnorm(ops, adt, odt, rows, width):
     close(h, h0 + af, torch.float32)
 
 
+@pytest.mark.parametrize("odt", DT)
+@pytest.mark.parametrize("rows,width", [(64, 2304), (100, 3584), (65, 4608), (300, 520), (70, 72), (64, 5120)])
+def test_add_rmsnorm_many_rows(ops, odt, rows, width):
+    """Many rows take the warp-per-row kernel (32-bit branch, bfloat16 weights); same numbers as the formula."""
+    h0, a = rnd(rows, width, s=2.0), rnd(rows, width, s=5.0, seed=1)
+    wa, wb = rnd(width, dt=torch.bfloat16, s=0.2, seed=2), rnd(width, dt=torch.bfloat16, s=0.2, seed=3)
+    add = a * torch.rsqrt((a * a).mean(-1, keepdim=True) + 1e-6) * (1.0 + wa.float())
+    hn = h0 + add
+    h = h0.clone()
+    x = ops.add_rmsnorm(h, a, wa, 1e-6, 1.0, wb, 1e-5, 1.0, odt)
+    close(h, hn, torch.float32, 2.0)
+    close(x, hn * torch.rsqrt((hn * hn).mean(-1, keepdim=True) + 1e-5) * (1.0 + wb.float()), odt, 2.0)
+    h = h0.clone()
+    assert ops.add_rmsnorm(h, a, wa, 1e-6, 1.0) is None
+    close(h, hn, torch.float32, 2.0)
+
+
 @pytest.mark.parametrize("rows,width,splits", [(8, 2304, 8), (3, 72, 2), (1, 12000, 5)])
 def test_add_rmsnorm_from_partial_sums(ops, rows, width, splits):
     part = rnd(splits, rows, width, s=2.0)

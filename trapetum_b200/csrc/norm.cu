@@ -153,6 +153,60 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TA* __restrict__
     }
 }
 
+// Many rows (prefill): one warp per row, the row held in registers (NV float4 per lane), no shared memory and
+// no block-wide barrier.  32-bit branch input (one partial sum), bfloat16 weights: the engine's hot case.
+template <typename TO, int NV>
+__global__ void __launch_bounds__(256) add_rmsnorm_rows_kernel(float* __restrict__ h, const float* __restrict__ a,
+                                                               const bf16* __restrict__ wa, float eps_a, float off_a,
+                                                               const bf16* __restrict__ wb, float eps_b, float off_b,
+                                                               TO* __restrict__ out, int rows, int width) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const size_t base = (size_t)row * width;
+    float v[NV][4];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; k++) {
+        const int i = (k * 32 + lane) * 4;
+        if (i < width) {
+            Vec4<float>::load(a + base + i, v[k]);
+            ss += v[k][0] * v[k][0] + v[k][1] * v[k][1] + v[k][2] * v[k][2] + v[k][3] * v[k][3];
+        }
+    }
+    ss = warp_sum(ss);
+    const float ra = rsqrtf(ss / (float)width + eps_a);
+    float s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; k++) {
+        const int i = (k * 32 + lane) * 4;
+        if (i < width) {
+            float hv[4], g[4];
+            Vec4<float>::load(h + base + i, hv);
+            Vec4<bf16>::load(wa + i, g);
+#pragma unroll
+            for (int e = 0; e < 4; e++) { v[k][e] = hv[e] + v[k][e] * ra * (off_a + g[e]); s2 += v[k][e] * v[k][e]; }
+            Vec4<float>::store(h + base + i, v[k]);
+        }
+    }
+    if (out == nullptr) return;
+    s2 = warp_sum(s2);
+    const float rb = rsqrtf(s2 / (float)width + eps_b);
+#pragma unroll
+    for (int k = 0; k < NV; k++) {
+        const int i = (k * 32 + lane) * 4;
+        if (i < width) {
+            float g[4], y[4];
+            Vec4<bf16>::load(wb + i, g);
+#pragma unroll
+            for (int e = 0; e < 4; e++) y[e] = v[k][e] * rb * (off_b + g[e]);
+            Vec4<TO>::store(out + base + i, y);
+        }
+    }
+}
+
 static int norm_threads(int width, int vec) {
     int t = ((width + vec - 1) / vec + 31) / 32 * 32;      // one access per thread and pass, if a block holds it
     return t < 64 ? 64 : (t > 1024 ? 1024 : t);
@@ -209,6 +263,21 @@ extern "C" int tb_add_rmsnorm(float* h, const void* a, int a_dtype, int n_splits
     const size_t smem = row_cache ? (size_t)width * sizeof(float) : 0;
     const bool vec = width % 4 == 0 && split_stride % 4 == 0 && aligned16(h) && aligned16(a) && aligned16(wa) &&
                      aligned16(wb) && aligned16(out);
+    if (vec && rows >= 64 && n_splits == 1 && a_dtype == TB_F32 && w_dtype == TB_BF16 && width <= 40 * 128) {
+        // one warp per row, the row in registers
+        const int nv = (width / 4 + 31) / 32;
+        const unsigned blocks = (unsigned)((rows + 7) / 8);
+#define ROWS(NV_)                                                                                                  \
+        do {                                                                                                       \
+            if (out_dtype == TB_BF16) tb_launch(add_rmsnorm_rows_kernel<bf16, NV_>, dim3(blocks), dim3(256), 0, stream, \
+                h, (const float*)a, (const bf16*)wa, eps_a, off_a, (const bf16*)wb, eps_b, off_b, (bf16*)out, rows, width); \
+            else tb_launch(add_rmsnorm_rows_kernel<float, NV_>, dim3(blocks), dim3(256), 0, stream,                  \
+                h, (const float*)a, (const bf16*)wa, eps_a, off_a, (const bf16*)wb, eps_b, off_b, (float*)out, rows, width); \
+        } while (0)
+        if (nv <= 8) ROWS(8); else if (nv <= 16) ROWS(16); else if (nv <= 24) ROWS(24); else if (nv <= 32) ROWS(32); else ROWS(40);
+#undef ROWS
+        return tb_launch_status();
+    }
     if (vec)
         DISPATCH3(a_dtype, w_dtype, out_dtype,
             tb_launch(add_rmsnorm_kernel<TX, TW, TO, 4>, dim3(rows), dim3(norm_threads(width, 4)), smem, stream,
