@@ -1,7 +1,8 @@
-"""The kernels at the layer sizes of Gemma-2-2B (head_dim 256, 8 heads over 4 kv heads, hidden 2304,
-intermediate 9216, vocabulary 256000), two layers, random weights: the engine in bfloat16 and in true
-32-bit against the plain implementation.  The tiny models never reach the tensor-core tile sizes, the
-split-K paths or the 256-wide heads that the real sizes use."""
+"""The kernels at the layer sizes of Gemma-2-2B, 9B and 27B, two layers each, random weights: the engine in
+bfloat16 and in true 32-bit against the plain implementation.  The tiny models never reach the tensor-core
+tile sizes, the split-K paths or the 128- and 256-wide heads that the real sizes use.  2B keeps the real
+vocabulary (256000); 9B and 27B use a smaller one so that the oracle's output product stays quick on a CPU.
+27B has query_pre_attn_scalar (144) different from head_dim (128)."""
 import pytest
 import torch
 
@@ -10,36 +11,49 @@ from conftest import TOL, bf16_budget, make_prompts, rel_l2, sharpen
 
 pytestmark = pytest.mark.gpu
 
-CFG = {
-    "architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2", "num_hidden_layers": 2, "hidden_size": 2304,
-    "num_attention_heads": 8, "num_key_value_heads": 4, "head_dim": 256, "intermediate_size": 9216,
-    "vocab_size": 256000, "rope_theta": 10000.0, "sliding_window": 96, "query_pre_attn_scalar": 256,
-    "attn_logit_softcapping": 50.0, "final_logit_softcapping": 30.0, "rms_norm_eps": 1e-6,
-    "hidden_activation": "gelu_pytorch_tanh", "tie_word_embeddings": True, "max_position_embeddings": 8192,
+BASE = {
+    "architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2", "num_hidden_layers": 2,
+    "rope_theta": 10000.0, "sliding_window": 96, "attn_logit_softcapping": 50.0, "final_logit_softcapping": 30.0,
+    "rms_norm_eps": 1e-6, "hidden_activation": "gelu_pytorch_tanh", "tie_word_embeddings": True,
+    "max_position_embeddings": 8192,
 }
+SHAPES = {
+    "2b": dict(BASE, hidden_size=2304, num_attention_heads=8, num_key_value_heads=4, head_dim=256,
+               intermediate_size=9216, vocab_size=256000, query_pre_attn_scalar=256),
+    "9b": dict(BASE, hidden_size=3584, num_attention_heads=16, num_key_value_heads=8, head_dim=256,
+               intermediate_size=14336, vocab_size=32000, query_pre_attn_scalar=256),
+    "27b": dict(BASE, hidden_size=4608, num_attention_heads=32, num_key_value_heads=16, head_dim=128,
+                intermediate_size=36864, vocab_size=32000, query_pre_attn_scalar=144),
+}
+SEEDS = {"2b": 2, "9b": 3, "27b": 4}
 
 
 @pytest.fixture(scope="module")
-def folder(tmp_path_factory):
+def models(tmp_path_factory):
+    """shape name -> (folder, config, weights, prompts, oracle logits), made on first use."""
     import trapetum_b200 as tb
-    d = str(tmp_path_factory.mktemp("real_sizes"))
-    tb.write_random_model(d, CFG, seed=2, std=0.02, norm_std=0.1)
-    sharpen(d, 2.0)
-    return d
+    made = {}
 
-
-@pytest.fixture(scope="module")
-def truth(folder):
-    cfg, w = plain.load_folder(folder)
-    prompts = make_prompts(CFG["vocab_size"], [150, 37, 220], seed=4)
-    return cfg, w, prompts, [plain.forward(cfg, w, p) for p in prompts]
+    def get(name):
+        if name not in made:
+            d = str(tmp_path_factory.mktemp("real_" + name))
+            tb.write_random_model(d, SHAPES[name], seed=SEEDS[name], std=0.02, norm_std=0.1)
+            sharpen(d, 2.0)
+            # float64: with inner sizes of up to 36864 the oracle's own rounding in float32 would be as large
+            # as the 32-bit engine's, and the oracle has to be the more exact of the two
+            cfg, w = plain.load_folder(d, dtype=torch.float64)
+            prompts = make_prompts(cfg["vocab_size"], [150, 37, 220], seed=4)
+            made[name] = (d, cfg, w, prompts, [plain.forward(cfg, w, p) for p in prompts])
+        return made[name]
+    return get
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_logits_at_real_layer_sizes(folder, truth, dtype):
+@pytest.mark.parametrize("shape", ["2b", "9b", "27b"])
+def test_logits_at_real_layer_sizes(models, shape, dtype):
     import trapetum_b200 as tb
     from trapetum_b200.csrc import ops
-    cfg, w, prompts, want = truth
+    folder, cfg, w, prompts, want = models(shape)
     tol = TOL["float32"] if dtype == "float32" else bf16_budget(cfg, w, prompts[:1])
     model = tb.load_model(folder, dtype)
     eng = tb.Engine(model, max_tokens=64 * 12)

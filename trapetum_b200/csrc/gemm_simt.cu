@@ -6,8 +6,9 @@
 // 32-bit weights).  Weights are [out, in] as the checkpoint stores them, so a
 // row of W is one output column's dot-product vector, like the reference's
 // dense GEMV (runtime/cuda/codebook_gemv.cu:482-517).  Products and sums are
-// 32-bit; each C element adds its K terms in ascending k whatever M and N are,
-// so a token's result does not depend on what else is in the batch.
+// 32-bit; each C element adds its K terms in the same order whatever M and N are
+// (k-tiles of 16 in ascending order, each tile summed on its own first), so a
+// token's result does not depend on what else is in the batch.
 // Optional epilogue: tanh soft cap (the final logit cap, runtime/src/lib.rs:4559-4560).
 #include "common.cuh"
 
@@ -44,6 +45,13 @@ gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restr
             Ws[lk + j][lr] = (n < N && k < K) ? to_f<TW>(W[(size_t)n * ldw + k]) : 0.f;
         }
         __syncthreads();
+        // blocked summation: the 16 products of a k-tile are added up on their own and the tile's sum is then
+        // added to the running total, so that rounding errors grow with K/16 + 16 terms instead of K
+        float part[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) part[i][j] = 0.f;
 #pragma unroll
         for (int k = 0; k < BK; k++) {
             float a[4], w[4];
@@ -54,8 +62,12 @@ gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restr
 #pragma unroll
             for (int i = 0; i < 4; i++)
 #pragma unroll
-                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+                for (int j = 0; j < 4; j++) part[i][j] = fmaf(a[i], w[j], part[i][j]);
         }
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) acc[i][j] += part[i][j];
         __syncthreads();
     }
 #pragma unroll
