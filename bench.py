@@ -272,9 +272,9 @@ def main() -> int:
         out["prefill"] = {"value": round(PREFILL_TOKENS * 1e3 / pms, 1), "tokens": PREFILL_TOKENS, "ms": round(pms, 3),
                           "frac": round(fl / (pms * 1e-3) / (bf16_tflops * 1e12), 4), "of": peak_src}
     from trapetum_b200.csrc import ops
-    err = ops.gemm_tc_error()
+    err = ops.kernel_errors()
     if err:
-        out["error"] = f"a bounded wait ran out in the tensor-core GEMM (role {err})"
+        out["error"] = f"a bounded wait ran out: {err}"
     print(json.dumps(out))
     return 0
 

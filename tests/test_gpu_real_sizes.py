@@ -76,4 +76,4 @@ def test_logits_at_real_layer_sizes(models, shape, dtype):
             assert e <= tol, f"{dtype}: request {r} decoded token {t}: {e:.3e} > {tol:.1e}"
     eng.release(s)
     torch.cuda.synchronize()
-    assert ops.gemm_tc_error() == 0 and ops.attn_decode_error() == 0
+    assert ops.kernel_errors() == {}

@@ -166,6 +166,11 @@ def load(name: str) -> ctypes.CDLL:
         return lib
 
 
+def loaded() -> List[str]:
+    """Names of the kernel libraries this process has loaded so far."""
+    return list(_libs)
+
+
 def build_all() -> List[str]:
     require(SOURCES)
     return [library_path(n) for n in SOURCES]

@@ -484,6 +484,23 @@ def sum_partials(part: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def kernel_errors() -> dict:
+    """Error words of the kernels with bounded waits that this process has loaded: {} when no wait ever ran
+    out.  Synchronises the device and clears the words."""
+    out = {}
+    loaded = build.loaded()
+    if "gemm_tc" in loaded and gemm_tc_error():
+        out["gemm_tc"] = "a bounded wait ran out"
+    if "attention_decode" in loaded and attn_decode_error():
+        out["attention_decode"] = "a bounded wait ran out"
+    for name in loaded:
+        if name.startswith("attention_prefill_tc@"):
+            v = int(build.load(name).tb_attn_prefill_tc_error())
+            if v:
+                out[name] = f"error word {v}"
+    return out
+
+
 def gemm_tc_error() -> int:
     """Reads and clears the tensor-core GEMM's error word (synchronises): 0, or the role whose
     bounded wait ran out (1 loader, 2 MMA issuer, 3 epilogue)."""
