@@ -9,7 +9,7 @@
 //     heads of the group from one read of K and V;
 //   * pages (64 keys x head_dim, contiguous in the pool) are brought into shared
 //     memory by bulk copies of the TMA unit, several pages ahead, tracked by mbarriers;
-//   * each of the 8 warps takes 8 keys of a page; a key's head_dim is spread over
+//   * each of the 16 warps takes 4 keys of a page; a key's head_dim is spread over
 //     head_dim/8 lanes (16 bytes each); partial dot products are reduced with a
 //     butterfly that leaves one (key, head) score per lane, so cap, exp and the
 //     running softmax are computed once per score;
@@ -29,8 +29,6 @@
 TB_EXPORT_ERROR()
 
 #define PAGE 64
-#define NWARP 8
-#define KPW (PAGE / NWARP)          // keys of a page per warp
 
 __device__ int g_attn_error = 0;
 
@@ -46,6 +44,8 @@ struct DecodeArgs {
 };
 
 template <int HD> struct DCfg {
+    static constexpr int NWARP = HD >= 64 ? 16 : 8;                  // more warps hide more latency; a warp needs
+    static constexpr int KPW = PAGE / NWARP;                         // at least one pass of 256 / HD keys per page
     static constexpr int PAGE_BYTES = PAGE * HD * 2;                 // one page of K (or V) for one kv head
     static constexpr int STAGE_BYTES = 2 * PAGE_BYTES;
     static constexpr int STAGES_RAW = (192 * 1024) / STAGE_BYTES;
@@ -63,9 +63,10 @@ __device__ __forceinline__ void bf16x8_to_f32(const uint4& w, float* f) {
 }
 
 template <int HD, int G>
-__global__ void __launch_bounds__(NWARP * 32, 1) attn_decode_kernel(DecodeArgs a) {
+__global__ void __launch_bounds__(DCfg<HD>::NWARP * 32, 1) attn_decode_kernel(DecodeArgs a) {
     pdl_launch_dependents();
     using C = DCfg<HD>;
+    constexpr int NWARP = C::NWARP, KPW = C::KPW;
     constexpr int LPK = HD / 8;                    // lanes per key
     constexpr int KP = 32 / LPK;                   // keys per pass of a warp
     constexpr int NP = KPW / KP;                   // passes per page
@@ -660,7 +661,7 @@ static int launch(const DecodeArgs& a, int batch, cudaStream_t stream) {
         attr_set = true;
     }
     dim3 grid(batch, a.n_kv_heads, a.n_splits);
-    tb_launch(kern, dim3(grid), dim3(NWARP * 32), C::SMEM, stream, a);
+    tb_launch(kern, dim3(grid), dim3(C::NWARP * 32), C::SMEM, stream, a);
     return tb_launch_status();
 }
 
