@@ -166,12 +166,11 @@ def time_decode(engine, torch, batch, ctx, steps, warmup, vocab, sampler=None):
         # end to end: host token lists in, chosen token ids out, each step feeding the next
         cur = next(it)
         for _ in range(warmup):
-            cur = ops.argmax(engine.step(slots, [[t] for t in cur], borrow=True)).cpu().tolist()
+            cur = engine.step(slots, [[t] for t in cur], borrow=True, greedy=True).cpu().tolist()
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         for _ in range(steps):
-            logits = engine.step(slots, [[t] for t in cur], borrow=True)
-            cur = ops.argmax(logits).cpu().tolist()
+            cur = engine.step(slots, [[t] for t in cur], borrow=True, greedy=True).cpu().tolist()
         torch.cuda.synchronize()
         e2e_ms = (time.perf_counter() - t0) * 1e3 / steps
         shape = next((d for (b, _), d in engine._decode.items() if b == batch), None)

@@ -78,11 +78,14 @@ class Engine:
 
     # -- the step -------------------------------------------------------------------
     def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],
-             want: Optional[Sequence[Sequence[int]]] = None, borrow: bool = False) -> Optional[torch.Tensor]:
+             want: Optional[Sequence[Sequence[int]]] = None, borrow: bool = False,
+             greedy: bool = False) -> Optional[torch.Tensor]:
         """Run one step; returns float32 logits [wanted, vocab] on the device (None if nothing is wanted).
 
         ``borrow=True`` lets the result alias a buffer that the next step overwrites (the generation
-        loop consumes the logits at once and saves the copy)."""
+        loop consumes the logits at once and saves the copy).  ``greedy=True`` returns, instead of the
+        logits, the int32 ids of the largest logit at each wanted place (the smallest id on a tie),
+        chosen on the device; in a decode step the choice is part of the captured graph."""
         slots = list(slots)
         is_prefill = classify(self.cache, slots, tokens)
         B = len(slots)
@@ -105,7 +108,7 @@ class Engine:
         self.cache.grow({s: n for s, n in zip(slots, lens)})          # raises CacheFull before anything ran
         after = [b + n for b, n in zip(before, lens)]
         if not is_prefill and self.use_graphs and self._graph_safe:
-            return self._decode_step(slots, tokens, want, before, after, borrow)
+            return self._decode_step(slots, tokens, want, before, after, borrow, greedy)
 
         T = sum(lens)
         starts = np.zeros(B + 1, dtype=np.int32)
@@ -136,7 +139,8 @@ class Engine:
             self.model.forward(dev["ids"], ctx, self.cache, dev["want"][:0])
             return None
         all_rows = n_want == T and bool((arrays["want"] == np.arange(T)).all())
-        return self.model.forward(dev["ids"], ctx, self.cache, None if all_rows else dev["want"])
+        logits = self.model.forward(dev["ids"], ctx, self.cache, None if all_rows else dev["want"])
+        return ops.argmax(logits) if greedy else logits
 
     def _table(self, gi: int, slots: Sequence[int], width: int) -> np.ndarray:
         tab = np.zeros((len(slots), width), dtype=np.int32)
@@ -146,7 +150,7 @@ class Engine:
         return tab
 
     # -- one token per sequence, as a CUDA graph ---------------------------------------
-    def _decode_step(self, slots, tokens, want, before, after, borrow):
+    def _decode_step(self, slots, tokens, want, before, after, borrow, greedy=False):
         """A decode step's launches do not depend on the tokens, the positions or the pages, only on
         the batch size and on the bucket of the longest context: the inputs live in buffers of a fixed layout,
         the first step of a shape runs eagerly (it also sets up every kernel), the second is captured
@@ -167,21 +171,25 @@ class Engine:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, pool=self._graph_pool):
                 dg.logits = self.model.forward(dg.dev["ids"], ctx, self.cache, None)
+                dg.greedy = ops.argmax(dg.logits)      # the greedy choice rides along in the graph
             dg.graph = graph
         if dg.graph is not None:
             dg.graph.replay()
-            logits = dg.logits
+            logits, ids = dg.logits, dg.greedy
             ops.count_launches(dg.n_kernels)
         else:
             n0 = ops.launches()
             logits = self.model.forward(dg.dev["ids"], dg.context(slots, max_after), self.cache, None)
+            ids = ops.argmax(logits)
             dg.n_kernels = ops.launches() - n0
         rows = [i for i, w in enumerate(want) for _ in w]
         if not rows:
             return None
         if rows == list(range(B)):
-            return logits if (borrow or dg.graph is None) else logits.clone()
-        return ops.gather_rows(logits, torch.tensor(rows, dtype=torch.int32, device=self.rt.device))
+            out = ids if greedy else logits
+            return out if (borrow or dg.graph is None) else out.clone()
+        idx = torch.tensor(rows, dtype=torch.int32, device=self.rt.device)
+        return ops.argmax(ops.gather_rows(logits, idx)) if greedy else ops.gather_rows(logits, idx)
 
 
 class _DecodeShape:
@@ -191,7 +199,9 @@ class _DecodeShape:
         self.B, self.bucket = B, bucket
         self.graph = None
         self.logits = None
+        self.greedy = None
         self.hits = 0
+        self._tables_of = None                # (slots, page counts) the device tables were last written for
         self.n_kernels = 0
         cache = engine.cache
         cap = min(engine.model.spec.max_positions, cache.max_tokens)
@@ -221,11 +231,16 @@ class _DecodeShape:
         hv["positions"][:] = before
         hv["len_after"][:] = after
         hv["slot_ids"][:] = slots
-        for gi, w in enumerate(self.widths):
-            t = hv[f"table{gi}"]
-            for i, s in enumerate(slots):
-                pg = engine.cache.pages(s, gi)
-                t[i, :len(pg)] = pg
+        # the page tables change only when the batch's slots change or a sequence takes a new page
+        cache = engine.cache
+        key = (tuple(slots), tuple(len(cache.pages(s, gi)) for gi in range(len(self.widths)) for s in slots))
+        if key != self._tables_of:
+            self._tables_of = key
+            for gi, w in enumerate(self.widths):
+                t = hv[f"table{gi}"]
+                for i, s in enumerate(slots):
+                    pg = cache.pages(s, gi)
+                    t[i, :len(pg)] = pg
         self.buf.copy_(self.host, non_blocking=True)
         self.copied = torch.cuda.Event()
         self.copied.record()

@@ -99,6 +99,7 @@ def generate(model_or_engine, prompts: Sequence[Sequence[int]], max_tokens: int 
     if max_tokens == 0 or not prompts:
         return outputs
     sampler = Sampler(params, engine.rt.device)
+    greedy = not params.needs_sampler           # the engine then picks the token itself, on the device
     batches = plan_batches([len(p) for p in prompts], max_tokens, min(max_batch, engine.cache.max_slots),
                            engine.cache.max_tokens, spec.max_positions)
     for batch in batches:
@@ -107,7 +108,7 @@ def generate(model_or_engine, prompts: Sequence[Sequence[int]], max_tokens: int 
         try:
             for q in live:
                 sampler.begin(q.request, prompts[q.request])
-            logits = engine.step([q.slot for q in live], [prompts[q.request] for q in live], borrow=True)
+            logits = engine.step([q.slot for q in live], [prompts[q.request] for q in live], borrow=True, greedy=greedy)
             for q in live:
                 q.length = len(prompts[q.request])
             while live:
@@ -127,7 +128,7 @@ def generate(model_or_engine, prompts: Sequence[Sequence[int]], max_tokens: int 
                         engine.release([q.slot])
                 live = nxt
                 if live:
-                    logits = engine.step([q.slot for q in live], [[q.new[-1]] for q in live], borrow=True)
+                    logits = engine.step([q.slot for q in live], [[q.new[-1]] for q in live], borrow=True, greedy=greedy)
                     for q in live:
                         q.length += 1
         except BaseException:

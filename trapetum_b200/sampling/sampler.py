@@ -37,9 +37,12 @@ class Sampler:
 
     def choose(self, logits: torch.Tensor, requests: Sequence[int]) -> List[int]:
         """``logits`` float32 [rows, vocab] on the device, row i for ``requests[i]``; returns the
-        chosen ids (host) and records them in the penalty windows."""
+        chosen ids (host) and records them in the penalty windows.  If the engine already made the
+        greedy choice on the device (``Engine.step(greedy=True)``), ``logits`` is that int32 tensor."""
         p = self.params
-        if not p.needs_sampler:
+        if logits.dtype == torch.int32:
+            ids = logits
+        elif not p.needs_sampler:
             ids = ops.argmax(logits)
         else:
             rows = len(requests)
