@@ -173,7 +173,7 @@ def time_decode(engine, torch, batch, ctx, steps, warmup, vocab, sampler=None):
             cur = engine.step(slots, [[t] for t in cur], borrow=True, greedy=True).cpu().tolist()
         torch.cuda.synchronize()
         e2e_ms = (time.perf_counter() - t0) * 1e3 / steps
-        shape = next((d for (b, _), d in engine._decode.items() if b == batch), None)
+        shape = next((d for key, d in engine._decode.items() if key[0] == batch), None)
         h2d = shape.h2d_bytes if shape is not None else 0
         return dev_ms, e2e_ms, launches, h2d
     finally:

@@ -257,6 +257,14 @@ def decode_impls(ops, dt, nh, nkv, hd):
     impls = [ops.attn_decode_simt]
     if ops.attn_decode_takes(dt, nh, nkv, hd):
         impls.append(ops.attn_decode_tma)
+        if ops.attn_decode_stream_takes(dt, nh, nkv, hd, 64):
+            # the stream partition, with CTA counts that leave parts of a sequence to several CTAs, one page to
+            # each CTA (more CTAs than pages), and everything to one CTA; `splits` is not used by it
+            for n_ctas in (None, 7, 1, 1000):
+                def stream(q, kp, vp, table, la, nh, nkv, hd, scale, cap, window, ring, splits, n_ctas=n_ctas):
+                    return ops.attn_decode_stream(q, kp, vp, table, la, nh, nkv, hd, scale, cap, window, ring, n_ctas)
+                stream.__name__ = f"attn_decode_stream[{n_ctas}]"
+                impls.append(stream)
         if nh // nkv in (1, 2, 4, 8):
             lanes = functools.partial(ops.attn_decode_tma, variant="lanes")
             lanes.__name__ = "attn_decode_lanes"

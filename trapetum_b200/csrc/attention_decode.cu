@@ -41,6 +41,8 @@ struct DecodeArgs {
     float* partial;
     int n_heads, n_kv_heads, hd, page_rows, ring_rows, window, n_splits;
     float scale, cap;
+    int* tickets;                 // [B, n_kv_heads] zeros, or null: with it the tensor-core kernel folds its
+                                  // splits itself (the last CTA to finish) and leaves the counters at zero
 };
 
 template <int HD> struct DCfg {
@@ -321,18 +323,36 @@ __global__ void __launch_bounds__(DCfg<HD>::NWARP * 32, 1) attn_decode_kernel(De
 }
 
 // ---------------------------------------------------------------------------
-// Tensor-core variant: the group's query heads are the first rows of a 16-row MMA tile.
+// Tensor-core variant: a page's 64 keys are the rows of the MMA tiles, the group's query heads
+// (up to 8) their 8 columns.
 //
-// Q.K^T and P.V run as mma.sync m16n8k16 (bfloat16 operands, 32-bit accumulators): per page of
-// 64 keys a warp issues 64 MMAs instead of some 600 scalar instructions, so the kernel's time
-// is the time of its page copies.  A page arrives as head_dim/64 tiled TMA copies of 64 keys x
-// 64 dims with the 128-byte swizzle (8 KB each), the layout in which every ldmatrix is
-// conflict-free; a dense copy would put all rows of a page on the same banks.  Each of the
-// 4 warps owns 16 keys of a page for both products and keeps its own running softmax; the warps
-// are folded at the end.  Rows of a page that are not keys of the sequence get their scores
-// masked and their V rows zeroed in shared memory before use.
+//   S^T = K Q^T   [64 keys x 8 heads]:  A = K rows as they lie in the page, B = Q held in registers
+//   O^T = V^T P^T [head_dim x 8 heads]: A = V read through ldmatrix.trans, B = P^T built in registers
+//
+// as mma.sync m16n8k16 (bfloat16 operands, 32-bit accumulators).  With keys on the 16-row side no
+// MMA row is wasted on padding, so a page costs head_dim/2 MMAs and as many ldmatrix for the whole
+// CTA instead of some 5,000 scalar instructions, and the kernel's time is the time of its page
+// copies.  A page arrives as head_dim/64 tiled TMA copies of 64 keys x 64 dims with the 128-byte
+// swizzle (8 KB each), the layout in which every ldmatrix is conflict-free.  Per page the 8 warps
+// run three short phases with a CTA barrier between them:
+//   A  warp (m-tile, half of head_dim) multiplies its 16 keys with its half of the dims and leaves
+//      the partial scores in shared memory;
+//   B  one thread per (key, head) adds the two halves, applies scale, cap and the validity mask,
+//      leaves the final score in shared memory; each warp leaves the maximum of its 32 keys;
+//   C  every warp owns head_dim/8 dims of O^T: it reads the page's maxima and scores, updates the
+//      running maximum and sum (identically in all warps), and multiplies its slice of V^T with P^T.
+// The stage of page i is refilled once every warp has passed phase A of page i+1.  Rows of a page
+// that are not keys of the sequence get -inf scores, and their V rows are zeroed in shared memory
+// before use (0 * NaN would still poison O).
+//
+// Before griddepcontrol.wait the kernel already fetches pages that this step does not write (all
+// but the one that takes the new token): they were complete before the step began.
+//
+// Splits write (max, sum, O) partials; the CTA that finishes last for a (sequence, kv head), found
+// with a ticket counter, folds them in split order, so the sum does not depend on which CTA that is.
 // ---------------------------------------------------------------------------
-#define MW 4                                       // warps per CTA
+#define TW 8                                       // warps per CTA
+#define SROW 72                                    // floats between heads in the score arrays (64 keys + 8: no bank conflicts)
 template <int HD> struct MCfg {
     static constexpr int BOXES = HD / 64;                            // 64-dim column boxes per page
     static constexpr int BOX_BYTES = PAGE * 128;                     // 64 keys x 128 bytes, swizzled
@@ -340,7 +360,12 @@ template <int HD> struct MCfg {
     static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
     static constexpr int STAGES_RAW = (192 * 1024) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 6 ? 6 : STAGES_RAW;
-    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /* alignment */ + 128;
+    static constexpr int KS_W = HD / 32;                             // k-steps of phase A per warp (half of head_dim)
+    static constexpr int MT_W = HD >= 128 ? HD / 128 : 1;            // 16-dim tiles of O^T per warp
+    static constexpr int PV_WARPS = HD / 16 / MT_W;                  // warps that own a slice of O^T
+    static constexpr int SCORE_FLOATS = 3 * 8 * SROW + 16;           // partial halves, final, page maxima
+    static constexpr int SMEM = STAGES * STAGE_BYTES + SCORE_FLOATS * 4 + 64 /* barriers */ + (1024 + 1) * 4 /* stream: page prefix */
+                                + 1024 /* alignment */;
 };
 // byte offset of (key row r, 16-byte chunk c of the head dim) inside a swizzled page
 __device__ __forceinline__ int sw_off(int r, int c) {
@@ -360,52 +385,131 @@ __device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t&
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
 }
-// D += A B with rows 8..15 of A all zero (a1 = a3 = 0): only the group's heads occupy rows
-__device__ __forceinline__ void mma_rows8(float* d, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
-    const uint32_t z = 0u;
+__device__ __forceinline__ void mma_16816(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a0), "r"(z), "r"(a2), "r"(z), "r"(b0), "r"(b1));
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int HD>
-__global__ void __launch_bounds__(MW * 32, 1)
-attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, DecodeArgs a) {
+// cap * tanh(x / cap) as cap * (1 - 2 / (e^(2x/cap) + 1)) with the fast exponential and division: the absolute
+// error stays near cap * 2^-22, far below what rounding the probabilities to bfloat16 costs, at a tenth of the
+// instructions of tanhf.  Large |x| saturate to +-cap without overflow trouble (e^y = inf gives 1, e^y = 0 gives -1).
+__device__ __forceinline__ float softcap_fast(float x, float cap, float inv_cap) {
+    const float e = __expf(2.f * x * inv_cap);
+    return cap * (1.f - __fdividef(2.f, e + 1.f));
+}
+
+// How a launch's pages are dealt out to CTAs.
+//   split:  grid (sequence, kv head, piece); a sequence's pages are cut into n_splits equal pieces
+//           (the caller picks n_splits from the longest sequence).
+//   stream: grid (CTAs); all pages of the launch, ordered by (sequence, kv head, page), are cut into
+//           gridDim.x equal runs, wherever the sequences end.  Every SM gets the same number of pages
+//           whatever the batch and the lengths are, and a CTA's copy pipeline never drains between
+//           sequences.  A run that covers only part of a (sequence, kv head) leaves a partial: in the
+//           CTA's slot 1 if it begins the pair, in slot 0 if it continues one.
+#define STREAM_MAX_BATCH 1024
+
+// Walks pages in (sequence, kv head, page) order.  The same code runs in every thread (consumer side)
+// and, ahead of it, in the thread that issues the copies.
+struct PageCursor {
+    int b, kvh, pg;            // sequence, kv head, page within the pair (0 = first page that holds keys)
+    int np, first_page, hot;   // of sequence b: pages with keys, first of them (table index), the page this step writes
+    int left;                  // pages still to visit
+};
+
+template <int HD, bool STREAM>
+__global__ void __launch_bounds__(TW * 32, 1)
+attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, DecodeArgs a,
+                       int batch) {
     pdl_launch_dependents();
     using C = MCfg<HD>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* full = (uint64_t*)(smem + C::STAGES * C::STAGE_BYTES);
-    __shared__ int s_abort;
+    float* sp = (float*)(smem + C::STAGES * C::STAGE_BYTES);         // [2 halves][8 heads][SROW] partial scores
+    float* sf = sp + 2 * 8 * SROW;                                   // [8 heads][SROW] final scores
+    float* pm = sf + 8 * SROW;                                       // [8 heads][2] maxima of the page's two key halves
+    uint64_t* full = (uint64_t*)(pm + 16);
+    int* pref = (int*)(full + 8);                                    // stream: [batch + 1] pages before each sequence
+    __shared__ int s_last[2], s_pend[2][4];         // per pending part: sequence, kv head, parts of the pair, first CTA
 
-    const int G = a.n_heads / a.n_kv_heads;                         // 1..8 query heads on rows 0..G-1
-    const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int g = lane >> 2, t = lane & 3;
+    const int G = a.n_heads / a.n_kv_heads;                         // 1..8 query heads on columns 0..G-1
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int quad = lane >> 2, t = lane & 3;
 
-    const int len = a.len_after[b];
-    const int lo = (a.window > 0 && len > a.window) ? len - a.window : 0;
-    int first_page, n_pages;
-    if (a.ring_rows > 0) { first_page = 0; n_pages = (min(len, a.ring_rows) + PAGE - 1) / PAGE; }
-    else { first_page = lo / PAGE; n_pages = (len - 1) / PAGE - first_page + 1; }
-    const int per = (n_pages + a.n_splits - 1) / a.n_splits;
-    const int pg_beg = first_page + split * per;
-    const int pg_end = min(first_page + n_pages, pg_beg + per);
-    const int n = max(0, pg_end - pg_beg);
-    const int* pt = a.page_table + (size_t)b * a.pt_stride;
+    // geometry of a sequence: its pages that hold keys, in row space (positions, or ring rows)
+    auto seq_pages = [&](int b, int& first_page, int& hot) -> int {
+        const int len = a.len_after[b];
+        const int lo = (a.window > 0 && len > a.window) ? len - a.window : 0;
+        hot = ((a.ring_rows > 0) ? (len - 1) % a.ring_rows : (len - 1)) / PAGE;
+        if (a.ring_rows > 0) { first_page = 0; return (min(len, a.ring_rows) + PAGE - 1) / PAGE; }
+        first_page = lo / PAGE;
+        return (len - 1) / PAGE - first_page + 1;
+    };
 
-    if (threadIdx.x == 0) {
+    if (tid == 0) {
         for (int s = 0; s < C::STAGES; s++) mbar_init(&full[s], 1);
-        s_abort = 0;
         mbar_init_fence();
     }
-    __syncthreads();
+    if (tid < 16) pm[tid] = -INFINITY;
+
+    PageCursor cur;
+    long long g_beg = 0, total = 0;                                  // stream: this CTA's first page, all pages
+    int n_ctas = 1;                                                  // stream: CTAs that take part
+    if (STREAM) {
+        // pages before each sequence (one kv head's worth), by warp 0
+        if (warp == 0) {
+            int carry = 0;
+            for (int base = 0; base < batch; base += 32) {
+                int fp, hot;
+                int v = (base + lane < batch) ? seq_pages(base + lane, fp, hot) : 0;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) { const int u = __shfl_up_sync(0xffffffffu, v, o); if (lane >= o) v += u; }
+                if (base + lane < batch) pref[base + lane + 1] = carry + v;
+                carry += __shfl_sync(0xffffffffu, v, 31);
+            }
+            if (lane == 0) pref[0] = 0;
+        }
+        __syncthreads();
+        total = (long long)pref[batch] * a.n_kv_heads;
+        n_ctas = (int)min((long long)gridDim.x, total);             // no CTA without a page: the rest leave
+        if ((int)blockIdx.x >= n_ctas) return;
+        g_beg = (long long)blockIdx.x * total / n_ctas;
+        const long long g_end = (long long)(blockIdx.x + 1) * total / n_ctas;
+        cur.left = (int)(g_end - g_beg);
+        int lo_b = 0, hi_b = batch - 1;                              // the last sequence that begins at or before g_beg
+        while (lo_b < hi_b) {
+            const int mid = (lo_b + hi_b + 1) >> 1;
+            if ((long long)pref[mid] * a.n_kv_heads <= g_beg) lo_b = mid; else hi_b = mid - 1;
+        }
+        cur.b = lo_b;
+        cur.np = seq_pages(cur.b, cur.first_page, cur.hot);
+        const int within = (int)(g_beg - (long long)pref[cur.b] * a.n_kv_heads);
+        cur.kvh = within / cur.np;
+        cur.pg = within % cur.np;
+    } else {
+        __syncthreads();
+        cur.b = blockIdx.x; cur.kvh = blockIdx.y;
+        cur.np = seq_pages(cur.b, cur.first_page, cur.hot);
+        const int per = (cur.np + a.n_splits - 1) / a.n_splits;
+        cur.pg = min(cur.np, (int)blockIdx.z * per);
+        cur.left = min(per, cur.np - cur.pg);
+    }
+    auto advance = [&](PageCursor& c) {
+        c.left--;
+        if (++c.pg == c.np && c.left > 0) {
+            c.pg = 0;
+            if (++c.kvh == a.n_kv_heads) { c.kvh = 0; c.b++; c.np = seq_pages(c.b, c.first_page, c.hot); }
+        }
+    };
 
     // one thread issues the copies of a page: head_dim/64 boxes of K and as many of V
-    auto issue = [&](int i) {
-        const int s = i % C::STAGES;
-        const int page = pt[pg_beg + i];
-        const int row = (page * a.n_kv_heads + kvh) * PAGE;          // row of the pool seen as [rows, head_dim]
+    PageCursor ahead = cur;
+    int issued = 0;                                                  // pages whose copies are under way (issuing thread)
+    constexpr int ISSUER = (TW - 1) * 32;                            // a warp with little to do in phase B
+    auto issue = [&]() {
+        const int s = issued % C::STAGES;
+        const int page = a.page_table[(size_t)ahead.b * a.pt_stride + ahead.first_page + ahead.pg];
+        const int row = (page * a.n_kv_heads + ahead.kvh) * PAGE;   // row of the pool seen as [rows, head_dim]
         uint8_t* dst = smem + s * C::STAGE_BYTES;
         mbar_expect_tx(&full[s], C::STAGE_BYTES);
 #pragma unroll
@@ -413,34 +517,43 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             tma_load_box(dst + bx * C::BOX_BYTES, &map_k, &full[s], bx * 64, row);
             tma_load_box(dst + C::TILE_BYTES + bx * C::BOX_BYTES, &map_v, &full[s], bx * 64, row);
         }
+        issued++;
+        advance(ahead);
     };
-    pdl_wait();                                     // the cache rows of this step and q come from earlier kernels
-    if (threadIdx.x == 0)
-        for (int i = 0; i < n && i < C::STAGES; i++) issue(i);
+    // pages that this step does not write were complete before the step began: fetch them at once
+    if (tid == ISSUER)
+        while (ahead.left > 0 && issued < C::STAGES && ahead.first_page + ahead.pg != ahead.hot) issue();
+    pdl_wait();                                     // the new token's cache rows and q come from earlier kernels
+    if (tid == ISSUER)
+        while (ahead.left > 0 && issued < C::STAGES) issue();
 
-    // A fragments of Q: a0 = Q[g][16 ks + 2t, +1], a2 = Q[g][16 ks + 8 + 2t, +1]; rows >= G are zero
-    uint32_t qa[HD / 16][2];
-    {
-        const bf16* qp = (const bf16*)a.q + (size_t)b * a.q_stride + (size_t)(kvh * G + g) * HD;
+    const float inv_cap = a.cap > 0.f ? 1.f / a.cap : 0.f;
+    const int mt = warp & 3, kh = warp >> 2;        // phase A role: 16 keys (m-tile) x half of head_dim
+    const bool pv_warp = warp < C::PV_WARPS;        // phase C role: dims [d0, d0 + 16 MT_W) of O^T
+    const int d0 = warp * C::MT_W * 16;
+    // where this lane's ldmatrix rows lie inside a stage: the same for every page, so computed once
+    const uint32_t smem_base = smem_u32(smem);
+    uint32_t koff[C::KS_W], voff[C::MT_W][4];
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ks++) {
-            qa[ks][0] = (g < G) ? *(const uint32_t*)(qp + ks * 16 + 2 * t) : 0u;
-            qa[ks][1] = (g < G) ? *(const uint32_t*)(qp + ks * 16 + 8 + 2 * t) : 0u;
-        }
-    }
-    float o[HD / 8][4];
+    for (int ks = 0; ks < C::KS_W; ks++)
+        koff[ks] = sw_off(mt * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), (kh * C::KS_W + ks) * 2 + (lane >> 4));
 #pragma unroll
-    for (int d = 0; d < HD / 8; d++) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
-    float m_run = -INFINITY, l_run = 0.f;                           // of row g (meaningful for g < G)
+    for (int m = 0; m < C::MT_W; m++)
+#pragma unroll
+        for (int ks = 0; ks < 4; ks++)
+            voff[m][ks] = C::TILE_BYTES + sw_off(ks * 16 + (lane >> 4) * 8 + (lane & 7), (d0 + m * 16) / 8 + ((lane >> 3) & 1));
 
+    // ---- one loop over this CTA's pages; a run of pages of one (sequence, kv head) begins and ends inside it
+    int visited = 0;                                // pages this CTA has consumed
+    bool aborted = false;
+    int run_left = 0;                               // pages left in the current run; 0: the next page begins one
+    int n_pend = 0;                                 // parts whose pairs still have to be folded (s_pend)
+    int b = 0, kvh = 0, seg_pg0 = 0, seg_n = 0, seg_np = 0, seg_first = 0, len = 0, lo = 0;
+    bool wrapped = false, no_invalid = false;
+    int n_old = 0, old_beg = 0;
     // Which rows (in row space) are keys.  Without a ring, or before the ring has wrapped: lo <= R < len.
     // Once it has wrapped (len >= ring_rows) every row holds a token; too old are the ring_rows - window rows
     // that follow the newest one, a single circular run that starts at old_beg.
-    const bool wrapped = a.ring_rows > 0 && len >= a.ring_rows;
-    const int newest = wrapped ? (len - 1) % a.ring_rows : 0;
-    const int n_old = wrapped ? a.ring_rows - a.window : 0;
-    const int old_beg = wrapped ? (newest + 1 == a.ring_rows ? 0 : newest + 1) : 0;
-    const bool no_invalid = wrapped && n_old == 0;                  // a full ring whose every row is in the window
     auto is_key = [&](int R) -> bool {
         if (wrapped) {
             int d = R - old_beg;                                    // distance past the start of the old run
@@ -449,135 +562,257 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         }
         return R >= lo && R < len;
     };
-
-    int consumed = 0;
-    for (int i = 0; i < n; i++) {
-        const int s = i % C::STAGES;
-        const bool got = mbar_wait(&full[s], (i / C::STAGES) & 1);
-        if (!__syncthreads_and(got)) { if (threadIdx.x == 0) s_abort = 1; break; }
-        consumed = i + 1;
-        uint8_t* k_s = smem + s * C::STAGE_BYTES;
-        uint8_t* v_s = k_s + C::TILE_BYTES;
-        const int key0 = warp * 16;                                  // this warp's keys within the page
-        const int row0 = (pg_beg + i) * PAGE + key0;
-
-        // ---- which of this warp's 16 rows are keys of the sequence
-        bool all_ok;
-        if (no_invalid) all_ok = true;
-        else {
-            all_ok = is_key(row0) && is_key(row0 + 15);
-            // in a ring the rows that are too old form one circular run; it may lie inside these 16 rows
-            if (wrapped && all_ok) all_ok = !(old_beg > row0 && old_beg <= row0 + 15);
-        }
-        if (!all_ok) {
-            // zero the V rows that are not keys: p is 0 there, but 0 * NaN would still poison o
-            for (int r = 0; r < 16; r++) {
-                if (!is_key(row0 + r)) {
-                    for (int c = lane; c < HD / 8; c += 32)
-                        *(uint4*)(v_s + sw_off(key0 + r, c)) = make_uint4(0, 0, 0, 0);
-                }
-            }
-            // these rows were written by ordinary stores; the stage is later refilled by bulk copies
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-        }
-
-        // ---- S = Q K^T: 16 rows x 16 keys (two n-tiles)
-        float sc[2][4], sc2[2][4];                                   // two chains per n-tile: even and odd k-steps
+    // B fragments of Q^T for this warp's half of the dims:
+    // b0 = Q[head quad][16 ks + 2t, +1], b1 = Q[head quad][16 ks + 8 + 2t, +1]; heads >= G are zero
+    uint32_t qb[C::KS_W][2];
+    float o[C::MT_W][4], o2[C::MT_W][4];            // accumulator rows are dims, columns heads 2t, 2t+1; two chains
+    // running maximum of the heads this lane meets: `quad` (its P^T column) and 2t, 2t+1 (its O^T columns)
+    float m_b = -INFINITY, m_c0 = -INFINITY, m_c1 = -INFINITY, l_b = 0.f;
+    auto begin_run = [&]() {
+        b = cur.b; kvh = cur.kvh;
+        seg_pg0 = cur.pg; seg_n = min(cur.left, cur.np - cur.pg); seg_np = cur.np; seg_first = cur.first_page;
+        run_left = seg_n;
+        len = a.len_after[b];
+        lo = (a.window > 0 && len > a.window) ? len - a.window : 0;
+        wrapped = a.ring_rows > 0 && len >= a.ring_rows;
+        const int newest = wrapped ? (len - 1) % a.ring_rows : 0;
+        n_old = wrapped ? a.ring_rows - a.window : 0;
+        old_beg = wrapped ? (newest + 1 == a.ring_rows ? 0 : newest + 1) : 0;
+        no_invalid = wrapped && n_old == 0;                         // a full ring whose every row is in the window
+        const bf16* qp = (const bf16*)a.q + (size_t)b * a.q_stride + (size_t)(kvh * G + quad) * HD + kh * (HD / 2);
 #pragma unroll
-        for (int nt = 0; nt < 2; nt++)
-#pragma unroll
-            for (int e = 0; e < 4; e++) { sc[nt][e] = 0.f; sc2[nt][e] = 0.f; }
-#pragma unroll
-        for (int ks = 0; ks < HD / 16; ks++) {
-            uint32_t b0, b1, b2, b3;
-            ldsm_x4(smem_u32(k_s + sw_off(key0 + (lane >> 4) * 8 + (lane & 7), ks * 2 + ((lane >> 3) & 1))), b0, b1, b2, b3);
-            if (ks & 1) { mma_rows8(sc2[0], qa[ks][0], qa[ks][1], b0, b1); mma_rows8(sc2[1], qa[ks][0], qa[ks][1], b2, b3); }
-            else { mma_rows8(sc[0], qa[ks][0], qa[ks][1], b0, b1); mma_rows8(sc[1], qa[ks][0], qa[ks][1], b2, b3); }
+        for (int ks = 0; ks < C::KS_W; ks++) {
+            qb[ks][0] = (quad < G) ? *(const uint32_t*)(qp + ks * 16 + 2 * t) : 0u;
+            qb[ks][1] = (quad < G) ? *(const uint32_t*)(qp + ks * 16 + 8 + 2 * t) : 0u;
         }
 #pragma unroll
-        for (int nt = 0; nt < 2; nt++) { sc[nt][0] += sc2[nt][0]; sc[nt][1] += sc2[nt][1]; }
-        // ---- scale, cap, mask; row g lives in sc[nt][0..1] of the quad's four lanes
-        float mx = -INFINITY;
+        for (int m = 0; m < C::MT_W; m++) { o[m][0] = o[m][1] = o[m][2] = o[m][3] = 0.f; o2[m][0] = o2[m][1] = o2[m][2] = o2[m][3] = 0.f; }
+        m_b = -INFINITY; m_c0 = -INFINITY; m_c1 = -INFINITY; l_b = 0.f;
+    };
+    // the run is done: write the result or a part of it, and fold the parts if this was the last one
+    auto end_run = [&]() {
+        cur.left -= seg_n;
+        cur.pg += seg_n;
+        if (cur.pg == cur.np && cur.left > 0) {
+            cur.pg = 0;
+            if (++cur.kvh == a.n_kv_heads) { cur.kvh = 0; cur.b++; cur.np = seq_pages(cur.b, cur.first_page, cur.hot); }
+        }
+        // the sums of the quad's four lanes are the head's sum (the same in every warp)
 #pragma unroll
-        for (int nt = 0; nt < 2; nt++)
+        for (int m = 0; m < C::MT_W; m++) { o[m][0] += o2[m][0]; o[m][1] += o2[m][1]; o[m][2] += o2[m][2]; o[m][3] += o2[m][3]; }
+        l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+        l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+        const float L0 = __shfl_sync(0xffffffffu, l_b, 4 * (2 * t)), L1 = __shfl_sync(0xffffffffu, l_b, 4 * (2 * t + 1));
+        const bool begins = seg_pg0 == 0, whole = STREAM ? (begins && seg_n == seg_np) : (a.n_splits == 1);
+        // where the parts of this (sequence, kv head) lie, and how many there are
+        int n_parts, my_part, c_first = 0;
+        if (STREAM) {
+            const long long g0 = (long long)pref[b] * a.n_kv_heads + (long long)kvh * seg_np;   // the pair's first page
+            c_first = (int)(((g0 + 1) * n_ctas - 1) / total);       // the CTA whose run holds page g: floor(((g + 1) n - 1) / total)
+            const int c_last = (int)(((g0 + seg_np) * n_ctas - 1) / total);
+            n_parts = c_last - c_first + 1;
+            my_part = blockIdx.x - c_first;
+        } else {
+            n_parts = a.n_splits;
+            my_part = blockIdx.z;
+        }
+        auto part_of = [&](int k, int hg) -> float* {               // part k of head hg of this pair
+            if (STREAM) return a.partial + ((size_t)((c_first + k) * 2 + (k == 0 ? 1 : 0)) * G + hg) * (HD + 2);
+            return a.partial + (((size_t)b * a.n_heads + kvh * G + hg) * a.n_splits + k) * (HD + 2);
+        };
+        if (pv_warp) {
 #pragma unroll
             for (int e = 0; e < 2; e++) {
-                float v = sc[nt][e] * a.scale;
-                if (a.cap > 0.f) v = softcap_f(v, a.cap);
-                const bool ok = all_ok || is_key(row0 + nt * 8 + 2 * t + e);
-                v = ok ? v : -INFINITY;
-                sc[nt][e] = v;
-                mx = fmaxf(mx, v);
+                const int hg = 2 * t + e;
+                if (hg >= G) continue;
+                const float L = e ? L1 : L0, M = e ? m_c1 : m_c0;
+                if (whole) {
+                    bf16* dst = (bf16*)a.out + ((size_t)b * a.n_heads + kvh * G + hg) * HD;
+#pragma unroll
+                    for (int m = 0; m < C::MT_W; m++) {
+                        dst[d0 + m * 16 + quad] = __float2bfloat16_rn(o[m][e] / L);
+                        dst[d0 + m * 16 + quad + 8] = __float2bfloat16_rn(o[m][2 + e] / L);
+                    }
+                } else {
+                    float* dst = part_of(my_part, hg);
+#pragma unroll
+                    for (int m = 0; m < C::MT_W; m++) {
+                        dst[d0 + m * 16 + quad] = o[m][e];
+                        dst[d0 + m * 16 + quad + 8] = o[m][2 + e];
+                    }
+                    if (warp == 0 && quad == 0) { dst[HD] = M; dst[HD + 1] = L; }
+                }
             }
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float mn = fmaxf(m_run, mx);
-        const float msafe = (mn == -INFINITY) ? 0.f : mn;
-        const float corr = (m_run == -INFINITY) ? 0.f : __expf(m_run - msafe);
-        m_run = mn;
-        float p[2][2];
-        float ps = 0.f;
-#pragma unroll
-        for (int nt = 0; nt < 2; nt++)
-#pragma unroll
-            for (int e = 0; e < 2; e++) { p[nt][e] = __expf(sc[nt][e] - msafe); ps += p[nt][e]; }
-        l_run = l_run * corr + ps;
-#pragma unroll
-        for (int d = 0; d < HD / 8; d++) { o[d][0] *= corr; o[d][1] *= corr; }
-        __nv_bfloat162 h0 = __floats2bfloat162_rn(p[0][0], p[0][1]), h1 = __floats2bfloat162_rn(p[1][0], p[1][1]);
-        const uint32_t pa0 = (g < G) ? *(uint32_t*)&h0 : 0u, pa2 = (g < G) ? *(uint32_t*)&h1 : 0u;
-        // ---- O += P V over this warp's 16 keys
-#pragma unroll
-        for (int d = 0; d < HD / 8; d += 2) {
-            uint32_t b0, b1, b2, b3;
-            ldsm_x4_t(smem_u32(v_s + sw_off(key0 + ((lane >> 3) & 1) * 8 + (lane & 7), d + (lane >> 4))), b0, b1, b2, b3);
-            mma_rows8(o[d], pa0, pa2, b0, b1);
-            mma_rows8(o[d + 1], pa0, pa2, b2, b3);
         }
-        __syncthreads();                                            // everyone is done with stage s
-        if (threadIdx.x == 0 && i + C::STAGES < n) issue(i + C::STAGES);
-    }
-
-    if (s_abort) {
-        if (threadIdx.x == 0) {
-            atomicExch(&g_attn_error, 1);
-            const int issued = min(n, consumed + C::STAGES);
-            for (int i = consumed; i < issued; i++) mbar_wait(&full[i % C::STAGES], (i / C::STAGES) & 1);
+        if (whole || a.tickets == nullptr) return;
+        if (tid == 0) { s_pend[n_pend][0] = b; s_pend[n_pend][1] = kvh; s_pend[n_pend][2] = n_parts; s_pend[n_pend][3] = c_first; }
+        n_pend++;
+    };
+    // the CTA that finishes a pair's last part folds the parts, in their order
+    auto fold_pending = [&]() {
+        if (n_pend == 0) return;
+        __threadfence();
+        __syncthreads();
+        if (tid < n_pend) {
+            int* ticket = a.tickets + (size_t)s_pend[tid][0] * a.n_kv_heads + s_pend[tid][1];
+            const int old = atomicAdd(ticket, 1);
+            s_last[tid] = (old == s_pend[tid][2] - 1);
+            if (s_last[tid]) *ticket = 0;                           // left at zero for the next launch
         }
         __syncthreads();
-        return;
-    }
+        for (int q = 0; q < n_pend; q++) {
+            if (!s_last[q]) continue;
+            __threadfence();
+            const int fb = s_pend[q][0], fkvh = s_pend[q][1], n_parts = s_pend[q][2], c_first = s_pend[q][3];
+            auto part_of = [&](int k, int hg) -> const float* {
+                if (STREAM) return a.partial + ((size_t)((c_first + k) * 2 + (k == 0 ? 1 : 0)) * G + hg) * (HD + 2);
+                return a.partial + (((size_t)fb * a.n_heads + fkvh * G + hg) * a.n_splits + k) * (HD + 2);
+            };
+            for (int x = tid; x < G * HD; x += TW * 32) {
+                const int hg = x / HD, d = x % HD;
+                float M = -INFINITY;
+                for (int k = 0; k < n_parts; k++) M = fmaxf(M, __ldcg(part_of(k, hg) + HD));
+                float L = 0.f, acc = 0.f;
+                for (int k = 0; k < n_parts; k++) {
+                    const float* pk = part_of(k, hg);
+                    const float ms = __ldcg(pk + HD);
+                    if (ms != -INFINITY) { const float f = __expf(ms - M); L += __ldcg(pk + HD + 1) * f; acc += __ldcg(pk + d) * f; }
+                }
+                ((bf16*)a.out)[((size_t)fb * a.n_heads + fkvh * G + hg) * HD + d] = __float2bfloat16_rn(acc / L);
+            }
+        }
+    };
 
-    // ---- fold the four warps: row sums over the quad first
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-    __syncthreads();
-    float* red = (float*)smem;                                      // [MW][G][HD + 2]
-    if (g < G) {
-        float* r = red + ((size_t)warp * G + g) * (HD + 2);
-#pragma unroll
-        for (int d = 0; d < HD / 8; d++) { r[d * 8 + 2 * t] = o[d][0]; r[d * 8 + 2 * t + 1] = o[d][1]; }
-        if (t == 0) { r[HD] = m_run; r[HD + 1] = l_run; }
+    const int my_pages = cur.left;
+    if (my_pages == 0) {                            // (split only) an empty piece still reports "nothing here"
+        begin_run();
+        end_run();
     }
-    __syncthreads();
-    for (int x = threadIdx.x; x < G * HD; x += blockDim.x) {
-        const int gg = x / HD, d = x % HD;
-        float M = -INFINITY;
-        for (int w = 0; w < MW; w++) M = fmaxf(M, red[((size_t)w * G + gg) * (HD + 2) + HD]);
-        float L = 0.f, acc = 0.f;
-        for (int w = 0; w < MW; w++) {
-            const float* r = red + ((size_t)w * G + gg) * (HD + 2);
-            if (r[HD] != -INFINITY) { const float f = __expf(r[HD] - M); L += r[HD + 1] * f; acc += r[d] * f; }
+    for (int i = 0; i < my_pages; i++) {
+        if (run_left == 0) begin_run();
+        {
+            const int j = seg_n - run_left;
+
+            const int s = i % C::STAGES;
+            const bool got = mbar_wait(&full[s], (i / C::STAGES) & 1);
+            const uint32_t stage = smem_base + s * C::STAGE_BYTES;
+            uint8_t* v_s = smem + s * C::STAGE_BYTES + C::TILE_BYTES;
+            const int row0 = (seg_first + seg_pg0 + j) * PAGE;
+
+            // ---- A: partial S^T of this warp's 16 keys over its half of the dims (two chains)
+            {
+                float c[4][4];                               // four chains: the MMAs of a chain wait for one another
+#pragma unroll
+                for (int x = 0; x < 4; x++) { c[x][0] = c[x][1] = c[x][2] = c[x][3] = 0.f; }
+#pragma unroll
+                for (int ks = 0; ks < C::KS_W; ks++) {
+                    uint32_t a0, a1, a2, a3;
+                    ldsm_x4(stage + koff[ks], a0, a1, a2, a3);
+                    mma_16816(c[ks & 3], a0, a1, a2, a3, qb[ks][0], qb[ks][1]);
+                }
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const int h = 2 * t + e;
+                    if (h < G) {
+                        float* dst = sp + (kh * 8 + h) * SROW + mt * 16 + quad;
+                        dst[0] = (c[0][e] + c[1][e]) + (c[2][e] + c[3][e]);
+                        dst[8] = (c[0][2 + e] + c[1][2 + e]) + (c[2][2 + e] + c[3][2 + e]);
+                    }
+                }
+            }
+            // rows of the page that are not keys: zero their V rows
+            bool all_ok = no_invalid;
+            if (!all_ok) {
+                all_ok = is_key(row0) && is_key(row0 + PAGE - 1);
+                // in a ring the rows that are too old form one circular run; it may lie inside the page
+                if (wrapped && all_ok) all_ok = !(old_beg > row0 && old_beg <= row0 + PAGE - 1);
+            }
+            if (!all_ok) {
+                for (int x = tid; x < PAGE * (HD / 8); x += TW * 32) {
+                    const int r = x / (HD / 8), c = x % (HD / 8);
+                    if (!is_key(row0 + r)) *(uint4*)(v_s + sw_off(r, c)) = make_uint4(0, 0, 0, 0);
+                }
+                // these rows were written by ordinary stores; the stage is later refilled by bulk copies
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            }
+            if (!__syncthreads_and(got)) { aborted = true; break; }  // the same answer in every thread: leave the page loop
+            visited = i + 1;
+            // every warp has left phase C of the page before: that page's stage can take the next copy
+            if (tid == ISSUER && i >= 1 && ahead.left > 0) issue();
+
+            // ---- B: final scores, one thread per (key, head); heads h and h+4 share a thread
+            {
+                const int key = tid & 63;
+#pragma unroll
+                for (int hh = 0; hh < 2; hh++) {
+                    const int h = (tid >> 6) + 4 * hh;              // uniform over a warp
+                    if (h < G) {
+                        float v = (sp[h * SROW + key] + sp[(8 + h) * SROW + key]) * a.scale;
+                        if (a.cap > 0.f) v = softcap_fast(v, a.cap, inv_cap);
+                        if (!(all_ok || is_key(row0 + key))) v = -INFINITY;
+                        sf[h * SROW + key] = v;
+                        const float wm = warp_max(v);
+                        if (lane == 0) pm[h * 2 + ((tid >> 5) & 1)] = wm;
+                    }
+                }
+            }
+            __syncthreads();
+
+            // ---- C: running softmax (the same numbers in every warp), then O^T += V^T P^T
+            {
+                const float pb_max = fmaxf(pm[quad * 2], pm[quad * 2 + 1]);        // -inf for heads >= G
+                const float pc0 = fmaxf(pm[4 * t], pm[4 * t + 1]), pc1 = fmaxf(pm[4 * t + 2], pm[4 * t + 3]);
+                const float nb = fmaxf(m_b, pb_max), n0 = fmaxf(m_c0, pc0), n1 = fmaxf(m_c1, pc1);
+                const float sb = (nb == -INFINITY) ? 0.f : nb;
+                const float corr_b = (m_b == -INFINITY) ? 0.f : __expf(m_b - sb);
+                const float corr0 = (m_c0 == -INFINITY) ? 0.f : __expf(m_c0 - ((n0 == -INFINITY) ? 0.f : n0));
+                const float corr1 = (m_c1 == -INFINITY) ? 0.f : __expf(m_c1 - ((n1 == -INFINITY) ? 0.f : n1));
+                m_b = nb; m_c0 = n0; m_c1 = n1;
+                uint32_t pb[4][2];
+                float ps = 0.f;
+                if (quad < G) {
+                    const float* srow = sf + quad * SROW + 2 * t;
+#pragma unroll
+                    for (int ks = 0; ks < 4; ks++) {
+                        const float2 x = *(const float2*)(srow + ks * 16), y = *(const float2*)(srow + ks * 16 + 8);
+                        const float p0 = __expf(x.x - sb), p1 = __expf(x.y - sb), p2 = __expf(y.x - sb), p3 = __expf(y.y - sb);
+                        ps += (p0 + p1) + (p2 + p3);
+                        __nv_bfloat162 h0 = __floats2bfloat162_rn(p0, p1), h1 = __floats2bfloat162_rn(p2, p3);
+                        pb[ks][0] = *(uint32_t*)&h0; pb[ks][1] = *(uint32_t*)&h1;
+                    }
+                } else {
+#pragma unroll
+                    for (int ks = 0; ks < 4; ks++) { pb[ks][0] = 0u; pb[ks][1] = 0u; }
+                }
+                l_b = l_b * corr_b + ps;
+                if (pv_warp) {
+#pragma unroll
+                    for (int m = 0; m < C::MT_W; m++) {
+                        o[m][0] *= corr0; o[m][1] *= corr1; o[m][2] *= corr0; o[m][3] *= corr1;
+                        o2[m][0] *= corr0; o2[m][1] *= corr1; o2[m][2] *= corr0; o2[m][3] *= corr1;
+#pragma unroll
+                        for (int ks = 0; ks < 4; ks++) {
+                            uint32_t a0, a1, a2, a3;
+                            ldsm_x4_t(stage + voff[m][ks], a0, a1, a2, a3);
+                            mma_16816((ks & 1) ? o2[m] : o[m], a0, a1, a2, a3, pb[ks][0], pb[ks][1]);
+                        }
+                    }
+                }
+            }
         }
-        const int h = kvh * G + gg;
-        if (a.n_splits == 1) {
-            ((bf16*)a.out)[((size_t)b * a.n_heads + h) * HD + d] = __float2bfloat16_rn(acc / L);
-        } else {
-            float* pp = a.partial + (((size_t)b * a.n_heads + h) * a.n_splits + split) * (HD + 2);
-            pp[d] = acc;
-            if (d == 0) { pp[HD] = M; pp[HD + 1] = L; }
+        if (--run_left == 0) {
+            end_run();
+            // stream: folding at once, not when the CTA is through: a part that continues a pair ends early in the
+            // CTA's run, so the pair's fold falls to the CTA before this one and every CTA folds one pair at its end
+            if (STREAM) { fold_pending(); n_pend = 0; }
         }
+    }
+    if (!STREAM && !aborted) fold_pending();        // split: the CTA has one run; kept out of the page loop
+
+    if (aborted && tid == ISSUER) {
+        // a wait ran out: record it, and let copies that were issued land before the CTA ends
+        atomicExch(&g_attn_error, 1);
+        for (int i = visited; i < issued; i++) mbar_wait(&full[i % C::STAGES], (i / C::STAGES) & 1);
     }
 }
 
@@ -610,20 +845,23 @@ static int pool_map(CUtensorMap* m, const void* pool, long long rows, int hd) {
     return 0;
 }
 
-template <int HD>
-static int launch_mma(const DecodeArgs& a, int batch, long long pool_rows, cudaStream_t stream) {
+template <int HD, bool STREAM>
+static int launch_mma(const DecodeArgs& a, int batch, int n_ctas, cudaStream_t stream) {
     using C = MCfg<HD>;
     static bool attr_set = false;
-    auto kern = attn_decode_mma_kernel<HD>;
+    auto kern = attn_decode_mma_kernel<HD, STREAM>;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
     }
+    // the map's row count only bounds the copy engine's address check; pages come from the table
+    const long long pool_rows = 0x7fffff00LL;
     CUtensorMap mk, mv;
     if (pool_map(&mk, a.k_pool, pool_rows, HD) || pool_map(&mv, a.v_pool, pool_rows, HD)) return -1;
     dim3 grid(batch, a.n_kv_heads, a.n_splits);
-    tb_launch(kern, dim3(grid), dim3(MW * 32), C::SMEM, stream, mk, mv, a);
+    if (STREAM) grid = dim3(n_ctas);
+    tb_launch(kern, dim3(grid), dim3(TW * 32), C::SMEM, stream, mk, mv, a, batch);
     return tb_launch_status();
 }
 
@@ -702,12 +940,10 @@ static int run_decode(const DecodeArgs* args, int dtype, int batch, bool tensor_
     int st = -1;
     if (a.hd < 64) tensor_cores = false;            // a 64-byte row has no 128-byte swizzled box
     if (tensor_cores) {
-        // the map's row count only bounds the copy engine's address check; pages come from the table
-        const long long rows = 0x7fffff00LL;
         switch (a.hd) {
-        case 64: st = launch_mma<64>(a, batch, rows, stream); break;
-        case 128: st = launch_mma<128>(a, batch, rows, stream); break;
-        default: st = launch_mma<256>(a, batch, rows, stream); break;
+        case 64: st = launch_mma<64, false>(a, batch, 0, stream); break;
+        case 128: st = launch_mma<128, false>(a, batch, 0, stream); break;
+        default: st = launch_mma<256, false>(a, batch, 0, stream); break;
         }
     } else {
     if (!(g == 1 || g == 2 || g == 4 || g == 8))
@@ -728,11 +964,40 @@ static int run_decode(const DecodeArgs* args, int dtype, int batch, bool tensor_
 #undef GO
     }
     if (st) return st;
-    if (a.n_splits > 1) {
+    if (a.n_splits > 1 && !(tensor_cores && a.tickets != nullptr)) {
         tb_launch(attn_combine_kernel, dim3((unsigned)batch * a.n_heads), dim3(128), 0, stream, a.partial, (bf16*)a.out, a.n_splits, a.hd);
         st = tb_launch_status();
     }
     return st;
+}
+
+// The tensor-core kernel with the launch's pages dealt out evenly to `n_ctas` CTAs (see "stream" above): no
+// piece count to choose, every SM equally loaded whatever the lengths are.  `args->n_splits` is ignored;
+// `args->partial` must hold tb_attn_decode_stream_scratch_floats() floats and `args->tickets` batch * n_kv_heads
+// zeroed counters, which the launch leaves at zero.
+extern "C" long long tb_attn_decode_stream_scratch_floats(int n_ctas, int n_heads, int n_kv_heads, int hd) {
+    return (long long)n_ctas * 2 * (n_heads / (n_kv_heads > 0 ? n_kv_heads : 1)) * (hd + 2);
+}
+extern "C" int tb_attn_decode_stream(const DecodeArgs* args, int dtype, int batch, int n_ctas, cudaStream_t stream) {
+    if (batch <= 0) return 0;
+    DecodeArgs a = *args;
+    if (!tb_attn_decode_takes(dtype, a.n_heads, a.n_kv_heads, a.hd) || a.hd < 64)
+        return tb_refuse("attn_decode_stream: takes bfloat16, head_dim 64/128/256 and 1 to 8 heads per kv head "
+                         "(got dtype %d, %d heads, %d kv heads, head_dim %d)", dtype, a.n_heads, a.n_kv_heads, a.hd);
+    if (a.page_rows != PAGE) return tb_refuse("attn_decode: pages of %d rows, this kernel is built for %d", a.page_rows, PAGE);
+    if (batch > STREAM_MAX_BATCH) return tb_refuse("attn_decode_stream: batch %d, takes up to %d", batch, STREAM_MAX_BATCH);
+    if (n_ctas < 1 || n_ctas > 65535) return tb_refuse("attn_decode_stream: n_ctas=%d", n_ctas);
+    if (a.partial == nullptr || a.tickets == nullptr) return tb_refuse("attn_decode_stream: needs scratch and ticket counters");
+    if (a.ring_rows > 0 && (a.ring_rows % PAGE || a.window <= 0 || a.window > a.ring_rows))
+        return tb_refuse("attn_decode: a ring of %d rows cannot hold a window of %d", a.ring_rows, a.window);
+    if (((uintptr_t)a.q & 15) || (a.q_stride % 8) || ((uintptr_t)a.k_pool & 15) || ((uintptr_t)a.v_pool & 15))
+        return tb_refuse("attn_decode: q rows and the pools must be 16-byte aligned");
+    a.n_splits = 0;
+    switch (a.hd) {
+    case 64: return launch_mma<64, true>(a, batch, n_ctas, stream);
+    case 128: return launch_mma<128, true>(a, batch, n_ctas, stream);
+    default: return launch_mma<256, true>(a, batch, n_ctas, stream);
+    }
 }
 
 // Reads and clears the error word (1: a bounded wait on a page copy ran out).  Synchronises.
@@ -762,9 +1027,14 @@ extern "C" int tb_attn_decode_error() {
 #include <mutex>
 
 static __device__ __align__(256) float g_noalloc_scratch[TB_ATTN_DECODE_NOALLOC_MAX_FLOATS];
+// ticket counters of the split fold, one per (sequence, kv head); zero when the library is loaded and
+// left at zero by every launch.  A call with more pairs than this folds with a second kernel instead.
+#define NOALLOC_MAX_TICKETS 16384
+static __device__ int g_noalloc_tickets[NOALLOC_MAX_TICKETS];
 
 #define NOALLOC_MAX_DEVICES 64
 static float* g_noalloc_ptr[NOALLOC_MAX_DEVICES];          // device address of the array, per device
+static int* g_noalloc_tickets_ptr[NOALLOC_MAX_DEVICES];
 static std::mutex g_noalloc_mutex;
 
 extern "C" int tb_attn_decode_noalloc(const DecodeArgs* args, int dtype, int batch, cudaStream_t stream) {
@@ -781,6 +1051,7 @@ extern "C" int tb_attn_decode_noalloc(const DecodeArgs* args, int dtype, int bat
     if (e != cudaSuccess) return (int)e;
     if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return tb_refuse("attn_decode_noalloc: device index %d", dev);
     float* ptr;
+    int* tickets;
     {
         std::lock_guard<std::mutex> lock(g_noalloc_mutex);
         if (g_noalloc_ptr[dev] == nullptr) {
@@ -788,10 +1059,16 @@ extern "C" int tb_attn_decode_noalloc(const DecodeArgs* args, int dtype, int bat
             void* p = nullptr;
             e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
             if (e != cudaSuccess) return (int)e;
+            void* t = nullptr;
+            e = cudaGetSymbolAddress(&t, g_noalloc_tickets);
+            if (e != cudaSuccess) return (int)e;
+            g_noalloc_tickets_ptr[dev] = (int*)t;
             g_noalloc_ptr[dev] = (float*)p;
         }
         ptr = g_noalloc_ptr[dev];
+        tickets = g_noalloc_tickets_ptr[dev];
     }
     a.partial = need ? ptr : nullptr;
+    a.tickets = (need && (long long)batch * a.n_kv_heads <= NOALLOC_MAX_TICKETS) ? tickets : nullptr;
     return tb_attn_decode(&a, dtype, batch, stream);
 }

@@ -128,6 +128,7 @@ struct DecodeArgs {
     float* partial;                             // [B, n_heads, n_splits, hd + 2] (when n_splits > 1)
     int n_heads, n_kv_heads, hd, page_rows, ring_rows, window, n_splits;
     float scale, cap;
+    int* tickets;                               // used by the tensor-core kernel only; ignored here
 };
 
 template <typename T, int NC>

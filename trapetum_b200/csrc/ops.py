@@ -292,7 +292,7 @@ class _DecodeArgs(ctypes.Structure):
                 ("partial", c_void_p),
                 ("n_heads", c_int), ("n_kv_heads", c_int), ("hd", c_int), ("page_rows", c_int),
                 ("ring_rows", c_int), ("window", c_int), ("n_splits", c_int),
-                ("scale", c_float), ("cap", c_float)]
+                ("scale", c_float), ("cap", c_float), ("tickets", c_void_p)]
 
 
 def attn_decode_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
@@ -622,6 +622,22 @@ def attn_decode_takes(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_di
     return (head_dim in (64, 128, 256) and 1 <= g <= 8) or (head_dim == 32 and g in (1, 2, 4, 8))
 
 
+_TICKETS: dict = {}
+_TICKET_SLOTS = 1 << 16
+
+
+def _tickets(device: torch.device) -> torch.Tensor:
+    """Zeroed counters with which the split pieces of a decode attention launch find out which of them
+    finishes last; every launch leaves them at zero.  One array per device: launches that may overlap on
+    the GPU (different streams with no order between them) must not both use split pieces."""
+    t = _TICKETS.get(device.index)
+    if t is None:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("attn_decode: the first launch on a device must not be inside a graph capture")
+        t = _TICKETS[device.index] = torch.zeros(_TICKET_SLOTS, dtype=torch.int32, device=device)
+    return t
+
+
 def attn_decode_tma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
                     len_after: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
                     softcap: float, window: int, ring_rows: int, n_splits: int = 1,
@@ -653,16 +669,69 @@ def attn_decode_tma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.hd = head_dim; a.page_rows = PAGE_ROWS
     a.ring_rows = ring_rows; a.window = window or 0; a.n_splits = n_splits
     a.scale = scale; a.cap = softcap or 0.0
+    fused_fold = variant == "mma" and head_dim >= 64 and n_splits > 1 and B * n_kv_heads <= _TICKET_SLOTS
+    a.tickets = _tickets(q.device).data_ptr() if fused_fold else None
     lib = build.load("attention_decode")
     fn = lib.tb_attn_decode if variant == "mma" else lib.tb_attn_decode_lanes
     _check(lib, fn(ctypes.byref(a), c_int(code(q.dtype)), c_int(B), _stream()), "attn_decode",
-           2 if n_splits > 1 else 1)
+           2 if (n_splits > 1 and not fused_fold) else 1)
     return out
 
 
+def attn_decode_stream(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
+                       len_after: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
+                       softcap: float, window: int, ring_rows: int, n_ctas: Optional[int] = None) -> torch.Tensor:
+    """Decode attention on tensor cores with all pages of the launch dealt out evenly to ``n_ctas`` CTAs
+    (default: one per SM), wherever the sequences end: the time of a launch follows the sum of the lengths,
+    not the longest one (see attention_decode.cu)."""
+    _cuda(q, k_pool, v_pool, page_table, len_after)
+    _rows_contig(q, "attention: q")
+    B = q.shape[0]
+    if not attn_decode_stream_takes(q.dtype, n_heads, n_kv_heads, head_dim, B):
+        raise KernelError(f"attn_decode_stream does not take {q.dtype}, {n_heads}/{n_kv_heads} heads, "
+                          f"head_dim {head_dim}, batch {B}")
+    if page_table.dtype != torch.int32 or page_table.dim() != 2 or page_table.stride(1) != 1 or page_table.shape[0] < B:
+        raise KernelError("attention: page_table must be int32 [batch, pages]")
+    if len_after.dtype != torch.int32 or len_after.numel() < B:
+        raise KernelError("attention: len_after must be int32 [batch]")
+    if tuple(k_pool.shape[1:]) != (n_kv_heads, PAGE_ROWS, head_dim) or k_pool.shape != v_pool.shape \
+            or not k_pool.is_contiguous() or not v_pool.is_contiguous() or k_pool.dtype != q.dtype:
+        raise KernelError("attention: pools must be contiguous [pages, n_kv_heads, PAGE_ROWS, head_dim] of q's dtype")
+    if n_ctas is None:
+        n_ctas = sm_count(q.device)
+    lib = build.load("attention_decode")
+    lib.tb_attn_decode_stream_scratch_floats.restype = c_longlong
+    need = int(lib.tb_attn_decode_stream_scratch_floats(c_int(n_ctas), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim)))
+    out = torch.empty((B, n_heads * head_dim), dtype=q.dtype, device=q.device)
+    scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+    a = _DecodeArgs()
+    a.q = q.data_ptr(); a.q_stride = q.stride(0)
+    a.k_pool = k_pool.data_ptr(); a.v_pool = v_pool.data_ptr()
+    a.page_table = page_table.data_ptr(); a.pt_stride = page_table.stride(0)
+    a.len_after = len_after.data_ptr(); a.out = out.data_ptr()
+    a.partial = scratch.data_ptr()
+    a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.hd = head_dim; a.page_rows = PAGE_ROWS
+    a.ring_rows = ring_rows; a.window = window or 0; a.n_splits = 0
+    a.scale = scale; a.cap = softcap or 0.0
+    a.tickets = _tickets(q.device).data_ptr()
+    _check(lib, lib.tb_attn_decode_stream(ctypes.byref(a), c_int(code(q.dtype)), c_int(B), c_int(n_ctas), _stream()),
+           "attn_decode_stream")
+    return out
+
+
+def attn_decode_stream_takes(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int, batch: int) -> bool:
+    return (attn_decode_takes(dtype, n_heads, n_kv_heads, head_dim) and head_dim >= 64
+            and batch <= 1024 and batch * n_kv_heads <= _TICKET_SLOTS)
+
+
 def attn_decode_error() -> int:
-    """Reads and clears the decode attention's error word (synchronises); 0 = no wait ran out."""
-    return int(build.load("attention_decode").tb_attn_decode_error())
+    """Reads and clears the decode attention's error word (synchronises); 0 = no wait ran out.  After an
+    error the ticket counters are zeroed again (a launch that gave up may have left them half counted)."""
+    v = int(build.load("attention_decode").tb_attn_decode_error())
+    if v:
+        for t in _TICKETS.values():
+            t.zero_()
+    return v
 
 
 def choose_decode_splits(batch: int, n_kv_heads: int, pages: int, sms: int) -> int:
@@ -686,16 +755,20 @@ def choose_decode_splits(batch: int, n_kv_heads: int, pages: int, sms: int) -> i
 
 
 def attn_decode(q, k_pool, v_pool, page_table, len_after, n_heads, n_kv_heads, head_dim, scale, softcap, window,
-                ring_rows, len_bucket: int) -> torch.Tensor:
-    """Decode attention, kernel and split count chosen here.  ``len_bucket``: an upper bound of the longest
-    context of the batch (the engine passes a power of two so that the choice is stable across steps)."""
+                ring_rows, len_bucket: int, uneven: bool = False) -> torch.Tensor:
+    """Decode attention, kernel and partition chosen here.  ``len_bucket``: an upper bound of the longest
+    context of the batch (the engine passes a power of two so that the choice is stable across steps).
+    ``uneven``: the batch's contexts differ much in length; the pages are then dealt out to the CTAs as one
+    stream, so that the launch's time follows the sum of the lengths and not the longest one."""
+    B = q.shape[0]
+    if uneven and attn_decode_stream_takes(q.dtype, n_heads, n_kv_heads, head_dim, B):
+        return attn_decode_stream(q, k_pool, v_pool, page_table, len_after, n_heads, n_kv_heads, head_dim, scale,
+                                  softcap, window, ring_rows)
     rows = min(len_bucket, ring_rows) if ring_rows else len_bucket
     pages = max(1, (rows + PAGE_ROWS - 1) // PAGE_ROWS)
-    splits = choose_decode_splits(q.shape[0], n_kv_heads, pages, sm_count(q.device))
+    splits = choose_decode_splits(B, n_kv_heads, pages, sm_count(q.device))
     if attn_decode_takes(q.dtype, n_heads, n_kv_heads, head_dim):
-        g = n_heads // n_kv_heads
-        # one lane group per key is the faster variant for small groups; tensor cores pay off above
-        variant = "lanes" if (g <= 2 or head_dim < 64) else "mma"
+        variant = "lanes" if head_dim < 64 else "mma"     # a 64-byte row has no swizzled box for the tensor-core kernel
         return attn_decode_tma(q, k_pool, v_pool, page_table, len_after, n_heads, n_kv_heads, head_dim, scale,
                                softcap, window, ring_rows, splits, variant)
     return attn_decode_simt(q, k_pool, v_pool, page_table, len_after, n_heads, n_kv_heads, head_dim, scale,

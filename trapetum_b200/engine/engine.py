@@ -34,6 +34,12 @@ def _sm_count(device) -> int:
     return _SM_COUNT[idx]
 
 
+def uneven_lengths(lens: Sequence[int]) -> bool:
+    """Whether a batch's context lengths differ so much that work dealt out by the longest one would leave
+    most of the GPU idle: the sum is under three quarters of batch x longest."""
+    return len(lens) > 1 and 4 * sum(lens) < 3 * len(lens) * max(lens)
+
+
 def len_bucket(max_len: int) -> int:
     """The smallest power of two (at least 256) that is not below ``max_len``.  Launch shapes of a decode
     step (how attention cuts the keys) depend on the longest context only through this bucket, so they stay
@@ -132,7 +138,8 @@ class Engine:
         ctx = StepContext(is_prefill=is_prefill, n_tokens=T, batch=B, positions=dev["positions"],
                           token_seq=dev["token_seq"], seq_start=dev["seq_start"], len_after=dev["len_after"],
                           slot_ids=dev["slot_ids"], slots=slots, seq_lens=lens, max_seq_len=max(lens),
-                          max_len_after=max_after, len_bucket=len_bucket(max_after))
+                          max_len_after=max_after, len_bucket=len_bucket(max_after),
+                          uneven=(not is_prefill) and uneven_lengths(after))
         n_want = arrays["want"].size
         if n_want == 0:
             # nothing is asked for: the layers still run (they fill the cache), the head does not
@@ -158,10 +165,11 @@ class Engine:
         B = len(slots)
         max_after = max(after)
         bucket = len_bucket(max_after)
-        key = (B, bucket)
+        uneven = uneven_lengths(after)
+        key = (B, bucket, uneven)
         dg = self._decode.get(key)
         if dg is None:
-            dg = self._decode[key] = _DecodeShape(B, bucket, self)
+            dg = self._decode[key] = _DecodeShape(B, bucket, self, uneven)
         dg.fill(self, slots, [t[0] for t in tokens], before, after)
         for gi, g in enumerate(self.cache.groups):
             g.table = dg.dev[f"table{gi}"]
@@ -195,8 +203,8 @@ class Engine:
 class _DecodeShape:
     """The fixed-layout inputs, and later the graph, of decode steps of one batch size and length bucket."""
 
-    def __init__(self, B: int, bucket: int, engine: "Engine"):
-        self.B, self.bucket = B, bucket
+    def __init__(self, B: int, bucket: int, engine: "Engine", uneven: bool = False):
+        self.B, self.bucket, self.uneven = B, bucket, uneven
         self.graph = None
         self.logits = None
         self.greedy = None
@@ -250,4 +258,4 @@ class _DecodeShape:
         return StepContext(is_prefill=False, n_tokens=self.B, batch=self.B, positions=d["positions"],
                            token_seq=d["token_seq"], seq_start=d["seq_start"], len_after=d["len_after"],
                            slot_ids=d["slot_ids"], slots=list(slots), seq_lens=[1] * self.B, max_seq_len=1,
-                           max_len_after=max_after, len_bucket=self.bucket)
+                           max_len_after=max_after, len_bucket=self.bucket, uneven=self.uneven)

@@ -102,7 +102,8 @@ class Attention(Mixer):
                                  self.scale, self.softcap, self.window or 0, ctx.max_seq_len, ctx.seq_lens, ctx.memo)
         else:
             o = ops.attn_decode(q, line.k, line.v, line.page_table, ctx.len_after, self.n_heads, self.n_kv,
-                                self.hd, self.scale, self.softcap, self.window or 0, line.ring_rows, ctx.len_bucket)
+                                self.hd, self.scale, self.softcap, self.window or 0, line.ring_rows, ctx.len_bucket,
+                                ctx.uneven)
         return linear_partials(o, self.w_o)
 
 
