@@ -297,6 +297,48 @@ def test_attn_decode(ops, dt, nh, nkv, hd, cap, window, splits):
     assert ops.attn_decode_error() == 0
 
 
+@pytest.mark.parametrize("nh,nkv,hd,rot,cap,window", [(8, 4, 256, 256, 50.0, 0), (8, 4, 256, 256, 50.0, 128), (6, 2, 64, 32, 0.0, 70),
+                                                     (5, 5, 128, 0, 0.0, 0), (14, 2, 256, 64, 30.0, 200), (4, 1, 128, 128, 0.0, 64)])
+def test_attn_decode_that_rotates_and_appends_by_itself(ops, nh, nkv, hd, rot, cap, window):
+    """Given the partial sums of the q/k/v product, the tensor-core decode kernel must do what the rotation kernel
+    followed by the attention kernel does: the same output, and the same new rows in the cache, bit for bit (same
+    sums in the same order).  The new token lies on a page's first row, last row and in the middle; in a ring it
+    overwrites the oldest row."""
+    dt = torch.bfloat16
+    lens = [1, 64, 65, 200, 333, 128]
+    ring = ((window + PAGE - 1) // PAGE) * PAGE if window else 0
+    ks = [rnd(n, nkv, hd, dt=dt, seed=i).cpu() for i, n in enumerate(lens)]
+    vs = [rnd(n, nkv, hd, dt=dt, seed=10 + i).cpu() for i, n in enumerate(lens)]
+    kp, vp, table = paged([k.cuda() for k in ks], [v.cuda() for v in vs], lens, ring, 64, seed=hd)
+    la = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    B, width = len(lens), (nh + 2 * nkv) * hd
+    part = rnd(3, B, width, dt=torch.float32, s=0.6, seed=5)         # three splits of the product
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))).cuda() if rot else None
+    pos = (la - 1).contiguous()
+    seq = torch.arange(B, dtype=torch.int32, device="cuda")
+    scale = 0.37 / math.sqrt(hd)
+    # the two-kernel path, on its own copy of the cache
+    kp1, vp1 = kp.clone(), vp.clone()
+    qkv = torch.empty(B, width, dtype=dt, device="cuda")
+    ops.rope_kv(qkv, nh, nkv, hd, rot, inv_freq, pos, seq, la, kp1, vp1, table, ring, part)
+    want = ops.attn_decode_tma(qkv[:, :nh * hd], kp1, vp1, table, la, nh, nkv, hd, scale, cap, window, ring, 2)
+    runs = [("split 1", lambda k, v: ops.attn_decode_tma(part, k, v, table, la, nh, nkv, hd, scale, cap, window, ring, 1, "mma", (inv_freq, rot))),
+            ("split 3", lambda k, v: ops.attn_decode_tma(part, k, v, table, la, nh, nkv, hd, scale, cap, window, ring, 3, "mma", (inv_freq, rot)))]
+    for n_ctas in (None, 5, 1, 1000):
+        runs.append((f"stream {n_ctas}", lambda k, v, n_ctas=n_ctas: ops.attn_decode_stream(
+            part, k, v, table, la, nh, nkv, hd, scale, cap, window, ring, n_ctas, (inv_freq, rot))))
+    for name, run in runs:
+        kp2, vp2 = kp.clone(), vp.clone()
+        got = run(kp2, vp2)
+        torch.cuda.synchronize()
+        assert torch.isfinite(got.float()).all(), name
+        # NaN marks rows that no token has written: equal_nan compares them too
+        assert torch.equal(torch.nan_to_num(kp2.float(), nan=-7.0), torch.nan_to_num(kp1.float(), nan=-7.0)), f"{name}: k rows"
+        assert torch.equal(torch.nan_to_num(vp2.float(), nan=-7.0), torch.nan_to_num(vp1.float(), nan=-7.0)), f"{name}: v rows"
+        close(got, want, dt, 2.0)
+    assert ops.attn_decode_error() == 0
+
+
 @pytest.mark.parametrize("dt", DT)
 def test_attn_decode_far_key_and_window_edge(ops, dt):
     """One key is made to stand out.  Among hundreds it must win the softmax; one step outside the

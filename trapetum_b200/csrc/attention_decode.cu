@@ -43,6 +43,12 @@ struct DecodeArgs {
     float scale, cap;
     int* tickets;                 // [B, n_kv_heads] zeros, or null: with it the tensor-core kernel folds its
                                   // splits itself (the last CTA to finish) and leaves the counters at zero
+    // Tensor-core kernel only.  If set, q is not read: the step's q, k and v rows are taken from these 32-bit
+    // partial sums of the q/k/v product ([qkv_splits][batch][row], columns q heads, k heads, v heads), added in
+    // split order, rotated (rotate-half pairing over the first rotary_dim dims; none if inv_freq is null) at
+    // position len_after - 1 and rounded to bfloat16; k and v are also written to their cache row.
+    const float* qkv_part; int qkv_splits; long long qkv_split_stride, qkv_row_stride;
+    const float* inv_freq; int rotary_dim;
 };
 
 template <int HD> struct DCfg {
@@ -364,8 +370,8 @@ template <int HD> struct MCfg {
     static constexpr int MT_W = HD >= 128 ? HD / 128 : 1;            // 16-dim tiles of O^T per warp
     static constexpr int PV_WARPS = HD / 16 / MT_W;                  // warps that own a slice of O^T
     static constexpr int SCORE_FLOATS = 3 * 8 * SROW + 16;           // partial halves, final, page maxima
-    static constexpr int SMEM = STAGES * STAGE_BYTES + SCORE_FLOATS * 4 + 64 /* barriers */ + (1024 + 1) * 4 /* stream: page prefix */
-                                + 1024 /* alignment */;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + SCORE_FLOATS * 4 + 64 /* barriers */ + (1024 + 4) * 4 /* stream: page prefix */
+                                + 8 * HD * 2 /* rotated queries */ + 1024 /* alignment */;
 };
 // byte offset of (key row r, 16-byte chunk c of the head dim) inside a swizzled page
 __device__ __forceinline__ int sw_off(int r, int c) {
@@ -430,6 +436,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     float* pm = sf + 8 * SROW;                                       // [8 heads][2] maxima of the page's two key halves
     uint64_t* full = (uint64_t*)(pm + 16);
     int* pref = (int*)(full + 8);                                    // stream: [batch + 1] pages before each sequence
+    bf16* q_s = (bf16*)(pref + 1024 + 4);                            // [8 heads][HD] this run's queries, rotated (fused rotation)
     __shared__ int s_last[2], s_pend[2][4];         // per pending part: sequence, kv head, parts of the pair, first CTA
 
     const int G = a.n_heads / a.n_kv_heads;                         // 1..8 query heads on columns 0..G-1
@@ -524,8 +531,80 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     if (tid == ISSUER)
         while (ahead.left > 0 && issued < C::STAGES && ahead.first_page + ahead.pg != ahead.hot) issue();
     pdl_wait();                                     // the new token's cache rows and q come from earlier kernels
-    if (tid == ISSUER)
+
+    // ---- fused rotation: this step's q, k, v come as partial sums of their product
+    const bool fused = a.qkv_part != nullptr;
+    const int half = (a.inv_freq != nullptr) ? (a.rotary_dim >> 1) : 0;      // rotated pairs per head
+    const int k_off = a.n_heads * HD, v_off = (a.n_heads + a.n_kv_heads) * HD;
+    auto qkv_val = [&](int b, int col) -> float {   // column `col` of sequence b's row: the splits added in order
+        const float* p = a.qkv_part + (size_t)b * a.qkv_row_stride + col;
+        float v = p[0];
+        for (int s0 = 1; s0 < a.qkv_splits; s0 += 4) {              // four independent loads at a time
+            float t4[4];
+#pragma unroll
+            for (int k = 0; k < 4; k++) t4[k] = (s0 + k < a.qkv_splits) ? p[(size_t)(s0 + k) * a.qkv_split_stride] : 0.f;
+#pragma unroll
+            for (int k = 0; k < 4; k++) if (s0 + k < a.qkv_splits) v += t4[k];
+        }
+        return v;
+    };
+    // head `col0` (first column) of sequence b, rotated at `pos`, rounded, to dst[0..HD) (and dst2 if set)
+    auto rotate_head = [&](int b, int col0, int pos, bf16* dst, bf16* dst2, int x) {
+        // x in [0, HD - half): a rotated pair, or a dim beyond the rotary part that passes through
+        if (x < half) {
+            float sn, cs;
+            sincosf((float)pos * a.inv_freq[x], &sn, &cs);
+            const float x0 = qkv_val(b, col0 + x), x1 = qkv_val(b, col0 + x + half);
+            const bf16 y0 = __float2bfloat16_rn(x0 * cs - x1 * sn), y1 = __float2bfloat16_rn(x1 * cs + x0 * sn);
+            dst[x] = y0; dst[x + half] = y1;
+            if (dst2) { dst2[x] = y0; dst2[x + half] = y1; }
+        } else {
+            const int d = x + half;
+            const bf16 y = __float2bfloat16_rn(qkv_val(b, col0 + d));
+            dst[d] = y;
+            if (dst2) dst2[d] = y;
+        }
+    };
+    if (fused && warp >= TW / 2) {
+        // the upper half of the warps rotates the first run's query heads into shared memory meanwhile
+        const int len0 = a.len_after[cur.b], per = HD - half;
+        for (int x = tid - (TW / 2) * 32; x < G * per; x += (TW / 2) * 32)
+            rotate_head(cur.b, (cur.kvh * G + x / per) * HD, len0 - 1, q_s + (x / per) * HD, nullptr, x % per);
+    }
+    if (fused) {
+        // The runs of this CTA that hold the page of their sequence's new token: this CTA, and no other, reads
+        // that page, so it (the lower half of its warps) writes the token's k and v rows there first.
+        PageCursor w = cur;
+        while (w.left > 0 && warp < TW / 2) {
+            const int n = min(w.left, w.np - w.pg), hot_rel = w.hot - w.first_page;
+            if (hot_rel >= w.pg && hot_rel < w.pg + n) {
+                const int len = a.len_after[w.b], pos = len - 1;
+                const int r = (a.ring_rows > 0) ? pos % a.ring_rows : pos;
+                const int page = a.page_table[(size_t)w.b * a.pt_stride + r / PAGE];
+                const size_t off = ((size_t)(page * a.n_kv_heads + w.kvh) * PAGE + (r % PAGE)) * HD;
+                bf16* kd = (bf16*)a.k_pool + off;
+                bf16* vd = (bf16*)a.v_pool + off;
+                for (int x = tid; x < (HD - half) + HD; x += (TW / 2) * 32) {
+                    if (x < HD - half) rotate_head(w.b, k_off + w.kvh * HD, pos, kd, nullptr, x);
+                    else vd[x - (HD - half)] = __float2bfloat16_rn(qkv_val(w.b, v_off + w.kvh * HD + x - (HD - half)));
+                }
+            }
+            w.left -= n;
+            w.pg += n;
+            if (w.pg == w.np && w.left > 0) {
+                w.pg = 0;
+                if (++w.kvh == a.n_kv_heads) { w.kvh = 0; w.b++; w.np = seq_pages(w.b, w.first_page, w.hot); }
+            }
+        }
+        // the rows were written by ordinary stores and are read by the copy engine next
+        __threadfence();
+        asm volatile("fence.proxy.async;" ::: "memory");
+        __syncthreads();
+    }
+    if (tid == ISSUER) {
+        if (fused) asm volatile("fence.proxy.async;" ::: "memory");
         while (ahead.left > 0 && issued < C::STAGES) issue();
+    }
 
     const float inv_cap = a.cap > 0.f ? 1.f / a.cap : 0.f;
     const int mt = warp & 3, kh = warp >> 2;        // phase A role: 16 keys (m-tile) x half of head_dim
@@ -568,7 +647,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     float o[C::MT_W][4], o2[C::MT_W][4];            // accumulator rows are dims, columns heads 2t, 2t+1; two chains
     // running maximum of the heads this lane meets: `quad` (its P^T column) and 2t, 2t+1 (its O^T columns)
     float m_b = -INFINITY, m_c0 = -INFINITY, m_c1 = -INFINITY, l_b = 0.f;
-    auto begin_run = [&]() {
+    auto begin_run = [&](bool first_run) {
         b = cur.b; kvh = cur.kvh;
         seg_pg0 = cur.pg; seg_n = min(cur.left, cur.np - cur.pg); seg_np = cur.np; seg_first = cur.first_page;
         run_left = seg_n;
@@ -580,6 +659,18 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         old_beg = wrapped ? (newest + 1 == a.ring_rows ? 0 : newest + 1) : 0;
         no_invalid = wrapped && n_old == 0;                         // a full ring whose every row is in the window
         const bf16* qp = (const bf16*)a.q + (size_t)b * a.q_stride + (size_t)(kvh * G + quad) * HD + kh * (HD / 2);
+        if (fused) {
+            // the pair's query heads, rotated, go through shared memory: every thread rotates some of their dims
+            // (the first run's are there already)
+            if (!first_run) {
+                for (int x = tid; x < G * (HD - half); x += TW * 32) {
+                    const int g = x / (HD - half);
+                    rotate_head(b, (kvh * G + g) * HD, len - 1, q_s + g * HD, nullptr, x % (HD - half));
+                }
+                __syncthreads();
+            }
+            qp = q_s + quad * HD + kh * (HD / 2);
+        }
 #pragma unroll
         for (int ks = 0; ks < C::KS_W; ks++) {
             qb[ks][0] = (quad < G) ? *(const uint32_t*)(qp + ks * 16 + 2 * t) : 0u;
@@ -684,12 +775,10 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     };
 
     const int my_pages = cur.left;
-    if (my_pages == 0) {                            // (split only) an empty piece still reports "nothing here"
-        begin_run();
-        end_run();
-    }
+    begin_run(true);                                // the first run; further ones (stream only) begin inside the loop
+    if (my_pages == 0) end_run();                   // (split only) an empty piece still reports "nothing here"
     for (int i = 0; i < my_pages; i++) {
-        if (run_left == 0) begin_run();
+        if (STREAM && run_left == 0) begin_run(false);
         {
             const int j = seg_n - run_left;
 
@@ -914,6 +1003,14 @@ extern "C" int tb_attn_decode_takes(int dtype, int n_heads, int n_kv_heads, int 
 
 static int run_decode(const DecodeArgs* args, int dtype, int batch, bool tensor_cores, cudaStream_t stream);
 
+static int check_rotation(const DecodeArgs& a) {
+    if (a.qkv_splits < 1 || a.qkv_row_stride < (long long)(a.n_heads + 2 * a.n_kv_heads) * a.hd)
+        return tb_refuse("attn_decode: the q/k/v partial sums need at least one split and rows of (n_heads + 2 n_kv_heads) * head_dim");
+    if (a.inv_freq != nullptr && (a.rotary_dim <= 0 || (a.rotary_dim & 1) || a.rotary_dim > a.hd))
+        return tb_refuse("attn_decode: rotary_dim=%d must be even and within head_dim=%d", a.rotary_dim, a.hd);
+    return 0;
+}
+
 // The product path: tensor-core variant.
 extern "C" int tb_attn_decode(const DecodeArgs* args, int dtype, int batch, cudaStream_t stream) {
     return run_decode(args, dtype, batch, true, stream);
@@ -939,6 +1036,10 @@ static int run_decode(const DecodeArgs* args, int dtype, int batch, bool tensor_
     const int g = a.n_heads / a.n_kv_heads;
     int st = -1;
     if (a.hd < 64) tensor_cores = false;            // a 64-byte row has no 128-byte swizzled box
+    if (a.qkv_part != nullptr) {
+        if (!tensor_cores) return tb_refuse("attn_decode: only the tensor-core kernel (head_dim >= 64) rotates by itself");
+        if (int r = check_rotation(a)) return r;
+    } else if (a.q == nullptr) return tb_refuse("attn_decode: q is missing");
     if (tensor_cores) {
         switch (a.hd) {
         case 64: st = launch_mma<64, false>(a, batch, 0, stream); break;
@@ -988,6 +1089,8 @@ extern "C" int tb_attn_decode_stream(const DecodeArgs* args, int dtype, int batc
     if (batch > STREAM_MAX_BATCH) return tb_refuse("attn_decode_stream: batch %d, takes up to %d", batch, STREAM_MAX_BATCH);
     if (n_ctas < 1 || n_ctas > 65535) return tb_refuse("attn_decode_stream: n_ctas=%d", n_ctas);
     if (a.partial == nullptr || a.tickets == nullptr) return tb_refuse("attn_decode_stream: needs scratch and ticket counters");
+    if (a.qkv_part != nullptr) { if (int r = check_rotation(a)) return r; }
+    else if (a.q == nullptr) return tb_refuse("attn_decode_stream: q is missing");
     if (a.ring_rows > 0 && (a.ring_rows % PAGE || a.window <= 0 || a.window > a.ring_rows))
         return tb_refuse("attn_decode: a ring of %d rows cannot hold a window of %d", a.ring_rows, a.window);
     if (((uintptr_t)a.q & 15) || (a.q_stride % 8) || ((uintptr_t)a.k_pool & 15) || ((uintptr_t)a.v_pool & 15))

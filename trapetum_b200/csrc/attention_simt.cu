@@ -129,6 +129,8 @@ struct DecodeArgs {
     int n_heads, n_kv_heads, hd, page_rows, ring_rows, window, n_splits;
     float scale, cap;
     int* tickets;                               // used by the tensor-core kernel only; ignored here
+    const float* qkv_part; int qkv_splits; long long qkv_split_stride, qkv_row_stride;   // likewise
+    const float* inv_freq; int rotary_dim;
 };
 
 template <typename T, int NC>

@@ -292,7 +292,9 @@ class _DecodeArgs(ctypes.Structure):
                 ("partial", c_void_p),
                 ("n_heads", c_int), ("n_kv_heads", c_int), ("hd", c_int), ("page_rows", c_int),
                 ("ring_rows", c_int), ("window", c_int), ("n_splits", c_int),
-                ("scale", c_float), ("cap", c_float), ("tickets", c_void_p)]
+                ("scale", c_float), ("cap", c_float), ("tickets", c_void_p),
+                ("qkv_part", c_void_p), ("qkv_splits", c_int), ("qkv_split_stride", c_longlong),
+                ("qkv_row_stride", c_longlong), ("inv_freq", c_void_p), ("rotary_dim", c_int)]
 
 
 def attn_decode_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
@@ -638,13 +640,47 @@ def _tickets(device: torch.device) -> torch.Tensor:
     return t
 
 
+def _decode_partials(part: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, variant: str, rotate):
+    """Checks the partial sums handed to a decode kernel that rotates by itself; returns them and a stand-in for q."""
+    inv_freq, rotary_dim = rotate
+    width = (n_heads + 2 * n_kv_heads) * head_dim
+    if variant != "mma" or head_dim < 64:
+        raise KernelError("attention: only the tensor-core decode kernel (head_dim >= 64) rotates by itself")
+    if part.dtype != torch.float32 or part.dim() != 3 or part.shape[2] != width or part.stride(2) != 1:
+        raise KernelError(f"attention: the q/k/v partial sums must be float32 [splits, batch, {width}]")
+    if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.numel() != rotary_dim // 2
+                                 or rotary_dim % 2 or not 0 < rotary_dim <= head_dim):
+        raise KernelError("attention: inv_freq must be float32 [rotary_dim/2], rotary_dim even and within head_dim")
+    _cuda(inv_freq)
+    return part, torch.empty((part.shape[1], 0), dtype=torch.bfloat16, device=part.device)
+
+
+def _set_rotation(a, part, rotate) -> None:
+    if part is None:
+        a.qkv_part = None; a.qkv_splits = 0; a.qkv_split_stride = 0; a.qkv_row_stride = 0
+        a.inv_freq = None; a.rotary_dim = 0
+        return
+    inv_freq, rotary_dim = rotate
+    a.q = None; a.q_stride = 0
+    a.qkv_part = part.data_ptr(); a.qkv_splits = part.shape[0]
+    a.qkv_split_stride = part.stride(0); a.qkv_row_stride = part.stride(1)
+    a.inv_freq = inv_freq.data_ptr() if inv_freq is not None else None
+    a.rotary_dim = rotary_dim if inv_freq is not None else 0
+
+
 def attn_decode_tma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
                     len_after: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
                     softcap: float, window: int, ring_rows: int, n_splits: int = 1,
-                    variant: str = "mma") -> torch.Tensor:
+                    variant: str = "mma", rotate=None) -> torch.Tensor:
     """Decode attention with pages staged in shared memory by bulk copies (see attention_decode.cu).
-    ``variant``: "mma" (tensor cores, the product path) or "lanes" (scalar, kept for comparison)."""
+    ``variant``: "mma" (tensor cores, the product path) or "lanes" (scalar, kept for comparison).
+    ``rotate`` = (inv_freq or None, rotary_dim), "mma" only: ``q`` is then the float32 partial sums
+    [splits, batch, (n_heads + 2 n_kv_heads) * head_dim] of the q/k/v product; the kernel adds them, rotates q and k
+    at the new token's position, and writes k and v to the cache itself (no separate rotation kernel)."""
     _cuda(q, k_pool, v_pool, page_table, len_after)
+    part = None
+    if rotate is not None:
+        part, q = _decode_partials(q, n_heads, n_kv_heads, head_dim, variant, rotate)
     _rows_contig(q, "attention: q")
     B = q.shape[0]
     if not attn_decode_takes(q.dtype, n_heads, n_kv_heads, head_dim):
@@ -671,6 +707,7 @@ def attn_decode_tma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     a.scale = scale; a.cap = softcap or 0.0
     fused_fold = variant == "mma" and head_dim >= 64 and n_splits > 1 and B * n_kv_heads <= _TICKET_SLOTS
     a.tickets = _tickets(q.device).data_ptr() if fused_fold else None
+    _set_rotation(a, part, rotate)
     lib = build.load("attention_decode")
     fn = lib.tb_attn_decode if variant == "mma" else lib.tb_attn_decode_lanes
     _check(lib, fn(ctypes.byref(a), c_int(code(q.dtype)), c_int(B), _stream()), "attn_decode",
@@ -680,11 +717,15 @@ def attn_decode_tma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
 
 def attn_decode_stream(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
                        len_after: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
-                       softcap: float, window: int, ring_rows: int, n_ctas: Optional[int] = None) -> torch.Tensor:
+                       softcap: float, window: int, ring_rows: int, n_ctas: Optional[int] = None,
+                       rotate=None) -> torch.Tensor:
     """Decode attention on tensor cores with all pages of the launch dealt out evenly to ``n_ctas`` CTAs
     (default: one per SM), wherever the sequences end: the time of a launch follows the sum of the lengths,
-    not the longest one (see attention_decode.cu)."""
+    not the longest one (see attention_decode.cu).  ``rotate``: as in :func:`attn_decode_tma`."""
     _cuda(q, k_pool, v_pool, page_table, len_after)
+    part = None
+    if rotate is not None:
+        part, q = _decode_partials(q, n_heads, n_kv_heads, head_dim, "mma", rotate)
     _rows_contig(q, "attention: q")
     B = q.shape[0]
     if not attn_decode_stream_takes(q.dtype, n_heads, n_kv_heads, head_dim, B):
@@ -714,9 +755,15 @@ def attn_decode_stream(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tens
     a.ring_rows = ring_rows; a.window = window or 0; a.n_splits = 0
     a.scale = scale; a.cap = softcap or 0.0
     a.tickets = _tickets(q.device).data_ptr()
+    _set_rotation(a, part, rotate)
     _check(lib, lib.tb_attn_decode_stream(ctypes.byref(a), c_int(code(q.dtype)), c_int(B), c_int(n_ctas), _stream()),
            "attn_decode_stream")
     return out
+
+
+def attn_decode_rotates(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int) -> bool:
+    """Whether :func:`attn_decode` can take the q/k/v partial sums and rotate by itself (``rotate=``)."""
+    return attn_decode_takes(dtype, n_heads, n_kv_heads, head_dim) and head_dim >= 64
 
 
 def attn_decode_stream_takes(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int, batch: int) -> bool:
@@ -755,21 +802,27 @@ def choose_decode_splits(batch: int, n_kv_heads: int, pages: int, sms: int) -> i
 
 
 def attn_decode(q, k_pool, v_pool, page_table, len_after, n_heads, n_kv_heads, head_dim, scale, softcap, window,
-                ring_rows, len_bucket: int, uneven: bool = False) -> torch.Tensor:
+                ring_rows, len_bucket: int, uneven: bool = False, rotate=None) -> torch.Tensor:
     """Decode attention, kernel and partition chosen here.  ``len_bucket``: an upper bound of the longest
     context of the batch (the engine passes a power of two so that the choice is stable across steps).
     ``uneven``: the batch's contexts differ much in length; the pages are then dealt out to the CTAs as one
     stream, so that the launch's time follows the sum of the lengths and not the longest one."""
-    B = q.shape[0]
-    if uneven and attn_decode_stream_takes(q.dtype, n_heads, n_kv_heads, head_dim, B):
-        return attn_decode_stream(q, k_pool, v_pool, page_table, len_after, n_heads, n_kv_heads, head_dim, scale,
-                                  softcap, window, ring_rows)
+    B = q.shape[0] if rotate is None else q.shape[1]
+    dt = q.dtype if rotate is None else torch.bfloat16
     rows = min(len_bucket, ring_rows) if ring_rows else len_bucket
     pages = max(1, (rows + PAGE_ROWS - 1) // PAGE_ROWS)
-    splits = choose_decode_splits(B, n_kv_heads, pages, sm_count(q.device))
-    if attn_decode_takes(q.dtype, n_heads, n_kv_heads, head_dim):
+    sms = sm_count(q.device)
+    splits = choose_decode_splits(B, n_kv_heads, pages, sms)
+    # One stream of pages over one CTA per SM when the lengths differ much, and when cutting every sequence would
+    # take several rounds of CTAs: each CTA of a round pays its start-up again, a streaming CTA pays it once.
+    if (uneven or B * n_kv_heads * splits > 2 * sms) and attn_decode_stream_takes(dt, n_heads, n_kv_heads, head_dim, B):
+        return attn_decode_stream(q, k_pool, v_pool, page_table, len_after, n_heads, n_kv_heads, head_dim, scale,
+                                  softcap, window, ring_rows, rotate=rotate)
+    if attn_decode_takes(dt, n_heads, n_kv_heads, head_dim):
         variant = "lanes" if head_dim < 64 else "mma"     # a 64-byte row has no swizzled box for the tensor-core kernel
         return attn_decode_tma(q, k_pool, v_pool, page_table, len_after, n_heads, n_kv_heads, head_dim, scale,
-                               softcap, window, ring_rows, splits, variant)
+                               softcap, window, ring_rows, splits, variant, rotate)
+    if rotate is not None:
+        raise KernelError("attention: this shape's decode kernel does not rotate by itself")
     return attn_decode_simt(q, k_pool, v_pool, page_table, len_after, n_heads, n_kv_heads, head_dim, scale,
                             softcap, window, ring_rows, splits)

@@ -82,6 +82,13 @@ class Attention(Mixer):
             if dt == torch.bfloat16 and x.shape[0] <= 128 and ops.gemm_tc_takes(x, self.w_qkv):
                 # few tokens: the product comes as split-K partial sums, which the rotation kernel adds up
                 part = ops.gemm_tc(x, self.w_qkv, torch.float32, partials=True)
+                rotate = self.position.rotary_table()
+                if not ctx.is_prefill and rotate is not None and ops.attn_decode_rotates(dt, self.n_heads, self.n_kv, self.hd):
+                    # decoding: the attention kernel adds them up, rotates and appends to the cache by itself
+                    o = ops.attn_decode(part, line.k, line.v, line.page_table, ctx.len_after, self.n_heads, self.n_kv,
+                                        self.hd, self.scale, self.softcap, self.window or 0, line.ring_rows,
+                                        ctx.len_bucket, ctx.uneven, rotate)
+                    return linear_partials(o, self.w_o)
                 qkv = torch.empty(part.shape[1:], dtype=dt, device=x.device)
                 self.position.rotate_and_store(qkv, self.n_heads, self.n_kv, ctx, line, store=True, partial=part)
             else:

@@ -102,7 +102,11 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
-    pass
+    def rotary_table(self):
+        """``(inv_freq, rotary_dim)`` if this encoding is the rotate-half rotation of the first ``rotary_dim`` dims
+        of q and k by ``position * inv_freq[i]`` (``(None, 0)``: it changes nothing), so that a mixer's kernel
+        may apply it itself; None if it is anything else (the mixer then calls ``rotate_and_store``)."""
+        return None
 
 
 class Mixer(Part):

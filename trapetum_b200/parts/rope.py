@@ -36,6 +36,9 @@ class Rope(PositionEncoding):
     def kernel_files(self):
         return ("rope_kv",)
 
+    def rotary_table(self):
+        return self.inv_freq, self.rotary_dim
+
     def rotate_and_store(self, qkv, n_heads, n_kv_heads, ctx, line, store: bool, partial=None) -> None:
         """Rotate q and k inside ``qkv`` at the step's positions; with ``store`` also
         write k and v into the cache line.  ``partial``: split-K partial sums of the projection
@@ -55,6 +58,9 @@ class NoPosition(PositionEncoding):
 
     def kernel_files(self):
         return ("rope_kv",)
+
+    def rotary_table(self):
+        return None, 0
 
     def rotate_and_store(self, qkv, n_heads, n_kv_heads, ctx, line, store: bool, partial=None) -> None:
         if store or partial is not None:
