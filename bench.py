@@ -199,6 +199,63 @@ def time_prefill(engine, torch, T, vocab, reps, warmup):
     return times[len(times) // 2]
 
 
+def leave_out_report(engine, model, cfg, torch, args, warmup) -> int:
+    """What each kind of launch costs inside the step's graph: the step is timed whole, then with that kind
+    replaced by a stand-in that launches nothing and returns a buffer of the right shape."""
+    from trapetum_b200.csrc import ops
+    from trapetum_b200.engine import Engine
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    qd, kvd = cfg["num_attention_heads"] * cfg["head_dim"], cfg["num_key_value_heads"] * cfg["head_dim"]
+    real = {k: getattr(ops, k) for k in ("attn_decode", "add_rmsnorm", "gemm_tc")}
+    bufs = {}
+
+    def buf(key, shape, dtype):
+        k = (key, tuple(shape), dtype)
+        if k not in bufs:
+            bufs[k] = torch.zeros(shape, dtype=dtype, device="cuda:0")
+        return bufs[k]
+
+    def no_attn(q, *a, **kw):
+        rows = q.shape[1] if q.dim() == 3 else q.shape[0]
+        return buf("attn", (rows, qd), torch.bfloat16)
+
+    def no_norm(h, a, wa, ea, oa, wb=None, eps_b=0.0, off_b=0.0, out_dtype=None):
+        return buf("norm", h.shape, out_dtype) if wb is not None else None
+
+    def no_gemm(shape):
+        def f(a, w, out_dtype, softcap=0.0, splits=None, out=None, partials=False, gated_act=None):
+            if tuple(w.shape) != shape:
+                return real["gemm_tc"](a, w, out_dtype, softcap, splits, out, partials, gated_act)
+            M, N = a.shape[0], w.shape[0]
+            if gated_act:
+                return buf("g", (M, N // 2), torch.bfloat16)
+            return buf("p", (1, M, N), torch.float32) if partials else buf("o", (M, N), out_dtype)
+        return f
+
+    kinds = {"nothing": {}, "attention": {"attn_decode": no_attn}, "add_rmsnorm": {"add_rmsnorm": no_norm},
+             "gemm qkv": {"gemm_tc": no_gemm((qd + 2 * kvd, H))}, "gemm o": {"gemm_tc": no_gemm((H, qd))},
+             "gemm gate_up": {"gemm_tc": no_gemm((2 * I, H))}, "gemm down": {"gemm_tc": no_gemm((H, I))},
+             "gemm head": {"gemm_tc": no_gemm((V, H))}}
+    whole = None
+    try:
+        for name, patch in kinds.items():
+            for k, v in real.items():
+                setattr(ops, k, v)
+            for k, v in patch.items():
+                setattr(ops, k, v)
+            eng = Engine(model, max_tokens=args.batch * args.context, max_slots=args.batch)
+            ms, _, launches, _ = time_decode(eng, torch, args.batch, args.context, args.steps, warmup, V)
+            whole = ms if whole is None else whole
+            print(json.dumps({"left_out": name, "ms_per_step": round(ms, 4), "launches": launches,
+                              "saves_us": round((whole - ms) * 1e3, 1),
+                              "saves_us_per_layer": round((whole - ms) * 1e3 / args.layers, 2)}), flush=True)
+            del eng
+    finally:
+        for k, v in real.items():
+            setattr(ops, k, v)
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -210,6 +267,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=GEMMA2_2B["num_hidden_layers"],
                     help="fewer layers than the model has (same layer sizes); both numbers are reported")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    ap.add_argument("--leave-out", action="store_true",
+                    help="instead of the bench line: the decode step re-timed with one kind of launch left out at a "
+                         "time (its results are then wrong; only its time is of interest), one line per kind")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -234,6 +294,9 @@ def main() -> int:
     for g in engine.cache.groups:                         # random keys and values, small enough for a sane softmax
         g.k.normal_(0.0, 0.5)
         g.v.normal_(0.0, 0.5)
+
+    if args.leave_out:
+        return leave_out_report(engine, model, cfg, torch, args, warmup)
 
     with ClockSampler() as clocks:
         dev_ms, e2e_ms, launches, h2d = time_decode(engine, torch, args.batch, args.context, args.steps, warmup, V)
