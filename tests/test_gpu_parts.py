@@ -309,3 +309,193 @@ def test_a_toy_mixer_with_its_own_state_is_registered_built_and_stepped(tmp_path
     for tok in out[0]:
         assert tok == int(_toy_plain(cfg, pw, ids)[-1].argmax())
         ids.append(tok)
+
+
+# ---------------------------------------------------------------------------
+# A toy feed-forward with routing and a toy position encoding, defined here, around the library's attention
+# ---------------------------------------------------------------------------
+def _register_routed():
+    from trapetum_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, register_architecture
+    from trapetum_b200.config.base import _get
+    from trapetum_b200.csrc import ops
+    from trapetum_b200.parts import FeedForward, PositionEncoding, build_part, register_part
+    from trapetum_b200.weights import TensorSpec
+
+    class Damped(PositionEncoding):
+        """q_t *= 1 + rise * t and k_j *= cos(swing * j): not a rotation, so it answers no rotary table and the
+        attention part has to call it.  Plain torch on the device, then the library's cache write."""
+
+        def __init__(self, params, prefix, rt):
+            super().__init__(params, prefix, rt)
+            self.head_dim, self.rise, self.swing = int(params["head_dim"]), float(params["rise"]), float(params["swing"])
+
+        def kernel_files(self):
+            return ("rope_kv",)
+
+        def rotate_and_store(self, qkv, n_heads, n_kv_heads, ctx, line, store, partial=None):
+            if partial is not None:
+                qkv.copy_(partial.sum(0))
+            pos = ctx.positions.float()[:, None]
+            qw, kw = n_heads * self.head_dim, n_kv_heads * self.head_dim
+            qkv[:, :qw] = (qkv[:, :qw].float() * (1.0 + self.rise * pos)).to(qkv.dtype)
+            if kw:
+                qkv[:, qw:qw + kw] = (qkv[:, qw:qw + kw].float() * torch.cos(self.swing * pos)).to(qkv.dtype)
+            if store:
+                ops.rope_kv(qkv, n_heads, n_kv_heads, self.head_dim, 0, None, ctx.positions, ctx.token_seq,
+                            ctx.len_after, line.k, line.v, line.page_table, line.ring_rows)
+
+    class Routed(FeedForward):
+        """Each token goes to the expert with the largest router logit (32-bit), weighted by that logit's
+        softmax probability; the experts are the library's gated feed-forwards.  All experts run on all
+        tokens and a mask keeps the chosen one: a toy, with no launch that depends on host values."""
+
+        def __init__(self, params, prefix, rt):
+            super().__init__(params, prefix, rt)
+            self.h, self.n = int(params["hidden_size"]), int(params["experts"])
+            self.experts = [build_part("feed_forward", PartSpec("gated_mlp", {
+                "hidden_size": self.h, "intermediate_size": int(params["intermediate_size"]), "activation": "silu",
+                "gate": "g.weight", "up": "u.weight", "down": "d.weight"}), f"{prefix}experts.{e}.", rt)
+                for e in range(self.n)]
+
+        def tensor_specs(self):
+            specs = {self._name("router"): TensorSpec((self.n, self.h))}
+            for e in self.experts:
+                specs.update(e.tensor_specs())
+            return specs
+
+        def bind(self, tensors):
+            self.router = tensors[self._name("router")].float()
+            for e in self.experts:
+                e.bind(tensors)
+
+        def kernel_files(self):
+            return tuple(k for e in self.experts for k in e.kernel_files())
+
+        def forward(self, x, ctx):
+            p = torch.softmax(x.float() @ self.router.T, -1)                    # router in 32-bit
+            top = p.argmax(-1)
+            out = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+            for e, part in enumerate(self.experts):
+                y = _whole(part.forward(x, ctx)).float()
+                out += y * (p[:, e] * (top == e))[:, None]
+            return out
+
+    register_part("position", "test_damped", Damped)
+    register_part("feed_forward", "test_routed", Routed)
+
+    @dataclass(frozen=True)
+    class RoutedConfig:
+        layers: int; hidden: int; heads: int; kv_heads: int; head_dim: int; inter: int; experts: int; vocab: int; eps: float
+
+        @classmethod
+        def from_dict(cls, d):
+            g = lambda k, t=int: _get(d, "r_" + k, t)
+            return cls(g("layers"), g("hidden"), g("heads"), g("kv_heads"), g("head_dim"), g("inter"), g("experts"),
+                       g("vocab"), g("eps", float))
+
+    def spec(c):
+        norm = lambda n: PartSpec("rmsnorm", {"size": c.hidden, "eps": c.eps, "unit_offset": False, "weight": n})
+        layers = tuple(LayerSpec(
+            block=PartSpec("pre_norm", {"pre_mixer_norm": norm("n1.weight"), "pre_ffn_norm": norm("n2.weight")}),
+            mixer=PartSpec("attention", {"hidden_size": c.hidden, "num_heads": c.heads, "num_kv_heads": c.kv_heads,
+                                         "head_dim": c.head_dim, "scale": c.head_dim ** -0.5, "softcap": None,
+                                         "window": None, "q": "q.weight", "k": "k.weight", "v": "v.weight", "o": "o.weight",
+                                         "position": PartSpec("test_damped", {"head_dim": c.head_dim, "rise": 0.01,
+                                                                              "swing": 0.3})}),
+            feed_forward=PartSpec("test_routed", {"hidden_size": c.hidden, "intermediate_size": c.inter,
+                                                  "experts": c.experts, "router": "router.weight"}),
+            prefix=f"blocks.{i}.") for i in range(c.layers))
+        return ModelSpec(architecture="TestRoutedLM", hidden_size=c.hidden, vocab_size=c.vocab,
+                         embedding=PartSpec("embedding", {"vocab_size": c.vocab, "hidden_size": c.hidden, "scale": 1.0,
+                                                          "weight": "emb.weight"}),
+                         layers=layers, schedule=tuple(ScheduleEntry(i) for i in range(c.layers)),
+                         final_norm=norm("out_norm.weight"),
+                         head=PartSpec("linear_head", {"vocab_size": c.vocab, "hidden_size": c.hidden, "softcap": None,
+                                                       "weight": "head.weight", "tied_to": None}),
+                         max_positions=512)
+    register_architecture("TestRoutedLM", RoutedConfig, spec)
+
+
+def _routed_plain(cfg, w, ids):
+    """The routed toy model, whole sequence, plain torch on the CPU in 64-bit."""
+    H, nh, nkv, hd, eps = cfg["r_hidden"], cfg["r_heads"], cfg["r_kv_heads"], cfg["r_head_dim"], cfg["r_eps"]
+    w = {k: v.double() for k, v in w.items()}
+    norm = lambda x, g: x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * g
+    T = len(ids)
+    pos = torch.arange(T, dtype=torch.float64)[:, None, None]
+    h = w["emb.weight"][torch.tensor(ids)]
+    margin = torch.full((T,), float("inf"), dtype=torch.float64)    # how clear the closest routing decision at a place is
+    for i in range(cfg["r_layers"]):
+        p = f"blocks.{i}."
+        x = norm(h, w[p + "n1.weight"])
+        q = (x @ w[p + "q.weight"].T).view(T, nh, hd) * (1.0 + 0.01 * pos)
+        k = (x @ w[p + "k.weight"].T).view(T, nkv, hd) * torch.cos(0.3 * pos)
+        v = (x @ w[p + "v.weight"].T).view(T, nkv, hd)
+        o = torch.zeros(T, nh, hd, dtype=torch.float64)
+        for hh in range(nh):
+            s = (q[:, hh] @ k[:, hh // (nh // nkv)].T) * hd ** -0.5
+            s = s.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
+            o[:, hh] = torch.softmax(s, -1) @ v[:, hh // (nh // nkv)]
+        h = h + o.reshape(T, nh * hd) @ w[p + "o.weight"].T
+        x = norm(h, w[p + "n2.weight"])
+        pr = torch.softmax(x @ w[p + "router.weight"].T, -1)
+        top = pr.argmax(-1)
+        best2 = pr.topk(2, -1).values
+        margin = torch.minimum(margin, best2[:, 0] - best2[:, 1])
+        y = torch.zeros_like(h)
+        for e in range(cfg["r_experts"]):
+            g = x @ w[p + f"experts.{e}.g.weight"].T
+            ye = ((g * torch.sigmoid(g)) * (x @ w[p + f"experts.{e}.u.weight"].T)) @ w[p + f"experts.{e}.d.weight"].T
+            y += ye * (pr[:, e] * (top == e))[:, None]
+        h = h + y
+    return (norm(h, w["out_norm.weight"]) @ w["head.weight"].T).float(), margin.float()
+
+
+@pytest.mark.parametrize("dtype,hd", [("float32", 24), ("bfloat16", 64)])
+def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_around_the_library_attention(tmp_path, dtype, hd):
+    """Parts of the test's own (a feed-forward that routes, a position encoding that is no rotation) are
+    registered, built into a model with the library's attention, cache and step function, and stepped:
+    prompts of unequal lengths, then token by token, against a plain whole-sequence computation.  In
+    bfloat16 with a head size the tensor-core decode kernel takes, this is also the path on which that kernel
+    must NOT rotate by itself."""
+    import trapetum_b200 as tb
+    _register_routed()
+    cfg = {"architectures": ["TestRoutedLM"], "r_layers": 2, "r_hidden": 48, "r_heads": 3, "r_kv_heads": 1, "r_head_dim": hd,
+           "r_inter": 80, "r_experts": 3, "r_vocab": 70, "r_eps": 1e-5}
+    d = str(tmp_path / "routed")
+    tb.write_random_model(d, cfg, 4, 0.15, 0.3)
+    # a router with random weights of this size is nearly undecided everywhere: make it decide
+    from safetensors.torch import load_file, save_file
+    stored = load_file(d + "/model.safetensors")
+    for k in stored:
+        if k.endswith("router.weight"):
+            stored[k] = (stored[k].float() * 25.0).to(stored[k].dtype)
+    save_file(stored, d + "/model.safetensors")
+    pw = plain.load_folder(d)[1]
+    model = tb.load_model(d, dtype)
+    eng = tb.Engine(model, 64 * 6, max_slots=3)
+    prompts = make_prompts(70, [33, 9, 20], seed=2)
+    both = [_routed_plain(cfg, pw, p) for p in prompts]
+    truth = [b[0] for b in both]
+    # In bfloat16 a routing decision that is nearly a tie may fall the other way: that is another function, not
+    # an error, and it changes every later place of its sequence through the keys and values.  So a sequence is
+    # compared up to its first place whose closest decision is not clear in the 64-bit computation.
+    clear = 0.0 if dtype == "float32" else 0.1
+    upto = []
+    for _, margin in both:
+        unclear = (margin <= clear).nonzero()
+        upto.append(int(unclear[0]) if len(unclear) else len(margin))
+    tol = 2e-5 if dtype == "float32" else 4e-2
+    s = eng.start(3)
+    cut = [20, 4, 11]
+    first = eng.step(s, [p[:c] for p, c in zip(prompts, cut)], [list(range(c)) for c in cut])
+    errs, o = [], 0
+    for r in range(3):
+        errs += [rel_l2(first[o + i], truth[r][i]) for i in range(min(cut[r], upto[r]))]
+        o += cut[r]
+    for t in range(5):
+        out = eng.step(s, [[prompts[r][cut[r] + t]] for r in range(3)])
+        errs += [rel_l2(out[r], truth[r][cut[r] + t]) for r in range(3) if cut[r] + t < upto[r]]
+    eng.release(s)
+    assert len(errs) >= 20, f"too few places with clear routing to say anything: {upto}"
+    assert max(errs) < tol, sorted(errs)[-5:]
