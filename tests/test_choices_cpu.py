@@ -24,3 +24,14 @@ def test_decode_splits():
         for pages in (1, 9, 64, 128, 1000):
             s = choose_decode_splits(batch, 4, pages, 148)
             assert 1 <= s <= 64 and (s == 1 or pages // s >= 8)
+
+
+def test_uneven_lengths():
+    """The engine tells the kernels when a batch's contexts differ so much that cutting every sequence alike
+    would leave most CTAs with nothing to do; it is part of the key of a captured decode step."""
+    from trapetum_b200.engine.engine import uneven_lengths
+    assert not uneven_lengths([8000])                       # one sequence is never uneven
+    assert not uneven_lengths([8000, 8000, 7000, 8192])
+    assert uneven_lengths([8000, 100, 100, 100])
+    assert uneven_lengths([1, 1, 1, 64])
+    assert not uneven_lengths([3, 3, 4])
