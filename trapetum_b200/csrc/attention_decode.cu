@@ -457,6 +457,10 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         for (int s = 0; s < C::STAGES; s++) mbar_init(&full[s], 1);
         mbar_init_fence();
     }
+    if (tid == 32) {                                // the tensor maps, ahead of the first copy that uses them
+        asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&map_k) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&map_v) : "memory");
+    }
     if (tid < 16) pm[tid] = -INFINITY;
 
     PageCursor cur;

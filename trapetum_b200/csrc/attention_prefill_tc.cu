@@ -112,6 +112,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         mbar_init_fence();
     }
     if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+    if (threadIdx.x == 64) { tma_prefetch_map(&map_q); tma_prefetch_map(&map_k); tma_prefetch_map(&map_vt); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();

@@ -53,10 +53,11 @@ struct GemmParams {
 // of a 32-column chunk) or in one warp (swapped tiles: lanes l and l + 16).  The output has half the width:
 // out[token][16 b + j] = act(gate) * up, computed on the 32-bit accumulators
 // (the reference's gelu_mul_k does this as a kernel of its own, runtime/cuda/codebook_gemv.cu:531-537).
+// The result is rounded to bfloat16, so tanh and the logistic function are taken through the fast exponential
+// and division (relative error near 2^-21): 0.5 (1 + tanh(y)) = 1 / (1 + e^(-2y)).
 __device__ __forceinline__ float gated(float g, float u, int act) {
-    const float a = act == 0 ? 0.5f * g * (1.0f + tanhf(0.7978845608f * (g + 0.044715f * g * g * g)))
-                             : g / (1.0f + expf(-g));
-    return a * u;
+    const float y = act == 0 ? 1.5957691216f * (g + 0.044715f * g * g * g) : g;     // 2 sqrt(2/pi) (g + 0.044715 g^3)
+    return __fdividef(g, 1.0f + __expf(-y)) * u;
 }
 
 // Shared-memory budget: as many stages as an SM holds.  (Half of it, so that the next product's CTAs could
@@ -89,6 +90,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+    if (threadIdx.x == 32) { tma_prefetch_map(&map_p); tma_prefetch_map(&map_q); }
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         for (int a = 0; a < 2; a++) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
