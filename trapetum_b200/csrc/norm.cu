@@ -249,6 +249,83 @@ extern "C" int tb_rmsnorm(const void* x, int x_dtype, const void* w, int w_dtype
     return tb_launch_status();
 }
 
+// The same for few rows (decoding), where the kernel's time is a chain of memory round trips, not bandwidth: a
+// thread keeps its NV groups of four columns in registers, the norm weights are fetched before the dependency
+// wait (they do not depend on the kernel before), and the residual row and all partial sums are requested at
+// once, so that the whole kernel waits for memory about once.
+template <typename TA, typename TW, typename TO, int NV>
+__global__ void __launch_bounds__(1024)
+add_rmsnorm_few_kernel(float* __restrict__ h, const TA* __restrict__ a, int n_splits, long long split_stride,
+                       const TW* __restrict__ wa, float eps_a, float off_a,
+                       const TW* __restrict__ wb, float eps_b, float off_b, TO* __restrict__ out, int width) {
+    pdl_launch_dependents();
+    __shared__ float red[33];
+    const size_t base = (size_t)blockIdx.x * width;
+    float ga[NV][4], gb[NV][4], hv[NV][4], av[NV][4];
+#pragma unroll
+    for (int v = 0; v < NV; v++) {
+        const int i = (threadIdx.x + v * blockDim.x) * 4;
+        if (i < width) {
+            Vec4<TW>::load(wa + i, ga[v]);
+            if (wb != nullptr) Vec4<TW>::load(wb + i, gb[v]);
+        }
+    }
+    pdl_wait();
+#pragma unroll
+    for (int v = 0; v < NV; v++) {
+        const int i = (threadIdx.x + v * blockDim.x) * 4;
+        if (i < width) Vec4<float>::load(h + base + i, hv[v]);
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; v++) {
+        const int i = (threadIdx.x + v * blockDim.x) * 4;
+#pragma unroll
+        for (int e = 0; e < 4; e++) av[v][e] = 0.f;
+        if (i < width) {
+            const TA* p = a + base + i;
+            for (int s0 = 0; s0 < n_splits; s0 += 8) {          // eight splits requested at a time, added in order
+                float t[8][4];
+#pragma unroll
+                for (int k = 0; k < 8; k++) if (s0 + k < n_splits) Vec4<TA>::load(p + (size_t)(s0 + k) * split_stride, t[k]);
+#pragma unroll
+                for (int k = 0; k < 8; k++)
+                    if (s0 + k < n_splits) {
+#pragma unroll
+                        for (int e = 0; e < 4; e++) av[v][e] = (s0 + k == 0) ? t[k][e] : av[v][e] + t[k][e];
+                    }
+            }
+#pragma unroll
+            for (int e = 0; e < 4; e++) ss += av[v][e] * av[v][e];
+        }
+    }
+    ss = block_sum(ss, red);
+    const float ra = rsqrtf(ss / (float)width + eps_a);
+    float s2 = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; v++) {
+        const int i = (threadIdx.x + v * blockDim.x) * 4;
+        if (i < width) {
+#pragma unroll
+            for (int e = 0; e < 4; e++) { hv[v][e] = hv[v][e] + av[v][e] * ra * (off_a + ga[v][e]); s2 += hv[v][e] * hv[v][e]; }
+            Vec4<float>::store(h + base + i, hv[v]);
+        }
+    }
+    if (out == nullptr) return;
+    s2 = block_sum(s2, red);
+    const float rb = rsqrtf(s2 / (float)width + eps_b);
+#pragma unroll
+    for (int v = 0; v < NV; v++) {
+        const int i = (threadIdx.x + v * blockDim.x) * 4;
+        if (i < width) {
+            float o[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) o[e] = hv[v][e] * rb * (off_b + gb[v][e]);
+            Vec4<TO>::store(out + base + i, o);
+        }
+    }
+}
+
 extern "C" int tb_add_rmsnorm(float* h, const void* a, int a_dtype, int n_splits, long long split_stride,
                               const void* wa, float eps_a, float off_a,
                               const void* wb, float eps_b, float off_b, int w_dtype,
@@ -276,6 +353,21 @@ extern "C" int tb_add_rmsnorm(float* h, const void* a, int a_dtype, int n_splits
         } while (0)
         if (nv <= 8) ROWS(8); else if (nv <= 16) ROWS(16); else if (nv <= 24) ROWS(24); else if (nv <= 32) ROWS(32); else ROWS(40);
 #undef ROWS
+        return tb_launch_status();
+    }
+    if (vec && rows < 64 && width <= 4 * 1024 * 4) {
+        // few rows: one pass with everything in registers; as many threads as the row has groups of four
+        // (measured faster than half as many threads with two groups each)
+        const int groups = width / 4;
+        const int nv = groups <= 1024 ? 1 : groups <= 2048 ? 2 : 4;
+        const int threads = ((groups + nv - 1) / nv + 31) / 32 * 32;
+#define FEW(NV_)                                                                                                   \
+        DISPATCH3(a_dtype, w_dtype, out_dtype,                                                                     \
+            tb_launch(add_rmsnorm_few_kernel<TX, TW, TO, NV_>, dim3(rows), dim3(threads), 0, stream,               \
+                h, (const TX*)a, n_splits, split_stride, (const TW*)wa, eps_a, off_a, (const TW*)wb, eps_b, off_b, \
+                (TO*)out, width))
+        if (nv == 1) FEW(1); else if (nv == 2) FEW(2); else FEW(4);
+#undef FEW
         return tb_launch_status();
     }
     if (vec)
