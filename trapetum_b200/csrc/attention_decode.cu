@@ -746,18 +746,19 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     // the CTA that finishes a pair's last part folds the parts, in their order
     auto fold_pending = [&]() {
         if (n_pend == 0) return;
-        __threadfence();
+        // The parts were written by all threads; the barrier orders them before thread q's counting, and the
+        // counting is a release (for the parts) and an acquire (for the other CTAs' parts) at GPU scope.
         __syncthreads();
         if (tid < n_pend) {
             int* ticket = a.tickets + (size_t)s_pend[tid][0] * a.n_kv_heads + s_pend[tid][1];
-            const int old = atomicAdd(ticket, 1);
+            int old;
+            asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(old) : "l"(ticket) : "memory");
             s_last[tid] = (old == s_pend[tid][2] - 1);
             if (s_last[tid]) *ticket = 0;                           // left at zero for the next launch
         }
         __syncthreads();
         for (int q = 0; q < n_pend; q++) {
             if (!s_last[q]) continue;
-            __threadfence();
             const int fb = s_pend[q][0], fkvh = s_pend[q][1], n_parts = s_pend[q][2], c_first = s_pend[q][3];
             auto part_of = [&](int k, int hg) -> const float* {
                 if (STREAM) return a.partial + ((size_t)((c_first + k) * 2 + (k == 0 ? 1 : 0)) * G + hg) * (HD + 2);
@@ -765,13 +766,26 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             };
             for (int x = tid; x < G * HD; x += TW * 32) {
                 const int hg = x / HD, d = x % HD;
-                float M = -INFINITY;
-                for (int k = 0; k < n_parts; k++) M = fmaxf(M, __ldcg(part_of(k, hg) + HD));
-                float L = 0.f, acc = 0.f;
-                for (int k = 0; k < n_parts; k++) {
-                    const float* pk = part_of(k, hg);
-                    const float ms = __ldcg(pk + HD);
-                    if (ms != -INFINITY) { const float f = __expf(ms - M); L += __ldcg(pk + HD + 1) * f; acc += __ldcg(pk + d) * f; }
+                // out = sum_k e^(m_k - M) o_k / sum_k e^(m_k - M) l_k in the parts' order, eight parts requested at a
+                // time; M is the running maximum, by which the sums so far are rescaled
+                float M = -INFINITY, L = 0.f, acc = 0.f;
+                for (int k0 = 0; k0 < n_parts; k0 += 8) {
+                    float ms[8], ls[8], os[8];
+#pragma unroll
+                    for (int k = 0; k < 8; k++)
+                        if (k0 + k < n_parts) {
+                            const float* pk = part_of(k0 + k, hg);
+                            ms[k] = __ldcg(pk + HD); ls[k] = __ldcg(pk + HD + 1); os[k] = __ldcg(pk + d);
+                        }
+                    float Mn = M;
+#pragma unroll
+                    for (int k = 0; k < 8; k++) if (k0 + k < n_parts) Mn = fmaxf(Mn, ms[k]);
+                    if (Mn == -INFINITY) continue;
+                    const float r = (M == -INFINITY) ? 0.f : __expf(M - Mn);
+                    L *= r; acc *= r; M = Mn;
+#pragma unroll
+                    for (int k = 0; k < 8; k++)
+                        if (k0 + k < n_parts && ms[k] != -INFINITY) { const float f = __expf(ms[k] - M); L += ls[k] * f; acc += os[k] * f; }
                 }
                 ((bf16*)a.out)[((size_t)fb * a.n_heads + fkvh * G + hg) * HD + d] = __float2bfloat16_rn(acc / L);
             }
