@@ -77,3 +77,39 @@ def test_logits_at_real_layer_sizes(models, shape, dtype):
     eng.release(s)
     torch.cuda.synchronize()
     assert ops.kernel_errors() == {}
+
+
+@pytest.mark.parametrize("lens", [[3000, 2900, 3100, 2950, 3050, 3000, 2980, 3020], [6000, 70, 300, 64, 1500, 9, 640, 1]])
+def test_decoding_repeats_bit_for_bit_over_long_contexts(models, lens):
+    """Decode steps over contexts of thousands of tokens (cache filled with random keys and values), once with
+    lengths that are nearly equal (the split partition) and once with lengths that differ widely (the stream
+    partition).  The attention kernel's pieces are counted with atomics and folded by whichever CTA finishes
+    last: the result must not depend on that, so two engines with the same cache content must give the same
+    bits, step after step."""
+    import trapetum_b200 as tb
+    from trapetum_b200.csrc import ops
+    from trapetum_b200.engine.engine import uneven_lengths
+    folder, cfg, _, _, _ = models("2b")
+    model = tb.load_model(folder, "bfloat16")
+    B, steps = len(lens), 12
+    outs = []
+    for run in range(2):
+        eng = tb.Engine(model, max_tokens=sum(-(-(n + steps) // 64) * 64 for n in lens), max_slots=B)
+        gen = torch.Generator(device="cuda").manual_seed(11)
+        for g in eng.cache.groups:
+            g.k.copy_(torch.randn(g.k.shape, device="cuda", generator=gen).mul_(0.5))
+            g.v.copy_(torch.randn(g.v.shape, device="cuda", generator=gen).mul_(0.5))
+        slots = eng.start(B)
+        eng.cache.grow({s: n for s, n in zip(slots, lens)})
+        toks = torch.randint(0, cfg["vocab_size"], (steps, B), generator=torch.Generator().manual_seed(5)).tolist()
+        got = []
+        for t in range(steps):
+            got.append(eng.step(slots, [[x] for x in toks[t]]).clone())
+        torch.cuda.synchronize()
+        outs.append(torch.stack(got))
+        eng.release(slots)
+        del eng
+    assert uneven_lengths(lens) == (min(lens) < 100)
+    assert torch.isfinite(outs[0]).all()
+    assert torch.equal(outs[0], outs[1])
+    assert ops.kernel_errors() == {}
