@@ -267,6 +267,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=GEMMA2_2B["num_hidden_layers"],
                     help="fewer layers than the model has (same layer sizes); both numbers are reported")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    ap.add_argument("--prefill-only", action="store_true",
+                    help="instead of the bench line: time only the prompt of 2,048 tokens and print one line about it")
     ap.add_argument("--leave-out", action="store_true",
                     help="instead of the bench line: the decode step re-timed with one kind of launch left out at a "
                          "time (its results are then wrong; only its time is of interest), one line per kind")
@@ -297,6 +299,12 @@ def main() -> int:
 
     if args.leave_out:
         return leave_out_report(engine, model, cfg, torch, args, warmup)
+    if args.prefill_only:
+        pms = time_prefill(engine, torch, PREFILL_TOKENS, V, reps=max(1, args.steps), warmup=warmup)
+        print(json.dumps({"prefill_ms": round(pms, 3), "tokens": PREFILL_TOKENS, "layers": args.layers,
+                          "frac": round(prefill_flops(cfg, PREFILL_TOKENS) / (pms * 1e-3) / (bf16_tflops * 1e12), 4),
+                          "of": peak_src}))
+        return 0
 
     with ClockSampler() as clocks:
         dev_ms, e2e_ms, launches, h2d = time_decode(engine, torch, args.batch, args.context, args.steps, warmup, V)

@@ -131,6 +131,107 @@ __global__ void rope_kv_kernel(RopeKvArgs a) {
     }
 }
 
+// The same for many tokens (a prompt), bfloat16, head_dim a multiple of 16 with the whole head rotated or
+// rotary_dim a multiple of 16: one warp per token, 16-byte accesses.  A lane owns eight neighbouring pairs
+// (dims i..i+7 and i+half..i+half+7) of every second head slot; their sines and cosines are computed once and
+// reused for all the heads the lane visits.
+__global__ void __launch_bounds__(256) rope_kv_rows_kernel(RopeKvArgs a, int n_tokens) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= n_tokens) return;
+    const int hd = a.head_dim, half = a.rotary_dim >> 1;
+    const int groups = half >> 3;                       // groups of eight pairs per head (0: no rotation)
+    const int chunks = hd >> 3;                         // 16-byte chunks per head
+    bf16* row = (bf16*)a.qkv + (size_t)t * a.row_stride;
+    const int pos = a.positions[t];
+    size_t cache_off = 0;
+    bool store = false;
+    if (a.k_pool != nullptr) {
+        const int b = a.token_seq[t];
+        store = true;
+        int r = pos;
+        if (a.ring_rows > 0) { store = pos >= a.len_after[b] - a.ring_rows; r = pos % a.ring_rows; }
+        if (store) {
+            const int page = a.page_table[(size_t)b * a.pt_stride + r / a.page_rows];
+            cache_off = ((size_t)page * a.n_kv_heads * a.page_rows + (r % a.page_rows)) * hd;
+        }
+    }
+    auto unpack = [](const uint4& w, float* f) {
+        const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) { f[2 * i] = __uint_as_float(u[i] << 16); f[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u); }
+    };
+    auto pack = [](const float* f) -> uint4 {
+        uint32_t u[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) { __nv_bfloat162 h2 = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]); u[i] = *(uint32_t*)&h2; }
+        return make_uint4(u[0], u[1], u[2], u[3]);
+    };
+    const int qk_slots = a.n_heads + a.n_kv_heads;
+    // ---- rotated part of q and k heads: work items (head slot, group of eight pairs)
+    if (groups > 0) {
+        const int lanes_per_head = groups < 32 ? groups : 32;          // groups <= 16 for head_dim <= 256
+        const int heads_at_once = 32 / lanes_per_head;
+        const int g = lane % lanes_per_head, h0 = lane / lanes_per_head;
+        float sn[8], cs[8];
+        if (h0 < heads_at_once) {
+#pragma unroll
+            for (int e = 0; e < 8; e++) sincosf((float)pos * a.inv_freq[g * 8 + e], &sn[e], &cs[e]);
+            // four head slots at a time: their loads are requested together, so that a warp waits for memory
+            // once per four heads and not once per head
+            for (int hs0 = h0; hs0 < qk_slots; hs0 += 4 * heads_at_once) {
+                uint4 wlo[4], whi[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int hs = hs0 + u * heads_at_once;
+                    if (hs < qk_slots) {
+                        const int col0 = hs < a.n_heads ? a.q_off + hs * hd : a.k_off + (hs - a.n_heads) * hd;
+                        wlo[u] = *(const uint4*)(row + col0 + g * 8);
+                        whi[u] = *(const uint4*)(row + col0 + half + g * 8);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int hs = hs0 + u * heads_at_once;
+                    if (hs < qk_slots) {
+                        const bool is_q = hs < a.n_heads;
+                        const int col0 = is_q ? a.q_off + hs * hd : a.k_off + (hs - a.n_heads) * hd;
+                        float x0[8], x1[8], y0[8], y1[8];
+                        unpack(wlo[u], x0); unpack(whi[u], x1);
+#pragma unroll
+                        for (int e = 0; e < 8; e++) { y0[e] = x0[e] * cs[e] - x1[e] * sn[e]; y1[e] = x1[e] * cs[e] + x0[e] * sn[e]; }
+                        const uint4 w0 = pack(y0), w1 = pack(y1);
+                        *(uint4*)(row + col0 + g * 8) = w0;
+                        *(uint4*)(row + col0 + half + g * 8) = w1;
+                        if (!is_q && store) {
+                            bf16* dst = (bf16*)a.k_pool + cache_off + (size_t)(hs - a.n_heads) * a.page_rows * hd;
+                            *(uint4*)(dst + g * 8) = w0;
+                            *(uint4*)(dst + half + g * 8) = w1;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    if (!store) return;
+    // ---- what is only copied to the cache: k dims beyond the rotary part, and v
+    const int k_tail = chunks - 2 * groups;             // chunks per k head that pass through
+    for (int x = lane; x < a.n_kv_heads * (k_tail + chunks); x += 32) {
+        const int kvh = x / (k_tail + chunks), c = x % (k_tail + chunks);
+        if (c < k_tail) {
+            const int d = 2 * half + c * 8;
+            *(uint4*)((bf16*)a.k_pool + cache_off + (size_t)kvh * a.page_rows * hd + d) =
+                *(const uint4*)(row + a.k_off + kvh * hd + d);
+        } else {
+            const int d = (c - k_tail) * 8;
+            *(uint4*)((bf16*)a.v_pool + cache_off + (size_t)kvh * a.page_rows * hd + d) =
+                *(const uint4*)(row + a.v_off + kvh * hd + d);
+        }
+    }
+}
+
 extern "C" int tb_rope_kv(const RopeKvArgs* args, int dtype, int n_tokens, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     RopeKvArgs a = *args;
@@ -141,6 +242,16 @@ extern "C" int tb_rope_kv(const RopeKvArgs* args, int dtype, int n_tokens, cudaS
         return tb_refuse("rope: a cache write needs page_rows > 0, a page table and both pools");
     if (a.ring_rows > 0 && a.ring_rows % a.page_rows != 0)
         return tb_refuse("rope: ring_rows=%d must be a multiple of page_rows=%d", a.ring_rows, a.page_rows);
+    // many tokens in bfloat16 with 16-byte aligned rows and heads: the warp-per-token kernel
+    if (dtype == TB_BF16 && n_tokens >= 128 && a.partial == nullptr && a.head_dim % 16 == 0 &&
+        (a.inv_freq == nullptr || a.rotary_dim == 0 || a.rotary_dim % 16 == 0) && a.rotary_dim / 16 <= 32 &&
+        a.row_stride % 8 == 0 && a.q_off % 8 == 0 && a.k_off % 8 == 0 && a.v_off % 8 == 0 && ((uintptr_t)a.qkv & 15) == 0 &&
+        ((uintptr_t)a.k_pool & 15) == 0 && ((uintptr_t)a.v_pool & 15) == 0) {
+        RopeKvArgs b = a;
+        if (b.inv_freq == nullptr) b.rotary_dim = 0;
+        tb_launch(rope_kv_rows_kernel, dim3((n_tokens + 7) / 8), dim3(256), 0, stream, b, n_tokens);
+        return tb_launch_status();
+    }
     const int slots = a.n_heads + 2 * a.n_kv_heads;
     int tx = 16;                                     // threads over pairs (two pairs each)
     while (tx < 128 && tx * 4 < a.head_dim) tx <<= 1;
