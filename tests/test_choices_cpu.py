@@ -12,8 +12,8 @@ def test_len_bucket_is_a_power_of_two_not_below():
 
 
 def test_decode_splits():
-    # one sequence: many pieces, to put a CTA on as many SMs as the pages allow (at least 8 pages each)
-    assert choose_decode_splits(1, 4, 128, 148) == 16
+    # one sequence: many pieces, to put a CTA on as many SMs as the pages allow (at least 4 pages each)
+    assert choose_decode_splits(1, 4, 128, 148) == 31
     # a short context is not cut
     assert choose_decode_splits(8, 4, 4, 148) == 1 and choose_decode_splits(1, 4, 7, 148) == 1
     # 32 (sequence, kv head) pairs on 148 SMs: four pieces fill one round
@@ -23,7 +23,7 @@ def test_decode_splits():
     for batch in (1, 3, 8, 64, 200):
         for pages in (1, 9, 64, 128, 1000):
             s = choose_decode_splits(batch, 4, pages, 148)
-            assert 1 <= s <= 64 and (s == 1 or pages // s >= 8)
+            assert 1 <= s <= 64 and (s == 1 or pages // s >= 4)
 
 
 def test_uneven_lengths():

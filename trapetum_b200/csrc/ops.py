@@ -784,11 +784,11 @@ def attn_decode_error() -> int:
 def choose_decode_splits(batch: int, n_kv_heads: int, pages: int, sms: int) -> int:
     """In how many pieces decode attention cuts a sequence's pages.  A CTA serves one (sequence, kv head,
     piece); all CTAs of a launch are about equally long, so the launch takes ceil(CTAs / SMs) rounds.
-    Among the piece counts that keep at least 8 pages per piece, take the one that wastes least of the
+    Among the piece counts that keep at least 4 pages per piece, take the one that wastes least of the
     last round (ties: fewer pieces)."""
     items = max(1, batch * n_kv_heads)
     best, best_eff = 1, 0.0
-    for s in range(1, max(1, pages // 8) + 1):
+    for s in range(1, max(1, pages // 4) + 1):
         if s > 64:
             break
         ctas = items * s
