@@ -339,25 +339,31 @@ __global__ void __launch_bounds__(DCfg<HD>::NWARP * 32, 1) attn_decode_kernel(De
 // MMA row is wasted on padding, so a page costs head_dim/2 MMAs and as many ldmatrix for the whole
 // CTA instead of some 5,000 scalar instructions, and the kernel's time is the time of its page
 // copies.  A page arrives as head_dim/64 tiled TMA copies of 64 keys x 64 dims with the 128-byte
-// swizzle (8 KB each), the layout in which every ldmatrix is conflict-free.  Per page the 8 warps
-// run three short phases with a CTA barrier between them:
-//   A  warp (m-tile, half of head_dim) multiplies its 16 keys with its half of the dims and leaves
-//      the partial scores in shared memory;
-//   B  one thread per (key, head) adds the two halves, applies scale, cap and the validity mask,
-//      leaves the final score in shared memory; each warp leaves the maximum of its 32 keys;
-//   C  every warp owns head_dim/8 dims of O^T: it reads the page's maxima and scores, updates the
-//      running maximum and sum (identically in all warps), and multiplies its slice of V^T with P^T.
-// The stage of page i is refilled once every warp has passed phase A of page i+1.  Rows of a page
-// that are not keys of the sequence get -inf scores, and their V rows are zeroed in shared memory
-// before use (0 * NaN would still poison O).
+// swizzle (8 KB each), the layout in which every ldmatrix is conflict-free.
+//
+// The nine warps of a CTA have three roles and meet only through mbarriers (every wait bounded):
+//   warps 0..3  scores: warp w multiplies the page's keys 16w..16w+15 with all of head_dim (four chains of
+//               MMAs), applies scale, cap and the validity mask on the accumulators and leaves the scores and
+//               their maximum per head in shared memory (two pages' worth, so that it may run a page ahead);
+//   warps 4..7  outputs: each owns head_dim/4 dims of O^T: it reads the four maxima and the scores of the
+//               page, updates the running maximum and sum (identically in all four warps), builds P^T in
+//               registers and multiplies its slice of V^T with it;
+//   warp 8      copies: one lane refills a stage as soon as all eight computing warps have let go of it, so the
+//               page-table lookup and the copy instructions are on nobody's critical path.
+// A page's dependent chain (wait, ldmatrix, MMAs, cap, maximum / exponentials, MMAs) is thus cut in two halves
+// that overlap across pages; with one CTA-wide barrier per phase the same work took 1.37 us a page on an idle
+// GPU, as much as the page's copy takes when all SMs stream.  Rows of a page that are not keys of the sequence
+// get -inf scores, and their V rows are zeroed in shared memory before use (0 * NaN would still poison O).
 //
 // Before griddepcontrol.wait the kernel already fetches pages that this step does not write (all
 // but the one that takes the new token): they were complete before the step began.
 //
 // Splits write (max, sum, O) partials; the CTA that finishes last for a (sequence, kv head), found
-// with a ticket counter, folds them in split order, so the sum does not depend on which CTA that is.
+// with a ticket counter, folds them in split order, so the sum does not depend on which CTA that is
+// (split partition: all eight computing warps fold; stream partition: the output warps, between two runs).
 // ---------------------------------------------------------------------------
-#define TW 8                                       // warps per CTA
+#define TW 8                                       // warps that compute: 0..3 the scores, 4..7 the outputs
+#define NTHREADS ((TW + 1) * 32)                   // and one warp that issues the page copies
 #define SROW 72                                    // floats between heads in the score arrays (64 keys + 8: no bank conflicts)
 template <int HD> struct MCfg {
     static constexpr int BOXES = HD / 64;                            // 64-dim column boxes per page
@@ -366,11 +372,10 @@ template <int HD> struct MCfg {
     static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
     static constexpr int STAGES_RAW = (192 * 1024) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 6 ? 6 : STAGES_RAW;
-    static constexpr int KS_W = HD / 32;                             // k-steps of phase A per warp (half of head_dim)
-    static constexpr int MT_W = HD >= 128 ? HD / 128 : 1;            // 16-dim tiles of O^T per warp
-    static constexpr int PV_WARPS = HD / 16 / MT_W;                  // warps that own a slice of O^T
-    static constexpr int SCORE_FLOATS = 3 * 8 * SROW + 16;           // partial halves, final, page maxima
-    static constexpr int SMEM = STAGES * STAGE_BYTES + SCORE_FLOATS * 4 + 64 /* barriers */ + (1024 + 4) * 4 /* stream: page prefix */
+    static constexpr int KS = HD / 16;                               // k-steps of S^T = K Q^T
+    static constexpr int MT_W = HD / 64;                             // 16-dim tiles of O^T per output warp (head_dim / 4 dims)
+    static constexpr int SCORE_FLOATS = 2 * 8 * SROW + 2 * 8 * 4;    // two pages' scores, and their maxima per score warp
+    static constexpr int SMEM = STAGES * STAGE_BYTES + SCORE_FLOATS * 4 + 256 /* barriers */ + (1024 + 4) * 4 /* stream: page prefix */
                                 + 8 * HD * 2 /* rotated queries */ + 1024 /* alignment */;
 };
 // byte offset of (key row r, 16-byte chunk c of the head dim) inside a swizzled page
@@ -424,20 +429,24 @@ struct PageCursor {
 };
 
 template <int HD, bool STREAM>
-__global__ void __launch_bounds__(TW * 32, 1)
+__global__ void __launch_bounds__(NTHREADS, 1)
 attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, DecodeArgs a,
                        int batch) {
     pdl_launch_dependents();
     using C = MCfg<HD>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    float* sp = (float*)(smem + C::STAGES * C::STAGE_BYTES);         // [2 halves][8 heads][SROW] partial scores
-    float* sf = sp + 2 * 8 * SROW;                                   // [8 heads][SROW] final scores
-    float* pm = sf + 8 * SROW;                                       // [8 heads][2] maxima of the page's two key halves
-    uint64_t* full = (uint64_t*)(pm + 16);
-    int* pref = (int*)(full + 8);                                    // stream: [batch + 1] pages before each sequence
+    float* sf = (float*)(smem + C::STAGES * C::STAGE_BYTES);         // [page parity][8 heads][SROW] scores: scaled, capped, masked
+    float* pm = sf + 2 * 8 * SROW;                                   // [page parity][8 heads][4] their maxima per score warp
+    uint64_t* full = (uint64_t*)(pm + 2 * 8 * 4);                    // [STAGES] a page has landed
+    uint64_t* empty = full + C::STAGES;                              // [STAGES] all eight warps are done with it
+    uint64_t* s_full = empty + C::STAGES;                            // [2] the four score warps have written a page's scores
+    uint64_t* s_empty = s_full + 2;                                  // [2] the four output warps have read them
+    uint64_t* grp = s_empty + 2;                                     // [3] meeting points of the score warps, of the output warps, of all eight
+    int* pref = (int*)(full + 32);                                   // stream: [batch + 1] pages before each sequence
     bf16* q_s = (bf16*)(pref + 1024 + 4);                            // [8 heads][HD] this run's queries, rotated (fused rotation)
-    __shared__ int s_last[2], s_pend[2][4];         // per pending part: sequence, kv head, parts of the pair, first CTA
+    __shared__ int s_last, s_job[3];                // split: the pair to fold (sequence, kv head, parts)
+    __shared__ volatile int s_abort;
 
     const int G = a.n_heads / a.n_kv_heads;                         // 1..8 query heads on columns 0..G-1
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -454,14 +463,17 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     };
 
     if (tid == 0) {
-        for (int s = 0; s < C::STAGES; s++) mbar_init(&full[s], 1);
+        for (int s = 0; s < C::STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], TW); }
+        for (int u = 0; u < 2; u++) { mbar_init(&s_full[u], TW / 2); mbar_init(&s_empty[u], TW / 2); mbar_init(&grp[u], TW / 2); }
+        mbar_init(&grp[2], TW);
+        s_abort = 0;
+        s_last = 0;
         mbar_init_fence();
     }
     if (tid == 32) {                                // the tensor maps, ahead of the first copy that uses them
         asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&map_k) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&map_v) : "memory");
     }
-    if (tid < 16) pm[tid] = -INFINITY;
 
     PageCursor cur;
     long long g_beg = 0, total = 0;                                  // stream: this CTA's first page, all pages
@@ -516,7 +528,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     // one thread issues the copies of a page: head_dim/64 boxes of K and as many of V
     PageCursor ahead = cur;
     int issued = 0;                                                  // pages whose copies are under way (issuing thread)
-    constexpr int ISSUER = (TW - 1) * 32;                            // a warp with little to do in phase B
+    constexpr int ISSUER = TW * 32;                                  // lane 0 of the ninth warp
     auto issue = [&]() {
         const int s = issued % C::STAGES;
         const int page = a.page_table[(size_t)ahead.b * a.pt_stride + ahead.first_page + ahead.pg];
@@ -569,7 +581,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             if (dst2) dst2[d] = y;
         }
     };
-    if (fused && warp >= TW / 2) {
+    if (fused && warp >= TW / 2 && warp < TW) {
         // the upper half of the warps rotates the first run's query heads into shared memory meanwhile
         const int len0 = a.len_after[cur.b], per = HD - half;
         for (int x = tid - (TW / 2) * 32; x < G * per; x += (TW / 2) * 32)
@@ -611,32 +623,37 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     }
 
     const float inv_cap = a.cap > 0.f ? 1.f / a.cap : 0.f;
-    const int mt = warp & 3, kh = warp >> 2;        // phase A role: 16 keys (m-tile) x half of head_dim
-    const bool pv_warp = warp < C::PV_WARPS;        // phase C role: dims [d0, d0 + 16 MT_W) of O^T
-    const int d0 = warp * C::MT_W * 16;
-    // where this lane's ldmatrix rows lie inside a stage: the same for every page, so computed once
     const uint32_t smem_base = smem_u32(smem);
-    uint32_t koff[C::KS_W], voff[C::MT_W][4];
-#pragma unroll
-    for (int ks = 0; ks < C::KS_W; ks++)
-        koff[ks] = sw_off(mt * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), (kh * C::KS_W + ks) * 2 + (lane >> 4));
-#pragma unroll
-    for (int m = 0; m < C::MT_W; m++)
-#pragma unroll
-        for (int ks = 0; ks < 4; ks++)
-            voff[m][ks] = C::TILE_BYTES + sw_off(ks * 16 + (lane >> 4) * 8 + (lane & 7), (d0 + m * 16) / 8 + ((lane >> 3) & 1));
 
-    // ---- one loop over this CTA's pages; a run of pages of one (sequence, kv head) begins and ends inside it
-    int visited = 0;                                // pages this CTA has consumed
-    bool aborted = false;
-    int run_left = 0;                               // pages left in the current run; 0: the next page begins one
-    int n_pend = 0;                                 // parts whose pairs still have to be folded (s_pend)
-    int b = 0, kvh = 0, seg_pg0 = 0, seg_n = 0, seg_np = 0, seg_first = 0, len = 0, lo = 0;
+    // A warp that gives up (a bounded wait ran out) says so; the others notice at their next wait.
+    auto wait_on = [&](uint64_t* bar, uint32_t parity) -> bool {
+        if (s_abort) return false;
+        if (mbar_wait(bar, parity)) return true;
+        s_abort = 1;
+        return false;
+    };
+    // the four warps of a role meet (a bounded barrier): every lane waits until all four have arrived
+    auto meet = [&](int which, uint32_t& phase) -> bool {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&grp[which]);
+        const bool ok = wait_on(&grp[which], phase & 1);
+        phase++;
+        return ok;
+    };
+    // geometry of the run that the cursor stands on: which rows (in row space) are keys.  Without a ring, or
+    // before the ring has wrapped: lo <= R < len.  Once it has wrapped (len >= ring_rows) every row holds a token;
+    // too old are the ring_rows - window rows that follow the newest one, a single circular run from old_beg.
+    int len = 0, lo = 0, n_old = 0, old_beg = 0;
     bool wrapped = false, no_invalid = false;
-    int n_old = 0, old_beg = 0;
-    // Which rows (in row space) are keys.  Without a ring, or before the ring has wrapped: lo <= R < len.
-    // Once it has wrapped (len >= ring_rows) every row holds a token; too old are the ring_rows - window rows
-    // that follow the newest one, a single circular run that starts at old_beg.
+    auto set_geometry = [&](int b) {
+        len = a.len_after[b];
+        lo = (a.window > 0 && len > a.window) ? len - a.window : 0;
+        wrapped = a.ring_rows > 0 && len >= a.ring_rows;
+        const int newest = wrapped ? (len - 1) % a.ring_rows : 0;
+        n_old = wrapped ? a.ring_rows - a.window : 0;
+        old_beg = wrapped ? (newest + 1 == a.ring_rows ? 0 : newest + 1) : 0;
+        no_invalid = wrapped && n_old == 0;                         // a full ring whose every row is in the window
+    };
     auto is_key = [&](int R) -> bool {
         if (wrapped) {
             int d = R - old_beg;                                    // distance past the start of the old run
@@ -645,77 +662,233 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         }
         return R >= lo && R < len;
     };
-    // B fragments of Q^T for this warp's half of the dims:
-    // b0 = Q[head quad][16 ks + 2t, +1], b1 = Q[head quad][16 ks + 8 + 2t, +1]; heads >= G are zero
-    uint32_t qb[C::KS_W][2];
-    float o[C::MT_W][4], o2[C::MT_W][4];            // accumulator rows are dims, columns heads 2t, 2t+1; two chains
-    // running maximum of the heads this lane meets: `quad` (its P^T column) and 2t, 2t+1 (its O^T columns)
-    float m_b = -INFINITY, m_c0 = -INFINITY, m_c1 = -INFINITY, l_b = 0.f;
-    auto begin_run = [&](bool first_run) {
-        b = cur.b; kvh = cur.kvh;
-        seg_pg0 = cur.pg; seg_n = min(cur.left, cur.np - cur.pg); seg_np = cur.np; seg_first = cur.first_page;
-        run_left = seg_n;
-        len = a.len_after[b];
-        lo = (a.window > 0 && len > a.window) ? len - a.window : 0;
-        wrapped = a.ring_rows > 0 && len >= a.ring_rows;
-        const int newest = wrapped ? (len - 1) % a.ring_rows : 0;
-        n_old = wrapped ? a.ring_rows - a.window : 0;
-        old_beg = wrapped ? (newest + 1 == a.ring_rows ? 0 : newest + 1) : 0;
-        no_invalid = wrapped && n_old == 0;                         // a full ring whose every row is in the window
-        const bf16* qp = (const bf16*)a.q + (size_t)b * a.q_stride + (size_t)(kvh * G + quad) * HD + kh * (HD / 2);
-        if (fused) {
-            // the pair's query heads, rotated, go through shared memory: every thread rotates some of their dims
-            // (the first run's are there already)
-            if (!first_run) {
-                for (int x = tid; x < G * (HD - half); x += TW * 32) {
-                    const int g = x / (HD - half);
-                    rotate_head(b, (kvh * G + g) * HD, len - 1, q_s + g * HD, nullptr, x % (HD - half));
-                }
-                __syncthreads();
-            }
-            qp = q_s + quad * HD + kh * (HD / 2);
-        }
-#pragma unroll
-        for (int ks = 0; ks < C::KS_W; ks++) {
-            qb[ks][0] = (quad < G) ? *(const uint32_t*)(qp + ks * 16 + 2 * t) : 0u;
-            qb[ks][1] = (quad < G) ? *(const uint32_t*)(qp + ks * 16 + 8 + 2 * t) : 0u;
-        }
-#pragma unroll
-        for (int m = 0; m < C::MT_W; m++) { o[m][0] = o[m][1] = o[m][2] = o[m][3] = 0.f; o2[m][0] = o2[m][1] = o2[m][2] = o2[m][3] = 0.f; }
-        m_b = -INFINITY; m_c0 = -INFINITY; m_c1 = -INFINITY; l_b = 0.f;
+    auto page_all_keys = [&](int row0) -> bool {
+        if (no_invalid) return true;
+        bool ok = is_key(row0) && is_key(row0 + PAGE - 1);
+        // in a ring the rows that are too old form one circular run; it may lie inside the page
+        if (wrapped && ok) ok = !(old_beg > row0 && old_beg <= row0 + PAGE - 1);
+        return ok;
     };
-    // the run is done: write the result or a part of it, and fold the parts if this was the last one
-    auto end_run = [&]() {
-        cur.left -= seg_n;
-        cur.pg += seg_n;
-        if (cur.pg == cur.np && cur.left > 0) {
-            cur.pg = 0;
-            if (++cur.kvh == a.n_kv_heads) { cur.kvh = 0; cur.b++; cur.np = seq_pages(cur.b, cur.first_page, cur.hot); }
+    auto next_run = [&](PageCursor& c, int n) {                     // the cursor moves past a run of n pages
+        c.left -= n;
+        c.pg += n;
+        if (c.pg == c.np && c.left > 0) {
+            c.pg = 0;
+            if (++c.kvh == a.n_kv_heads) { c.kvh = 0; c.b++; c.np = seq_pages(c.b, c.first_page, c.hot); }
         }
-        // the sums of the quad's four lanes are the head's sum (the same in every warp)
+    };
+
+    if (warp == TW) {
+        // ================= the copies: a stage is refilled when all eight warps have let go of it =================
+        if (lane == 0) {
+            bool ok = true;
+            while (ahead.left > 0) {
+                const int s = issued % C::STAGES;
+                if (issued >= C::STAGES && !wait_on(&empty[s], ((issued / C::STAGES) - 1) & 1)) { ok = false; break; }
+                issue();
+            }
+            if (!ok || s_abort) {
+                // a wait ran out: record it, and let copies that were issued land before the CTA ends
+                atomicExch(&g_attn_error, 1);
+                for (int j = max(0, issued - C::STAGES); j < issued; j++) mbar_wait(&full[j % C::STAGES], (j / C::STAGES) & 1);
+            }
+        }
+    } else if (warp < TW / 2) {
+        // ================= scores: S^T = K Q^T of this warp's 16 keys, scaled, capped, masked =================
+        const int mt = warp;
+        uint32_t koff[C::KS];                                       // where this lane's ldmatrix rows lie inside a stage
 #pragma unroll
-        for (int m = 0; m < C::MT_W; m++) { o[m][0] += o2[m][0]; o[m][1] += o2[m][1]; o[m][2] += o2[m][2]; o[m][3] += o2[m][3]; }
-        l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
-        l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
-        const float L0 = __shfl_sync(0xffffffffu, l_b, 4 * (2 * t)), L1 = __shfl_sync(0xffffffffu, l_b, 4 * (2 * t + 1));
-        const bool begins = seg_pg0 == 0, whole = STREAM ? (begins && seg_n == seg_np) : (a.n_splits == 1);
-        // where the parts of this (sequence, kv head) lie, and how many there are
-        int n_parts, my_part, c_first = 0;
-        if (STREAM) {
-            const long long g0 = (long long)pref[b] * a.n_kv_heads + (long long)kvh * seg_np;   // the pair's first page
-            c_first = (int)(((g0 + 1) * n_ctas - 1) / total);       // the CTA whose run holds page g: floor(((g + 1) n - 1) / total)
-            const int c_last = (int)(((g0 + seg_np) * n_ctas - 1) / total);
-            n_parts = c_last - c_first + 1;
-            my_part = blockIdx.x - c_first;
-        } else {
-            n_parts = a.n_splits;
-            my_part = blockIdx.z;
+        for (int ks = 0; ks < C::KS; ks++)
+            koff[ks] = sw_off(mt * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), ks * 2 + (lane >> 4));
+        uint32_t meet_phase = 0;
+        int i = 0;                                                  // pages done
+        bool first_run = true;
+        while (cur.left > 0) {
+            const int b = cur.b, kvh = cur.kvh, seg_pg0 = cur.pg, seg_n = min(cur.left, cur.np - cur.pg);
+            const int seg_first = cur.first_page;
+            set_geometry(b);
+            // B fragments of Q^T: b0 = Q[head quad][16 ks + 2t, +1], b1 = Q[head quad][16 ks + 8 + 2t, +1]; heads >= G zero
+            const bf16* qp = (const bf16*)a.q + (size_t)b * a.q_stride + (size_t)(kvh * G + quad) * HD;
+            if (fused) {
+                // the pair's query heads, rotated, go through shared memory (the first run's are there already)
+                if (!first_run) {
+                    if (!meet(0, meet_phase)) break;                // nobody reads the run before's queries any more
+                    for (int x = tid; x < G * (HD - half); x += (TW / 2) * 32) {
+                        const int g = x / (HD - half);
+                        rotate_head(b, (kvh * G + g) * HD, len - 1, q_s + g * HD, nullptr, x % (HD - half));
+                    }
+                    if (!meet(0, meet_phase)) break;
+                }
+                qp = q_s + quad * HD;
+            }
+            first_run = false;
+            uint32_t qb[C::KS][2];
+#pragma unroll
+            for (int ks = 0; ks < C::KS; ks++) {
+                qb[ks][0] = (quad < G) ? *(const uint32_t*)(qp + ks * 16 + 2 * t) : 0u;
+                qb[ks][1] = (quad < G) ? *(const uint32_t*)(qp + ks * 16 + 8 + 2 * t) : 0u;
+            }
+            bool ok = true;
+            for (int j = 0; j < seg_n; j++, i++) {
+                const int s = i % C::STAGES, u = i & 1;
+                if (!wait_on(&full[s], (i / C::STAGES) & 1) || !wait_on(&s_empty[u], ((i >> 1) & 1) ^ 1)) { ok = false; break; }
+                const uint32_t stage = smem_base + s * C::STAGE_BYTES;
+                const int row0 = (seg_first + seg_pg0 + j) * PAGE;
+                const bool all_ok = page_all_keys(row0);
+                float c[4][4];                                       // four chains: the MMAs of a chain wait for one another
+#pragma unroll
+                for (int x = 0; x < 4; x++) { c[x][0] = c[x][1] = c[x][2] = c[x][3] = 0.f; }
+#pragma unroll
+                for (int ks = 0; ks < C::KS; ks++) {
+                    uint32_t a0, a1, a2, a3;
+                    ldsm_x4(stage + koff[ks], a0, a1, a2, a3);
+                    mma_16816(c[ks & 3], a0, a1, a2, a3, qb[ks][0], qb[ks][1]);
+                }
+                // the accumulators hold keys quad, quad + 8 for heads 2t, 2t + 1
+                float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int h = 2 * t + (e & 1), key = mt * 16 + quad + (e >> 1) * 8;
+                    float v = ((c[0][e] + c[1][e]) + (c[2][e] + c[3][e])) * a.scale;
+                    if (a.cap > 0.f) v = softcap_fast(v, a.cap, inv_cap);
+                    if (!(all_ok || is_key(row0 + key))) v = -INFINITY;
+                    if (h < G) sf[(u * 8 + h) * SROW + key] = v;
+                    mx[e & 1] = fmaxf(mx[e & 1], v);
+                }
+#pragma unroll
+                for (int o = 4; o < 32; o <<= 1) {                  // over the warp's keys: lanes that differ in quad
+                    mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], o));
+                    mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], o));
+                }
+                if (quad == 0) { pm[(u * 8 + 2 * t) * 4 + mt] = mx[0]; pm[(u * 8 + 2 * t + 1) * 4 + mt] = mx[1]; }
+                __syncwarp();
+                if (lane == 0) { mbar_arrive(&s_full[u]); mbar_arrive(&empty[s]); }
+            }
+            if (!ok) break;
+            next_run(cur, seg_n);
         }
-        auto part_of = [&](int k, int hg) -> float* {               // part k of head hg of this pair
-            if (STREAM) return a.partial + ((size_t)((c_first + k) * 2 + (k == 0 ? 1 : 0)) * G + hg) * (HD + 2);
-            return a.partial + (((size_t)b * a.n_heads + kvh * G + hg) * a.n_splits + k) * (HD + 2);
-        };
-        if (pv_warp) {
+    } else {
+        // ================= outputs: running softmax, O^T += V^T P^T for head_dim / 4 dims of this warp =================
+        const int ow = warp - TW / 2;
+        const int d0 = ow * (HD / 4);
+        uint32_t voff[C::MT_W][4];
+#pragma unroll
+        for (int m = 0; m < C::MT_W; m++)
+#pragma unroll
+            for (int ks = 0; ks < 4; ks++)
+                voff[m][ks] = C::TILE_BYTES + sw_off(ks * 16 + (lane >> 4) * 8 + (lane & 7), (d0 + m * 16) / 8 + ((lane >> 3) & 1));
+        uint32_t meet_phase = 0;
+        int i = 0;
+        bool once = !STREAM;                                        // (split only) an empty piece still reports "nothing here"
+        while (cur.left > 0 || once) {
+            once = false;
+            const int b = cur.b, kvh = cur.kvh, seg_pg0 = cur.pg, seg_n = min(cur.left, cur.np - cur.pg), seg_np = cur.np;
+            const int seg_first = cur.first_page;
+            set_geometry(b);
+            float o[C::MT_W][4], o2[C::MT_W][4];                    // accumulator rows are dims, columns heads 2t, 2t+1; two chains
+#pragma unroll
+            for (int m = 0; m < C::MT_W; m++) { o[m][0] = o[m][1] = o[m][2] = o[m][3] = 0.f; o2[m][0] = o2[m][1] = o2[m][2] = o2[m][3] = 0.f; }
+            // running maximum of the heads this lane meets: `quad` (its P^T column) and 2t, 2t+1 (its O^T columns)
+            float m_b = -INFINITY, m_c0 = -INFINITY, m_c1 = -INFINITY, l_b = 0.f;
+            bool ok = true;
+            for (int j = 0; j < seg_n; j++, i++) {
+                const int s = i % C::STAGES, u = i & 1;
+                if (!wait_on(&s_full[u], (i >> 1) & 1)) { ok = false; break; }
+                // the page's maximum per head from the four score warps; the scores of this lane's 16 keys for head quad
+                const float4 qb4 = *(const float4*)(pm + (u * 8 + quad) * 4);
+                const float4 c04 = *(const float4*)(pm + (u * 8 + 2 * t) * 4), c14 = *(const float4*)(pm + (u * 8 + 2 * t + 1) * 4);
+                float sc[4][4];
+                {
+                    const float* s0 = sf + (u * 8 + (quad < G ? quad : 0)) * SROW + 2 * t;
+#pragma unroll
+                    for (int ks = 0; ks < 4; ks++) {
+                        const float2 x = *(const float2*)(s0 + ks * 16), y = *(const float2*)(s0 + ks * 16 + 8);
+                        sc[ks][0] = x.x; sc[ks][1] = x.y; sc[ks][2] = y.x; sc[ks][3] = y.y;
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s_empty[u]);
+                const float pb_max = quad < G ? fmaxf(fmaxf(qb4.x, qb4.y), fmaxf(qb4.z, qb4.w)) : -INFINITY;
+                const float pc0 = 2 * t < G ? fmaxf(fmaxf(c04.x, c04.y), fmaxf(c04.z, c04.w)) : -INFINITY;
+                const float pc1 = 2 * t + 1 < G ? fmaxf(fmaxf(c14.x, c14.y), fmaxf(c14.z, c14.w)) : -INFINITY;
+                const float nb = fmaxf(m_b, pb_max), n0 = fmaxf(m_c0, pc0), n1 = fmaxf(m_c1, pc1);
+                const float sb = (nb == -INFINITY) ? 0.f : nb;
+                const float corr_b = (m_b == -INFINITY) ? 0.f : __expf(m_b - sb);
+                const float corr0 = (m_c0 == -INFINITY) ? 0.f : __expf(m_c0 - ((n0 == -INFINITY) ? 0.f : n0));
+                const float corr1 = (m_c1 == -INFINITY) ? 0.f : __expf(m_c1 - ((n1 == -INFINITY) ? 0.f : n1));
+                m_b = nb; m_c0 = n0; m_c1 = n1;
+                uint32_t pb[4][2];
+                float ps = 0.f;
+                if (quad < G) {
+#pragma unroll
+                    for (int ks = 0; ks < 4; ks++) {
+                        const float p0 = __expf(sc[ks][0] - sb), p1 = __expf(sc[ks][1] - sb), p2 = __expf(sc[ks][2] - sb), p3 = __expf(sc[ks][3] - sb);
+                        ps += (p0 + p1) + (p2 + p3);
+                        __nv_bfloat162 h0 = __floats2bfloat162_rn(p0, p1), h1 = __floats2bfloat162_rn(p2, p3);
+                        pb[ks][0] = *(uint32_t*)&h0; pb[ks][1] = *(uint32_t*)&h1;
+                    }
+                } else {
+#pragma unroll
+                    for (int ks = 0; ks < 4; ks++) { pb[ks][0] = 0u; pb[ks][1] = 0u; }
+                }
+                l_b = l_b * corr_b + ps;
+                // the page's values (the score warps have seen it land; so does this warp)
+                if (!wait_on(&full[s], (i / C::STAGES) & 1)) { ok = false; break; }
+                const uint32_t stage = smem_base + s * C::STAGE_BYTES;
+                const int row0 = (seg_first + seg_pg0 + j) * PAGE;
+                const bool all_ok = page_all_keys(row0);
+                if (!all_ok) {
+                    // rows of the page that are not keys: their probabilities are 0, but 0 * NaN would still poison O,
+                    // so this warp zeroes them in the columns it reads
+                    uint8_t* v_s = smem + s * C::STAGE_BYTES + C::TILE_BYTES;
+                    for (int x = lane; x < PAGE * (HD / 32); x += 32) {
+                        const int r = x / (HD / 32), cc = d0 / 8 + x % (HD / 32);
+                        if (!is_key(row0 + r)) *(uint4*)(v_s + sw_off(r, cc)) = make_uint4(0, 0, 0, 0);
+                    }
+                    __syncwarp();
+                }
+#pragma unroll
+                for (int m = 0; m < C::MT_W; m++) {
+                    o[m][0] *= corr0; o[m][1] *= corr1; o[m][2] *= corr0; o[m][3] *= corr1;
+                    o2[m][0] *= corr0; o2[m][1] *= corr1; o2[m][2] *= corr0; o2[m][3] *= corr1;
+#pragma unroll
+                    for (int ks = 0; ks < 4; ks++) {
+                        uint32_t a0, a1, a2, a3;
+                        ldsm_x4_t(stage + voff[m][ks], a0, a1, a2, a3);
+                        mma_16816((ks & 1) ? o2[m] : o[m], a0, a1, a2, a3, pb[ks][0], pb[ks][1]);
+                    }
+                }
+                // rows zeroed by ordinary stores; the stage is refilled by the copy engine
+                if (!all_ok) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[s]);
+            }
+            if (!ok) break;
+            next_run(cur, seg_n);
+
+            // ---- the run is done.  The sums of the quad's four lanes are the head's sum (the same in every warp).
+#pragma unroll
+            for (int m = 0; m < C::MT_W; m++) { o[m][0] += o2[m][0]; o[m][1] += o2[m][1]; o[m][2] += o2[m][2]; o[m][3] += o2[m][3]; }
+            l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+            l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+            const float L0 = __shfl_sync(0xffffffffu, l_b, 4 * (2 * t)), L1 = __shfl_sync(0xffffffffu, l_b, 4 * (2 * t + 1));
+            const bool begins = seg_pg0 == 0, whole = STREAM ? (begins && seg_n == seg_np) : (a.n_splits == 1);
+            // where the parts of this (sequence, kv head) lie, and how many there are
+            int n_parts, my_part, c_first = 0;
+            if (STREAM) {
+                const long long g0 = (long long)pref[b] * a.n_kv_heads + (long long)kvh * seg_np;   // the pair's first page
+                c_first = (int)(((g0 + 1) * n_ctas - 1) / total);   // the CTA whose run holds page g: floor(((g + 1) n - 1) / total)
+                const int c_last = (int)(((g0 + seg_np) * n_ctas - 1) / total);
+                n_parts = c_last - c_first + 1;
+                my_part = blockIdx.x - c_first;
+            } else {
+                n_parts = a.n_splits;
+                my_part = blockIdx.z;
+            }
+            auto part_of = [&](int k, int hg) -> float* {           // part k of head hg of this pair
+                if (STREAM) return a.partial + ((size_t)((c_first + k) * 2 + (k == 0 ? 1 : 0)) * G + hg) * (HD + 2);
+                return a.partial + (((size_t)b * a.n_heads + kvh * G + hg) * a.n_splits + k) * (HD + 2);
+            };
 #pragma unroll
             for (int e = 0; e < 2; e++) {
                 const int hg = 2 * t + e;
@@ -735,191 +908,87 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                         dst[d0 + m * 16 + quad] = o[m][e];
                         dst[d0 + m * 16 + quad + 8] = o[m][2 + e];
                     }
-                    if (warp == 0 && quad == 0) { dst[HD] = M; dst[HD + 1] = L; }
+                    if (ow == 0 && quad == 0) { dst[HD] = M; dst[HD + 1] = L; }
                 }
             }
-        }
-        if (whole || a.tickets == nullptr) return;
-        if (tid == 0) { s_pend[n_pend][0] = b; s_pend[n_pend][1] = kvh; s_pend[n_pend][2] = n_parts; s_pend[n_pend][3] = c_first; }
-        n_pend++;
-    };
-    // the CTA that finishes a pair's last part folds the parts, in their order
-    auto fold_pending = [&]() {
-        if (n_pend == 0) return;
-        // The parts were written by all threads; the barrier orders them before thread q's counting, and the
-        // counting is a release (for the parts) and an acquire (for the other CTAs' parts) at GPU scope.
-        __syncthreads();
-        if (tid < n_pend) {
-            int* ticket = a.tickets + (size_t)s_pend[tid][0] * a.n_kv_heads + s_pend[tid][1];
-            int old;
-            asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(old) : "l"(ticket) : "memory");
-            s_last[tid] = (old == s_pend[tid][2] - 1);
-            if (s_last[tid]) *ticket = 0;                           // left at zero for the next launch
-        }
-        __syncthreads();
-        for (int q = 0; q < n_pend; q++) {
-            if (!s_last[q]) continue;
-            const int fb = s_pend[q][0], fkvh = s_pend[q][1], n_parts = s_pend[q][2], c_first = s_pend[q][3];
-            auto part_of = [&](int k, int hg) -> const float* {
-                if (STREAM) return a.partial + ((size_t)((c_first + k) * 2 + (k == 0 ? 1 : 0)) * G + hg) * (HD + 2);
-                return a.partial + (((size_t)fb * a.n_heads + fkvh * G + hg) * a.n_splits + k) * (HD + 2);
-            };
-            for (int x = tid; x < G * HD; x += TW * 32) {
-                const int hg = x / HD, d = x % HD;
-                // out = sum_k e^(m_k - M) o_k / sum_k e^(m_k - M) l_k in the parts' order, eight parts requested at a
-                // time; M is the running maximum, by which the sums so far are rescaled
-                float M = -INFINITY, L = 0.f, acc = 0.f;
-                for (int k0 = 0; k0 < n_parts; k0 += 8) {
-                    float ms[8], ls[8], os[8];
-#pragma unroll
-                    for (int k = 0; k < 8; k++)
-                        if (k0 + k < n_parts) {
-                            const float* pk = part_of(k0 + k, hg);
-                            ms[k] = __ldcg(pk + HD); ls[k] = __ldcg(pk + HD + 1); os[k] = __ldcg(pk + d);
-                        }
-                    float Mn = M;
-#pragma unroll
-                    for (int k = 0; k < 8; k++) if (k0 + k < n_parts) Mn = fmaxf(Mn, ms[k]);
-                    if (Mn == -INFINITY) continue;
-                    const float r = (M == -INFINITY) ? 0.f : __expf(M - Mn);
-                    L *= r; acc *= r; M = Mn;
-#pragma unroll
-                    for (int k = 0; k < 8; k++)
-                        if (k0 + k < n_parts && ms[k] != -INFINITY) { const float f = __expf(ms[k] - M); L += ls[k] * f; acc += os[k] * f; }
-                }
-                ((bf16*)a.out)[((size_t)fb * a.n_heads + fkvh * G + hg) * HD + d] = __float2bfloat16_rn(acc / L);
+            if (whole || a.tickets == nullptr) continue;
+
+            // ---- the CTA that finishes the pair's last part folds the parts, in their order.  The parts were written by
+            // all four output warps; their meeting orders them before the counting, which is a release (for this CTA's
+            // part) and an acquire (for the others') at GPU scope.
+            if (!meet(1, meet_phase)) break;
+            if (ow == 0 && lane == 0) {
+                int* ticket = a.tickets + (size_t)b * a.n_kv_heads + kvh;
+                int old;
+                asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(old) : "l"(ticket) : "memory");
+                s_last = (old == n_parts - 1);
+                if (s_last) *ticket = 0;                            // left at zero for the next launch
+                s_job[0] = b; s_job[1] = kvh; s_job[2] = n_parts;
             }
-        }
-    };
-
-    const int my_pages = cur.left;
-    begin_run(true);                                // the first run; further ones (stream only) begin inside the loop
-    if (my_pages == 0) end_run();                   // (split only) an empty piece still reports "nothing here"
-    for (int i = 0; i < my_pages; i++) {
-        if (STREAM && run_left == 0) begin_run(false);
-        {
-            const int j = seg_n - run_left;
-
-            const int s = i % C::STAGES;
-            const bool got = mbar_wait(&full[s], (i / C::STAGES) & 1);
-            const uint32_t stage = smem_base + s * C::STAGE_BYTES;
-            uint8_t* v_s = smem + s * C::STAGE_BYTES + C::TILE_BYTES;
-            const int row0 = (seg_first + seg_pg0 + j) * PAGE;
-
-            // ---- A: partial S^T of this warp's 16 keys over its half of the dims (two chains)
-            {
-                float c[4][4];                               // four chains: the MMAs of a chain wait for one another
+            if (!meet(1, meet_phase)) break;
+            if (!STREAM) break;                                     // split: one run; all eight warps fold it together below
+            if (s_last) {
+                for (int x = tid - (TW / 2) * 32; x < G * HD; x += (TW / 2) * 32) {
+                    const int hg = x / HD, d = x % HD;
+                    // out = sum_k e^(m_k - M) o_k / sum_k e^(m_k - M) l_k in the parts' order, eight parts requested at a
+                    // time; M is the running maximum, by which the sums so far are rescaled
+                    float M = -INFINITY, L = 0.f, acc = 0.f;
+                    for (int k0 = 0; k0 < n_parts; k0 += 8) {
+                        float ms[8], ls[8], os[8];
 #pragma unroll
-                for (int x = 0; x < 4; x++) { c[x][0] = c[x][1] = c[x][2] = c[x][3] = 0.f; }
+                        for (int k = 0; k < 8; k++)
+                            if (k0 + k < n_parts) {
+                                const float* pk = part_of(k0 + k, hg);
+                                ms[k] = __ldcg(pk + HD); ls[k] = __ldcg(pk + HD + 1); os[k] = __ldcg(pk + d);
+                            }
+                        float Mn = M;
 #pragma unroll
-                for (int ks = 0; ks < C::KS_W; ks++) {
-                    uint32_t a0, a1, a2, a3;
-                    ldsm_x4(stage + koff[ks], a0, a1, a2, a3);
-                    mma_16816(c[ks & 3], a0, a1, a2, a3, qb[ks][0], qb[ks][1]);
-                }
+                        for (int k = 0; k < 8; k++) if (k0 + k < n_parts) Mn = fmaxf(Mn, ms[k]);
+                        if (Mn == -INFINITY) continue;
+                        const float r = (M == -INFINITY) ? 0.f : __expf(M - Mn);
+                        L *= r; acc *= r; M = Mn;
 #pragma unroll
-                for (int e = 0; e < 2; e++) {
-                    const int h = 2 * t + e;
-                    if (h < G) {
-                        float* dst = sp + (kh * 8 + h) * SROW + mt * 16 + quad;
-                        dst[0] = (c[0][e] + c[1][e]) + (c[2][e] + c[3][e]);
-                        dst[8] = (c[0][2 + e] + c[1][2 + e]) + (c[2][2 + e] + c[3][2 + e]);
+                        for (int k = 0; k < 8; k++)
+                            if (k0 + k < n_parts && ms[k] != -INFINITY) { const float f = __expf(ms[k] - M); L += ls[k] * f; acc += os[k] * f; }
                     }
+                    ((bf16*)a.out)[((size_t)b * a.n_heads + kvh * G + hg) * HD + d] = __float2bfloat16_rn(acc / L);
                 }
             }
-            // rows of the page that are not keys: zero their V rows
-            bool all_ok = no_invalid;
-            if (!all_ok) {
-                all_ok = is_key(row0) && is_key(row0 + PAGE - 1);
-                // in a ring the rows that are too old form one circular run; it may lie inside the page
-                if (wrapped && all_ok) all_ok = !(old_beg > row0 && old_beg <= row0 + PAGE - 1);
-            }
-            if (!all_ok) {
-                for (int x = tid; x < PAGE * (HD / 8); x += TW * 32) {
-                    const int r = x / (HD / 8), c = x % (HD / 8);
-                    if (!is_key(row0 + r)) *(uint4*)(v_s + sw_off(r, c)) = make_uint4(0, 0, 0, 0);
-                }
-                // these rows were written by ordinary stores; the stage is later refilled by bulk copies
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            }
-            if (!__syncthreads_and(got)) { aborted = true; break; }  // the same answer in every thread: leave the page loop
-            visited = i + 1;
-            // every warp has left phase C of the page before: that page's stage can take the next copy
-            if (tid == ISSUER && i >= 1 && ahead.left > 0) issue();
-
-            // ---- B: final scores, one thread per (key, head); heads h and h+4 share a thread
-            {
-                const int key = tid & 63;
-#pragma unroll
-                for (int hh = 0; hh < 2; hh++) {
-                    const int h = (tid >> 6) + 4 * hh;              // uniform over a warp
-                    if (h < G) {
-                        float v = (sp[h * SROW + key] + sp[(8 + h) * SROW + key]) * a.scale;
-                        if (a.cap > 0.f) v = softcap_fast(v, a.cap, inv_cap);
-                        if (!(all_ok || is_key(row0 + key))) v = -INFINITY;
-                        sf[h * SROW + key] = v;
-                        const float wm = warp_max(v);
-                        if (lane == 0) pm[h * 2 + ((tid >> 5) & 1)] = wm;
-                    }
-                }
-            }
-            __syncthreads();
-
-            // ---- C: running softmax (the same numbers in every warp), then O^T += V^T P^T
-            {
-                const float pb_max = fmaxf(pm[quad * 2], pm[quad * 2 + 1]);        // -inf for heads >= G
-                const float pc0 = fmaxf(pm[4 * t], pm[4 * t + 1]), pc1 = fmaxf(pm[4 * t + 2], pm[4 * t + 3]);
-                const float nb = fmaxf(m_b, pb_max), n0 = fmaxf(m_c0, pc0), n1 = fmaxf(m_c1, pc1);
-                const float sb = (nb == -INFINITY) ? 0.f : nb;
-                const float corr_b = (m_b == -INFINITY) ? 0.f : __expf(m_b - sb);
-                const float corr0 = (m_c0 == -INFINITY) ? 0.f : __expf(m_c0 - ((n0 == -INFINITY) ? 0.f : n0));
-                const float corr1 = (m_c1 == -INFINITY) ? 0.f : __expf(m_c1 - ((n1 == -INFINITY) ? 0.f : n1));
-                m_b = nb; m_c0 = n0; m_c1 = n1;
-                uint32_t pb[4][2];
-                float ps = 0.f;
-                if (quad < G) {
-                    const float* srow = sf + quad * SROW + 2 * t;
-#pragma unroll
-                    for (int ks = 0; ks < 4; ks++) {
-                        const float2 x = *(const float2*)(srow + ks * 16), y = *(const float2*)(srow + ks * 16 + 8);
-                        const float p0 = __expf(x.x - sb), p1 = __expf(x.y - sb), p2 = __expf(y.x - sb), p3 = __expf(y.y - sb);
-                        ps += (p0 + p1) + (p2 + p3);
-                        __nv_bfloat162 h0 = __floats2bfloat162_rn(p0, p1), h1 = __floats2bfloat162_rn(p2, p3);
-                        pb[ks][0] = *(uint32_t*)&h0; pb[ks][1] = *(uint32_t*)&h1;
-                    }
-                } else {
-#pragma unroll
-                    for (int ks = 0; ks < 4; ks++) { pb[ks][0] = 0u; pb[ks][1] = 0u; }
-                }
-                l_b = l_b * corr_b + ps;
-                if (pv_warp) {
-#pragma unroll
-                    for (int m = 0; m < C::MT_W; m++) {
-                        o[m][0] *= corr0; o[m][1] *= corr1; o[m][2] *= corr0; o[m][3] *= corr1;
-                        o2[m][0] *= corr0; o2[m][1] *= corr1; o2[m][2] *= corr0; o2[m][3] *= corr1;
-#pragma unroll
-                        for (int ks = 0; ks < 4; ks++) {
-                            uint32_t a0, a1, a2, a3;
-                            ldsm_x4_t(stage + voff[m][ks], a0, a1, a2, a3);
-                            mma_16816((ks & 1) ? o2[m] : o[m], a0, a1, a2, a3, pb[ks][0], pb[ks][1]);
-                        }
-                    }
-                }
-            }
-        }
-        if (--run_left == 0) {
-            end_run();
-            // stream: folding at once, not when the CTA is through: a part that continues a pair ends early in the
-            // CTA's run, so the pair's fold falls to the CTA before this one and every CTA folds one pair at its end
-            if (STREAM) { fold_pending(); n_pend = 0; }
+            if (!meet(1, meet_phase)) break;                        // s_last is rewritten by the next run
         }
     }
-    if (!STREAM && !aborted) fold_pending();        // split: the CTA has one run; kept out of the page loop
-
-    if (aborted && tid == ISSUER) {
-        // a wait ran out: record it, and let copies that were issued land before the CTA ends
-        atomicExch(&g_attn_error, 1);
-        for (int i = visited; i < issued; i++) mbar_wait(&full[i % C::STAGES], (i / C::STAGES) & 1);
+    if (!STREAM && warp < TW && a.n_splits > 1 && a.tickets != nullptr) {
+        // split: the CTA had one run.  If it was the pair's last part, all eight warps fold the parts, in their order:
+        // out = sum_k e^(m_k - M) o_k / sum_k e^(m_k - M) l_k, eight parts requested at a time; M is the running
+        // maximum, by which the sums so far are rescaled.
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&grp[2]);
+        if (!wait_on(&grp[2], 0) || !s_last) return;
+        const int b = s_job[0], kvh = s_job[1], n_parts = s_job[2];
+        for (int x = tid; x < G * HD; x += TW * 32) {
+            const int hg = x / HD, d = x % HD;
+            const float* p0 = a.partial + ((size_t)b * a.n_heads + kvh * G + hg) * a.n_splits * (HD + 2);
+            float M = -INFINITY, L = 0.f, acc = 0.f;
+            for (int k0 = 0; k0 < n_parts; k0 += 8) {
+                float ms[8], ls[8], os[8];
+#pragma unroll
+                for (int k = 0; k < 8; k++)
+                    if (k0 + k < n_parts) {
+                        const float* pk = p0 + (size_t)(k0 + k) * (HD + 2);
+                        ms[k] = __ldcg(pk + HD); ls[k] = __ldcg(pk + HD + 1); os[k] = __ldcg(pk + d);
+                    }
+                float Mn = M;
+#pragma unroll
+                for (int k = 0; k < 8; k++) if (k0 + k < n_parts) Mn = fmaxf(Mn, ms[k]);
+                if (Mn == -INFINITY) continue;
+                const float r = (M == -INFINITY) ? 0.f : __expf(M - Mn);
+                L *= r; acc *= r; M = Mn;
+#pragma unroll
+                for (int k = 0; k < 8; k++)
+                    if (k0 + k < n_parts && ms[k] != -INFINITY) { const float f = __expf(ms[k] - M); L += ls[k] * f; acc += os[k] * f; }
+            }
+            ((bf16*)a.out)[((size_t)b * a.n_heads + kvh * G + hg) * HD + d] = __float2bfloat16_rn(acc / L);
+        }
     }
 }
 
@@ -968,7 +1037,7 @@ static int launch_mma(const DecodeArgs& a, int batch, int n_ctas, cudaStream_t s
     if (pool_map(&mk, a.k_pool, pool_rows, HD) || pool_map(&mv, a.v_pool, pool_rows, HD)) return -1;
     dim3 grid(batch, a.n_kv_heads, a.n_splits);
     if (STREAM) grid = dim3(n_ctas);
-    tb_launch(kern, dim3(grid), dim3(TW * 32), C::SMEM, stream, mk, mv, a, batch);
+    tb_launch(kern, dim3(grid), dim3(NTHREADS), C::SMEM, stream, mk, mv, a, batch);
     return tb_launch_status();
 }
 
