@@ -60,12 +60,16 @@ __device__ __forceinline__ float gated(float g, float u, int act) {
     return __fdividef(g, 1.0f + __expf(-y)) * u;
 }
 
-// Shared-memory budget: as many stages as an SM holds.  (Half of it, so that the next product's CTAs could
-// already sit on the SM and stream weights while this one drains, was measured slower: bytes in flight
-// per SM matter more than the overlap.)
+// Shared-memory budget.  Many tokens (tiles are reused, the tensor cores are the limit): as many stages as an SM
+// holds.  Few tokens (swapped tiles, a stream of weights): half of an SM, so that the next product's CTAs already
+// sit beside this one's, fetch their tensor maps and fill their stages with weights while this one drains; the
+// two kernels together keep as many bytes in flight as one with the whole SM.
+#ifndef TB_SWAP_KB
+#define TB_SWAP_KB 108
+#endif
 template <int BN, bool SWAP> struct Cfg {
     static constexpr int STAGE_BYTES = BM * BK * 2 + BN * BK * 2;
-    static constexpr int BUDGET = 200 * 1024;
+    static constexpr int BUDGET = (SWAP ? TB_SWAP_KB : 200) * 1024;
     static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 10 ? 10 : STAGES_RAW;
     static constexpr int ACC_COLS = BN < 32 ? 32 : BN;               // columns of one accumulator stage
