@@ -67,9 +67,9 @@ __device__ __forceinline__ float gated(float g, float u, int act) {
 #ifndef TB_SWAP_KB
 #define TB_SWAP_KB 108
 #endif
-template <int BN, bool SWAP> struct Cfg {
+template <int BN, bool SWAP, bool WIDE = false> struct Cfg {
     static constexpr int STAGE_BYTES = BM * BK * 2 + BN * BK * 2;
-    static constexpr int BUDGET = (SWAP ? TB_SWAP_KB : 200) * 1024;
+    static constexpr int BUDGET = ((SWAP && !WIDE) ? TB_SWAP_KB : 200) * 1024;
     static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 10 ? 10 : STAGES_RAW;
     static constexpr int ACC_COLS = BN < 32 ? 32 : BN;               // columns of one accumulator stage
@@ -77,11 +77,11 @@ template <int BN, bool SWAP> struct Cfg {
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
 };
 
-template <int BN, bool SWAP, typename TOut, bool GATED>
+template <int BN, bool SWAP, typename TOut, bool GATED, bool WIDE>
 __global__ void __launch_bounds__(192, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, GemmParams p) {
     pdl_launch_dependents();
-    using C = Cfg<BN, SWAP>;
+    using C = Cfg<BN, SWAP, WIDE>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(smem + C::STAGES * C::STAGE_BYTES);
@@ -369,11 +369,11 @@ static int make_map(CUtensorMap* m, const void* base, long long rows, long long 
 
 static int g_sms = 0;
 
-template <int BN, bool SWAP, typename TOut, bool GATED = false>
+template <int BN, bool SWAP, typename TOut, bool GATED = false, bool WIDE = false>
 static int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmParams& p, cudaStream_t stream) {
-    using C = Cfg<BN, SWAP>;
+    using C = Cfg<BN, SWAP, WIDE>;
     static bool attr_set = false;
-    auto kern = gemm_tc_kernel<BN, SWAP, TOut, GATED>;
+    auto kern = gemm_tc_kernel<BN, SWAP, TOut, GATED, WIDE>;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
         if (e != cudaSuccess) return (int)e;
@@ -477,7 +477,13 @@ extern "C" int tb_gemm_tc(const void* A, const void* W, void* C, int c_dtype, in
 #undef GG
     } else if (swap) {
         switch (bn) {
-        case 16: st = GO(16, true); break;
+        case 16:
+            // a long stream (several tiles per CTA: an output head): the kernel's own bytes in flight count for more
+            // than the overlap with its neighbours, so it takes the whole SM
+            if (c_dtype == TB_F32 && (long long)p.tiles_p * p.tiles_q * p.splits >= 4LL * g_sms)
+                st = launch<16, true, float, false, true>(mp, mq, p, stream);
+            else st = GO(16, true);
+            break;
         case 32: st = GO(32, true); break;
         case 64: st = GO(64, true); break;
         default: st = GO(128, true); break;
