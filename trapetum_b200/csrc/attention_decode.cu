@@ -959,7 +959,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     }
     if (!STREAM && warp < TW && a.n_splits > 1 && a.tickets != nullptr) {
         // split: the CTA had one run.  If it was the pair's last part, all eight warps fold the parts, in their order:
-        // out = sum_k e^(m_k - M) o_k / sum_k e^(m_k - M) l_k, eight parts requested at a time; M is the running
+        // out = sum_k e^(m_k - M) o_k / sum_k e^(m_k - M) l_k, sixteen parts requested at a time; M is the running
         // maximum, by which the sums so far are rescaled.
         __syncwarp();
         if (lane == 0) mbar_arrive(&grp[2]);
@@ -969,22 +969,22 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             const int hg = x / HD, d = x % HD;
             const float* p0 = a.partial + ((size_t)b * a.n_heads + kvh * G + hg) * a.n_splits * (HD + 2);
             float M = -INFINITY, L = 0.f, acc = 0.f;
-            for (int k0 = 0; k0 < n_parts; k0 += 8) {
-                float ms[8], ls[8], os[8];
+            for (int k0 = 0; k0 < n_parts; k0 += 16) {
+                float ms[16], ls[16], os[16];
 #pragma unroll
-                for (int k = 0; k < 8; k++)
+                for (int k = 0; k < 16; k++)
                     if (k0 + k < n_parts) {
                         const float* pk = p0 + (size_t)(k0 + k) * (HD + 2);
                         ms[k] = __ldcg(pk + HD); ls[k] = __ldcg(pk + HD + 1); os[k] = __ldcg(pk + d);
                     }
                 float Mn = M;
 #pragma unroll
-                for (int k = 0; k < 8; k++) if (k0 + k < n_parts) Mn = fmaxf(Mn, ms[k]);
+                for (int k = 0; k < 16; k++) if (k0 + k < n_parts) Mn = fmaxf(Mn, ms[k]);
                 if (Mn == -INFINITY) continue;
                 const float r = (M == -INFINITY) ? 0.f : __expf(M - Mn);
                 L *= r; acc *= r; M = Mn;
 #pragma unroll
-                for (int k = 0; k < 8; k++)
+                for (int k = 0; k < 16; k++)
                     if (k0 + k < n_parts && ms[k] != -INFINITY) { const float f = __expf(ms[k] - M); L += ls[k] * f; acc += os[k] * f; }
             }
             ((bf16*)a.out)[((size_t)b * a.n_heads + kvh * G + hg) * HD + d] = __float2bfloat16_rn(acc / L);
