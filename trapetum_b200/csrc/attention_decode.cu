@@ -19,9 +19,9 @@
 // not even multiplied by zero: stale or uninitialised rows cannot leak.
 //
 // Takes head_dim in {32, 64, 128, 256} and up to 8 query heads per kv head; other shapes are
-// refused and the caller uses the generic kernel.  Two variants share the staging: the scalar
-// one described above (tb_attn_decode_lanes) and the tensor-core one further down (tb_attn_decode,
-// the product path).
+// refused and the caller uses the generic kernel.  Two kernels live here: the scalar one described
+// above (tb_attn_decode_lanes: head_dim 32, and comparison) and the tensor-core one further down
+// (tb_attn_decode, tb_attn_decode_stream: the product path for head_dim 64, 128 and 256).
 #include "common.cuh"
 #include "async.cuh"
 #include <cuda.h>
