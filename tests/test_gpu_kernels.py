@@ -521,23 +521,25 @@ def _args(rows, temperature, top_p, penalty, draws):
     return f(temperature), f(top_p), f(penalty), f(draws)
 
 
-def test_sample_greedy_and_penalty(ops):
-    V = 1000
+@pytest.mark.parametrize("V", [1000, 40001])      # one CTA a row; several CTAs a row (the ids lie in different chunks)
+def test_sample_greedy_and_penalty(ops, V):
+    a, b, c, d = 10, V - 7, V // 2 + 3, 5
     x = rnd(4, V)
-    x[:, 10] = 9.0; x[:, 20] = 8.0
+    x[:, a] = 9.0; x[:, b] = 8.0
     recent = torch.full((4, 128), -1, dtype=torch.int32, device="cuda")
-    recent[1, :3] = torch.tensor([10, 10, 5], dtype=torch.int32)        # 10 twice: penalised once
-    recent[2, 0] = 20
-    x[3, 10] = -0.5; x[3, 20] = -0.6; x[3, 30] = -0.55
+    recent[1, :3] = torch.tensor([a, a, d], dtype=torch.int32)          # a twice: penalised once
+    recent[1, 100] = a
+    recent[2, 0] = b
+    x[3, a] = -0.5; x[3, b] = -0.6; x[3, c] = -0.55
     x[3, :] = torch.minimum(x[3, :], torch.tensor(-0.5, device="cuda"))
-    recent[3, 0] = 10
+    recent[3, 0] = a
     before = x.clone()
     t, p, pen, u = _args(4, 0.0, 0.95, 1.2, 0.5)
     got = ops.sample(x, t, p, pen, u, recent).cpu().tolist()
     want = [plain.greedy(plain.repetition_penalty(before[i].cpu(), recent[i].cpu().tolist(), 1.2)) for i in range(4)]
-    assert got == want and got[0] == 10 and got[1] == 20 and got[2] == 10
-    assert float(x[1, 10]) == pytest.approx(9.0 / 1.2) and float(x[1, 5]) == pytest.approx(
-        float(before[1, 5]) / 1.2 if before[1, 5] > 0 else float(before[1, 5]) * 1.2)
+    assert got == want and got[0] == a and got[1] == b and got[2] == a
+    assert float(x[1, a]) == pytest.approx(9.0 / 1.2) and float(x[1, d]) == pytest.approx(
+        float(before[1, d]) / 1.2 if before[1, d] > 0 else float(before[1, d]) * 1.2)
 
 
 @pytest.mark.parametrize("V", [301, 256000])
@@ -557,8 +559,9 @@ def test_sample_draws_follow_the_inverse_cdf(ops, V, temperature, top_p):
         assert lo - 1e-4 <= float(u[i]) <= float(cdf[tok]) + 1e-4
 
 
-def test_sample_mixed_rows(ops):
-    x = rnd(3, 500, s=3.0)
+@pytest.mark.parametrize("V", [500, 20011])
+def test_sample_mixed_rows(ops, V):
+    x = rnd(3, V, s=3.0)
     t = torch.tensor([0.0, 1.0, 0.0]); p = torch.tensor([1.0, 1.0, 1.0])
     got = ops.sample(x.clone(), t.cuda(), p.cuda(), torch.ones(3).cuda(), torch.tensor([0.3, 0.3, 0.3]).cuda(), None)
     assert got[0] == x[0].argmax() and got[2] == x[2].argmax()

@@ -351,10 +351,14 @@ class _SampleArgs(ctypes.Structure):
                 ("recent", c_void_p), ("n_recent", c_int), ("out", c_void_p)]
 
 
+WIDE_SAMPLING_FROM = 16384          # vocabularies from this size on are sampled by many CTAs per row
+
+
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor, penalty: torch.Tensor,
-           draw: torch.Tensor, recent: Optional[torch.Tensor]) -> torch.Tensor:
+           draw: torch.Tensor, recent: Optional[torch.Tensor], nucleus: bool = True) -> torch.Tensor:
     """Per row: repetition penalty over ``recent`` ids (changes ``logits`` in place), then argmax if
-    the row's temperature is <= 0, else a nucleus draw with the row's ``draw`` in [0,1)."""
+    the row's temperature is <= 0, else a nucleus draw with the row's ``draw`` in [0,1).  ``nucleus=False``:
+    the caller knows that every row's top_p is >= 1 (saves the launches that search the threshold)."""
     _cuda(logits, temperature, top_p, penalty, draw, recent)
     if logits.dtype != torch.float32:
         raise KernelError("sample: logits must be float32")
@@ -375,6 +379,13 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor,
     a.n_recent = recent.shape[1] if recent is not None else 0
     a.out = out.data_ptr()
     lib = build.load("sampling")
+    if V >= WIDE_SAMPLING_FROM:
+        lib.tb_sample_wide_scratch_bytes.restype = c_longlong
+        need = int(lib.tb_sample_wide_scratch_bytes(c_int(rows), c_int(V)))
+        scratch = torch.empty(need, dtype=torch.uint8, device=logits.device)
+        _check(lib, lib.tb_sample_wide(ctypes.byref(a), c_int(rows), _ptr(scratch), c_int(1 if nucleus else 0), _stream()),
+               "sample", 10 if nucleus else 4)
+        return out
     _check(lib, lib.tb_sample(ctypes.byref(a), c_int(rows), _stream()), "sample")
     return out
 

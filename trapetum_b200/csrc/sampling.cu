@@ -221,6 +221,347 @@ __global__ void __launch_bounds__(1024) sample_kernel(SampleArgs a) {
     if (tid == 0) a.out[row] = chosen;
 }
 
+// ---------------------------------------------------------------------------
+// Sampling over a large vocabulary: the same four steps, but a row's elements are spread over many CTAs and
+// every pass over the row is one launch of (chunks x rows) CTAs, so that a row of 256,000 logits is read at the
+// speed of the whole GPU and not of one SM (the one-CTA kernel above takes 1.7 ms for such rows with a nucleus,
+// most of a decode step).
+//
+// Masses are fixed-point: m_i = round(2^32 e^((l_i - max) / T)), summed in 64-bit integers.  Integer sums do not
+// depend on their order, so histograms can be built with atomics and the draw still repeats bit for bit.
+// The nucleus threshold is found by a radix search on the order-preserving key of the logit: three rounds
+// (11 + 11 + 10 bits), each a histogram of mass per digit among the elements that match the digits found so far,
+// and a scan from the top for the digit at which the mass above reaches top_p x total.
+//
+//   sample_chunk_max  per chunk: repetition penalty on the chunk's ids, then (max, index)   [also the greedy choice];
+//                     clears the row's histograms
+//   sample_hist<R>    per chunk: (R > 0: first the digit of round R-1, found by every CTA for itself from the
+//                     finished histogram;) mass histogram of round R            [rows with a nucleus only]
+//   sample_chunk_mass per chunk: the last digit, hence the threshold; mass of the chunk's kept elements
+//   sample_pick       per row: target = u x kept mass; the chunk and then the element at which the running sum
+//                     of kept masses, in index order, passes the target
+// ---------------------------------------------------------------------------
+#define S_CHUNK 8192
+#define S_BINS 2048
+typedef unsigned long long u64;
+
+struct SampleState {              // per row
+    u64 mass_above;               // mass of the elements above the digits found so far
+    u64 want;                     // top_p x total mass
+    unsigned prefix;              // the digits found so far (the high bits of the threshold key)
+    int nucleus;                  // 1: this row searches a threshold; 0: keeps everything (or is greedy)
+};
+
+struct SampleWide {
+    SampleArgs a;
+    int n_chunks;
+    float* pmax; int* pidx;       // [rows][n_chunks]
+    u64* hist;                    // [rows][3][S_BINS]
+    u64* cmass;                   // [rows][n_chunks]
+    SampleState* state;           // [rows][3]: after round 0, 1, 2
+};
+
+__device__ __forceinline__ u64 fixed_mass(float l, float mx, float invT) {
+    return __float2ull_rn(expf((l - mx) * invT) * 4294967296.0f);
+}
+// the row's maximum from the chunk maxima (every thread of the CTA gets it)
+__device__ __forceinline__ float row_max(const SampleWide& w, int row, float* red /* 33 */) {
+    float m = -INFINITY;
+    for (int c = threadIdx.x; c < w.n_chunks; c += blockDim.x) m = fmaxf(m, w.pmax[(size_t)row * w.n_chunks + c]);
+    return block_max(m, red);
+}
+
+__global__ void __launch_bounds__(256) sample_chunk_max_kernel(SampleWide w) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ ValIdx red[32];
+    __shared__ int rec_s[1024];
+    const int row = blockIdx.y, chunk = blockIdx.x, tid = threadIdx.x;
+    const SampleArgs& a = w.a;
+    float* x = a.logits + (size_t)row * a.row_stride;
+    const int beg = chunk * S_CHUNK, end = min(a.vocab, beg + S_CHUNK);
+    // this CTA's share of the row's histograms starts at zero
+    for (int i = chunk * 256 + tid; i < 3 * S_BINS; i += gridDim.x * 256) w.hist[(size_t)row * 3 * S_BINS + i] = 0ull;
+    // repetition penalty, each distinct recent id once; a CTA sees to the ids of its own chunk
+    const float pen = a.penalty ? a.penalty[row] : 1.f;
+    if (pen > 1.f && a.recent) {
+        const int* rec = a.recent + (size_t)row * a.n_recent;
+        for (int j0 = 0; j0 < a.n_recent; j0 += 1024) {            // (lists longer than 1024 in pieces; each id is
+            const int n = min(1024, a.n_recent - j0);               //  compared with the whole list before it)
+            __syncthreads();
+            for (int j = tid; j < n; j += 256) rec_s[j] = rec[j0 + j];
+            __syncthreads();
+            for (int j = tid; j < n; j += 256) {
+                const int id = rec_s[j];
+                if (id < beg || id >= end) continue;
+                bool first = true;
+                for (int k = 0; k < j && first; k++) first = rec_s[k] != id;
+                for (int k = 0; k < j0 && first; k++) first = rec[k] != id;
+                if (first) { const float l = x[id]; x[id] = l > 0.f ? l / pen : l * pen; }
+            }
+        }
+        __syncthreads();
+    }
+    ValIdx b; b.v = -INFINITY; b.i = 0x7fffffff;
+    for (int i = beg + tid; i < end; i += 256) { ValIdx c; c.v = x[i]; c.i = i; b = better(b, c); }
+    b = block_best(b, red);
+    if (tid == 0) { w.pmax[(size_t)row * w.n_chunks + chunk] = b.v; w.pidx[(size_t)row * w.n_chunks + chunk] = b.i; }
+}
+
+// the digit of round R of a key, and whether the key matches the digits found before it
+template <int R> __device__ __forceinline__ bool digit_of(unsigned key, unsigned prefix, int& bin) {
+    if (R == 0) { bin = key >> 21; return true; }
+    if (R == 1) { bin = (key >> 10) & 2047; return (key >> 21) == prefix; }
+    bin = key & 1023; return (key >> 10) == prefix;
+}
+
+// The digit of round R from its finished histogram `g` (in shared memory), by a CTA of 256 threads: each thread sums
+// eight digits, warp 0 scans the sums from the top, and the lane in which the mass above reaches `want` walks down
+// its own sums and then the eight digits of one of them.  `*st` (shared memory) is the state before the round on
+// entry and the state after it on return.
+template <int R>
+__device__ void select_digit(const u64* g, u64* part /* 256 */, SampleState* st_io, float top_p) {
+    const int tid = threadIdx.x, lane = tid & 31;
+    u64 s = 0ull;
+#pragma unroll
+    for (int k = 0; k < 8; k++) s += g[tid * 8 + k];
+    part[tid] = s;
+    __syncthreads();
+    if (tid < 32) {
+        SampleState st = *st_io;
+        u64 mine = 0ull;
+#pragma unroll
+        for (int k = 0; k < 8; k++) mine += part[lane * 8 + k];
+        u64 incl = mine;                             // this lane's sum and those of the lanes above it (higher digits)
+        for (int o = 1; o < 32; o <<= 1) { const u64 v = __shfl_down_sync(0xffffffffu, incl, o); if (lane + o < 32) incl += v; }
+        if (R == 0) {
+            const u64 tot = __shfl_sync(0xffffffffu, incl, 0);       // the total mass, and what the nucleus has to reach
+            const double want = (double)top_p * (double)tot;
+            st.want = want < 1.0 ? 1ull : (u64)want;
+            if (st.want > tot) st.want = tot;
+        }
+        const u64 above = st.mass_above + incl - mine;
+        const bool here = above < st.want && above + mine >= st.want;
+        u64 acc = above;
+        int b = 0;
+        if (here) {
+            int t = lane * 8 + 7;
+            for (; t > lane * 8; t--) { if (acc + part[t] >= st.want) break; acc += part[t]; }
+            b = t * 8 + 7;
+            for (; b > t * 8; b--) { if (acc + g[b] >= st.want) break; acc += g[b]; }
+        }
+        const unsigned who = __ballot_sync(0xffffffffu, here);
+        const int src = who ? __ffs(who) - 1 : 0;    // (exactly one lane, unless the masses are all zero)
+        st.mass_above = __shfl_sync(0xffffffffu, acc, src);
+        b = __shfl_sync(0xffffffffu, b, src);
+        st.prefix = (R == 0) ? (unsigned)b : (R == 1) ? ((st.prefix << 11) | (unsigned)b) : ((st.prefix << 10) | (unsigned)b);
+        if (lane == 0) *st_io = st;
+    }
+    __syncthreads();
+}
+
+// The state before round R for this CTA (R == 0: the start), into shared memory: found from the finished histogram
+// of round R-1; the CTA of chunk 0 also leaves it in memory for the launches after this one.  `g`: S_BINS sums.
+template <int R>
+__device__ void state_before_round(const SampleWide& w, int row, u64* g, u64* part, SampleState* out) {
+    if (threadIdx.x == 0) {
+        SampleState st;
+        if (R <= 1) {
+            const float T = w.a.temperature ? w.a.temperature[row] : 0.f;
+            const float tp = w.a.top_p ? w.a.top_p[row] : 1.f;
+            st.mass_above = 0ull; st.want = 0ull; st.prefix = 0u; st.nucleus = (T > 0.f && tp < 1.f) ? 1 : 0;
+        } else {
+            st = w.state[(size_t)row * 3 + (R > 1 ? R - 2 : 0)];
+        }
+        *out = st;
+    }
+    __syncthreads();
+    if constexpr (R > 0) {
+        if (!out->nucleus) return;
+        const u64* gg = w.hist + ((size_t)row * 3 + (R - 1)) * S_BINS;
+        for (int j = threadIdx.x; j < S_BINS; j += blockDim.x) g[j] = gg[j];
+        __syncthreads();
+        select_digit<R - 1>(g, part, out, R == 1 ? w.a.top_p[row] : 0.f);
+        if (threadIdx.x == 0 && blockIdx.x == 0) w.state[(size_t)row * 3 + (R - 1)] = *out;
+    }
+}
+
+template <int R>
+__global__ void __launch_bounds__(256) sample_hist_kernel(SampleWide w) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ u64 g[S_BINS];
+    __shared__ u64 part[256];
+    __shared__ SampleState s_st;
+    __shared__ float red[33];
+    const int row = blockIdx.y, chunk = blockIdx.x;
+    state_before_round<R>(w, row, g, part, &s_st);
+    const SampleState st = s_st;
+    if (!st.nucleus) return;
+    __syncthreads();
+    // A mass is at most 2^32.  Its low 16 bits and the rest are summed in two 32-bit histograms, whose atomics the
+    // shared memory has natively (a 64-bit one is a compare-and-swap loop, slow where most of a row falls into a
+    // few digits); a chunk's 8192 elements cannot overflow either.
+    unsigned* lo = (unsigned*)g;
+    unsigned* hi = lo + S_BINS;
+    for (int i = threadIdx.x; i < 2 * S_BINS; i += blockDim.x) lo[i] = 0u;
+    const float* x = w.a.logits + (size_t)row * w.a.row_stride;
+    const float mx = row_max(w, row, red), invT = 1.f / w.a.temperature[row];   // (block_max has the barriers)
+    const int beg = chunk * S_CHUNK, end = min(w.a.vocab, beg + S_CHUNK);
+    for (int i = beg + threadIdx.x; i < end; i += blockDim.x) {
+        const float l = x[i];
+        int bin;
+        if (!digit_of<R>(f2key(l), st.prefix, bin)) continue;
+        const u64 m = fixed_mass(l, mx, invT);
+        atomicAdd(&lo[bin], (unsigned)(m & 0xffffu));
+        atomicAdd(&hi[bin], (unsigned)(m >> 16));
+    }
+    __syncthreads();
+    u64* out = w.hist + ((size_t)row * 3 + R) * S_BINS;
+    for (int i = threadIdx.x; i < S_BINS; i += blockDim.x) {
+        const u64 m = (u64)lo[i] + ((u64)hi[i] << 16);
+        if (m) atomicAdd(&out[i], m);
+    }
+}
+
+__global__ void __launch_bounds__(256) sample_chunk_mass_kernel(SampleWide w, int nucleus) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ u64 g[S_BINS];
+    __shared__ u64 part[256];
+    __shared__ SampleState s_st;
+    __shared__ u64 red8[8];
+    __shared__ float red[33];
+    const int row = blockIdx.y, chunk = blockIdx.x;
+    const float T = w.a.temperature ? w.a.temperature[row] : 0.f;
+    if (!(T > 0.f)) return;
+    unsigned thr = 0u;                                              // keep everything
+    if (nucleus) {
+        state_before_round<3>(w, row, g, part, &s_st);
+        if (s_st.nucleus) thr = s_st.prefix;                       // after the last round the digits are the whole key
+    }
+    const float* x = w.a.logits + (size_t)row * w.a.row_stride;
+    const float mx = row_max(w, row, red), invT = 1.f / T;
+    const int beg = chunk * S_CHUNK, end = min(w.a.vocab, beg + S_CHUNK);
+    u64 m = 0ull;
+    for (int i = beg + threadIdx.x; i < end; i += blockDim.x) {
+        const float l = x[i];
+        if (f2key(l) >= thr) m += fixed_mass(l, mx, invT);
+    }
+    for (int o = 16; o > 0; o >>= 1) m += __shfl_xor_sync(0xffffffffu, m, o);
+    if ((threadIdx.x & 31) == 0) red8[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        u64 t = 0ull;
+        for (int k = 0; k < (int)(blockDim.x >> 5); k++) t += red8[k];
+        w.cmass[(size_t)row * w.n_chunks + chunk] = t;
+    }
+}
+
+__global__ void __launch_bounds__(256) sample_pick_kernel(SampleWide w, int nucleus) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ u64 part[256];
+    __shared__ u64 cm[256];                                          // the chunks' kept masses: read side by side
+    __shared__ float red[33];
+    __shared__ int s_chunk;
+    __shared__ u64 s_base, s_target;
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const SampleArgs& a = w.a;
+    const float T = a.temperature ? a.temperature[row] : 0.f;
+    if (!(T > 0.f)) {
+        // greedy: the best of the chunk maxima, the smallest index on a tie
+        if (tid == 0) {
+            ValIdx b; b.v = -INFINITY; b.i = 0x7fffffff;
+            for (int c = 0; c < w.n_chunks; c++) {
+                ValIdx v; v.v = w.pmax[(size_t)row * w.n_chunks + c]; v.i = w.pidx[(size_t)row * w.n_chunks + c];
+                b = better(b, v);
+            }
+            a.out[row] = (b.i == 0x7fffffff) ? 0 : b.i;
+        }
+        return;
+    }
+    unsigned thr = 0u;
+    if (nucleus) { const SampleState st = w.state[(size_t)row * 3 + 2]; if (st.nucleus) thr = st.prefix; }
+    for (int c = tid; c < w.n_chunks; c += 256) cm[c] = w.cmass[(size_t)row * w.n_chunks + c];
+    const float mx = row_max(w, row, red);                          // (has the barriers that cm needs, too)
+    if (tid == 0) {
+        u64 kept = 0ull;
+        for (int c = 0; c < w.n_chunks; c++) kept += cm[c];
+        const double tg = (double)a.draw[row] * (double)kept;
+        u64 target = (u64)tg;
+        if (target >= kept) target = kept - 1;                      // (kept >= 2^32: the row's maximum has mass 2^32)
+        u64 base = 0ull;
+        int c = 0;
+        for (; c < w.n_chunks - 1; c++) { if (base + cm[c] > target) break; base += cm[c]; }
+        s_chunk = c; s_base = base; s_target = target;
+    }
+    __syncthreads();
+    const float* x = a.logits + (size_t)row * a.row_stride;
+    const float invT = 1.f / T;
+    constexpr int PER = S_CHUNK / 256;                              // consecutive elements per thread: index order
+    const int beg = s_chunk * S_CHUNK + tid * PER, end = min(a.vocab, beg + PER);
+    u64 mine = 0ull;
+    for (int i = beg; i < end; i++) { const float l = x[i]; if (f2key(l) >= thr) mine += fixed_mass(l, mx, invT); }
+    part[tid] = mine;
+    __syncthreads();
+    if (tid < 32) {
+        // exclusive prefix over 256 sums: a lane sums its 8, the lanes scan, each lane writes its 8 prefixes
+        u64 loc[8], sum = 0ull;
+#pragma unroll
+        for (int k = 0; k < 8; k++) { loc[k] = part[tid * 8 + k]; sum += loc[k]; }
+        u64 incl = sum;
+        for (int o = 1; o < 32; o <<= 1) { const u64 v = __shfl_up_sync(0xffffffffu, incl, o); if (tid >= o) incl += v; }
+        u64 run = s_base + incl - sum;
+#pragma unroll
+        for (int k = 0; k < 8; k++) { part[tid * 8 + k] = run; run += loc[k]; }
+    }
+    __syncthreads();
+    const u64 before = part[tid], target = s_target;
+    if (mine > 0ull && target >= before && target < before + mine) {
+        u64 run = before; int pick = beg;
+        for (int i = beg; i < end; i++) {
+            const float l = x[i];
+            if (f2key(l) >= thr) { run += fixed_mass(l, mx, invT); pick = i; if (target < run) break; }
+        }
+        a.out[row] = pick;
+    }
+}
+
+extern "C" long long tb_sample_wide_scratch_bytes(int rows, int vocab) {
+    const long long chunks = (vocab + S_CHUNK - 1) / S_CHUNK;
+    return (long long)rows * (chunks * (4 + 4 + 8) + 3LL * S_BINS * 8 + 3LL * (long long)sizeof(SampleState)) + 256;
+}
+
+// `nucleus`: 0 if the caller knows that every row has top_p >= 1 (the threshold rounds are then not launched).
+extern "C" int tb_sample_wide(const SampleArgs* args, int rows, void* scratch, int nucleus, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    SampleWide w;
+    w.a = *args;
+    if (w.a.vocab <= 0) return tb_refuse("sample: vocab=%d", w.a.vocab);
+    if (w.a.draw == nullptr) return tb_refuse("sample: the draws are missing");
+    if (rows > 65535) return tb_refuse("sample: %d rows is more than one call takes", rows);
+    if ((w.a.vocab + S_CHUNK - 1) / S_CHUNK > 256) return tb_refuse("sample: a vocabulary of %d is more than this kernel takes", w.a.vocab);
+    if (scratch == nullptr || ((uintptr_t)scratch & 15)) return tb_refuse("sample: needs 16-byte aligned scratch");
+    w.n_chunks = (w.a.vocab + S_CHUNK - 1) / S_CHUNK;
+    char* p = (char*)scratch;
+    w.hist = (u64*)p; p += (size_t)rows * 3 * S_BINS * 8;
+    w.cmass = (u64*)p; p += (size_t)rows * w.n_chunks * 8;
+    w.state = (SampleState*)p; p += (size_t)rows * 3 * sizeof(SampleState);
+    w.pmax = (float*)p; p += (size_t)rows * w.n_chunks * 4;
+    w.pidx = (int*)p;
+    const dim3 per_chunk(w.n_chunks, rows);
+    tb_launch(sample_chunk_max_kernel, dim3(per_chunk), dim3(256), 0, stream, w);
+    if (nucleus) {
+        tb_launch(sample_hist_kernel<0>, dim3(per_chunk), dim3(256), 0, stream, w);
+        tb_launch(sample_hist_kernel<1>, dim3(per_chunk), dim3(256), 0, stream, w);
+        tb_launch(sample_hist_kernel<2>, dim3(per_chunk), dim3(256), 0, stream, w);
+    }
+    tb_launch(sample_chunk_mass_kernel, dim3(per_chunk), dim3(256), 0, stream, w, nucleus);
+    tb_launch(sample_pick_kernel, dim3(rows), dim3(256), 0, stream, w, nucleus);
+    return tb_launch_status();
+}
+
 extern "C" int tb_sample(const SampleArgs* args, int rows, cudaStream_t stream) {
     if (rows <= 0) return 0;
     SampleArgs a = *args;

@@ -57,7 +57,7 @@ class Sampler:
                     w = self._recent[r]
                     rec[i, :len(w)] = list(w)
                 recent = torch.from_numpy(rec).to(self.device)
-            ids = ops.sample(logits, fd[0], fd[1], fd[2], fd[3], recent)
+            ids = ops.sample(logits, fd[0], fd[1], fd[2], fd[3], recent, nucleus=p.top_p < 1.0)
         out = ids.cpu().tolist()
         for r, t in zip(requests, out):
             self._recent[r].append(t)
