@@ -7,14 +7,19 @@
 //     (128 x 64 x 16 and 128 x head_dim x 16) issued by one thread, with S and O in tensor memory;
 //   * tensor memory's lanes are the query rows, so a row's running maximum, exponentials and row sum
 //     stay with the row's threads: no shuffles across a warp;
-//   * Q, K and the transposed V tiles arrive by tiled TMA (128-byte swizzle); P is written to shared
+//   * K and the transposed V tiles arrive by tiled TMA (128-byte swizzle); P is written to shared
 //     memory in the same swizzled K-major layout and is the A operand of the second product;
+//   * Q lies in tensor memory (each softmax thread loads its row once) and is the first product's A operand
+//     from there: the tensor core would otherwise read the whole Q tile from shared memory again for every
+//     key block, and shared-memory bandwidth (operand reads, TMA writes, P) is what bounds a block's time;
 //   * the exponent's reference maximum is only raised when a block's maximum exceeds it by 2^8
 //     ("lazy rescaling"): then the thread scales its O row in tensor memory; otherwise O is left
 //     alone and p may reach 256, which bfloat16 and the 32-bit accumulators hold without loss;
-//   * warp 0 loads, warp 1 issues MMAs, warps 2..9 are the softmax (two threads per row, 32 keys of a
-//     block each; the row maximum crosses between them through shared memory); S and P are double-buffered so
-//     that the tensor cores run block j+1's Q K^T while block j's softmax is computed.
+//   * warp 0 loads, warp 1 issues MMAs, warps 2..9 are the softmax: two groups of four warps, one thread per
+//     row each; the first group takes the even key blocks, the second the odd ones, so two blocks' softmax run
+//     at a time (S and P are double-buffered) and one group's waits (for S, for tensor memory, for the P buffer)
+//     are covered by the other's exponentials.  A row's two threads hand its reference maximum back and forth
+//     through shared memory: the only thing block j+1 needs from block j.
 // V is needed as [dim][key] (keys contiguous) for the second product; tb_transpose_v makes that copy
 // per sequence, each sequence starting at a multiple of 64 keys so that every TMA copy is aligned.
 //
@@ -33,21 +38,25 @@ static_assert(HD == 64 || HD == 128 || HD == 256, "head_dim 64, 128 or 256");
 #define BM 128
 #define BN 64
 constexpr int QBOXES = HD / 64;                       // 64-dim boxes along the head dim
-constexpr int Q_BYTES = QBOXES * BM * 128;            // 128 rows x head_dim
 constexpr int K_BYTES = QBOXES * BN * 128;            // 64 keys x head_dim
 constexpr int VT_BYTES = HD * 128;                    // head_dim rows x 64 keys
 constexpr int P_BYTES = BM * 128;                     // 128 rows x 64 keys
-constexpr int TILE_BYTES = Q_BYTES + 2 * K_BYTES + 2 * VT_BYTES + 2 * P_BYTES;
-constexpr int ROWX_BYTES = 2 * 2 * BM * 4;         // the softmax threads' exchange
+constexpr int TILE_BYTES = 2 * K_BYTES + 2 * VT_BYTES + 2 * P_BYTES;
+constexpr int ROWX_BYTES = 2 * 2 * BM * 4;         // the softmax threads' exchange: references [2][BM], row sums [2][BM]
 constexpr int USED_BYTES = TILE_BYTES + ROWX_BYTES + 256;
 constexpr int SMEM_BYTES = USED_BYTES + 512;       // head_dim 256 uses all but 256 bytes of an SM's shared memory
 static_assert(SMEM_BYTES <= 232448, "does not fit an SM's shared memory");
-constexpr int TMEM_COLS = (2 * BN + HD) <= 256 ? 256 : 512;
+constexpr int Q_COLS = HD / 2;                        // Q in tensor memory: two bf16 per column
+constexpr int TMEM_COLS = (2 * BN + HD + Q_COLS) <= 256 ? 256 : 512;
+static_assert(2 * BN + HD + Q_COLS <= 512, "tensor memory holds S twice, O and Q");
 constexpr float RESCALE_AT = 8.f;                     // in log2 units
 
 __device__ int g_attn_tc_error = 0;
 
 struct PrefillTcArgs {
+    const bf16* q;                 // [T, q_stride]: head h of token t at q + t * q_stride + h * HD
+    long long q_stride;
+    int n_tokens;
     const int* seq_start;          // [B + 1] rows of the packed q/k matrices
     const int* vt_start;           // [B + 1] key columns of the transposed v (multiples of 64)
     bf16* out;                     // [T, n_heads * HD]
@@ -59,8 +68,7 @@ __device__ __forceinline__ float ex2f(float x) { float y; asm("ex2.approx.ftz.f3
 __device__ __forceinline__ float rcpf(float x) { float y; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 
 __global__ void __launch_bounds__(320, 1)
-attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                       const __grid_constant__ CUtensorMap map_vt, PrefillTcArgs a) {
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_vt, PrefillTcArgs a) {
     pdl_launch_dependents();
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -68,11 +76,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (threadIdx.x == 0) atomicExch(&g_attn_tc_error, 4);
         return;
     }
-    uint8_t* sQ = smem;
-    uint8_t* sK = sQ + Q_BYTES;                       // [2][K_BYTES]
+    uint8_t* sK = smem;                               // [2][K_BYTES]
     uint8_t* sVT = sK + 2 * K_BYTES;                  // [2][VT_BYTES]
     uint8_t* sP = sVT + 2 * VT_BYTES;                 // [2][P_BYTES]
-    float (*row_x)[2][BM] = (float (*)[2][BM])(sP + 2 * P_BYTES);   // [block parity][half][row]
+    float (*row_ref)[BM] = (float (*)[BM])(sP + 2 * P_BYTES);        // [block parity][row]: the reference after that block
+    float (*row_l)[BM] = row_ref + 2;                                // [group][row]: the groups' row sums at the end
     uint64_t* bars = (uint64_t*)(sP + 2 * P_BYTES + ROWX_BYTES);
     uint64_t* q_full = bars;                          // 1
     uint64_t* k_full = bars + 1;                      // [2]
@@ -82,8 +90,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     uint64_t* s_full = bars + 9;                      // [2]
     uint64_t* s_empty = bars + 11;                    // [2]
     uint64_t* p_full = bars + 13;                     // [2]
-    uint64_t* x_bar = bars + 15;                      // 1: the softmax warps' exchange, one phase per block
-    uint32_t* tmem_slot = (uint32_t*)(bars + 16);
+    uint64_t* x_bar = bars + 15;                      // 1: the softmax groups meet at the end
+    uint64_t* ref_full = bars + 16;                   // [2]: block j's reference is in row_ref[j & 1]
+    uint32_t* tmem_slot = (uint32_t*)(bars + 18);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -102,90 +111,97 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int nblocks = nb_hi - nb_lo;
 
     if (threadIdx.x == 0) {
-        mbar_init(q_full, 1);
+        mbar_init(q_full, 8);
         for (int s = 0; s < 2; s++) {
             mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
-            mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 8); mbar_init(&p_full[s], 8);
+            mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 4); mbar_init(&p_full[s], 4); mbar_init(&ref_full[s], 4);
         }
         mbar_init(x_bar, 8);
         *abort_flag = 0;
         mbar_init_fence();
     }
     if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
-    if (threadIdx.x == 64) { tma_prefetch_map(&map_q); tma_prefetch_map(&map_k); tma_prefetch_map(&map_vt); }
+    if (threadIdx.x == 64) { tma_prefetch_map(&map_k); tma_prefetch_map(&map_vt); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_s = tmem_base;                               // [2][BN] columns
     const uint32_t tmem_o = tmem_base + 2 * BN;                      // HD columns
+    const uint32_t tmem_q = tmem_o + HD;                             // Q_COLS columns
 
     if (warp == 0) {
-        // ---------------- loads ----------------
+        // ---------------- loads, and the second product's MMAs ----------------
+        // (One thread can issue an MMA every fifty cycles or so; the first product's MMAs run no longer than that.
+        //  So the two products have an issuing thread each, and neither waits behind the other's operands.)
         if (lane == 0) {
             pdl_wait();
+            constexpr uint32_t idesc_o = instr_desc(HD);
+            const uint32_t hi = desc_hi(smem_desc(0));
+            const uint32_t p_lo0 = desc_lo(smem_desc(smem_u32(sP))), v_lo0 = desc_lo(smem_desc(smem_u32(sVT)));
             bool ok = true;
-            mbar_expect_tx(q_full, Q_BYTES);
-            for (int c = 0; c < QBOXES; c++) tma_load_2d(sQ + c * BM * 128, &map_q, q_full, h * HD + c * 64, s0 + m0);
-            for (int j = 0; j < nblocks && ok; j++) {
-                const int s = j & 1; const uint32_t ph = (j >> 1) & 1;
-                const int key0 = (nb_lo + j) * BN;
-                if (*abort_flag || !mbar_wait(&k_empty[s], ph ^ 1)) { ok = false; break; }
-                mbar_expect_tx(&k_full[s], K_BYTES);
-                for (int c = 0; c < QBOXES; c++)
-                    tma_load_2d(sK + s * K_BYTES + c * BN * 128, &map_k, &k_full[s], kvh * HD + c * 64, s0 + key0);
-                if (*abort_flag || !mbar_wait(&v_empty[s], ph ^ 1)) { ok = false; break; }
-                mbar_expect_tx(&v_full[s], VT_BYTES);
-                tma_load_2d(sVT + s * VT_BYTES, &map_vt, &v_full[s], vt0 + key0, kvh * HD);
+            // K tiles, V^T tiles and the second products are started independently, each as soon as it has what it
+            // needs: the scores run up to two blocks ahead of the second product, and so must the K tiles
+            int jk = 0, jv = 0, jp = 0;
+            long long idle_since = clock64();
+            while (ok && jp < nblocks) {
+                bool moved = false;
+                if (jk < nblocks && mbar_test(&k_empty[jk & 1], ((jk >> 1) & 1) ^ 1)) {
+                    const int s = jk & 1, key0 = (nb_lo + jk) * BN;
+                    mbar_expect_tx(&k_full[s], K_BYTES);
+                    for (int c = 0; c < QBOXES; c++)
+                        tma_load_2d(sK + s * K_BYTES + c * BN * 128, &map_k, &k_full[s], kvh * HD + c * 64, s0 + key0);
+                    jk++; moved = true;
+                }
+                if (jv < nblocks && mbar_test(&v_empty[jv & 1], ((jv >> 1) & 1) ^ 1)) {
+                    const int s = jv & 1, key0 = (nb_lo + jv) * BN;
+                    mbar_expect_tx(&v_full[s], VT_BYTES);
+                    tma_load_2d(sVT + s * VT_BYTES, &map_vt, &v_full[s], vt0 + key0, kvh * HD);
+                    jv++; moved = true;
+                }
+                if (mbar_test(&v_full[jp & 1], (jp >> 1) & 1) && mbar_test(&p_full[jp & 1], (jp >> 1) & 1)) {
+                    const int s = jp & 1;
+                    tc_fence_after();
+                    const uint32_t p_lo = p_lo0 + s * (P_BYTES >> 4), v_lo = v_lo0 + s * (VT_BYTES >> 4);
+#pragma unroll
+                    for (int ks = 0; ks < BN / UMMA_K; ks++)
+                        umma_bf16_lh(tmem_o, p_lo + ks * 2, v_lo + ks * 2, hi, idesc_o, (jp > 0 || ks > 0) ? 1u : 0u);
+                    umma_commit(&v_empty[s]);         // V^T tile and P buffer are free again; O holds blocks 0..jp
+                    jp++; moved = true;
+                }
+                if (moved) idle_since = clock64();
+                else if (*abort_flag || clock64() - idle_since > WAIT_CYCLES) ok = false;
             }
             if (!ok && !*abort_flag) { atomicExch(&g_attn_tc_error, 1); *abort_flag = 1; }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issue ----------------
+        // ---------------- the first product's MMAs ----------------
         if (lane == 0) {
-            constexpr uint32_t idesc_s = instr_desc(BN), idesc_o = instr_desc(HD);
+            constexpr uint32_t idesc_s = instr_desc(BN);
+            const uint32_t hi = desc_hi(smem_desc(0));
+            const uint32_t k_lo0 = desc_lo(smem_desc(smem_u32(sK)));
             bool ok = mbar_wait(q_full, 0);
-            tc_fence_after();
-            const uint32_t q_addr = smem_u32(sQ);
-            auto issue_qk = [&](int j) -> bool {
+            // the scores of block j + 2 are issued when S of block j has been read, long before P of block j exists:
+            // the softmax does not wait for them
+            for (int j = 0; j < nblocks && ok; j++) {
                 const int s = j & 1; const uint32_t ph = (j >> 1) & 1;
-                if (*abort_flag || !mbar_wait(&k_full[s], ph) || !mbar_wait(&s_empty[s], ph ^ 1)) return false;
+                if (*abort_flag || !mbar_wait(&k_full[s], ph) || !mbar_wait(&s_empty[s], ph ^ 1)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t k_addr = smem_u32(sK + s * K_BYTES);
+                const uint32_t k_lo = k_lo0 + s * (K_BYTES >> 4), d = tmem_s + s * BN;
 #pragma unroll
-                for (int ks = 0; ks < HD / UMMA_K; ks++) {
-                    const uint32_t off_q = (ks >> 2) * (BM * 128) + (ks & 3) * 32;
-                    const uint32_t off_k = (ks >> 2) * (BN * 128) + (ks & 3) * 32;
-                    umma_bf16(tmem_s + s * BN, smem_desc(q_addr + off_q), smem_desc(k_addr + off_k), idesc_s, ks > 0 ? 1u : 0u);
-                }
+                for (int ks = 0; ks < HD / UMMA_K; ks++)
+                    umma_bf16_ta_lh(d, tmem_q + ks * (UMMA_K / 2), k_lo + (((ks >> 2) * (BN * 128) + (ks & 3) * 32) >> 4), hi,
+                                    idesc_s, ks > 0 ? 1u : 0u);
                 umma_commit(&k_empty[s]);             // K tile may be overwritten once these have run
                 umma_commit(&s_full[s]);              // and S is ready for the softmax
-                return true;
-            };
-            auto issue_pv = [&](int j) -> bool {
-                const int s = j & 1; const uint32_t ph = (j >> 1) & 1;
-                if (*abort_flag || !mbar_wait(&v_full[s], ph) || !mbar_wait(&p_full[s], ph)) return false;
-                tc_fence_after();
-                const uint32_t p_addr = smem_u32(sP + s * P_BYTES), v_addr = smem_u32(sVT + s * VT_BYTES);
-#pragma unroll
-                for (int ks = 0; ks < BN / UMMA_K; ks++)
-                    umma_bf16(tmem_o, smem_desc(p_addr + ks * 32), smem_desc(v_addr + ks * 32), idesc_o,
-                              (j > 0 || ks > 0) ? 1u : 0u);
-                umma_commit(&v_empty[s]);             // V^T tile and P buffer are free again; O holds blocks 0..j
-                return true;
-            };
-            if (ok) ok = issue_qk(0);
-            for (int j = 0; j < nblocks && ok; j++) {
-                if (j + 1 < nblocks) ok = issue_qk(j + 1);       // the next block's scores overlap this block's softmax
-                if (ok) ok = issue_pv(j);
             }
             if (!ok && !*abort_flag) { atomicExch(&g_attn_tc_error, 2); *abort_flag = 1; }
         }
     } else {
-        // ---------------- softmax: two threads per query row, 32 of the block's 64 keys each ----------------
+        // ---------------- softmax: one thread per query row and group; group g takes the blocks j = g, g + 2, .. ----------------
         const int sw = warp - 2;                                     // 0..7
         const int quarter = warp & 3;                                // the TMEM lanes this warp may touch
-        const int half = sw >> 2;                                    // which 32 columns of S (and which half of O)
+        const int group = sw >> 2;
         const int r = quarter * 32 + lane;                           // row of the tile = TMEM lane
         const int i = m0 + r;                                        // position of the query in its sequence
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
@@ -193,52 +209,80 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const float sc2 = a.scale * LOG2E;                           // scores in log2 units
         const float cap2 = a.cap * LOG2E;
         const float cap_k = a.cap > 0.f ? 2.f * a.scale / a.cap * LOG2E : 0.f;
-        float m_ref = -INFINITY, l_sum = 0.f;                        // l_sum: this thread's half of the row sum
+        float m_ref = -INFINITY, l_sum = 0.f;                        // this thread's reference and its share of the row sum
         bool ok = true;
         pdl_wait();
-        for (int j = 0; j < nblocks; j++) {
+        {
+            // this thread's query row into tensor memory (rows past the last token: zeros); with head sizes from 128
+            // the two threads of a row take half of it each
+            constexpr int PER = (Q_COLS >= 64) ? Q_COLS / 2 : Q_COLS;            // columns per thread that loads
+            const long long row = (long long)s0 + i;
+            const bool inside = row < a.n_tokens;
+            if (Q_COLS >= 64 || group == 0) {
+                const int col0 = (Q_COLS >= 64) ? group * PER : 0;
+                const uint4* src = (const uint4*)(a.q + row * a.q_stride + (size_t)h * HD + col0 * 2);
+#pragma unroll 1
+                for (int c0 = 0; c0 < PER; c0 += 32) {
+                    uint32_t w[32];
+#pragma unroll
+                    for (int k = 0; k < 8; k++) {
+                        const uint4 x = inside ? __ldg(src + c0 / 4 + k) : make_uint4(0u, 0u, 0u, 0u);
+                        w[4 * k] = x.x; w[4 * k + 1] = x.y; w[4 * k + 2] = x.z; w[4 * k + 3] = x.w;
+                    }
+                    tmem_st32(tmem_q + lane_addr + col0 + c0, w);
+                }
+                tmem_st_wait();
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(q_full);
+        }
+        for (int j = group; j < nblocks; j += 2) {
             const int s = j & 1; const uint32_t ph = (j >> 1) & 1;
             const bool got = !*abort_flag && mbar_wait(&s_full[s], ph);
             if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
             tc_fence_after();
-            uint32_t raw[32];
-            tmem_ld32(tmem_s + s * BN + lane_addr + half * 32, raw);
+            float v[BN];
+            tmem_ld32(tmem_s + s * BN + lane_addr, (uint32_t*)v);
+            tmem_ld32(tmem_s + s * BN + lane_addr + 32, (uint32_t*)v + 32);
             tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&s_empty[s]);                 // this warp has read its part of S
             // scale, cap, mask; values in log2 units
-            const int key0 = (nb_lo + j) * BN + half * 32;
-            const bool edge = (key0 + 31 > m0) || (key0 + 32 > len) || (a.window > 0 && (m0 + BM - 1) - key0 >= a.window);
-            float v[32];
-            float mx = -INFINITY;
+            const int key0 = (nb_lo + j) * BN;
+            const bool edge = (key0 + BN - 1 > m0) || (key0 + BN > len) || (a.window > 0 && (m0 + BM - 1) - key0 >= a.window);
             if (a.cap > 0.f) {
                 // cap * tanh(x * scale / cap) = cap - 2 cap / (e^(2 x scale / cap) + 1), in log2 units; 2^(+big) is
                 // inf and its reciprocal 0, 2^(-big) is 0: both ends come out right without a clamp
 #pragma unroll
-                for (int c = 0; c < 32; c++)
-                    v[c] = fmaf(-2.f * cap2, rcpf(ex2f(__uint_as_float(raw[c]) * cap_k) + 1.f), cap2);
+                for (int c = 0; c < BN; c++) v[c] = fmaf(-2.f * cap2, rcpf(ex2f(v[c] * cap_k) + 1.f), cap2);
             } else {
 #pragma unroll
-                for (int c = 0; c < 32; c++) v[c] = __uint_as_float(raw[c]) * sc2;
+                for (int c = 0; c < BN; c++) v[c] *= sc2;
             }
             if (edge) {
 #pragma unroll
-                for (int c = 0; c < 32; c++) {
+                for (int c = 0; c < BN; c++) {
                     const int jj = key0 + c;
                     if (!(jj <= i && jj < len && (a.window <= 0 || i - jj < a.window))) v[c] = -INFINITY;
                 }
             }
+            float mx = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < 32; c += 4)
+            for (int c = 0; c < BN; c += 4)
                 mx = fmaxf(mx, fmaxf(fmaxf(v[c], v[c + 1]), fmaxf(v[c + 2], v[c + 3])));
-            // the row's maximum over both halves (a bounded mbarrier wait, not bar.sync: no wait here may hang)
-            row_x[j & 1][half][r] = mx;
-            __syncwarp();
-            if (lane == 0) mbar_arrive(x_bar);
-            const bool met = mbar_wait(x_bar, j & 1);
-            if (!__all_sync(0xffffffffu, met)) { ok = false; break; }
-            mx = fmaxf(mx, row_x[j & 1][half ^ 1][r]);
+            // the row's reference after block j-1, from the other group (a bounded mbarrier wait: no wait here may hang)
+            float before = -INFINITY;
+            if (j > 0) {
+                const bool met = mbar_wait(&ref_full[(j - 1) & 1], ((j - 1) >> 1) & 1);
+                if (!__all_sync(0xffffffffu, met)) { ok = false; break; }
+                before = row_ref[(j - 1) & 1][r];
+            }
+            if (before != m_ref) {                                   // the other group raised it: this share follows
+                l_sum *= (m_ref == -INFINITY) ? 0.f : ex2f(m_ref - before);
+                m_ref = before;
+            }
             // lazy rescaling: raise the reference only when the block's maximum is far above it
             float factor = 1.f;
             bool raise = mx > m_ref + RESCALE_AT;
@@ -247,19 +291,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 factor = (m_ref == -INFINITY) ? 0.f : ex2f(m_ref - mx);
                 m_ref = mx;
             }
+            row_ref[j & 1][r] = m_ref;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ref_full[j & 1]);
             const float mr = (m_ref == -INFINITY) ? 0.f : m_ref;
-            uint32_t pk[16];
+            uint32_t pk[BN / 2];
             float ls0 = 0.f, ls1 = 0.f;
 #pragma unroll
-            for (int c = 0; c < 32; c += 2) {
+            for (int c = 0; c < BN; c += 2) {
                 const float p0 = ex2f(v[c] - mr), p1 = ex2f(v[c + 1] - mr);
                 ls0 += p0; ls1 += p1;
                 __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
                 pk[c >> 1] = *(uint32_t*)&h2;
             }
             l_sum = l_sum * factor + (ls0 + ls1);
-            // O holds blocks before j: scale this row if its reference moved (not for the first block: the
-            // second product starts O from zero).  Each of the row's two threads scales half of the columns.
+            // O holds the blocks before j: scale this row if its reference moved (not for the first block: the
+            // second product starts O from zero).
             const bool need = raise && j > 0;
             if (__any_sync(0xffffffffu, need)) {
                 // every MMA into O must have completed: block j-1's second product signals v_empty of its slot
@@ -268,7 +315,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 if (!__all_sync(0xffffffffu, done)) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll 1
-                for (int c0 = half * (HD / 2); c0 < (half + 1) * (HD / 2); c0 += 32) {
+                for (int c0 = 0; c0 < HD; c0 += 32) {
                     uint32_t ov[32];
                     tmem_ld32(tmem_o + lane_addr + c0, ov);
                     tmem_ld_wait();
@@ -283,8 +330,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (!__all_sync(0xffffffffu, freep)) { ok = false; break; }
             uint8_t* prow = sP + s * P_BYTES + r * 128;
 #pragma unroll
-            for (int c = 0; c < 4; c++)
-                *(uint4*)(prow + (((half * 4 + c) ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+            for (int c = 0; c < 8; c++)
+                *(uint4*)(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // visible to the tensor core's reads
             tc_fence_before();
             __syncwarp();
@@ -296,19 +343,30 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             ok = __all_sync(0xffffffffu, done);
         }
         if (ok) {
-            // the two halves of the row sum meet
-            row_x[nblocks & 1][half][r] = l_sum;
+            // both shares of the row sum at the row's last reference
+            const int last = nblocks - 1;
+            if ((last & 1) != group) {
+                const bool met = mbar_wait(&ref_full[last & 1], (last >> 1) & 1);
+                ok = __all_sync(0xffffffffu, met);
+                if (ok) {
+                    const float fin = row_ref[last & 1][r];
+                    if (fin != m_ref) l_sum *= (m_ref == -INFINITY) ? 0.f : ex2f(m_ref - fin);
+                }
+            }
+        }
+        if (ok) {
+            row_l[group][r] = l_sum;
             __syncwarp();
             if (lane == 0) mbar_arrive(x_bar);
-            const bool met = mbar_wait(x_bar, nblocks & 1);
+            const bool met = mbar_wait(x_bar, 0);
             ok = __all_sync(0xffffffffu, met);
         }
         if (ok) {
             tc_fence_after();
-            const float inv = 1.f / (l_sum + row_x[nblocks & 1][half ^ 1][r]);
+            const float inv = 1.f / (row_l[0][r] + row_l[1][r]);
             bf16* orow = a.out + ((size_t)(s0 + i) * a.n_heads + h) * HD;
 #pragma unroll 1
-            for (int c0 = half * (HD / 2); c0 < (half + 1) * (HD / 2); c0 += 32) {
+            for (int c0 = group * (HD / 2); c0 < (group + 1) * (HD / 2); c0 += 32) {   // each group writes half of the columns
                 uint32_t ov[32];
                 tmem_ld32(tmem_o + lane_addr + c0, ov);
                 tmem_ld_wait();
@@ -411,12 +469,12 @@ extern "C" int tb_attn_prefill_tc(const void* q, const void* k, const void* v, l
         int st = tb_launch_status();
         if (st) return st;
     }
-    CUtensorMap mq, mk, mvt;
-    if (make_map(&mq, q, n_tokens, (long long)n_heads * HD, q_stride, BM) ||
-        make_map(&mk, k, n_tokens, kvw, kv_stride, BN) ||
+    CUtensorMap mk, mvt;
+    if (make_map(&mk, k, n_tokens, kvw, kv_stride, BN) ||
         make_map(&mvt, vt, kvw, vt_cols, vt_cols, HD))
         return -1;
     PrefillTcArgs a;
+    a.q = (const bf16*)q; a.q_stride = q_stride; a.n_tokens = n_tokens;
     a.seq_start = seq_start; a.vt_start = vt_start; a.out = (bf16*)out;
     a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.window = window; a.scale = scale; a.cap = cap;
     static bool attr_set = false;
@@ -426,7 +484,7 @@ extern "C" int tb_attn_prefill_tc(const void* q, const void* k, const void* v, l
         attr_set = true;
     }
     dim3 grid((max_seq_len + BM - 1) / BM, n_heads, batch);
-    tb_launch(attn_prefill_tc_kernel, grid, dim3(320), SMEM_BYTES, stream, mq, mk, mvt, a);
+    tb_launch(attn_prefill_tc_kernel, grid, dim3(320), SMEM_BYTES, stream, mk, mvt, a);
     return tb_launch_status();
 }
 
