@@ -7,7 +7,7 @@
 //     (128 x 64 x 16 and 128 x head_dim x 16) issued by one thread, with S and O in tensor memory;
 //   * tensor memory's lanes are the query rows, so a row's running maximum, exponentials and row sum
 //     stay with the row's threads: no shuffles across a warp;
-//   * K and the transposed V tiles arrive by tiled TMA (128-byte swizzle); P is written to shared
+//   * K and V tiles arrive by tiled TMA (128-byte swizzle); P is written to shared
 //     memory in the same swizzled K-major layout and is the A operand of the second product;
 //   * Q lies in tensor memory (each softmax thread loads its row once) and is the first product's A operand
 //     from there: the tensor core would otherwise read the whole Q tile from shared memory again for every
@@ -20,8 +20,10 @@
 //     at a time (S and P are double-buffered) and one group's waits (for S, for tensor memory, for the P buffer)
 //     are covered by the other's exponentials.  A row's two threads hand its reference maximum back and forth
 //     through shared memory: the only thing block j+1 needs from block j.
-// V is needed as [dim][key] (keys contiguous) for the second product; tb_transpose_v makes that copy
-// per sequence, each sequence starting at a multiple of 64 keys so that every TMA copy is aligned.
+// V is the second product's B operand as it lies in memory, [key][dim] with the dims contiguous ("MN-major": the
+// descriptor's leading-dimension offset is the distance between panels of 64 dims, its stride offset the distance
+// between groups of 8 keys), so no transposed copy of V is made.  Keys past a sequence's end are the next
+// sequence's rows or, past the last token, the zeros that TMA fills in; their P is zero.
 //
 // All waits are bounded (async.cuh); a wait that runs out records an error word.
 // Compiled once per head size (-DTB_HD = 64, 128 or 256).
@@ -39,9 +41,9 @@ static_assert(HD == 64 || HD == 128 || HD == 256, "head_dim 64, 128 or 256");
 #define BN 64
 constexpr int QBOXES = HD / 64;                       // 64-dim boxes along the head dim
 constexpr int K_BYTES = QBOXES * BN * 128;            // 64 keys x head_dim
-constexpr int VT_BYTES = HD * 128;                    // head_dim rows x 64 keys
+constexpr int V_BYTES = K_BYTES;                      // 64 keys x head_dim, as K
 constexpr int P_BYTES = BM * 128;                     // 128 rows x 64 keys
-constexpr int TILE_BYTES = 2 * K_BYTES + 2 * VT_BYTES + 2 * P_BYTES;
+constexpr int TILE_BYTES = 2 * K_BYTES + 2 * V_BYTES + 2 * P_BYTES;
 constexpr int ROWX_BYTES = 2 * 2 * BM * 4;         // the softmax threads' exchange: references [2][BM], row sums [2][BM]
 constexpr int USED_BYTES = TILE_BYTES + ROWX_BYTES + 256;
 constexpr int SMEM_BYTES = USED_BYTES + 512;       // head_dim 256 uses all but 256 bytes of an SM's shared memory
@@ -58,7 +60,6 @@ struct PrefillTcArgs {
     long long q_stride;
     int n_tokens;
     const int* seq_start;          // [B + 1] rows of the packed q/k matrices
-    const int* vt_start;           // [B + 1] key columns of the transposed v (multiples of 64)
     bf16* out;                     // [T, n_heads * HD]
     int n_heads, n_kv_heads, window;
     float scale, cap;
@@ -68,7 +69,7 @@ __device__ __forceinline__ float ex2f(float x) { float y; asm("ex2.approx.ftz.f3
 __device__ __forceinline__ float rcpf(float x) { float y; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 
 __global__ void __launch_bounds__(320, 1)
-attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_vt, PrefillTcArgs a) {
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, PrefillTcArgs a) {
     pdl_launch_dependents();
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -77,8 +78,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         return;
     }
     uint8_t* sK = smem;                               // [2][K_BYTES]
-    uint8_t* sVT = sK + 2 * K_BYTES;                  // [2][VT_BYTES]
-    uint8_t* sP = sVT + 2 * VT_BYTES;                 // [2][P_BYTES]
+    uint8_t* sV = sK + 2 * K_BYTES;                   // [2][V_BYTES]
+    uint8_t* sP = sV + 2 * V_BYTES;                   // [2][P_BYTES]
     float (*row_ref)[BM] = (float (*)[BM])(sP + 2 * P_BYTES);        // [block parity][row]: the reference after that block
     float (*row_l)[BM] = row_ref + 2;                                // [group][row]: the groups' row sums at the end
     uint64_t* bars = (uint64_t*)(sP + 2 * P_BYTES + ROWX_BYTES);
@@ -102,7 +103,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const int m0 = qb * BM;
     if (m0 >= len) return;                                           // uniform for the CTA
     const int kvh = h / (a.n_heads / a.n_kv_heads);
-    const int vt0 = a.vt_start[b];
 
     // key blocks this query block can see
     const int i_last = min(len, m0 + BM) - 1;
@@ -121,7 +121,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         mbar_init_fence();
     }
     if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
-    if (threadIdx.x == 64) { tma_prefetch_map(&map_k); tma_prefetch_map(&map_vt); }
+    if (threadIdx.x == 64) { tma_prefetch_map(&map_k); tma_prefetch_map(&map_v); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -136,9 +136,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         //  So the two products have an issuing thread each, and neither waits behind the other's operands.)
         if (lane == 0) {
             pdl_wait();
-            constexpr uint32_t idesc_o = instr_desc(HD);
+            constexpr uint32_t idesc_o = instr_desc(HD) | (1u << 16);           // B (= V) is MN-major
             const uint32_t hi = desc_hi(smem_desc(0));
-            const uint32_t p_lo0 = desc_lo(smem_desc(smem_u32(sP))), v_lo0 = desc_lo(smem_desc(smem_u32(sVT)));
+            const uint32_t p_lo0 = desc_lo(smem_desc(smem_u32(sP)));
+            // V: panels of 64 dims lie BN * 128 bytes apart (leading-dimension offset, bits 16..29 of the low half);
+            // groups of 8 keys 1024 bytes apart, which is the stride offset that the K-major operands have too
+            const uint32_t v_lo0 = ((smem_u32(sV) & 0x3ffff) >> 4) | ((uint32_t)((BN * 128) >> 4) << 16);
             bool ok = true;
             // K tiles, V^T tiles and the second products are started independently, each as soon as it has what it
             // needs: the scores run up to two blocks ahead of the second product, and so must the K tiles
@@ -155,18 +158,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 }
                 if (jv < nblocks && mbar_test(&v_empty[jv & 1], ((jv >> 1) & 1) ^ 1)) {
                     const int s = jv & 1, key0 = (nb_lo + jv) * BN;
-                    mbar_expect_tx(&v_full[s], VT_BYTES);
-                    tma_load_2d(sVT + s * VT_BYTES, &map_vt, &v_full[s], vt0 + key0, kvh * HD);
+                    mbar_expect_tx(&v_full[s], V_BYTES);
+                    for (int c = 0; c < QBOXES; c++)
+                        tma_load_2d(sV + s * V_BYTES + c * BN * 128, &map_v, &v_full[s], kvh * HD + c * 64, s0 + key0);
                     jv++; moved = true;
                 }
                 if (mbar_test(&v_full[jp & 1], (jp >> 1) & 1) && mbar_test(&p_full[jp & 1], (jp >> 1) & 1)) {
                     const int s = jp & 1;
                     tc_fence_after();
-                    const uint32_t p_lo = p_lo0 + s * (P_BYTES >> 4), v_lo = v_lo0 + s * (VT_BYTES >> 4);
+                    const uint32_t p_lo = p_lo0 + s * (P_BYTES >> 4), v_lo = v_lo0 + s * (V_BYTES >> 4);
 #pragma unroll
-                    for (int ks = 0; ks < BN / UMMA_K; ks++)
-                        umma_bf16_lh(tmem_o, p_lo + ks * 2, v_lo + ks * 2, hi, idesc_o, (jp > 0 || ks > 0) ? 1u : 0u);
-                    umma_commit(&v_empty[s]);         // V^T tile and P buffer are free again; O holds blocks 0..jp
+                    for (int ks = 0; ks < BN / UMMA_K; ks++)          // 16 keys on: 32 bytes in a row of P, 16 rows of V
+                        umma_bf16_lh(tmem_o, p_lo + ks * 2, v_lo + ks * ((UMMA_K * 128) >> 4), hi, idesc_o,
+                                     (jp > 0 || ks > 0) ? 1u : 0u);
+                    umma_commit(&v_empty[s]);         // V tile and P buffer are free again; O holds blocks 0..jp
                     jp++; moved = true;
                 }
                 if (moved) idle_since = clock64();
@@ -394,29 +399,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
-// v [T, kv_stride] (token rows) -> vt [n_kv_heads * HD, vt_cols]: sequence b's keys at columns
-// vt_start[b] .. vt_start[b] + len_b, zero up to the next multiple of 64.
-__global__ void transpose_v_kernel(const bf16* __restrict__ v, long long kv_stride, bf16* __restrict__ vt, long long vt_cols,
-                                   const int* __restrict__ seq_start, const int* __restrict__ vt_start, int width) {
-    pdl_launch_dependents();
-    pdl_wait();
-    __shared__ bf16 tile[32][33];
-    const int b = blockIdx.z;
-    const int s0 = seq_start[b], len = seq_start[b + 1] - s0;
-    const int c0 = vt_start[b], cols = vt_start[b + 1] - c0;          // padded key count of this sequence
-    const int k0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
-    if (k0 >= cols) return;
-    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
-        const int key = k0 + r, d = d0 + threadIdx.x;
-        tile[r][threadIdx.x] = (key < len && d < width) ? v[(size_t)(s0 + key) * kv_stride + d] : __float2bfloat16(0.f);
-    }
-    __syncthreads();
-    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
-        const int d = d0 + r, key = k0 + threadIdx.x;
-        if (d < width && key < cols) vt[(size_t)d * vt_cols + c0 + key] = tile[threadIdx.x][r];
-    }
-}
-
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -447,35 +429,22 @@ static int make_map(CUtensorMap* m, const void* base, long long rows, long long 
 
 extern "C" int tb_attn_prefill_tc_head_dim() { return HD; }
 
-// vt: scratch of n_kv_heads * HD rows x vt_cols columns (bfloat16), vt_cols a multiple of 64 that holds every
-// sequence rounded up to 64 keys; vt_start [batch + 1] on the device, multiples of 64.
 extern "C" int tb_attn_prefill_tc(const void* q, const void* k, const void* v, long long q_stride, long long kv_stride,
-                                  const int* seq_start, const int* vt_start, void* vt, long long vt_cols, void* out,
-                                  int n_tokens, int batch, int max_seq_len, int n_heads, int n_kv_heads, int hd,
-                                  float scale, float cap, int window, cudaStream_t stream) {
+                                  const int* seq_start, void* out, int n_tokens, int batch, int max_seq_len, int n_heads,
+                                  int n_kv_heads, int hd, float scale, float cap, int window, cudaStream_t stream) {
     if (batch <= 0 || max_seq_len <= 0) return 0;
     if (hd != HD) return tb_refuse("attn_prefill_tc: this library is built for head_dim %d, got %d", HD, hd);
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads)
         return tb_refuse("attn_prefill_tc: %d heads cannot share %d kv heads", n_heads, n_kv_heads);
-    if (((uintptr_t)q & 15) || ((uintptr_t)k & 15) || ((uintptr_t)v & 15) || ((uintptr_t)vt & 15) || (q_stride % 8) ||
-        (kv_stride % 8) || (vt_cols % 64))
-        return tb_refuse("attn_prefill_tc: q, k, v rows must be 16-byte aligned and vt_cols a multiple of 64");
+    if (((uintptr_t)q & 15) || ((uintptr_t)k & 15) || ((uintptr_t)v & 15) || (q_stride % 8) || (kv_stride % 8))
+        return tb_refuse("attn_prefill_tc: q, k, v rows must be 16-byte aligned");
     if (n_heads > 65535 || batch > 65535) return tb_refuse("attn_prefill_tc: %d heads x %d sequences exceed one launch", n_heads, batch);
     const int kvw = n_kv_heads * HD;
-    {
-        dim3 grid((unsigned)((max_seq_len + 63) / 64 * 2), (kvw + 31) / 32, batch);
-        tb_launch(transpose_v_kernel, grid, dim3(32, 8), 0, stream, (const bf16*)v, kv_stride, (bf16*)vt, vt_cols,
-                  seq_start, vt_start, kvw);
-        int st = tb_launch_status();
-        if (st) return st;
-    }
-    CUtensorMap mk, mvt;
-    if (make_map(&mk, k, n_tokens, kvw, kv_stride, BN) ||
-        make_map(&mvt, vt, kvw, vt_cols, vt_cols, HD))
-        return -1;
+    CUtensorMap mk, mv;
+    if (make_map(&mk, k, n_tokens, kvw, kv_stride, BN) || make_map(&mv, v, n_tokens, kvw, kv_stride, BN)) return -1;
     PrefillTcArgs a;
     a.q = (const bf16*)q; a.q_stride = q_stride; a.n_tokens = n_tokens;
-    a.seq_start = seq_start; a.vt_start = vt_start; a.out = (bf16*)out;
+    a.seq_start = seq_start; a.out = (bf16*)out;
     a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.window = window; a.scale = scale; a.cap = cap;
     static bool attr_set = false;
     if (!attr_set) {
@@ -484,7 +453,7 @@ extern "C" int tb_attn_prefill_tc(const void* q, const void* k, const void* v, l
         attr_set = true;
     }
     dim3 grid((max_seq_len + BM - 1) / BM, n_heads, batch);
-    tb_launch(attn_prefill_tc_kernel, grid, dim3(320), SMEM_BYTES, stream, mk, mvt, a);
+    tb_launch(attn_prefill_tc_kernel, grid, dim3(320), SMEM_BYTES, stream, mk, mv, a);
     return tb_launch_status();
 }
 

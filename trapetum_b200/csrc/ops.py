@@ -563,21 +563,11 @@ def attn_prefill_tc_lib(head_dim: int) -> str:
     return f"attention_prefill_tc@TB_HD={head_dim}"
 
 
-def padded_starts(seq_lens, multiple: int = 64):
-    """Start column of each sequence when every sequence is rounded up to ``multiple`` keys: [batch + 1]."""
-    out = [0]
-    for n in seq_lens:
-        out.append(out[-1] + (n + multiple - 1) // multiple * multiple)
-    return out
-
-
 def attn_prefill_tc(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, seq_start: torch.Tensor, seq_lens,
-                    n_heads: int, n_kv_heads: int, head_dim: int, scale: float, softcap: float, window: int,
-                    vt_start: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    n_heads: int, n_kv_heads: int, head_dim: int, scale: float, softcap: float, window: int) -> torch.Tensor:
     """Causal attention of packed sequences on tcgen05 tensor cores (see attention_prefill_tc.cu).
-    ``seq_lens``: the sequences' lengths on the host; ``vt_start``: ``padded_starts(seq_lens)`` on the device
-    (made here if not given)."""
-    _cuda(q, k, v, seq_start, vt_start)
+    ``seq_lens``: the sequences' lengths on the host."""
+    _cuda(q, k, v, seq_start)
     for name, t in (("q", q), ("k", k), ("v", v)):
         _rows_contig(t, "attention: " + name)
     if not attn_prefill_tc_takes(q.dtype, head_dim) or k.dtype != q.dtype or v.dtype != q.dtype:
@@ -587,19 +577,13 @@ def attn_prefill_tc(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, seq_start
     B = len(seq_lens)
     if seq_start.dtype != torch.int32 or not seq_start.is_contiguous() or seq_start.numel() != B + 1:
         raise KernelError("attention: seq_start must be contiguous int32 [batch + 1]")
-    starts = padded_starts(seq_lens)
-    if vt_start is None:
-        vt_start = torch.tensor(starts, dtype=torch.int32, device=q.device)
     T = q.shape[0]
-    vt_cols = max(starts[-1], 64)
-    vt = torch.empty((n_kv_heads * head_dim, vt_cols), dtype=q.dtype, device=q.device)
     out = torch.empty((T, n_heads * head_dim), dtype=q.dtype, device=q.device)
     lib = build.load(attn_prefill_tc_lib(head_dim))
     _check(lib, lib.tb_attn_prefill_tc(_ptr(q), _ptr(k), _ptr(v), c_longlong(q.stride(0)), c_longlong(k.stride(0)),
-                                       _ptr(seq_start), _ptr(vt_start), _ptr(vt), c_longlong(vt_cols), _ptr(out),
-                                       c_int(T), c_int(B), c_int(max(seq_lens)), c_int(n_heads), c_int(n_kv_heads),
-                                       c_int(head_dim), c_float(scale), c_float(softcap or 0.0), c_int(window or 0),
-                                       _stream()), "attn_prefill_tc", 2)
+                                       _ptr(seq_start), _ptr(out), c_int(T), c_int(B), c_int(max(seq_lens)),
+                                       c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_float(scale),
+                                       c_float(softcap or 0.0), c_int(window or 0), _stream()), "attn_prefill_tc", 2)
     return out
 
 
@@ -611,16 +595,10 @@ def attn_prefill_tc_error(head_dim: int) -> int:
 def attn_prefill(q, k, v, seq_start, token_seq, n_heads, n_kv_heads, head_dim, scale, softcap, window,
                  max_seq_len: int, seq_lens=None, memo: Optional[dict] = None) -> torch.Tensor:
     """Prefill attention, kernel chosen here: tcgen05 for head sizes 64/128/256, mma.sync for other multiples
-    of 16, the generic kernel for the rest and for float32.  ``memo``: a per-step dict in which the padded
-    starts of the transposed v are kept, so that they are uploaded once per step and not once per layer."""
+    of 16, the generic kernel for the rest and for float32.  ``memo``: a per-step dict for what a kernel wants
+    uploaded once per step and not once per layer (none does at present)."""
     if attn_prefill_tc_takes(q.dtype, head_dim) and seq_lens is not None:
-        vt_start = None
-        if memo is not None:
-            vt_start = memo.get("vt_start")
-            if vt_start is None:
-                vt_start = memo["vt_start"] = torch.tensor(padded_starts(seq_lens), dtype=torch.int32, device=q.device)
-        return attn_prefill_tc(q, k, v, seq_start, seq_lens, n_heads, n_kv_heads, head_dim, scale, softcap, window,
-                               vt_start)
+        return attn_prefill_tc(q, k, v, seq_start, seq_lens, n_heads, n_kv_heads, head_dim, scale, softcap, window)
     if attn_prefill_takes(q.dtype, head_dim):
         return attn_prefill_mma(q, k, v, seq_start, n_heads, n_kv_heads, head_dim, scale, softcap, window, max_seq_len)
     return attn_prefill_simt(q, k, v, seq_start, token_seq, n_heads, n_kv_heads, head_dim, scale, softcap, window)
