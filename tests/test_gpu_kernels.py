@@ -395,7 +395,8 @@ def test_attn_prefill(ops, dt, nh, nkv, hd, cap, window):
 
 
 @pytest.mark.parametrize("nh,nkv,hd,cap,window,lens", [(8, 4, 256, 50.0, 0, [1000]), (8, 4, 256, 50.0, 300, [700, 64, 129]),
-                                                       (4, 1, 128, 0.0, 0, [513, 1]), (2, 2, 64, 20.0, 100, [400, 333])])
+                                                       (4, 1, 128, 0.0, 0, [513, 1]), (2, 2, 64, 20.0, 100, [400, 333]),
+                                                       (4, 2, 256, 50.0, 1024, [2500]), (4, 2, 128, 30.0, 0, [2100, 700])])
 def test_attn_prefill_tc_long(ops, nh, nkv, hd, cap, window, lens):
     """Long sequences: many key blocks, the lazy rescaling of O, the window's trailing edge, and query
     tiles whose rows belong to the next sequence of the packed batch."""

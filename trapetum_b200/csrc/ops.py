@@ -32,7 +32,15 @@ def code(dt: torch.dtype) -> int:
         raise KernelError(f"kernels take float32 and bfloat16 tensors, not {dt}") from None
 
 
+_RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_RAW_DEVICE = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream() -> c_void_p:
+    """The current stream's handle.  Every launch asks for it, so it is read through torch's raw accessors where
+    this torch has them (a Stream object costs several microseconds to make)."""
+    if _RAW_STREAM is not None and _RAW_DEVICE is not None:
+        return c_void_p(_RAW_STREAM(_RAW_DEVICE()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
