@@ -376,7 +376,8 @@ template <int HD> struct MCfg {
     static constexpr int MT_W = HD / 64;                             // 16-dim tiles of O^T per output warp (head_dim / 4 dims)
     static constexpr int SCORE_FLOATS = 2 * 8 * SROW + 2 * 8 * 4;    // two pages' scores, and their maxima per score warp
     static constexpr int SMEM = STAGES * STAGE_BYTES + SCORE_FLOATS * 4 + 256 /* barriers */ + (1024 + 4) * 4 /* stream: page prefix */
-                                + 8 * HD * 2 /* rotated queries */ + 1024 /* alignment */;
+                                + 8 * HD * 2 /* rotated queries */ + 10 * HD * 4 /* this step's q, k, v, summed */
+                                + 1024 /* alignment */;
 };
 // byte offset of (key row r, 16-byte chunk c of the head dim) inside a swizzled page
 __device__ __forceinline__ int sw_off(int r, int c) {
@@ -445,6 +446,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     uint64_t* grp = s_empty + 2;                                     // [3] meeting points of the score warps, of the output warps, of all eight
     int* pref = (int*)(full + 32);                                   // stream: [batch + 1] pages before each sequence
     bf16* q_s = (bf16*)(pref + 1024 + 4);                            // [8 heads][HD] this run's queries, rotated (fused rotation)
+    float* fold_s = (float*)(q_s + 8 * HD);                          // [G heads of q, then k, then v][HD]: the partial sums added up
     __shared__ int s_last, s_job[3];                // split: the pair to fold (sequence, kv head, parts)
     __shared__ volatile int s_abort;
 
@@ -581,13 +583,83 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             if (dst2) dst2[d] = y;
         }
     };
-    if (fused && warp >= TW / 2 && warp < TW) {
-        // the upper half of the warps rotates the first run's query heads into shared memory meanwhile
-        const int len0 = a.len_after[cur.b], per = HD - half;
-        for (int x = tid - (TW / 2) * 32; x < G * per; x += (TW / 2) * 32)
-            rotate_head(cur.b, (cur.kvh * G + x / per) * HD, len0 - 1, q_s + (x / per) * HD, nullptr, x % per);
-    }
-    if (fused) {
+    if (fused && !STREAM) {
+        // Split: the CTA has one run.  Every partial sum that it needs (its G query heads; k and v too if its run holds
+        // the page of the new token, which this CTA and no other reads) is requested at once, four columns a thread
+        // and eight splits each, added in the splits' order and left in shared memory: one wait for memory.  Then
+        // the rotation works from there.
+        const int len0 = a.len_after[cur.b], pos = len0 - 1;
+        const int hot_rel = cur.hot - cur.first_page;
+        const bool hot_here = cur.left > 0 && hot_rel >= cur.pg && hot_rel < cur.pg + cur.left;
+        const int n_cols = (G + (hot_here ? 2 : 0)) * HD;
+        const float* row = a.qkv_part + (size_t)cur.b * a.qkv_row_stride;
+        if (warp < TW) {
+            for (int c0 = tid; c0 < n_cols; c0 += 4 * TW * 32) {
+                float sum[4] = {0.f, 0.f, 0.f, 0.f};
+                const float* src[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int c = c0 + e * TW * 32;
+                    const int col = c < G * HD ? cur.kvh * G * HD + c
+                                  : c < (G + 1) * HD ? k_off + cur.kvh * HD + (c - G * HD) : v_off + cur.kvh * HD + (c - (G + 1) * HD);
+                    src[e] = row + col;
+                }
+                for (int s0 = 0; s0 < a.qkv_splits; s0 += 8) {
+                    float t8[4][8];
+#pragma unroll
+                    for (int e = 0; e < 4; e++)
+#pragma unroll
+                        for (int k = 0; k < 8; k++)
+                            if (c0 + e * TW * 32 < n_cols && s0 + k < a.qkv_splits) t8[e][k] = src[e][(size_t)(s0 + k) * a.qkv_split_stride];
+#pragma unroll
+                    for (int e = 0; e < 4; e++)
+#pragma unroll
+                        for (int k = 0; k < 8; k++)
+                            if (c0 + e * TW * 32 < n_cols && s0 + k < a.qkv_splits) sum[e] = (s0 + k == 0) ? t8[e][k] : sum[e] + t8[e][k];
+                }
+#pragma unroll
+                for (int e = 0; e < 4; e++) if (c0 + e * TW * 32 < n_cols) fold_s[c0 + e * TW * 32] = sum[e];
+            }
+        }
+        __syncthreads();
+        if (warp < TW) {
+            // head (first value fold_s[c0]) rotated at `pos` and rounded: item x is a rotated pair or a dim beyond the rotary part
+            auto rotate_from = [&](const float* hsrc, bf16* dst, int x) {
+                if (x < half) {
+                    float sn, cs;
+                    sincosf((float)pos * a.inv_freq[x], &sn, &cs);
+                    const float x0 = hsrc[x], x1 = hsrc[x + half];
+                    dst[x] = __float2bfloat16_rn(x0 * cs - x1 * sn);
+                    dst[x + half] = __float2bfloat16_rn(x1 * cs + x0 * sn);
+                } else {
+                    dst[x + half] = __float2bfloat16_rn(hsrc[x + half]);
+                }
+            };
+            const int per = HD - half;
+            for (int x = tid; x < G * per; x += TW * 32) rotate_from(fold_s + (x / per) * HD, q_s + (x / per) * HD, x % per);
+            if (hot_here) {
+                const int r = (a.ring_rows > 0) ? pos % a.ring_rows : pos;
+                const int page = a.page_table[(size_t)cur.b * a.pt_stride + r / PAGE];
+                const size_t off = ((size_t)(page * a.n_kv_heads + cur.kvh) * PAGE + (r % PAGE)) * HD;
+                bf16* kd = (bf16*)a.k_pool + off;
+                bf16* vd = (bf16*)a.v_pool + off;
+                for (int x = tid; x < per + HD; x += TW * 32) {
+                    if (x < per) rotate_from(fold_s + G * HD, kd, x);
+                    else vd[x - per] = __float2bfloat16_rn(fold_s[(G + 1) * HD + x - per]);
+                }
+                // the rows were written by ordinary stores and are read by the copy engine next
+                __threadfence();
+                asm volatile("fence.proxy.async;" ::: "memory");
+            }
+        }
+        __syncthreads();
+    } else if (fused) {
+        if (warp >= TW / 2 && warp < TW) {
+            // the upper half of the warps rotates the first run's query heads into shared memory meanwhile
+            const int len0 = a.len_after[cur.b], per = HD - half;
+            for (int x = tid - (TW / 2) * 32; x < G * per; x += (TW / 2) * 32)
+                rotate_head(cur.b, (cur.kvh * G + x / per) * HD, len0 - 1, q_s + (x / per) * HD, nullptr, x % per);
+        }
         // The runs of this CTA that hold the page of their sequence's new token: this CTA, and no other, reads
         // that page, so it (the lower half of its warps) writes the token's k and v rows there first.
         PageCursor w = cur;
@@ -958,36 +1030,74 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         }
     }
     if (!STREAM && warp < TW && a.n_splits > 1 && a.tickets != nullptr) {
-        // split: the CTA had one run.  If it was the pair's last part, all eight warps fold the parts, in their order:
-        // out = sum_k e^(m_k - M) o_k / sum_k e^(m_k - M) l_k, sixteen parts requested at a time; M is the running
-        // maximum, by which the sums so far are rescaled.
+        // split: the CTA had one run.  If it was the pair's last part, all eight warps fold the parts:
+        // out = sum_k w_k o_k with w_k = e^(m_k - M) / sum_j e^(m_j - M) l_j and M the largest m.  The parts' outputs are
+        // requested first (two outputs a thread, 32 parts each), the weights are made meanwhile by one warp a head from
+        // the parts' m and l, and the sum runs in the parts' order: one wait for memory, whatever else the GPU is doing.
         __syncwarp();
         if (lane == 0) mbar_arrive(&grp[2]);
         if (!wait_on(&grp[2], 0) || !s_last) return;
         const int b = s_job[0], kvh = s_job[1], n_parts = s_job[2];
-        for (int x = tid; x < G * HD; x += TW * 32) {
-            const int hg = x / HD, d = x % HD;
-            const float* p0 = a.partial + ((size_t)b * a.n_heads + kvh * G + hg) * a.n_splits * (HD + 2);
-            float M = -INFINITY, L = 0.f, acc = 0.f;
-            for (int k0 = 0; k0 < n_parts; k0 += 16) {
-                float ms[16], ls[16], os[16];
+        float* wts = sf;                                            // [8 heads][64 parts] (the scores' place; the run is over)
+        constexpr int FK = 32;
+        const float* p0 = a.partial + ((size_t)b * a.n_heads + kvh * G) * a.n_splits * (HD + 2);
+        const size_t head_stride = (size_t)a.n_splits * (HD + 2);
+        bool have_weights = false;
+        for (int x0 = tid; x0 < G * HD || !have_weights; x0 += 2 * TW * 32) {
+            float acc[2] = {0.f, 0.f};
+            for (int k0 = 0; k0 < n_parts; k0 += FK) {
+                float os[2][FK];
 #pragma unroll
-                for (int k = 0; k < 16; k++)
-                    if (k0 + k < n_parts) {
-                        const float* pk = p0 + (size_t)(k0 + k) * (HD + 2);
-                        ms[k] = __ldcg(pk + HD); ls[k] = __ldcg(pk + HD + 1); os[k] = __ldcg(pk + d);
+                for (int e = 0; e < 2; e++) {
+                    const int x = x0 + e * TW * 32;
+                    if (x < G * HD) {
+                        const float* px = p0 + (x / HD) * head_stride + (x % HD);
+#pragma unroll
+                        for (int k = 0; k < FK; k++) if (k0 + k < n_parts) os[e][k] = __ldcg(px + (size_t)(k0 + k) * (HD + 2));
                     }
-                float Mn = M;
+                }
+                if (!have_weights) {
+                    if (warp < G) {
+                        const float* ph = p0 + warp * head_stride;
+                        float m[2], l[2], M = -INFINITY;
 #pragma unroll
-                for (int k = 0; k < 16; k++) if (k0 + k < n_parts) Mn = fmaxf(Mn, ms[k]);
-                if (Mn == -INFINITY) continue;
-                const float r = (M == -INFINITY) ? 0.f : __expf(M - Mn);
-                L *= r; acc *= r; M = Mn;
+                        for (int e = 0; e < 2; e++) {
+                            const int k = lane + 32 * e;
+                            m[e] = k < n_parts ? __ldcg(ph + (size_t)k * (HD + 2) + HD) : -INFINITY;
+                            l[e] = k < n_parts ? __ldcg(ph + (size_t)k * (HD + 2) + HD + 1) : 0.f;
+                            M = fmaxf(M, m[e]);
+                        }
 #pragma unroll
-                for (int k = 0; k < 16; k++)
-                    if (k0 + k < n_parts && ms[k] != -INFINITY) { const float f = __expf(ms[k] - M); L += ls[k] * f; acc += os[k] * f; }
+                        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+                        float f[2], L = 0.f;
+#pragma unroll
+                        for (int e = 0; e < 2; e++) { f[e] = (m[e] == -INFINITY) ? 0.f : __expf(m[e] - M); L += f[e] * l[e]; }
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+                        const float inv = 1.f / L;
+#pragma unroll
+                        for (int e = 0; e < 2; e++) wts[warp * 64 + lane + 32 * e] = f[e] * inv;
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&grp[2]);
+                    if (!wait_on(&grp[2], 1)) return;
+                    have_weights = true;
+                }
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const int x = x0 + e * TW * 32;
+                    if (x < G * HD) {
+                        const float* w = wts + (x / HD) * 64 + k0;
+#pragma unroll
+                        for (int k = 0; k < FK; k++) if (k0 + k < n_parts) acc[e] = fmaf(w[k], os[e][k], acc[e]);
+                    }
+                }
             }
-            ((bf16*)a.out)[((size_t)b * a.n_heads + kvh * G + hg) * HD + d] = __float2bfloat16_rn(acc / L);
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const int x = x0 + e * TW * 32;
+                if (x < G * HD) ((bf16*)a.out)[((size_t)b * a.n_heads + kvh * G + x / HD) * HD + x % HD] = __float2bfloat16_rn(acc[e]);
+            }
         }
     }
 }
