@@ -113,3 +113,45 @@ def test_decoding_repeats_bit_for_bit_over_long_contexts(models, lens):
     assert torch.isfinite(outs[0]).all()
     assert torch.equal(outs[0], outs[1])
     assert ops.kernel_errors() == {}
+
+
+MID = dict(BASE, hidden_size=256, num_attention_heads=4, num_key_value_heads=2, head_dim=64, intermediate_size=512,
+           vocab_size=1000, query_pre_attn_scalar=64, sliding_window=200)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_prompts_through_the_tensor_core_attention(tmp_path_factory, dtype):
+    """Prompts of many key blocks (900 and 333 tokens, a window of 200 on the even layers) through a model whose
+    head size (64) takes the tcgen05 prefill kernel and the tensor-core decode kernel, then eight tokens one by
+    one: logits at the first position, around the window's edge, in the middle and at the end."""
+    import trapetum_b200 as tb
+    from trapetum_b200.csrc import ops
+    d = str(tmp_path_factory.mktemp("mid"))
+    tb.write_random_model(d, MID, seed=9, std=0.05, norm_std=0.1)
+    sharpen(d, 2.0)
+    cfg, w = plain.load_folder(d, dtype=torch.float64)
+    prompts = make_prompts(cfg["vocab_size"], [908, 341], seed=6)
+    want = [plain.forward(cfg, w, p) for p in prompts]
+    tol = TOL["float32"] if dtype == "float32" else bf16_budget(cfg, w, [prompts[1]])
+    model = tb.load_model(d, dtype)
+    eng = tb.Engine(model, max_tokens=64 * 22)
+    for g in eng.cache.groups:
+        g.k.fill_(float("nan")); g.v.fill_(float("nan"))
+    cut = [len(p) - 8 for p in prompts]
+    places = [[0, 127, 128, 199, 200, 201, c // 2, c - 1] for c in cut]
+    s = eng.start(2)
+    first = eng.step(s, [p[:c] for p, c in zip(prompts, cut)], places)
+    k = 0
+    for r in range(2):
+        for i in places[r]:
+            e = rel_l2(first[k], want[r][i])
+            assert e <= tol, f"{dtype}: prompt {r} position {i}: {e:.3e} > {tol:.1e}"
+            k += 1
+    for t in range(8):
+        out = eng.step(s, [[p[c + t]] for p, c in zip(prompts, cut)])
+        for r, c in enumerate(cut):
+            e = rel_l2(out[r], want[r][c + t])
+            assert e <= tol, f"{dtype}: request {r} decoded token {t}: {e:.3e} > {tol:.1e}"
+    eng.release(s)
+    torch.cuda.synchronize()
+    assert ops.kernel_errors() == {}
