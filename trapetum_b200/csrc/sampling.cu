@@ -229,14 +229,14 @@ __global__ void __launch_bounds__(1024) sample_kernel(SampleArgs a) {
 //
 // Masses are fixed-point: m_i = round(2^32 e^((l_i - max) / T)), summed in 64-bit integers.  Integer sums do not
 // depend on their order, so histograms can be built with atomics and the draw still repeats bit for bit.
-// The nucleus threshold is found by a radix search on the order-preserving key of the logit: three rounds
+// The nucleus threshold is found by a radix search on the order-preserving key of the logit: three passes
 // (11 + 11 + 10 bits), each a histogram of mass per digit among the elements that match the digits found so far,
 // and a scan from the top for the digit at which the mass above reaches top_p x total.
 //
 //   sample_chunk_max  per chunk: repetition penalty on the chunk's ids, then (max, index)   [also the greedy choice];
 //                     clears the row's histograms
-//   sample_hist<R>    per chunk: (R > 0: first the digit of round R-1, found by every CTA for itself from the
-//                     finished histogram;) mass histogram of round R            [rows with a nucleus only]
+//   sample_hist<R>    per chunk: (R > 0: first the digit of pass R-1, found by every CTA for itself from the
+//                     finished histogram;) mass histogram of pass R            [rows with a nucleus only]
 //   sample_chunk_mass per chunk: the last digit, hence the threshold; mass of the chunk's kept elements
 //   sample_pick       per row: target = u x kept mass; the chunk and then the element at which the running sum
 //                     of kept masses, in index order, passes the target
@@ -258,7 +258,7 @@ struct SampleWide {
     float* pmax; int* pidx;       // [rows][n_chunks]
     u64* hist;                    // [rows][3][S_BINS]
     u64* cmass;                   // [rows][n_chunks]
-    SampleState* state;           // [rows][3]: after round 0, 1, 2
+    SampleState* state;           // [rows][3]: after pass 0, 1, 2
 };
 
 __device__ __forceinline__ u64 fixed_mass(float l, float mx, float invT) {
@@ -308,16 +308,16 @@ __global__ void __launch_bounds__(256) sample_chunk_max_kernel(SampleWide w) {
     if (tid == 0) { w.pmax[(size_t)row * w.n_chunks + chunk] = b.v; w.pidx[(size_t)row * w.n_chunks + chunk] = b.i; }
 }
 
-// the digit of round R of a key, and whether the key matches the digits found before it
+// the digit of pass R of a key, and whether the key matches the digits found before it
 template <int R> __device__ __forceinline__ bool digit_of(unsigned key, unsigned prefix, int& bin) {
     if (R == 0) { bin = key >> 21; return true; }
     if (R == 1) { bin = (key >> 10) & 2047; return (key >> 21) == prefix; }
     bin = key & 1023; return (key >> 10) == prefix;
 }
 
-// The digit of round R from its finished histogram `g` (in shared memory), by a CTA of 256 threads: each thread sums
+// The digit of pass R from its finished histogram `g` (in shared memory), by a CTA of 256 threads: each thread sums
 // eight digits, warp 0 scans the sums from the top, and the lane in which the mass above reaches `want` walks down
-// its own sums and then the eight digits of one of them.  `*st` (shared memory) is the state before the round on
+// its own sums and then the eight digits of one of them.  `*st` (shared memory) is the state before the pass on
 // entry and the state after it on return.
 template <int R>
 __device__ void select_digit(const u64* g, u64* part /* 256 */, SampleState* st_io, float top_p) {
@@ -360,10 +360,10 @@ __device__ void select_digit(const u64* g, u64* part /* 256 */, SampleState* st_
     __syncthreads();
 }
 
-// The state before round R for this CTA (R == 0: the start), into shared memory: found from the finished histogram
-// of round R-1; the CTA of chunk 0 also leaves it in memory for the launches after this one.  `g`: S_BINS sums.
+// The state before pass R for this CTA (R == 0: the start), into shared memory: found from the finished histogram
+// of pass R-1; the CTA of chunk 0 also leaves it in memory for the launches after this one.  `g`: S_BINS sums.
 template <int R>
-__device__ void state_before_round(const SampleWide& w, int row, u64* g, u64* part, SampleState* out) {
+__device__ void state_before_pass(const SampleWide& w, int row, u64* g, u64* part, SampleState* out) {
     if (threadIdx.x == 0) {
         SampleState st;
         if (R <= 1) {
@@ -395,7 +395,7 @@ __global__ void __launch_bounds__(256) sample_hist_kernel(SampleWide w) {
     __shared__ SampleState s_st;
     __shared__ float red[33];
     const int row = blockIdx.y, chunk = blockIdx.x;
-    state_before_round<R>(w, row, g, part, &s_st);
+    state_before_pass<R>(w, row, g, part, &s_st);
     const SampleState st = s_st;
     if (!st.nucleus) return;
     __syncthreads();
@@ -437,8 +437,8 @@ __global__ void __launch_bounds__(256) sample_chunk_mass_kernel(SampleWide w, in
     if (!(T > 0.f)) return;
     unsigned thr = 0u;                                              // keep everything
     if (nucleus) {
-        state_before_round<3>(w, row, g, part, &s_st);
-        if (s_st.nucleus) thr = s_st.prefix;                       // after the last round the digits are the whole key
+        state_before_pass<3>(w, row, g, part, &s_st);
+        if (s_st.nucleus) thr = s_st.prefix;                       // after the last pass the digits are the whole key
     }
     const float* x = w.a.logits + (size_t)row * w.a.row_stride;
     const float mx = row_max(w, row, red), invT = 1.f / T;
@@ -533,7 +533,7 @@ extern "C" long long tb_sample_wide_scratch_bytes(int rows, int vocab) {
     return (long long)rows * (chunks * (4 + 4 + 8) + 3LL * S_BINS * 8 + 3LL * (long long)sizeof(SampleState)) + 256;
 }
 
-// `nucleus`: 0 if the caller knows that every row has top_p >= 1 (the threshold rounds are then not launched).
+// `nucleus`: 0 if the caller knows that every row has top_p >= 1 (the threshold passes are then not launched).
 extern "C" int tb_sample_wide(const SampleArgs* args, int rows, void* scratch, int nucleus, cudaStream_t stream) {
     if (rows <= 0) return 0;
     SampleWide w;
