@@ -50,14 +50,38 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+    """Samples SM clocks and throttle reasons (NVML, else nvidia-smi) while a timed region runs.  Reads only."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self):
         self.rows, self._stop, self._t = [], threading.Event(), None
 
+    def _run_nvml(self) -> bool:
+        """Reads the same values through NVML every 5 ms (an nvidia-smi call takes longer than a short timed
+        region); False if NVML cannot be used here."""
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(0)
+            top = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+            nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM), reasons(h)
+        except Exception:
+            return False
+        bits = (0x8, 0x40, 0x20, 0x4)          # hw_slowdown, hw_thermal_slowdown, sw_thermal_slowdown, sw_power_cap
+        while not self._stop.is_set():
+            try:
+                mhz, mask = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM), int(reasons(h))
+                self.rows.append([str(mhz), str(top)] + ["Active" if mask & b else "Not Active" for b in bits])
+            except Exception:
+                pass
+            self._stop.wait(0.005)
+        return True
+
     def _run(self):
+        if self._run_nvml():
+            return
         while not self._stop.is_set():
             try:
                 out = subprocess.run(["nvidia-smi", "-i", "0", "--query-gpu=" + self.Q, "--format=csv,noheader,nounits"],
