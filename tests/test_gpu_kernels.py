@@ -297,6 +297,28 @@ def test_attn_decode(ops, dt, nh, nkv, hd, cap, window, splits):
     assert ops.attn_decode_error() == 0
 
 
+@pytest.mark.parametrize("splits", [17, 33, 64, 70])
+def test_attn_decode_in_many_pieces(ops, splits):
+    """A long sequence cut into many pieces: the fold inside the kernel takes up to 32 pieces at a time and holds
+    the weights of 64; more than 64 pieces go to the fold launch."""
+    dt, nh, nkv, hd = torch.bfloat16, 4, 2, 64
+    lens = [PAGE * 70 + 5, 300]
+    ks = [rnd(n, nkv, hd, dt=dt, seed=i).cpu() for i, n in enumerate(lens)]
+    vs = [rnd(n, nkv, hd, dt=dt, seed=10 + i).cpu() for i, n in enumerate(lens)]
+    q = rnd(len(lens), nh * hd, dt=dt, seed=99)
+    kp, vp, table = paged([k.cuda() for k in ks], [v.cuda() for v in vs], lens, 0, 80, seed=3)
+    la = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    scale = 0.37 / math.sqrt(hd)
+    for rep in range(2):                                                # twice: the tickets are used again
+        got = ops.attn_decode_tma(q, kp, vp, table, la, nh, nkv, hd, scale, 30.0, 0, 0, splits)
+        assert torch.isfinite(got.float()).all()
+        for b, n in enumerate(lens):
+            want = ref_attention_one(q[b].view(nh, hd).cpu(), ks[b], vs[b], scale, 30.0, 0)
+            close(got[b].view(nh, hd), want, dt, 2.0)
+    torch.cuda.synchronize()
+    assert ops.attn_decode_error() == 0
+
+
 @pytest.mark.parametrize("nh,nkv,hd,rot,cap,window", [(8, 4, 256, 256, 50.0, 0), (8, 4, 256, 256, 50.0, 128), (6, 2, 64, 32, 0.0, 70),
                                                      (5, 5, 128, 0, 0.0, 0), (14, 2, 256, 64, 30.0, 200), (4, 1, 128, 128, 0.0, 64)])
 def test_attn_decode_that_rotates_and_appends_by_itself(ops, nh, nkv, hd, rot, cap, window):

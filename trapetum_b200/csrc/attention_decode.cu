@@ -1233,6 +1233,7 @@ static int run_decode(const DecodeArgs* args, int dtype, int batch, bool tensor_
     const int g = a.n_heads / a.n_kv_heads;
     int st = -1;
     if (a.hd < 64) tensor_cores = false;            // a 64-byte row has no 128-byte swizzled box
+    if (a.n_splits > 64) a.tickets = nullptr;       // the fold inside the kernel holds the weights of 64 pieces: more go to the fold launch
     if (a.qkv_part != nullptr) {
         if (!tensor_cores) return tb_refuse("attn_decode: only the tensor-core kernel (head_dim >= 64) rotates by itself");
         if (int r = check_rotation(a)) return r;
