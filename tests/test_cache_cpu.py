@@ -131,3 +131,47 @@ def test_random_churn_keeps_invariants():
         c.release(s)
     c.check()
     assert all(g.pool.free == g.pool.capacity for g in c.groups)
+
+
+def test_epoch_counts_every_change_of_hands():
+    """Two batches can hold the same slots with the same numbers of pages and yet other pages: whoever keeps
+    a page table must be able to tell (the epoch differs)."""
+    c = make(max_tokens=PAGE_ROWS * 8)
+    a = [c.claim(), c.claim()]
+    c.grow({a[0]: 40, a[1]: 40})
+    for _ in range(30):
+        c.grow({a[0]: 1, a[1]: 1})
+    tables_a = [[list(c.pages(s, g)) for g in range(len(c.groups))] for s in a]
+    seen = c.epoch
+    for s in a:
+        c.release(s)
+    b = [c.claim(), c.claim()]
+    c.grow({b[0]: 70, b[1]: 70})
+    tables_b = [[list(c.pages(s, g)) for g in range(len(c.groups))] for s in b]
+    assert b == a and [[len(p) for p in t] for t in tables_b] == [[len(p) for p in t] for t in tables_a]
+    assert tables_b != tables_a                # same slots, same counts, other pages
+    assert c.epoch != seen
+    e = c.epoch
+    c.grow({b[0]: 1, b[1]: 1})                 # no new page: nothing changed hands
+    assert c.epoch == e
+    c.grow({b[0]: 64, b[1]: 64})
+    assert c.epoch != e
+
+
+def test_shrink_undoes_a_grow():
+    c = make(max_tokens=PAGE_ROWS * 8, window=100)
+    s = c.claim()
+    c.grow({s: 70})
+    before = [list(c.pages(s, g)) for g in range(len(c.groups))]
+    free = [g.pool.free for g in c.groups]
+    c.grow({s: 130})
+    c.shrink({s: 130})
+    assert c.length(s) == 70 and [list(c.pages(s, g)) for g in range(len(c.groups))] == before
+    assert [g.pool.free for g in c.groups] == free
+    c.check()
+    with pytest.raises(CacheError):
+        c.shrink({s: 71})
+    c.shrink({s: 70})
+    assert c.length(s) == 0 and all(g.pool.held == 0 for g in c.groups)
+    c.release(s)
+    c.check()

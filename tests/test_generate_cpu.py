@@ -70,6 +70,10 @@ class FakeEngine:
         self.cache = Cache({0: KVNeed(1, 8, None)}, {}, max_tokens, torch.float32, "cpu")
         self.model, self.rt = _Model(), _Rt()
         self.sums, self.steps = {}, []
+        self.checks = []                       # live sequences at each look at the kernels' error words
+
+    def check_kernels(self):
+        self.checks.append(len(self.cache.live_slots()))
 
     def start(self, n):
         return [self.cache.claim() for _ in range(n)]
@@ -146,3 +150,13 @@ def test_context_limit_ends_a_sequence(monkeypatch):
     eng = FakeEngine()
     outs = gen.generate(eng, [[1] * 38], max_tokens=10, stop_ids=[])
     assert len(outs[0]) == 2 and eng.cache.live_slots() == []          # positions 38 and 39, then the limit
+
+
+def test_kernel_error_words_are_read_at_the_end_of_every_batch_and_now_and_then(monkeypatch):
+    eng = FakeEngine(max_tokens=PAGE_ROWS * 2)
+    gen.generate(eng, [[1], [2], [3]], max_tokens=3, stop_ids=[], max_batch=1)
+    assert eng.checks == [0, 0, 0]             # three batches of one: one look each, when the batch has ended
+    monkeypatch.setattr(gen, "CHECK_EVERY", 2)
+    eng = FakeEngine()
+    gen.generate(eng, [[1]], max_tokens=7, stop_ids=[])
+    assert eng.checks.count(1) >= 2 and eng.checks[-1] == 0

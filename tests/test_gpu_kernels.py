@@ -471,7 +471,8 @@ def test_attn_prefill_far_key_and_window_edge(ops):
 
 
 @pytest.mark.parametrize("dt", DT)
-@pytest.mark.parametrize("hd,rot,ring,theta", [(16, 16, 0, 1e4), (48, 48, 128, 5e4), (256, 256, 64, 1e4), (32, 16, 0, 1e3), (64, 0, 0, 1.0)])
+@pytest.mark.parametrize("hd,rot,ring,theta", [(16, 16, 0, 1e4), (48, 48, 128, 5e4), (256, 256, 64, 1e4), (32, 16, 0, 1e3), (64, 0, 0, 1.0),
+                                               (640, 640, 0, 1e4), (576, 530, 64, 1e4)])     # more pairs than a CTA has threads for
 def test_rope_kv(ops, dt, hd, rot, ring, theta):
     nh, nkv = 3, 2
     lens_before, new = [0, 0, 0], [5, 150, 70]                      # a first step

@@ -152,6 +152,41 @@ def test_long_decoding_and_first_tokens(engines, plain_models, name, dtype):
     check(got, truth, dtype, f"{name} long decoding")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_second_batch_with_the_same_slots_and_page_counts_but_other_pages(model_folders, plain_models, name, dtype):
+    """Batch one: two prompts of 40 tokens that decode 30 more, so each sequence ends with two pages, taken
+    alternately ([0, 2] and [1, 3]).  Batch two, in the same slots: two prompts of 70 tokens, two pages each
+    again, but taken in a row ([0, 1] and [2, 3]).  Its first decode step has the batch size, the length bucket
+    and the page counts of batch one's last step; page tables kept from batch one would make sequence 0 read
+    and write sequence 1's page."""
+    import trapetum_b200 as tb
+    cfg, w = plain_models[name]
+    eng = tb.Engine(tb.load_model(model_folders[name], dtype), max_tokens=64 * 8)
+    for g in eng.cache.groups:
+        g.k.fill_(float("nan")); g.v.fill_(float("nan"))
+    first = make_prompts(cfg["vocab_size"], [70, 70], seed=41)
+    second = make_prompts(cfg["vocab_size"], [90, 90], seed=42)
+    pages = []
+    for reqs, cut in ((first, 40), (second, 70)):
+        truth = [plain.forward(cfg, w, p) for p in reqs]
+        slots = eng.start(2)
+        got = [[x] for x in eng.step(slots, [p[:cut] for p in reqs], [list(range(cut))] * 2).split(cut)]
+        for t in range(cut, len(reqs[0])):
+            out = eng.step(slots, [[p[t]] for p in reqs])
+            for i in range(2):
+                got[i].append(out[i:i + 1])
+            if t == cut:
+                pages.append([[list(eng.cache.pages(s, gi)) for gi in range(len(eng.cache.groups))] for s in slots])
+        pages.append([[len(eng.cache.pages(s, gi)) for gi in range(len(eng.cache.groups))] for s in slots])
+        eng.release(slots)
+        for i in range(2):
+            check(torch.cat(got[i]), truth[i], dtype, f"{name} batch with {cut}-token prompts, request {i}")
+    assert pages[1] == [[len(p) for p in seq] for seq in pages[2]]      # the counts repeat ...
+    assert any(len(g) > 1 for seq in pages[2] for g in seq)             # ... over more than one page ...
+    eng.cache.check()
+
+
 @pytest.mark.parametrize("name", NAMES)
 def test_runs_repeat_bit_for_bit(engines, requests_and_truth, name):
     eng = engines(name, "bfloat16")

@@ -111,11 +111,16 @@ class Cache:
             self.groups.append(g)
         self._len: Dict[int, int] = {}                         # slot -> tokens held
         self._pages: Dict[int, List[List[int]]] = {}           # slot -> per group page list
+        # Counts every change of who holds which slot or page.  A page table written for (slots, epoch) stays
+        # right exactly as long as neither changes: equal page COUNTS do not mean equal page NUMBERS once
+        # sequences have ended and others have started.
+        self.epoch = 0
 
     # -- sequences -------------------------------------------------------------
     def claim(self) -> int:
         """Take a slot for a new sequence (length 0, state zeroed)."""
         (slot,) = self.slots.take(1)
+        self.epoch += 1
         self._len[slot] = 0
         self._pages[slot] = [[] for _ in self.groups]
         for st in self.states.values():
@@ -152,8 +157,29 @@ class Cache:
                                 f"{held} tokens; the cache was sized for {self.max_tokens})")
         for slot, gi, add in want:
             self._pages[slot][gi].extend(self.groups[gi].pool.take(add))
+        if want:
+            self.epoch += 1
         for slot, n in growth.items():
             self._len[slot] += n
+
+    def shrink(self, growth: Dict[int, int]) -> None:
+        """Undo a :meth:`grow` whose step did not run: the lengths go back and the pages that only the
+        growth needed are returned.  Rows of the undone tokens may have been written; no reader reaches them
+        (every reader is bounded by the length), and in a ring the rows they replaced lay outside every later
+        query's window."""
+        for slot, n in growth.items():
+            self._held(slot)
+            if n < 0 or n > self._len[slot]:
+                raise CacheError(f"slot {slot}: cannot shrink {self._len[slot]} tokens by {n}")
+        for slot, n in growth.items():
+            self._len[slot] -= n
+            for gi, g in enumerate(self.groups):
+                keep = pages_for(g.rows_held(self._len[slot]))
+                extra = self._pages[slot][gi][keep:]
+                if extra:
+                    del self._pages[slot][gi][keep:]
+                    g.pool.give_back(extra)
+        self.epoch += 1
 
     def release(self, slot: int) -> None:
         self._held(slot)
@@ -161,6 +187,7 @@ class Cache:
             g.pool.give_back(self._pages[slot][gi])
         del self._pages[slot], self._len[slot]
         self.slots.give_back([slot])
+        self.epoch += 1
 
     def live_slots(self) -> List[int]:
         return sorted(self._len)

@@ -32,24 +32,7 @@ TB_EXPORT_ERROR()
 
 __device__ int g_attn_error = 0;
 
-struct DecodeArgs {
-    const void* q; long long q_stride;
-    const void* k_pool; const void* v_pool;
-    const int* page_table; int pt_stride;
-    const int* len_after;
-    void* out;
-    float* partial;
-    int n_heads, n_kv_heads, hd, page_rows, ring_rows, window, n_splits;
-    float scale, cap;
-    int* tickets;                 // [B, n_kv_heads] zeros, or null: with it the tensor-core kernel folds its
-                                  // splits itself (the last CTA to finish) and leaves the counters at zero
-    // Tensor-core kernel only.  If set, q is not read: the step's q, k and v rows are taken from these 32-bit
-    // partial sums of the q/k/v product ([qkv_splits][batch][row], columns q heads, k heads, v heads), added in
-    // split order, rotated (rotate-half pairing over the first rotary_dim dims; none if inv_freq is null) at
-    // position len_after - 1 and rounded to bfloat16; k and v are also written to their cache row.
-    const float* qkv_part; int qkv_splits; long long qkv_split_stride, qkv_row_stride;
-    const float* inv_freq; int rotary_dim;
-};
+#include "decode_args.h"
 
 template <int HD> struct DCfg {
     static constexpr int NWARP = HD >= 64 ? 16 : 8;                  // more warps hide more latency; a warp needs
@@ -1301,14 +1284,6 @@ extern "C" int tb_attn_decode_stream(const DecodeArgs* args, int dtype, int batc
     }
 }
 
-// Reads and clears the error word (1: a bounded wait on a page copy ran out).  Synchronises.
-extern "C" int tb_attn_decode_error() {
-    int v = 0, zero = 0;
-    if (cudaMemcpyFromSymbol(&v, g_attn_error, sizeof(int)) != cudaSuccess) return -1;
-    if (v) cudaMemcpyToSymbol(g_attn_error, &zero, sizeof(int));
-    return v;
-}
-
 // ---------------------------------------------------------------------------
 // An entry point that allocates nothing (declared in attention_decode_noalloc.h; it has no
 // counterpart in the reference).
@@ -1372,4 +1347,19 @@ extern "C" int tb_attn_decode_noalloc(const DecodeArgs* args, int dtype, int bat
     a.partial = need ? ptr : nullptr;
     a.tickets = (need && (long long)batch * a.n_kv_heads <= NOALLOC_MAX_TICKETS) ? tickets : nullptr;
     return tb_attn_decode(&a, dtype, batch, stream);
+}
+
+// Reads and clears the error word (1: a bounded wait on a page copy ran out).  Synchronises.  A launch that
+// gave up may have left its ticket counters half counted: the built-in counters of tb_attn_decode_noalloc are
+// zeroed again here (the caller of tb_attn_decode zeroes its own).
+extern "C" int tb_attn_decode_error() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_attn_error, sizeof(int)) != cudaSuccess) return -1;
+    if (v) {
+        cudaMemcpyToSymbol(g_attn_error, &zero, sizeof(int));
+        void* t = nullptr;
+        if (cudaGetSymbolAddress(&t, g_noalloc_tickets) == cudaSuccess && t != nullptr)
+            cudaMemset(t, 0, sizeof(int) * NOALLOC_MAX_TICKETS);
+    }
+    return v;
 }

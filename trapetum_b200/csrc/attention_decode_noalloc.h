@@ -10,6 +10,7 @@
  *
  *   int tb_attn_decode_noalloc(const DecodeArgs* args, int dtype, int batch, cudaStream_t stream);
  *
+ * The argument block is defined in decode_args.h, which this header includes, so a C caller can fill it.
  * Same arguments, same result and same return convention as tb_attn_decode (0 = launched,
  * > 0 = a cudaError_t, < 0 = refused, tb_error() tells why).  `args->partial` is ignored.  The
  * caller still owns the query, the cache pools, the page table, the lengths and the output.
@@ -32,6 +33,7 @@
 #define TB_ATTENTION_DECODE_NOALLOC_H
 
 #include <cuda_runtime_api.h>
+#include "decode_args.h"         /* the argument block, with a comment on every field */
 
 #define TB_ATTN_DECODE_NOALLOC_MAX_FLOATS (1024 * 1024)
 
@@ -39,8 +41,7 @@
 extern "C" {
 #endif
 
-struct DecodeArgs;
-int tb_attn_decode_noalloc(const struct DecodeArgs* args, int dtype, int batch, cudaStream_t stream);
+int tb_attn_decode_noalloc(const DecodeArgs* args, int dtype, int batch, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

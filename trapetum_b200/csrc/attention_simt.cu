@@ -119,19 +119,7 @@ __global__ void attn_prefill_simt_kernel(const T* __restrict__ q, const T* __res
 // ---------------------------------------------------------------------------
 // Decode: one query per sequence, keys from the paged cache.
 // ---------------------------------------------------------------------------
-struct DecodeArgs {
-    const void* q; long long q_stride;          // [B] rows, heads contiguous
-    const void* k_pool; const void* v_pool;     // [n_pages][n_kv][page_rows][hd]
-    const int* page_table; int pt_stride;
-    const int* len_after;                       // [B] keys in cache, the new token included
-    void* out;                                  // [B, n_heads*hd] (when n_splits == 1)
-    float* partial;                             // [B, n_heads, n_splits, hd + 2] (when n_splits > 1)
-    int n_heads, n_kv_heads, hd, page_rows, ring_rows, window, n_splits;
-    float scale, cap;
-    int* tickets;                               // used by the tensor-core kernel only; ignored here
-    const float* qkv_part; int qkv_splits; long long qkv_split_stride, qkv_row_stride;   // likewise
-    const float* inv_freq; int rotary_dim;
-};
+#include "decode_args.h"
 
 template <typename T, int NC>
 __global__ void attn_decode_simt_kernel(DecodeArgs a) {

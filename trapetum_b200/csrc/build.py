@@ -97,7 +97,7 @@ def _digest(name: str) -> str:
     name, defines, _ = _split(name)
     h = hashlib.sha256()
     h.update(" ".join(defines).encode())
-    headers = sorted(fn for fn in os.listdir(_HERE) if fn.endswith(".cuh"))
+    headers = sorted(fn for fn in os.listdir(_HERE) if fn.endswith((".cuh", ".h")))
     for fn in [name + ".cu"] + headers:
         with open(os.path.join(_HERE, fn), "rb") as f:
             h.update(f.read())

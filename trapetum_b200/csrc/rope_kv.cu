@@ -100,14 +100,20 @@ __global__ void rope_kv_kernel(RopeKvArgs a) {
         if (!is_q && store)
             dst = (T*)(is_k ? a.k_pool : a.v_pool) + cache_off + (size_t)kvh * a.page_rows * hd;
         if ((is_q || is_k) && rotate) {
+            // the thread's first two pairs use the sines and cosines made above; a head with more pairs than
+            // the CTA has threads for (rotary_dim > 4 * blockDim.x) goes round again and makes its own
+            for (int ib = i0; ib < half; ib += blockDim.x * 2) {
 #pragma unroll
-            for (int e = 0; e < 2; e++) {
-                const int i = i0 + e;
-                if (i < half) {
-                    const float x0 = val(col0 + i), x1 = val(col0 + i + half);
-                    const T y0 = from_f<T>(x0 * cs[e] - x1 * sn[e]), y1 = from_f<T>(x1 * cs[e] + x0 * sn[e]);
-                    x[i] = y0; x[i + half] = y1;
-                    if (dst) { dst[i] = y0; dst[i + half] = y1; }
+                for (int e = 0; e < 2; e++) {
+                    const int i = ib + e;
+                    if (i < half) {
+                        float sne = sn[e], cse = cs[e];
+                        if (ib != i0) sincosf((float)pos * a.inv_freq[i], &sne, &cse);
+                        const float x0 = val(col0 + i), x1 = val(col0 + i + half);
+                        const T y0 = from_f<T>(x0 * cse - x1 * sne), y1 = from_f<T>(x1 * cse + x0 * sne);
+                        x[i] = y0; x[i + half] = y1;
+                        if (dst) { dst[i] = y0; dst[i + half] = y1; }
+                    }
                 }
             }
             // dims beyond the rotary part pass through

@@ -111,8 +111,30 @@ class Engine:
                     raise StepError(f"sequence {i}: wanted place {j} is outside its {lens[i]} tokens of this step")
 
         before = [self.cache.length(s) for s in slots]
-        self.cache.grow({s: n for s, n in zip(slots, lens)})          # raises CacheFull before anything ran
         after = [b + n for b, n in zip(before, lens)]
+        cap = self.model.spec.max_positions
+        for i, n in enumerate(after):
+            if n > cap:
+                raise StepError(f"sequence {i}: {n} tokens after this step, the model has {cap} positions")
+        growth = {s: n for s, n in zip(slots, lens)}
+        self.cache.grow(growth)                                       # raises CacheFull before anything ran
+        try:
+            return self._run(slots, tokens, want, is_prefill, lens, before, after, borrow, greedy)
+        except BaseException:
+            # the step did not run to its end: the cache must not claim tokens whose keys were never written
+            self.cache.shrink(growth)
+            raise
+
+    def check_kernels(self) -> None:
+        """Raise :class:`~trapetum_b200.csrc.ops.KernelError` if a kernel's bounded wait has run out since
+        the last check (its results are then garbage).  Synchronises the device, so callers place it where they
+        wait for the device anyway: the generation loop at the end of a batch, trace replay after a step."""
+        err = ops.kernel_errors()
+        if err:
+            raise ops.KernelError(f"a kernel gave up waiting and its results are not valid: {err}")
+
+    def _run(self, slots, tokens, want, is_prefill, lens, before, after, borrow, greedy):
+        B = len(slots)
         if not is_prefill and self.use_graphs and self._graph_safe:
             return self._decode_step(slots, tokens, want, before, after, borrow, greedy)
 
@@ -209,7 +231,7 @@ class _DecodeShape:
         self.logits = None
         self.greedy = None
         self.hits = 0
-        self._tables_of = None                # (slots, page counts) the device tables were last written for
+        self._tables_of = None                # (slots, cache epoch) the device tables were last written for
         self.n_kernels = 0
         cache = engine.cache
         cap = min(engine.model.spec.max_positions, cache.max_tokens)
@@ -239,9 +261,11 @@ class _DecodeShape:
         hv["positions"][:] = before
         hv["len_after"][:] = after
         hv["slot_ids"][:] = slots
-        # the page tables change only when the batch's slots change or a sequence takes a new page
+        # The page tables change only when the batch's slots change or when any slot or page of the cache
+        # changes hands (the cache counts those events): two batches may hold the same slots with the same
+        # numbers of pages and yet other pages.
         cache = engine.cache
-        key = (tuple(slots), tuple(len(cache.pages(s, gi)) for gi in range(len(self.widths)) for s in slots))
+        key = (tuple(slots), cache.epoch)
         if key != self._tables_of:
             self._tables_of = key
             for gi, w in enumerate(self.widths):

@@ -21,6 +21,9 @@ from .engine import Engine
 from .model import Model
 
 
+CHECK_EVERY = 64          # decode steps between two looks at the kernels' error words (and at a batch's end)
+
+
 def plan_batches(prompt_lens: Sequence[int], max_new: int, max_batch: int, max_tokens: int,
                  max_positions: int) -> List[List[int]]:
     """Cut requests, in order, into batches: at most ``max_batch`` sequences, and room in the cache
@@ -105,6 +108,7 @@ def generate(model_or_engine, prompts: Sequence[Sequence[int]], max_tokens: int 
     for batch in batches:
         slots = engine.start(len(batch))
         live = [_Seq(r, s, 0) for r, s in zip(batch, slots)]
+        steps = 0
         try:
             for q in live:
                 sampler.begin(q.request, prompts[q.request])
@@ -131,6 +135,11 @@ def generate(model_or_engine, prompts: Sequence[Sequence[int]], max_tokens: int 
                     logits = engine.step([q.slot for q in live], [[q.new[-1]] for q in live], borrow=True, greedy=greedy)
                     for q in live:
                         q.length += 1
+                steps += 1
+                if not live or steps % CHECK_EVERY == 0:
+                    # the chosen tokens were just read on the host, so the device is idle anyway: a kernel whose
+                    # bounded wait ran out must not pass its garbage on as tokens
+                    engine.check_kernels()
         except BaseException:
             for q in live:
                 if engine.cache.slots.is_held(q.slot):

@@ -36,6 +36,7 @@ class Replayer:
                                    [e.get("want", []) for e in entries])
             if out is not None:
                 logits = out.float().cpu().numpy()
+            self.engine.check_kernels()          # logits of a kernel that gave up waiting must not be written
         for i in rec.get("end", []):
             i = str(i)
             if i not in self.slot_of:
