@@ -1,17 +1,22 @@
 #!/usr/bin/env python3
-"""Benchmark: decode tokens per second of a Gemma-2-2B-shaped model with random weights.
+"""Benchmark: decode tokens per second of Gemma-2-shaped models with random weights.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 8192] [--layers L]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--model 2b|9b|27b] [--batch 8] [--context 8192] [--layers L]
     python bench.py --impl reference ...        # the reference arm: not installable here
 
 A step is one decode step: one new token for each of ``batch`` sequences whose caches hold about
 ``context`` tokens.  Prints ONE JSON line.  ``value`` is timed on the device with CUDA events around
-K steps; ``e2e`` runs the same steps through the public Python API with host token lists in and host
-token ids out (a pinned host-to-device copy of the step's inputs and a device-to-host read of the
-chosen tokens every step).  ``prefill`` times one 2,048-token prompt; ``roofline`` sets the bytes a
-decode step has to read (every weight once, the live requests' cache) against its time; ``points``
-repeats the decode measurement at batch 1 and 64.  Peaks come from MEASURED_PEAKS.json beside this
-file when the driver wrote it, otherwise from the fallback figures (6.65 TB/s, 1.59 PFLOP/s).
+K steps, as the median of five such regions (``spread`` gives the least and the most, and each region's
+median SM clock); ``e2e`` runs the same steps through the public Python API with host token lists in and
+host token ids out (a pinned host-to-device copy of the step's inputs and a device-to-host read of the
+chosen tokens every step).  ``prefill`` times one 2,048-token prompt; ``roofline`` sets the bytes a decode
+step has to read (every weight once, the live requests' cache) against its time; ``points`` repeats the
+decode measurement at batch 1 and 64; ``runs`` holds the other measurements that the three model shapes
+are quoted on (caches of 2,048 tokens, the 9B shape's unequal batch of 8, the 27B shape from 2,048-token
+prompts, each shape's prefill), every one with its bytes or FLOPs, its time and its fraction of the peak.
+Weights are made on the device by the counter-based generator (``tb.random_model``).  Peaks come from
+MEASURED_PEAKS.json beside this file when the driver wrote it, otherwise from the fallback figures
+(6.65 TB/s, 1.59 PFLOP/s).
 
 This library runs on one GPU: for --gpus > 1 it says so and exits with 2.
 """
@@ -26,16 +31,21 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# Layer sizes of Gemma-2-2B; weights are random (seed 2).
-GEMMA2_2B = {
-    "architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2",
-    "num_hidden_layers": 26, "hidden_size": 2304, "num_attention_heads": 8, "num_key_value_heads": 4,
-    "head_dim": 256, "intermediate_size": 9216, "vocab_size": 256000, "rope_theta": 10000.0,
-    "sliding_window": 4096, "query_pre_attn_scalar": 256, "attn_logit_softcapping": 50.0,
-    "final_logit_softcapping": 30.0, "rms_norm_eps": 1e-6, "hidden_activation": "gelu_pytorch_tanh",
-    "tie_word_embeddings": True, "max_position_embeddings": 8192,
-}
+def _shape(L, H, nh, nkv, hd, I, qpas):
+    return {"architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2", "num_hidden_layers": L, "hidden_size": H,
+            "num_attention_heads": nh, "num_key_value_heads": nkv, "head_dim": hd, "intermediate_size": I,
+            "vocab_size": 256000, "rope_theta": 10000.0, "sliding_window": 4096, "query_pre_attn_scalar": qpas,
+            "attn_logit_softcapping": 50.0, "final_logit_softcapping": 30.0, "rms_norm_eps": 1e-6,
+            "hidden_activation": "gelu_pytorch_tanh", "tie_word_embeddings": True, "max_position_embeddings": 8192}
+
+
+# Layer sizes of Gemma-2-2B, -9B and -27B; weights are random (seeds 2, 3, 4).
+MODELS = {"2b": _shape(26, 2304, 8, 4, 256, 9216, 256), "9b": _shape(42, 3584, 16, 8, 256, 14336, 256),
+          "27b": _shape(46, 4608, 32, 16, 128, 36864, 144)}
+SEEDS = {"2b": 2, "9b": 3, "27b": 4}
+GEMMA2_2B = MODELS["2b"]
 PREFILL_TOKENS = 2048
+REPEATS = 5              # timed regions per measurement; the median is reported
 
 
 def peaks():
@@ -55,7 +65,7 @@ class ClockSampler:
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self):
-        self.rows, self._stop, self._t = [], threading.Event(), None
+        self.rows, self.stamps, self._stop, self._t = [], [], threading.Event(), None
 
     def _run_nvml(self) -> bool:
         """Reads the same values through NVML every 5 ms (an nvidia-smi call takes longer than a short timed
@@ -74,6 +84,7 @@ class ClockSampler:
             try:
                 mhz, mask = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM), int(reasons(h))
                 self.rows.append([str(mhz), str(top)] + ["Active" if mask & b else "Not Active" for b in bits])
+                self.stamps.append(time.perf_counter())
             except Exception:
                 pass
             self._stop.wait(0.005)
@@ -88,6 +99,7 @@ class ClockSampler:
                                      capture_output=True, text=True, timeout=5).stdout.strip().splitlines()
                 if out:
                     self.rows.append([x.strip() for x in out[0].split(",")])
+                    self.stamps.append(time.perf_counter())
             except Exception:
                 pass
             self._stop.wait(0.2)
@@ -101,6 +113,11 @@ class ClockSampler:
         self._stop.set()
         self._t.join(timeout=6)
 
+    def mhz_between(self, t0, t1):
+        """Median SM clock of the samples taken between two host times (None if there is none)."""
+        m = sorted(int(r[0]) for r, t in zip(self.rows, self.stamps) if t0 <= t <= t1 and r[0].isdigit())
+        return m[len(m) // 2] if m else None
+
     def summary(self):
         if not self.rows:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi gave no samples"]}
@@ -113,20 +130,8 @@ class ClockSampler:
 
 
 def build_model(cfg, seed):
-    import torch
-
     import trapetum_b200 as tb
-    from trapetum_b200.config import load_config
-    from trapetum_b200.csrc import build
-    from trapetum_b200.engine.model import Model
-    from trapetum_b200.parts import Runtime
-    from trapetum_b200.weights.loader import random_tensors
-    _, spec = load_config(cfg)
-    model = Model(spec, Runtime(torch.bfloat16, torch.device("cuda:0")))
-    build.require(model.kernel_files())
-    tensors = dict(random_tensors(model.tensor_specs(), seed, 0.02, 0.1, device="cuda:0"))
-    model.bind(tensors)
-    return model
+    return tb.random_model(cfg, seed, 0.02, 0.1, "bfloat16", "cuda:0")
 
 
 def weight_bytes(cfg):
@@ -147,80 +152,171 @@ def cache_bytes(cfg, ctx):
     return total
 
 
-def prefill_flops(cfg, T):
+def prefill_flops(cfg, lens):
+    """FLOPs of one step that brings whole prompts of these lengths (the head runs on each last position)."""
+    if isinstance(lens, int):
+        lens = [lens]
     H, I, V, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"], cfg["num_hidden_layers"]
     qd, kvd = cfg["num_attention_heads"] * cfg["head_dim"], cfg["num_key_value_heads"] * cfg["head_dim"]
-    lin = 2 * T * ((qd + 2 * kvd) * H + H * qd + 2 * I * H + H * I)
+    lin = 2 * sum(lens) * ((qd + 2 * kvd) * H + H * qd + 2 * I * H + H * I)
     W = cfg["sliding_window"]
     att = 0
     for i in range(L):
-        pairs = sum(min(t + 1, W) if i % 2 == 0 else t + 1 for t in range(T))
-        att += 4 * qd * pairs
-    return L * lin + att + 2 * V * H               # the head runs on the last position only
+        for T in lens:
+            if i % 2 == 0 and T > W:
+                pairs = W * (W + 1) // 2 + (T - W) * W
+            else:
+                pairs = T * (T + 1) // 2
+            att += 4 * qd * pairs
+    return L * lin + att + 2 * V * H * len(lens)
 
 
-def fill_cache(engine, n, ctx):
-    """``n`` sequences whose caches hold ``ctx`` tokens of random keys and values (no prefill is run:
+def fill_cache(engine, lens):
+    """Sequences whose caches hold ``lens`` tokens of random keys and values (no prefill is run:
     the decode step's work does not depend on what the keys are)."""
-    slots = engine.start(n)
-    engine.cache.grow({s: ctx for s in slots})
+    slots = engine.start(len(lens))
+    engine.cache.grow({s: n for s, n in zip(slots, lens)})
     return slots
 
 
-def time_decode(engine, torch, batch, ctx, steps, warmup, vocab, sampler=None):
-    """(ms per step on the device, ms per step end to end, launches per step, h2d bytes per step)."""
+def time_decode(engine, torch, ctxs, steps, warmup, vocab, repeats=REPEATS, e2e=False, clocks=None):
+    """Decode steps of a batch whose caches hold about ``ctxs`` tokens (one number per sequence; they end the
+    measurement at these lengths).  ``repeats`` regions of ``steps`` steps each are timed with CUDA events.
+    Returns a dict: ms (median per step), ms_min, ms_max, regions [{ms, sm_mhz}], mean_ctx (per sequence, over
+    the timed steps), launches (per step), and with ``e2e`` also e2e_ms and h2d."""
     from trapetum_b200.csrc import ops
+    batch = len(ctxs)
     g = torch.Generator().manual_seed(batch)
-    slots = fill_cache(engine, batch, ctx - (warmup + steps) * 2 - 4)
+    total = warmup + repeats * steps + (2 * warmup + steps if e2e else 0)
+    start = [max(1, c - total) for c in ctxs]
+    slots = fill_cache(engine, start)
+    out = {}
     try:
-        toks = torch.randint(0, vocab, (2 * (warmup + steps) + 4, batch), generator=g).tolist()
+        toks = torch.randint(0, vocab, (total + 2, batch), generator=g).tolist()
         it = iter(toks)
         for _ in range(warmup):
             engine.step(slots, [[t] for t in next(it)], borrow=True)
         torch.cuda.synchronize()
+        regions, done = [], warmup
         n0 = ops.launches()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            engine.step(slots, [[t] for t in next(it)], borrow=True)
-        e1.record()
-        torch.cuda.synchronize()
-        dev_ms = e0.elapsed_time(e1) / steps
-        launches = (ops.launches() - n0) // steps
-        # end to end: host token lists in, chosen token ids out, each step feeding the next
-        cur = next(it)
-        for _ in range(warmup):
-            cur = engine.step(slots, [[t] for t in cur], borrow=True, greedy=True).cpu().tolist()
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        for _ in range(steps):
-            cur = engine.step(slots, [[t] for t in cur], borrow=True, greedy=True).cpu().tolist()
-        torch.cuda.synchronize()
-        e2e_ms = (time.perf_counter() - t0) * 1e3 / steps
-        shape = next((d for key, d in engine._decode.items() if key[0] == batch), None)
-        h2d = shape.h2d_bytes if shape is not None else 0
-        return dev_ms, e2e_ms, launches, h2d
+        for _ in range(repeats):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            e0.record()
+            for _ in range(steps):
+                engine.step(slots, [[t] for t in next(it)], borrow=True)
+            e1.record()
+            torch.cuda.synchronize()
+            t1 = time.perf_counter()
+            regions.append({"ms": round(e0.elapsed_time(e1) / steps, 4),
+                            "sm_mhz": clocks.mhz_between(t0, t1) if clocks is not None else None})
+        out["launches"] = (ops.launches() - n0) // (repeats * steps)
+        ms = sorted(r["ms"] for r in regions)
+        out.update(ms=ms[len(ms) // 2], ms_min=ms[0], ms_max=ms[-1], regions=regions)
+        # the context each timed step reads: the tokens before it, and its own
+        first = [s0 + warmup + 1 for s0 in start]
+        out["mean_ctx"] = [f + (repeats * steps - 1) / 2.0 for f in first]
+        if e2e:
+            # end to end: host token lists in, chosen token ids out, each step feeding the next
+            cur = next(it)
+            for _ in range(warmup):
+                cur = engine.step(slots, [[t] for t in cur], borrow=True, greedy=True).cpu().tolist()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(steps):
+                cur = engine.step(slots, [[t] for t in cur], borrow=True, greedy=True).cpu().tolist()
+            torch.cuda.synchronize()
+            out["e2e_ms"] = (time.perf_counter() - t0) * 1e3 / steps
+            shape = next((d for key, d in engine._decode.items() if key[0] == batch), None)
+            out["h2d"] = shape.h2d_bytes if shape is not None else 0
+        return out
     finally:
         engine.release(slots)
 
 
-def time_prefill(engine, torch, T, vocab, reps, warmup):
+def decode_record(cfg, r, hbm_gbs):
+    """What a decode measurement says against the memory roofline."""
+    nbytes = weight_bytes(cfg) + sum(cache_bytes(cfg, int(round(c))) for c in r["mean_ctx"])
+    gbs = nbytes / (r["ms"] * 1e-3) / 1e9
+    return {"value": round(len(r["mean_ctx"]) * 1e3 / r["ms"], 1), "unit": "tokens/s", "ms": r["ms"],
+            "ms_min": r["ms_min"], "ms_max": r["ms_max"], "bytes": nbytes, "gbs": round(gbs, 1),
+            "frac": round(gbs / hbm_gbs, 4)}
+
+
+def time_prefill(engine, torch, lens, vocab, reps, warmup):
+    """One step that brings whole prompts of ``lens`` tokens: (median ms on the device, median ms of host time
+    to issue the step, median ms from the call to the logits' arrival on the host)."""
+    if isinstance(lens, int):
+        lens = [lens]
     g = torch.Generator().manual_seed(7)
-    prompt = torch.randint(0, vocab, (T,), generator=g).tolist()
-    times = []
+    prompts = [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lens]
+    dev, host, whole = [], [], []
     for i in range(warmup + reps):
-        s = engine.start(1)
+        s = engine.start(len(lens))
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
         e0.record()
-        engine.step(s, [prompt], borrow=True)
+        logits = engine.step(s, prompts, borrow=True)
         e1.record()
+        t1 = time.perf_counter()
+        logits[:, :8].cpu()
+        t2 = time.perf_counter()
         torch.cuda.synchronize()
         engine.release(s)
         if i >= warmup:
-            times.append(e0.elapsed_time(e1))
-    times.sort()
-    return times[len(times) // 2]
+            dev.append(e0.elapsed_time(e1)); host.append((t1 - t0) * 1e3); whole.append((t2 - t0) * 1e3)
+    med = lambda v: sorted(v)[len(v) // 2]
+    return med(dev), med(host), med(whole)
+
+
+def prefill_record(cfg, lens, ms, host_ms, e2e_ms, bf16_tflops):
+    lens = [lens] if isinstance(lens, int) else lens
+    fl = prefill_flops(cfg, lens)
+    return {"value": round(sum(lens) * 1e3 / ms, 1), "unit": "tokens/s", "tokens": sum(lens), "ms": round(ms, 3),
+            "host_ms": round(host_ms, 3), "e2e_ms": round(e2e_ms, 3), "flops": fl,
+            "frac": round(fl / (ms * 1e-3) / (bf16_tflops * 1e12), 4)}
+
+
+def random_cache(engine):
+    for g in engine.cache.groups:                         # random keys and values, small enough for a sane softmax
+        g.k.normal_(0.0, 0.5)
+        g.v.normal_(0.0, 0.5)
+
+
+def other_runs(torch, which, steps, warmup, hbm_gbs, bf16_tflops, have=None):
+    """The measurements beside the headline: per model shape, decode at batch 1/8/64 with caches of 2,048 tokens
+    (the 9B shape: its unequal batch of 8, prompts U[64, 2048], decode and the prompts' own step), and a
+    2,048-token prompt.  ``have``: (name, model) already built.  Models are built and freed one after another."""
+    from trapetum_b200.engine import Engine
+    runs = {}
+    for name in which:
+        cfg = MODELS[name]
+        V = cfg["vocab_size"]
+        model = have[1] if have and have[0] == name else build_model(cfg, SEEDS[name])
+        engine = Engine(model, max_tokens=64 * 2112, max_slots=64)
+        random_cache(engine)
+        st = max(8, steps // 2)
+        for b in (1, 8, 64):
+            r = time_decode(engine, torch, [2048] * b, st, warmup, V, repeats=3)
+            runs[f"{name}_decode_b{b}_ctx2048"] = decode_record(cfg, r, hbm_gbs)
+        if name == "9b":
+            lens = torch.randint(64, 2049, (8,), generator=torch.Generator().manual_seed(3)).tolist()
+            r = time_decode(engine, torch, lens, st, warmup, V, repeats=3)
+            rec = decode_record(cfg, r, hbm_gbs)
+            rec["prompt_lens"] = " ".join(map(str, lens))
+            runs["9b_decode_unequal_b8"] = rec
+            runs["9b_prefill_unequal_b8"] = prefill_record(cfg, lens, *time_prefill(engine, torch, lens, V, 3, 3), bf16_tflops)
+        if name != "2b":
+            runs[f"{name}_prefill_{PREFILL_TOKENS}"] = prefill_record(
+                cfg, PREFILL_TOKENS, *time_prefill(engine, torch, PREFILL_TOKENS, V, 3, 3), bf16_tflops)
+        del engine, model
+        have = None
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+    return runs
 
 
 def leave_out_report(engine, model, cfg, torch, args, warmup) -> int:
@@ -268,7 +364,8 @@ def leave_out_report(engine, model, cfg, torch, args, warmup) -> int:
             for k, v in patch.items():
                 setattr(ops, k, v)
             eng = Engine(model, max_tokens=args.batch * args.context, max_slots=args.batch)
-            ms, _, launches, _ = time_decode(eng, torch, args.batch, args.context, args.steps, warmup, V)
+            r = time_decode(eng, torch, [args.context] * args.batch, args.steps, warmup, V, repeats=1)
+            ms, launches = r["ms"], r["launches"]
             whole = ms if whole is None else whole
             print(json.dumps({"left_out": name, "ms_per_step": round(ms, 4), "launches": launches,
                               "saves_us": round((whole - ms) * 1e3, 1),
@@ -283,14 +380,18 @@ def leave_out_report(engine, model, cfg, torch, args, warmup) -> int:
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="2b", choices=sorted(MODELS), help="the headline's model shape")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
-    ap.add_argument("--layers", type=int, default=GEMMA2_2B["num_hidden_layers"],
+    ap.add_argument("--layers", type=int, default=None,
                     help="fewer layers than the model has (same layer sizes); both numbers are reported")
-    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points, the prefill and the other runs")
+    ap.add_argument("--runs", default="2b,9b,27b",
+                    help="model shapes whose other measurements (caches of 2,048 tokens, prefill) are taken: a comma "
+                         "list out of 2b, 9b, 27b, or 'none'")
     ap.add_argument("--prefill-only", action="store_true",
                     help="instead of the bench line: time only the prompt of 2,048 tokens and print one line about it")
     ap.add_argument("--leave-out", action="store_true",
@@ -311,60 +412,84 @@ def main() -> int:
 
     import torch
     from trapetum_b200.engine import Engine
-    cfg = dict(GEMMA2_2B, num_hidden_layers=args.layers)
+    full = MODELS[args.model]
+    args.layers = args.layers or full["num_hidden_layers"]
+    cfg = dict(full, num_hidden_layers=args.layers)
     hbm_gbs, bf16_tflops, peak_src = peaks()
-    model = build_model(cfg, seed=2)
+    model = build_model(cfg, SEEDS[args.model])
     V = cfg["vocab_size"]
     max_batch = args.batch if args.no_points else max(args.batch, 64)
-    engine = Engine(model, max_tokens=max_batch * args.context, max_slots=max_batch)
-    for g in engine.cache.groups:                         # random keys and values, small enough for a sane softmax
-        g.k.normal_(0.0, 0.5)
-        g.v.normal_(0.0, 0.5)
+    if args.model == "27b":
+        max_batch = min(max_batch, 16)                    # 27B weights and 64 caches of 8,192 tokens do not fit
+    engine = Engine(model, max_tokens=max_batch * args.context, max_slots=max(max_batch, args.batch))
+    random_cache(engine)
 
     if args.leave_out:
         return leave_out_report(engine, model, cfg, torch, args, warmup)
     if args.prefill_only:
-        pms = time_prefill(engine, torch, PREFILL_TOKENS, V, reps=max(1, args.steps), warmup=warmup)
-        print(json.dumps({"prefill_ms": round(pms, 3), "tokens": PREFILL_TOKENS, "layers": args.layers,
+        pms, hms, wms = time_prefill(engine, torch, PREFILL_TOKENS, V, reps=max(1, args.steps), warmup=warmup)
+        print(json.dumps({"prefill_ms": round(pms, 3), "host_ms": round(hms, 3), "e2e_ms": round(wms, 3),
+                          "tokens": PREFILL_TOKENS, "layers": args.layers,
                           "frac": round(prefill_flops(cfg, PREFILL_TOKENS) / (pms * 1e-3) / (bf16_tflops * 1e12), 4),
                           "of": peak_src}))
         return 0
 
     with ClockSampler() as clocks:
-        dev_ms, e2e_ms, launches, h2d = time_decode(engine, torch, args.batch, args.context, args.steps, warmup, V)
-    value = args.batch * 1e3 / dev_ms
-    step_bytes = weight_bytes(cfg) + args.batch * cache_bytes(cfg, args.context - args.steps)
-    achieved = step_bytes / (dev_ms * 1e-3) / 1e9
+        r = time_decode(engine, torch, [args.context] * args.batch, args.steps, warmup, V, e2e=True, clocks=clocks)
+    dev_ms, e2e_ms = r["ms"], r["e2e_ms"]
+    rec = decode_record(cfg, r, hbm_gbs)
+    csum = clocks.summary()
+    mhz = csum.get("sm_mhz")
 
     out = {
-        "metric": "decode tok/s at batch %d (Gemma-2-2B)" % args.batch,
-        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+        "metric": "decode tok/s at batch %d (Gemma-2-%s)" % (args.batch, args.model.upper()),
+        "value": rec["value"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
         "ms_per_step": round(dev_ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic (random weights seed 2, uniform token ids, random cache contents)",
-        "config": {"model": "gemma-2-2b-shape", "global_batch": args.batch, "seq_len": args.context,
-                   "parallelism": "1 gpu", "layers": args.layers, "layers_of_model": GEMMA2_2B["num_hidden_layers"],
+        "dtype": "bf16", "data": "synthetic (random weights seed %d made on the device, uniform token ids, random "
+                                 "cache contents)" % SEEDS[args.model],
+        "config": {"model": "gemma-2-%s-shape" % args.model, "global_batch": args.batch, "seq_len": args.context,
+                   "parallelism": "1 gpu", "layers": args.layers, "layers_of_model": full["num_hidden_layers"],
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": V, "window": cfg["sliding_window"],
                    "prefill_tokens": PREFILL_TOKENS, "l2": "inputs larger than L2 (each step reads every weight)",
-                   "peaks": peak_src},
-        "clocks": clocks.summary(),
+                   "timed": "median of %d regions of %d steps" % (REPEATS, args.steps), "peaks": peak_src},
+        "clocks": csum,
+        "spread": {"ms_min": r["ms_min"], "ms_max": r["ms_max"], "regions": r["regions"],
+                   "ms_x_ghz": round(dev_ms * mhz / 1e3, 4) if mhz else None},
         "e2e": {"value": round(args.batch * 1e3 / e2e_ms, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch},
-        "gpu_launches": launches * args.steps,
-        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_gbs, "unit": "GB/s",
-                     "frac": round(achieved / hbm_gbs, 4), "of": peak_src, "bytes_per_step": step_bytes},
+                "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": 4 * args.batch},
+        "gpu_launches": r["launches"] * args.steps,
+        "roofline": {"bound": "hbm", "achieved": rec["gbs"], "peak": hbm_gbs, "unit": "GB/s",
+                     "frac": rec["frac"], "of": peak_src, "bytes_per_step": rec["bytes"]},
     }
     if not args.no_points:
-        pts = {}
+        pts, runs = {}, {}
         for b in (1, 64):
-            ms, _, _, _ = time_decode(engine, torch, b, args.context, max(8, args.steps // 2), warmup, V)
-            pts[f"decode_b{b}"] = round(b * 1e3 / ms, 1)
+            if b > engine.cache.max_slots:
+                continue
+            rb = time_decode(engine, torch, [args.context] * b, max(8, args.steps // 2), warmup, V, repeats=3, e2e=(b == 1))
+            rr = decode_record(cfg, rb, hbm_gbs)
+            pts[f"decode_b{b}"] = rr["value"]
+            if b == 1:
+                pts["e2e_b1"] = round(1e3 / rb["e2e_ms"], 1)
+            runs[f"{args.model}_decode_b{b}_ctx{args.context}"] = rr
+        pms, hms, wms = time_prefill(engine, torch, PREFILL_TOKENS, V, reps=5, warmup=3)
+        prec = prefill_record(cfg, PREFILL_TOKENS, pms, hms, wms, bf16_tflops)
+        out["prefill"] = dict(prec, of=peak_src)
         out["points"] = pts
-        pms = time_prefill(engine, torch, PREFILL_TOKENS, V, reps=5, warmup=3)
-        fl = prefill_flops(cfg, PREFILL_TOKENS)
-        out["prefill"] = {"value": round(PREFILL_TOKENS * 1e3 / pms, 1), "tokens": PREFILL_TOKENS, "ms": round(pms, 3),
-                          "frac": round(fl / (pms * 1e-3) / (bf16_tflops * 1e12), 4), "of": peak_src}
+        which = [] if args.runs == "none" else [w for w in args.runs.split(",") if w in MODELS]
+        if args.layers != full["num_hidden_layers"]:
+            which = []                                  # the other runs are of whole models
+        del engine
+        torch.cuda.empty_cache()
+        have = (args.model, model)
+        del model
+        runs.update(other_runs(torch, which, args.steps, warmup, hbm_gbs, bf16_tflops, have))
+        for k, v in runs.items():
+            if "decode" in k:
+                pts.setdefault(k, v["value"])
+        out["runs"] = runs
     from trapetum_b200.csrc import ops
     err = ops.kernel_errors()
     if err:

@@ -11,7 +11,7 @@ loop, sampling, trace replay, and hand-written CUDA kernels underneath.
 """
 from . import models  # noqa: F401  (registers the architectures)
 from .config import ConfigError, load_config, register_architecture
-from .engine import Engine, Model, load_model
+from .engine import Engine, Model, load_model, random_model
 from .parts import register_part
 from .weights import WeightError, write_random_model
 
@@ -24,4 +24,4 @@ def generate(*args, **kwargs):
 
 
 __all__ = ["ConfigError", "Engine", "Model", "WeightError", "generate", "load_config", "load_model",
-           "register_architecture", "register_part", "write_random_model"]
+           "random_model", "register_architecture", "register_part", "write_random_model"]

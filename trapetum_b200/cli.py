@@ -2,13 +2,16 @@
 
     gemma_run <model_dir> <prompt.bin> [<prompt.bin> ...] [options]
     gemma_run --random-weights <config.json> --seed S --out <model_dir>
+    gemma_run --random-weights <config.json> --seed S <prompt.bin> [...] [options]
 
 In the manner of the reference's ``gemma_run <model.cbk> <prompt.bin>``
 (runtime/src/bin/gemma_run.rs:2-18): positional model and prompt, the prompt a file
 of little-endian int32 token ids as its exporter writes it (model/export_gemma.py:77-78),
 greedy continuation of 24 tokens by default, and the same three lines of output
 (load time and prompt, continuation ids, ms/token and tok/s).  Several prompt
-files run as one batch.  The sampling options carry the names of the reference
+files run as one batch.  ``--random-weights`` with ``--out`` writes a model folder; without
+``--out`` the model of that configuration and seed is made on the device (the same values, no
+folder) and the prompts run on it.  The sampling options carry the names of the reference
 server's request fields (runtime/src/bin/serve.rs:1284-1292): ``--max_tokens``,
 ``--temperature``, ``--top_p``, ``--repetition_penalty``.
 """
@@ -44,22 +47,24 @@ def main(argv=None) -> int:
     ap.add_argument("--device", default="cuda:0")
     ap.add_argument("--max_batch", "--max-batch", type=int, default=64)
     ap.add_argument("--random-weights", "--random_weights", metavar="CONFIG_JSON",
-                    help="write a model folder with seeded random weights for this config.json and exit")
+                    help="seeded random weights for this config.json: written to --out, or, without --out, made on "
+                         "the device for this run")
     ap.add_argument("--out", help="folder that --random-weights writes")
     ap.add_argument("--std", type=float, default=0.02)
     ap.add_argument("--norm_std", "--norm-std", type=float, default=0.1)
     args = ap.parse_args(argv)
 
     import trapetum_b200 as tb
-    if args.random_weights:
-        if not args.out:
-            ap.error("--random-weights needs --out")
+    if args.random_weights and args.out:
         with open(args.random_weights) as f:
             cfg = json.load(f)
         tb.write_random_model(args.out, cfg, args.seed, args.std, args.norm_std)
         print(f"wrote {args.out} (seed {args.seed})")
         return 0
-    if not args.model:
+    if args.random_weights and args.model:
+        args.prompts = [args.model] + args.prompts          # no model folder: every positional is a prompt
+        args.model = None
+    if not args.model and not args.random_weights:
         ap.error("the model folder is missing")
     prompts = [read_prompt(p) for p in args.prompts]
     prompts += [[int(x) for x in s.split(",") if x.strip()] for s in args.prompt_ids]
@@ -67,7 +72,11 @@ def main(argv=None) -> int:
         ap.error("no prompt: give a prompt.bin file or --prompt_ids")
 
     t0 = time.time()
-    model = tb.load_model(args.model, args.dtype, args.device)
+    if args.random_weights:
+        with open(args.random_weights) as f:
+            model = tb.random_model(json.load(f), args.seed, args.std, args.norm_std, args.dtype, args.device)
+    else:
+        model = tb.load_model(args.model, args.dtype, args.device)
     print(f"loaded in {time.time() - t0:.1f}s vocab={model.vocab_size} "
           + " ".join(f"prompt={len(p)} tokens {p}" for p in prompts), flush=True)
     import torch

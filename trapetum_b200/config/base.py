@@ -20,7 +20,7 @@ from __future__ import annotations
 
 import json
 import os
-from dataclasses import dataclass, field
+from dataclasses import dataclass, field, replace
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 
@@ -193,11 +193,36 @@ def architecture_name(d: Dict[str, Any]) -> str:
     return archs[0]
 
 
+def generation_stop_ids(folder: str) -> Tuple[int, ...]:
+    """``eos_token_id`` (a number or a list) of the folder's generation_config.json, () if there is none.
+    The reference's server reads this file before config.json and stops at the ids of both
+    (runtime/src/bin/serve.rs:83-104)."""
+    p = os.path.join(folder, "generation_config.json")
+    if not os.path.isfile(p):
+        return ()
+    try:
+        with open(p, "r", encoding="utf-8") as f:
+            d = json.load(f)
+    except json.JSONDecodeError as e:
+        raise ConfigError(f"{p} is not valid JSON: {e}") from None
+    if not isinstance(d, dict):
+        raise ConfigError(f"{p}: top level must be an object")
+    try:
+        return _id_list(d, "eos_token_id")
+    except ConfigError as e:
+        raise ConfigError(str(e).replace("config.json", "generation_config.json")) from None
+
+
 def load_config(path_or_dict) -> Tuple[Any, ModelSpec]:
-    """Read a config.json and return (typed architecture config, ModelSpec)."""
+    """Read a config.json and return (typed architecture config, ModelSpec).  For a model folder the stop
+    ids are those of generation_config.json and of config.json together."""
     d = path_or_dict if isinstance(path_or_dict, dict) else read_config_dict(path_or_dict)
     entry = architecture(architecture_name(d))
     cfg = entry.config_cls.from_dict(d)
     spec = entry.to_spec(cfg)
+    if not isinstance(path_or_dict, dict) and os.path.isdir(path_or_dict):
+        more = generation_stop_ids(path_or_dict)
+        if more:
+            spec = replace(spec, stop_ids=tuple(sorted(set(more) | set(spec.stop_ids))))
     spec.validate()
     return cfg, spec

@@ -33,7 +33,7 @@ NVCC_FLAGS = [
 
 # every kernel file of the package; build_all() compiles them all.  A name of the form
 # "file@MACRO=value" is the file compiled with -DMACRO=value (one library per value).
-SOURCES = ["embed", "norm", "rope_kv", "activation", "gemm_simt", "gemm_tc", "attention_simt", "attention_decode", "sampling"] + \
+SOURCES = ["embed", "norm", "rope_kv", "activation", "gemm_simt", "gemm_tc", "attention_simt", "attention_decode", "sampling", "random_init"] + \
     [f"attention_prefill@TB_HD={hd}" for hd in (16, 32, 48, 64, 128, 256)] + \
     [f"attention_prefill_tc@TB_HD={hd}" for hd in (64, 128, 256)]
 

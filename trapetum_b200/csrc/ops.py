@@ -114,6 +114,18 @@ def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def random_normal(out: torch.Tensor, key, std: float) -> None:
+    """Fill ``out`` (bfloat16 or float32) with the counter-based normal numbers of ``key`` = (k0, k1), times
+    ``std``, rounded to bfloat16 (see random_init.cu; ``weights.random_init`` makes the key from seed and name)."""
+    _cuda(out)
+    if not out.is_contiguous():
+        raise KernelError("random_normal: the tensor must be contiguous")
+    lib = build.load("random_init")
+    _check(lib, lib.tb_random_normal(_ptr(out), c_int(code(out.dtype)), c_longlong(out.numel()),
+                                     ctypes.c_uint(key[0]), ctypes.c_uint(key[1]), c_float(std), _stream()),
+           "random_normal")
+
+
 # ---------------------------------------------------------------------------
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, offset: float, out_dtype: torch.dtype) -> torch.Tensor:
     """norm(x) * (offset + w), statistics in 32-bit."""

@@ -121,3 +121,24 @@ def load_model(folder: str, dtype="bfloat16", device="cuda:0") -> Model:
     tensors = load_tensors(folder, model.tensor_specs(), dt, dev)
     model.bind(tensors)
     return model
+
+
+def random_model(config, seed: int = 0, std: float = 0.02, norm_std: float = 0.1, dtype="bfloat16",
+                 device="cuda:0") -> Model:
+    """A model of ``config`` (a dict of config.json keys, or a path) whose weights are made on the device:
+    the same values that ``write_random_model(folder, config, seed, std, norm_std)`` stores, without the
+    folder and without a host copy (each tensor is filled in place by the counter-based generator, so a model
+    of any size that fits the GPU can be made).  The reference builds the synthetic models of its checks
+    inside the program as well (runtime/src/lib.rs:1604-1629)."""
+    import trapetum_b200.models  # noqa: F401  (registers the architectures)
+    from ..weights.loader import random_tensors
+    dt = parse_dtype(dtype)
+    dev = torch.device(device)
+    if dev.type != "cuda" or not torch.cuda.is_available():
+        raise RuntimeError("trapetum_b200 computes on a CUDA device only (no CPU path); got device " + str(device))
+    _, spec = load_config(config)
+    model = Model(spec, Runtime(dt, dev))
+    build.require(model.kernel_files() + ("random_init",))
+    with torch.cuda.device(dev):
+        model.bind(dict(random_tensors(model.tensor_specs(), seed, std, norm_std, dtype=dt, device=dev)))
+    return model

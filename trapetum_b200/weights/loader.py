@@ -118,35 +118,47 @@ def load_tensors(folder: str, wanted: Dict[str, TensorSpec], engine_dtype: torch
 def random_tensors(wanted: Dict[str, TensorSpec], seed: int, std: float, norm_std: float,
                    dtype: torch.dtype = torch.bfloat16, device="cpu",
                    norm_dtype: Optional[torch.dtype] = None) -> Iterable[Tuple[str, torch.Tensor]]:
-    """Seeded random tensors in the order of ``wanted`` (one generator, drawn in
-    that order, so a folder is reproducible from configuration and seed)."""
-    gen = torch.Generator(device=device)
-    gen.manual_seed(int(seed))
+    """Seeded random tensors, one at a time, made where they will live (``device``).  Element ``i`` of tensor
+    ``name`` depends on ``(seed, name, i)`` only (:mod:`.random_init`), so the order of ``wanted`` does not
+    matter and a tensor made on the device equals the one a model folder of the same seed holds.  Values are
+    bfloat16 numbers, whatever ``dtype`` stores them in."""
+    from .random_init import fill_normal
     for name, spec in wanted.items():
         if spec.optional:
             continue
         if spec.role == "table":
             yield name, torch.zeros(spec.shape, dtype=torch.int32, device=device)
             continue
-        s = norm_std if spec.role == "norm" else std
-        t = torch.empty(spec.shape, dtype=torch.float32, device=device)
-        t.normal_(0.0, s, generator=gen)
-        yield name, t.to(norm_dtype if (spec.role == "norm" and norm_dtype is not None) else dtype)
+        dt = norm_dtype if (spec.role == "norm" and norm_dtype is not None) else dtype
+        t = torch.empty(spec.shape, dtype=dt, device=device)
+        yield name, fill_normal(t, seed, name, norm_std if spec.role == "norm" else std)
 
 
 def write_random_model(folder: str, config: dict, seed: int, std: float = 0.02, norm_std: float = 0.1,
-                       norm_dtype: Optional[torch.dtype] = None) -> str:
+                       norm_dtype: Optional[torch.dtype] = None, device=None) -> str:
     """Random-weights mode: make ``folder`` a model folder for ``config``.
 
     The reference's checks build synthetic models from a fixed seed in the same
     spirit (runtime/src/bin/model.rs:158-177).  Values are rounded to bfloat16
-    before they are stored, so every reader sees the same numbers."""
+    before they are stored, so every reader sees the same numbers.  Tensors are
+    made and written one at a time (on ``device``; default: the GPU if there is
+    one, it is much faster, else the host; the bits are the same), so the model is
+    never held in memory as a whole."""
     from ..engine.model import tensor_specs_for_config  # late: avoids an import cycle
     wanted = tensor_specs_for_config(config)
+    if device is None:
+        device = "cuda" if torch.cuda.is_available() else "cpu"
     os.makedirs(folder, exist_ok=True)
     with open(os.path.join(folder, "config.json"), "w", encoding="utf-8") as f:
         json.dump(config, f, indent=1)
+    layout = []
+    for name, spec in wanted.items():
+        if spec.optional:
+            continue
+        dt = torch.int32 if spec.role == "table" else \
+            (norm_dtype if (spec.role == "norm" and norm_dtype is not None) else torch.bfloat16)
+        layout.append((name, dt, tuple(spec.shape)))
     write_safetensors(os.path.join(folder, "model.safetensors"),
-                      random_tensors(wanted, seed, std, norm_std, norm_dtype=norm_dtype),
-                      metadata={"format": "pt", "seed": seed})
+                      random_tensors(wanted, seed, std, norm_std, device=device, norm_dtype=norm_dtype),
+                      metadata={"format": "pt", "seed": seed}, layout=layout)
     return folder

@@ -129,18 +129,25 @@ def open_model_files(folder: str) -> Dict[str, SafetensorsFile]:
     return by_name
 
 
-def write_safetensors(path: str, tensors: Iterable[Tuple[str, torch.Tensor]], metadata=None) -> None:
-    """Write tensors (CPU, contiguous) in the order given."""
-    items = [(n, t.detach().cpu().contiguous()) for n, t in tensors]
+def write_safetensors(path: str, tensors: Iterable[Tuple[str, torch.Tensor]], metadata=None, layout=None) -> None:
+    """Write tensors in the order given.  ``layout``: a list of ``(name, dtype, shape)`` in that order; with
+    it the header is written first and the tensors are taken from the iterable and written one at a time,
+    so that a large model is never held in memory as a whole.  Without it the tensors are collected first."""
+    if layout is None:
+        tensors = [(n, t.detach().cpu().contiguous()) for n, t in tensors]
+        layout = [(n, t.dtype, tuple(t.shape)) for n, t in tensors]
     header = {}
     if metadata:
         header["__metadata__"] = {str(k): str(v) for k, v in metadata.items()}
     off = 0
-    for name, t in items:
-        if t.dtype not in _NAMES:
-            raise WeightFileError(f"cannot store dtype {t.dtype} of '{name}'")
-        nbytes = t.numel() * t.element_size()
-        header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + nbytes]}
+    for name, dt, shape in layout:
+        if dt not in _NAMES:
+            raise WeightFileError(f"cannot store dtype {dt} of '{name}'")
+        numel = 1
+        for d in shape:
+            numel *= int(d)
+        nbytes = numel * torch.empty((), dtype=dt).element_size()
+        header[name] = {"dtype": _NAMES[dt], "shape": [int(d) for d in shape], "data_offsets": [off, off + nbytes]}
         off += nbytes
     hj = json.dumps(header, separators=(",", ":")).encode("utf-8")
     hj += b" " * ((8 - len(hj) % 8) % 8)
@@ -148,8 +155,15 @@ def write_safetensors(path: str, tensors: Iterable[Tuple[str, torch.Tensor]], me
     with open(tmp, "wb") as f:
         f.write(struct.pack("<Q", len(hj)))
         f.write(hj)
-        for _, t in items:
+        it = iter(tensors)
+        for name, dt, shape in layout:
+            try:
+                got_name, t = next(it)
+            except StopIteration:
+                raise WeightFileError(f"the tensors end before '{name}'") from None
+            t = t.detach().cpu().contiguous()
+            if got_name != name or t.dtype != dt or tuple(t.shape) != tuple(shape):
+                raise WeightFileError(f"expected '{name}' {dt} {list(shape)}, got '{got_name}' {t.dtype} {list(t.shape)}")
             if t.numel():
-                f.write(t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() < (1 << 24)
-                        else memoryview(t.reshape(-1).view(torch.uint8).numpy()))
+                f.write(memoryview(t.reshape(-1).view(torch.uint8).numpy()))
     os.replace(tmp, path)
