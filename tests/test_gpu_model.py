@@ -9,7 +9,7 @@ import pytest
 import torch
 
 import plain_gemma2 as plain
-from conftest import ROOT, TINY, TOL, make_prompts, rel_l2
+from conftest import ROOT, TINY, TOL, make_prompts, rel_l2, within
 
 pytestmark = pytest.mark.gpu
 
@@ -61,8 +61,7 @@ def check(got, want, dtype, what):
     assert got.shape == want.shape, what
     assert torch.isfinite(got).all(), f"{what}: NaN or inf in the logits"
     worst = max(rel_l2(got[i], want[i]) for i in range(got.shape[0]))
-    tol = tolerance(what.split()[0], dtype)
-    assert worst <= tol, f"{what}: worst relative L2 error over positions {worst:.3e} > {tol:.1e}"
+    within(worst, tolerance(what.split()[0], dtype), dtype, what)
     if dtype == "float32":
         assert (got.cpu().argmax(-1) == want.argmax(-1)).all(), f"{what}: top-1 differs"
 
@@ -187,6 +186,31 @@ def test_second_batch_with_the_same_slots_and_page_counts_but_other_pages(model_
     eng.cache.check()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_unsharpened_models_keep_the_flat_tolerance(tmp_path, name, dtype):
+    """The same configurations with the weights as the generator makes them (no scaled q and k projections):
+    here 16-bit storage costs little, and the bfloat16 engine has to stay within the flat 2e-2."""
+    import trapetum_b200 as tb
+    cfg, seed, std, nstd, _ = TINY[name]
+    d = str(tmp_path / "plainweights")
+    tb.write_random_model(d, cfg, seed + 50, std, nstd)
+    pc, pw = plain.load_folder(d)
+    prompts = make_prompts(cfg["vocab_size"], [90, 33], seed=8)
+    truth = [plain.forward(pc, pw, p) for p in prompts]
+    eng = tb.Engine(tb.load_model(d, dtype), max_tokens=64 * 4)
+    cut = [60, 20]
+    s = eng.start(2)
+    first = eng.step(s, [p[:c] for p, c in zip(prompts, cut)], [list(range(c)) for c in cut])
+    worst = max(rel_l2(first[i], truth[0][i]) for i in range(cut[0]))
+    worst = max(worst, max(rel_l2(first[cut[0] + i], truth[1][i]) for i in range(cut[1])))
+    for t in range(13):
+        out = eng.step(s, [[p[c + t]] for p, c in zip(prompts, cut)])
+        worst = max(worst, rel_l2(out[0], truth[0][cut[0] + t]), rel_l2(out[1], truth[1][cut[1] + t]))
+    eng.release(s)
+    within(worst, TOL[dtype], dtype, f"{name} unsharpened")
+
+
 @pytest.mark.parametrize("name", NAMES)
 def test_runs_repeat_bit_for_bit(engines, requests_and_truth, name):
     eng = engines(name, "bfloat16")
@@ -234,7 +258,7 @@ def test_greedy_generation_through_the_entry_point(model_folders, plain_models, 
             for i, (a, b) in enumerate(zip(g, t)):
                 if a != b:
                     logits = plain.forward(cfg, w, p + t[:i])[-1]
-                    assert float(logits[b] - logits[a]) < 0.05 * float(logits.abs().max()), (p, i, a, b)
+                    assert float(logits[b] - logits[a]) < BUDGET[name] * float(logits.abs().max()), (p, i, a, b)
                     break
     # a stop id ends a request early and is not emitted
     stop = want[0][4]

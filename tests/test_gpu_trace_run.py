@@ -9,7 +9,7 @@ import pytest
 import torch
 
 import plain_gemma2 as plain
-from conftest import ROOT, TOL, make_prompts, rel_l2
+from conftest import ROOT, TOL, make_prompts, rel_l2, within
 
 pytestmark = pytest.mark.gpu
 
@@ -75,7 +75,7 @@ def test_replay_three_ways(model_folders, plain_models, budgets, tmp_path, name,
         got = torch.from_numpy(np.fromfile(os.path.join(out, f"{n}.f32"), dtype="<f4").reshape(-1, V))
         assert got.shape == want.shape
         worst = max(rel_l2(got[i], want[i]) for i in range(got.shape[0]))
-        assert worst <= budgets[name][dtype], f"step {n} ({steps[n]['entries'][0]['id']}...): {worst:.3e}"
+        within(worst, budgets[name][dtype], dtype, f"{name} replay step {n} ({steps[n]['entries'][0]['id']}...)")
 
 
 def test_replay_refuses_what_does_not_fit(model_folders, tmp_path):
