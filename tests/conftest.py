@@ -67,6 +67,22 @@ def bf16_budget(cfg, w, prompts, schedule=None) -> float:
     return max(TOL["bfloat16"], BUDGET_FACTOR * worst)
 
 
+_SEQ_BUDGET = {}
+
+
+def seq_tolerance(key, cfg, w, ids, dtype: str, schedule=None) -> float:
+    """The tolerance for the logits of ONE sequence: float32, rounding only; bfloat16, the budget that the
+    oracle gives for this very sequence (where on a sequence 16-bit storage costs most differs from sequence
+    to sequence, so a budget taken on other prompts would be too wide for some and too narrow for others).
+    ``key`` names the model; results are kept."""
+    if dtype == "float32":
+        return TOL["float32"]
+    k = (key, tuple(ids), None if schedule is None else tuple(schedule))
+    if k not in _SEQ_BUDGET:
+        _SEQ_BUDGET[k] = bf16_budget(cfg, w, [list(ids)], schedule)
+    return _SEQ_BUDGET[k]
+
+
 MEASURED = []          # (what, dtype, worst error, tolerance) of every logits comparison of the run
 
 
@@ -129,13 +145,12 @@ def plain_models(model_folders):
 
 
 @pytest.fixture(scope="session")
-def budgets(plain_models):
-    """name -> {"float32": ..., "bfloat16": ...} tolerances for the sharpened tiny models."""
-    out = {}
-    for name, (cfg, w) in plain_models.items():
-        prompts = make_prompts(cfg["vocab_size"], [45, 77, 150], seed=101)
-        out[name] = {"float32": TOL["float32"], "bfloat16": bf16_budget(cfg, w, prompts)}
-    return out
+def tolerance_of(plain_models):
+    """(model name, token ids, dtype) -> tolerance for that sequence's logits on the sharpened tiny models."""
+    def get(name, ids, dtype):
+        cfg, w = plain_models[name]
+        return seq_tolerance(name, cfg, w, ids, dtype)
+    return get
 
 
 def make_prompts(vocab: int, lengths, seed: int):

@@ -85,10 +85,12 @@ def visible(i: int, j: int, window: Optional[int]) -> bool:
 
 
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, cap: Optional[float],
-              window: Optional[int]) -> torch.Tensor:
+              window: Optional[int], rnd=_same) -> torch.Tensor:
     """q [T, nh, hd], k and v [T, nkv, hd] -> [T, nh, hd].
     s = (q.k) * scale; s = cap*tanh(s/cap); softmax with the maximum subtracted; sum of p*v
-    (runtime/cuda/codebook_gemv.cu:240-270); query head h reads kv head h // (nh // nkv) (:244)."""
+    (runtime/cuda/codebook_gemv.cu:240-270); query head h reads kv head h // (nh // nkv) (:244).
+    ``rnd`` is applied to the unnormalised probabilities before they meet v: a 16-bit engine hands
+    them to its tensor cores in 16 bits, while their sum stays 32-bit."""
     T, nh, hd = q.shape
     nkv = k.shape[1]
     out = torch.zeros_like(q)
@@ -101,8 +103,7 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, c
         s = s.masked_fill(~mask, float("-inf"))
         s = s - s.max(dim=-1, keepdim=True).values
         p = s.exp()
-        p = p / p.sum(dim=-1, keepdim=True)
-        out[:, h, :] = p @ v[:, kh, :]
+        out[:, h, :] = (rnd(p) @ v[:, kh, :]) / p.sum(dim=-1, keepdim=True)
     return out
 
 
@@ -133,7 +134,7 @@ def attention_block(x: torch.Tensor, w: Dict[str, torch.Tensor], prefix: str, cf
         k, v = kv_from
     scale = float(cfg.get("query_pre_attn_scalar", hd)) ** -0.5
     cap = cfg.get("attn_logit_softcapping") or None
-    o = rnd(attention(q, k, v, scale, cap, window))
+    o = rnd(attention(q, k, v, scale, cap, window, rnd))
     return o.reshape(T, nh * hd) @ w[prefix + "self_attn.o_proj.weight"].T, (k, v)
 
 

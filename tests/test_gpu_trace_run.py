@@ -25,7 +25,7 @@ def run_trace(folder, dtype, out, steps, max_tokens):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B"])
-def test_replay_three_ways(model_folders, plain_models, budgets, tmp_path, name, dtype):
+def test_replay_three_ways(model_folders, plain_models, tolerance_of, tmp_path, name, dtype):
     cfg, w = plain_models[name]
     V = cfg["vocab_size"]
     reqs = make_prompts(V, [40, 75, 130], seed=3)
@@ -75,7 +75,8 @@ def test_replay_three_ways(model_folders, plain_models, budgets, tmp_path, name,
         got = torch.from_numpy(np.fromfile(os.path.join(out, f"{n}.f32"), dtype="<f4").reshape(-1, V))
         assert got.shape == want.shape
         worst = max(rel_l2(got[i], want[i]) for i in range(got.shape[0]))
-        within(worst, budgets[name][dtype], dtype, f"{name} replay step {n} ({steps[n]['entries'][0]['id']}...)")
+        tol = max(tolerance_of(name, reqs[int(e["id"][-1])], dtype) for e in steps[n]["entries"])
+        within(worst, tol, dtype, f"{name} replay step {n} ({steps[n]['entries'][0]['id']}...)")
 
 
 def test_replay_refuses_what_does_not_fit(model_folders, tmp_path):

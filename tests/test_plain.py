@@ -137,3 +137,19 @@ def test_greedy_generation_stops():
     out = plain.generate_greedy(c, w, [1, 2, 3], 5)
     assert len(out) == 5
     assert plain.generate_greedy(c, w, [1, 2, 3], 5, stop_ids=[out[2]]) == out[:out.index(out[2])]
+
+
+def test_parts_against_the_outputs_of_the_reference_s_own_cuda_operators():
+    """tests/golden/reference_ops.json holds what runtime/cuda/codebook_gemv.cu (compiled unchanged, run on a
+    B200 by tests/golden/make_reference_ops_golden.py) computes on small float16 cases: RMS norm, rotation,
+    one-query attention with and without the soft cap, GeGLU, residual sum, greedy choice.  The plain
+    implementation's functions must give the same numbers to float16 accuracy."""
+    import json
+    import os
+    from reference_ops_check import check_all
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_ops.json")
+    with open(path) as f:
+        stored = json.load(f)["outputs"]
+    ref = {k: (v if isinstance(v, int) else torch.tensor(v["values"], dtype=torch.float32).reshape(v["shape"]))
+           for k, v in stored.items()}
+    assert check_all(ref) == 10
