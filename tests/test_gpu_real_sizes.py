@@ -201,3 +201,55 @@ def test_long_prompts_through_the_tensor_core_attention(tmp_path_factory, dtype)
     assert len({key[1] for key in eng2._decode}) >= 2                      # two buckets were used
     torch.cuda.synchronize()
     assert ops.kernel_errors() == {}
+
+
+class _LazyWeights:
+    """name -> tensor, read from the folder and widened when asked for and not kept: the plain implementation
+    walks a whole 26-layer model without ever holding more than one matrix in 64-bit."""
+
+    def __init__(self, folder, dtype):
+        from safetensors import safe_open
+        self.f = safe_open(folder + "/model.safetensors", framework="pt")
+        self.names, self.dtype = set(self.f.keys()), dtype
+
+    def __getitem__(self, name):
+        return self.f.get_tensor(name).to(self.dtype)
+
+    def __contains__(self, name):
+        return name in self.names
+
+    def get(self, name, default=None):
+        return self[name] if name in self.names else default
+
+
+def test_whole_2b_model_against_the_plain_implementation(tmp_path_factory):
+    """All 26 layers at Gemma-2-2B's sizes with its real vocabulary and the weights as the generator makes
+    them: a 64-token sequence, its first 48 tokens as a prompt and the rest one by one, in bfloat16 and in
+    32-bit, against the plain implementation in 64-bit on every position.  The engine's model is made on the
+    device (tb.random_model); the oracle reads the folder that write_random_model writes for the same seed."""
+    import json
+    import trapetum_b200 as tb
+    from trapetum_b200.csrc import ops
+    cfg = dict(SHAPES["2b"], num_hidden_layers=26, sliding_window=32)
+    d = str(tmp_path_factory.mktemp("whole_2b"))
+    tb.write_random_model(d, cfg, seed=2, std=0.02, norm_std=0.1)
+    ids = make_prompts(cfg["vocab_size"], [64], seed=12)[0]
+    want = plain.forward(json.load(open(d + "/config.json")), _LazyWeights(d, torch.float64), ids)
+    for dtype in ("bfloat16", "float32"):
+        model = tb.random_model(cfg, 2, 0.02, 0.1, dtype)
+        eng = tb.Engine(model, max_tokens=128)
+        for g in eng.cache.groups:
+            g.k.fill_(float("nan")); g.v.fill_(float("nan"))
+        s = eng.start(1)
+        got = [eng.step(s, [ids[:48]], [list(range(48))])]
+        for t in range(48, 64):
+            got.append(eng.step(s, [[ids[t]]]))
+        eng.release(s)
+        got = torch.cat(got)
+        assert torch.isfinite(got).all()
+        within(max(rel_l2(got[i], want[i]) for i in range(64)), TOL[dtype], dtype, "whole 2B model, 64 tokens")
+        if dtype == "float32":
+            assert (got.cpu().argmax(-1) == want.argmax(-1)).all()
+        del eng, model
+        torch.cuda.empty_cache()
+    assert ops.kernel_errors() == {}
