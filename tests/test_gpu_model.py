@@ -9,7 +9,7 @@ import pytest
 import torch
 
 import plain_gemma2 as plain
-from conftest import ROOT, TINY, TOL, make_prompts, rel_l2, within
+from conftest import ROOT, TINY, TOL, bf16_budget, make_prompts, rel_l2, within
 
 pytestmark = pytest.mark.gpu
 
@@ -205,6 +205,37 @@ def test_unsharpened_models_keep_the_flat_tolerance(tmp_path, name, dtype):
         worst = max(worst, rel_l2(out[0], truth[0][cut[0] + t]), rel_l2(out[1], truth[1][cut[1] + t]))
     eng.release(s)
     within(worst, TOL[dtype], dtype, f"{name} unsharpened")
+
+
+def test_float16_checkpoint_is_kept_exactly(model_folders, plain_models, tmp_path):
+    """The same weights stored in float16 (values that bfloat16 cannot hold: a multiple of 2^-10 is added):
+    the bfloat16 engine widens them rather than rounding them, so its logits follow the float16 values."""
+    import shutil
+    import trapetum_b200 as tb
+    from safetensors.torch import load_file, save_file
+    d = str(tmp_path / "f16")
+    shutil.copytree(model_folders["A"], d)
+    w = load_file(d + "/model.safetensors")
+    g = torch.Generator().manual_seed(0)
+    w16 = {k: (v.float() * (1.0 + 2.0 ** -9 * torch.randint(0, 2, v.shape, generator=g))).to(torch.float16) for k, v in w.items()}
+    save_file(w16, d + "/model.safetensors")
+    cfg, pw = plain.load_folder(d)
+    ids = make_prompts(cfg["vocab_size"], [50], seed=77)[0]
+    truth = plain.forward(cfg, pw, ids)
+    rounded = plain.forward(cfg, {k: v.bfloat16().float() for k, v in pw.items()}, ids)
+    gap = max(rel_l2(rounded[i], truth[i]) for i in range(50))           # what silent rounding of the weights would cost
+    for fp16, dtype in (("widen", "bfloat16"), ("widen", "float32")):
+        model = tb.load_model(d, dtype, fp16=fp16)
+        assert model.blocks[0].mixer.w_qkv.dtype == torch.float32 and model.blocks[0].mixer.w_o.dtype == torch.float32
+        eng = tb.Engine(model, max_tokens=128)
+        s = eng.start(1)
+        got = eng.step(s, [ids], [list(range(50))])
+        eng.release(s)
+        worst = max(rel_l2(got[i], truth[i]) for i in range(50))
+        if dtype == "float32":
+            assert worst < 1e-5 < gap
+        else:
+            within(worst, bf16_budget(cfg, pw, [ids]), dtype, "A stored in float16")
 
 
 @pytest.mark.parametrize("name", NAMES)

@@ -499,3 +499,136 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_around_the_librar
     eng.release(s)
     assert len(errs) >= 20, f"too few places with clear routing to say anything: {upto}"
     assert max(errs) < tol, sorted(errs)[-5:]
+
+
+# ---------------------------------------------------------------------------
+# The library's attention with biases and per-head norms of q and k: parameters, not a kernel edit
+# ---------------------------------------------------------------------------
+def _register_biased():
+    from trapetum_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, register_architecture
+    from trapetum_b200.config.base import _get
+
+    @dataclass(frozen=True)
+    class BiasedConfig:
+        layers: int; hidden: int; heads: int; kv_heads: int; head_dim: int; inter: int; vocab: int; eps: float; window: int
+
+        @classmethod
+        def from_dict(cls, d):
+            g = lambda k, t=int: _get(d, "b_" + k, t)
+            return cls(g("layers"), g("hidden"), g("heads"), g("kv_heads"), g("head_dim"), g("inter"), g("vocab"),
+                       g("eps", float), g("window"))
+
+    def spec(c):
+        norm = lambda n, size=c.hidden: PartSpec("rmsnorm", {"size": size, "eps": c.eps, "unit_offset": False, "weight": n})
+        layers = tuple(LayerSpec(
+            block=PartSpec("pre_norm", {"pre_mixer_norm": norm("n1.weight"), "pre_ffn_norm": norm("n2.weight")}),
+            mixer=PartSpec("attention", {
+                "hidden_size": c.hidden, "num_heads": c.heads, "num_kv_heads": c.kv_heads, "head_dim": c.head_dim,
+                "scale": c.head_dim ** -0.5, "softcap": None, "window": c.window if i % 2 else None,
+                "q": "q.weight", "k": "k.weight", "v": "v.weight", "o": "o.weight",
+                "bias": {"q": "q.bias", "k": "k.bias", "v": "v.bias", "o": "o.bias"},
+                "q_norm": norm("q_norm.weight", c.head_dim), "k_norm": norm("k_norm.weight", c.head_dim),
+                "position": PartSpec("rope", {"head_dim": c.head_dim, "theta": 1000.0, "rotary_dim": c.head_dim})}),
+            feed_forward=PartSpec("gated_mlp", {"hidden_size": c.hidden, "intermediate_size": c.inter, "activation": "silu",
+                                                "gate": "g.weight", "up": "u.weight", "down": "d.weight"}),
+            prefix=f"blocks.{i}.") for i in range(c.layers))
+        return ModelSpec(architecture="TestBiasedLM", hidden_size=c.hidden, vocab_size=c.vocab,
+                         embedding=PartSpec("embedding", {"vocab_size": c.vocab, "hidden_size": c.hidden, "scale": 1.0,
+                                                          "weight": "emb.weight"}),
+                         layers=layers, schedule=tuple(ScheduleEntry(i) for i in range(c.layers)),
+                         final_norm=norm("out_norm.weight"),
+                         head=PartSpec("linear_head", {"vocab_size": c.vocab, "hidden_size": c.hidden, "softcap": None,
+                                                       "weight": "head.weight", "tied_to": None}),
+                         max_positions=512)
+    register_architecture("TestBiasedLM", BiasedConfig, spec)
+
+
+def _biased_plain(cfg, w, ids, rnd=lambda x: x):
+    """The biased, head-normed toy model, whole sequence, in 64-bit on the CPU."""
+    nh, nkv, hd, eps, W = cfg["b_heads"], cfg["b_kv_heads"], cfg["b_head_dim"], cfg["b_eps"], cfg["b_window"]
+    w = {k: v.double() for k, v in w.items()}
+    norm = lambda x, g: x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * g
+    T = len(ids)
+    h = w["emb.weight"][torch.tensor(ids)]
+    for i in range(cfg["b_layers"]):
+        p = f"blocks.{i}."
+        x = rnd(norm(h, w[p + "n1.weight"]))
+        q = rnd(norm(rnd(x @ w[p + "q.weight"].T + w[p + "q.bias"]).view(T, nh, hd), w[p + "q_norm.weight"]))
+        k = rnd(norm(rnd(x @ w[p + "k.weight"].T + w[p + "k.bias"]).view(T, nkv, hd), w[p + "k_norm.weight"]))
+        v = rnd(x @ w[p + "v.weight"].T + w[p + "v.bias"]).view(T, nkv, hd)
+        q, k = rnd(plain.rope(q, torch.arange(T), 1000.0)), rnd(plain.rope(k, torch.arange(T), 1000.0))
+        o = rnd(plain.attention(q, k, v, hd ** -0.5, None, W if i % 2 else None, rnd))
+        h = h + o.reshape(T, nh * hd) @ w[p + "o.weight"].T + w[p + "o.bias"]
+        x = rnd(norm(h, w[p + "n2.weight"]))
+        g = rnd(x @ w[p + "g.weight"].T)
+        h = h + rnd((g * torch.sigmoid(g)) * rnd(x @ w[p + "u.weight"].T)) @ w[p + "d.weight"].T
+    return (rnd(norm(h, w["out_norm.weight"])) @ w["head.weight"].T).float()
+
+
+@pytest.mark.parametrize("dtype,hd", [("float32", 24), ("bfloat16", 64), ("bfloat16", 32)])
+def test_attention_with_biases_and_head_norms_is_a_matter_of_parameters(tmp_path, dtype, hd):
+    """The library's attention part with a bias on each projection and an RMS norm on every query and key head:
+    a model made of it is registered from here, built and stepped (prompts, then token by token, in a batch of
+    unequal lengths) against a plain computation.  With a head size that the tensor-core decode kernel takes,
+    the part must not hand that kernel its raw projection (the kernel's own prologue knows neither biases nor
+    norms): it says so through ``fused_decode()``."""
+    import trapetum_b200 as tb
+    _register_biased()
+    cfg = {"architectures": ["TestBiasedLM"], "b_layers": 2, "b_hidden": 64, "b_heads": 4, "b_kv_heads": 2, "b_head_dim": hd,
+           "b_inter": 96, "b_vocab": 120, "b_eps": 1e-5, "b_window": 7}
+    d = str(tmp_path / "biased")
+    tb.write_random_model(d, cfg, 21, 0.2, 0.3)
+    from safetensors.torch import load_file, save_file
+    stored = load_file(d + "/model.safetensors")
+    for k in stored:                                   # norm weights around 1, biases large enough to matter
+        if "norm" in k or ".n1." in k or ".n2." in k:
+            stored[k] = (1.0 + stored[k].float()).to(stored[k].dtype)
+        if k.endswith(".bias"):
+            stored[k] = (stored[k].float() * 3.0).to(stored[k].dtype)
+    save_file(stored, d + "/model.safetensors")
+    pw = plain.load_folder(d)[1]
+    model = tb.load_model(d, dtype)
+    assert not any(b.mixer.fused_decode() for b in model.blocks)
+    eng = tb.Engine(model, 64 * 6, max_slots=3)
+    for g in eng.cache.groups:
+        g.k.fill_(float("nan")); g.v.fill_(float("nan"))
+    prompts = make_prompts(120, [40, 9, 23], seed=5)
+    truth = [_biased_plain(cfg, pw, p) for p in prompts]
+    if dtype == "float32":
+        tol = [2e-5] * 3
+    else:
+        tol = [max(TOL["bfloat16"], 1.5 * max(rel_l2(a, b) for a, b in zip(_biased_plain(cfg, pw, p, plain.to_bf16), t)))
+               for p, t in zip(prompts, truth)]
+    cut = [28, 3, 12]
+    s = eng.start(3)
+    first = eng.step(s, [p[:c] for p, c in zip(prompts, cut)], [list(range(c)) for c in cut])
+    o = 0
+    for r in range(3):
+        worst = max(rel_l2(first[o + i], truth[r][i]) for i in range(cut[r]))
+        assert worst <= tol[r], f"request {r} prompt: {worst:.3e} > {tol[r]:.2e}"
+        o += cut[r]
+    for t in range(6):
+        out = eng.step(s, [[prompts[r][cut[r] + t]] for r in range(3)])
+        for r in range(3):
+            e = rel_l2(out[r], truth[r][cut[r] + t])
+            assert e <= tol[r], f"request {r} token {cut[r] + t}: {e:.3e} > {tol[r]:.2e}"
+    eng.release(s)
+    # without biases and head norms the same part does hand the decode kernel its raw projection
+    from trapetum_b200.config import load_config
+    plain_mixer = tb.load_config(dict(TINY_A))[1].layers[0].mixer
+    from trapetum_b200.parts import build_part
+    m = build_part("mixer", plain_mixer, "model.layers.0.", _rt(torch.bfloat16))
+    m.bind({n: torch.zeros(sp.shape, dtype=torch.bfloat16, device="cuda") for n, sp in m.tensor_specs().items()})
+    assert m.fused_decode()
+
+
+def test_a_state_of_another_dtype():
+    from trapetum_b200.cache import Cache
+    from trapetum_b200.parts import StateNeed
+    c = Cache({0: StateNeed((3, 5), torch.bfloat16), 1: StateNeed((2,), torch.int32)}, {}, 64 * 4, torch.bfloat16, "cuda", 4)
+    assert c.states[0].dtype == torch.bfloat16 and c.states[0].shape == (4, 3, 5) and c.states[1].dtype == torch.int32
+    s = c.claim()
+    c.view(0, 0).data[s].fill_(2.5)
+    c.view(1, 1).data[s].fill_(7)
+    c.release(s)
+    assert c.claim() == s and float(c.states[0][s].abs().sum()) == 0.0 and int(c.states[1][s].sum()) == 0

@@ -57,7 +57,9 @@ def test_truncated_and_garbled_files(tmp_path):
 def test_storage_rules():
     bf, f32 = torch.bfloat16, torch.float32
     assert storage_dtype(torch.bfloat16, "matrix", bf) == bf
-    assert storage_dtype(torch.float16, "matrix", bf) == bf
+    assert storage_dtype(torch.float16, "matrix", bf) == f32          # never rounded in silence: widened, exact
+    assert storage_dtype(torch.float16, "matrix", bf, fp16="round") == bf
+    assert storage_dtype(torch.float16, "matrix", f32, fp16="round") == f32
     assert storage_dtype(torch.float32, "norm", bf) == f32            # stored in 32 bits: stays so
     assert storage_dtype(torch.int64, "table", bf) == torch.int32      # integer tables become int32
     assert storage_dtype(torch.bfloat16, "matrix", f32) == f32         # the 32-bit engine up-casts
@@ -169,3 +171,20 @@ def test_golden_reader_of_the_reference(tmp_path):
         assert float(t.double().sum()) == pytest.approx(g["sum"], rel=1e-12, abs=1e-12)
         assert float(t.double().abs().sum()) == pytest.approx(g["abs_sum"], rel=1e-12)
         assert [float(x) for x in t.reshape(-1)[:4]] == g["first"]
+
+
+def test_float16_tensors_are_widened_rounded_or_refused_never_rounded_in_silence(tmp_path):
+    from trapetum_b200.weights import WeightError, load_tensors, write_safetensors
+    d = str(tmp_path)
+    x = torch.tensor([[1.0 + 2.0 ** -10, 3.0]], dtype=torch.float16)          # the first value does not fit bfloat16
+    write_safetensors(d + "/model.safetensors", [("w", x), ("n", torch.ones(2, dtype=torch.bfloat16))])
+    wanted = {"w": TensorSpec((1, 2)), "n": TensorSpec((2,), "norm")}
+    t = load_tensors(d, wanted, torch.bfloat16, "cpu")
+    assert t["w"].dtype == torch.float32 and torch.equal(t["w"], x.float()) and t["n"].dtype == torch.bfloat16
+    t = load_tensors(d, wanted, torch.bfloat16, "cpu", fp16="round")
+    assert t["w"].dtype == torch.bfloat16 and float(t["w"][0, 0]) == 1.0
+    with pytest.raises(WeightError, match="float16"):
+        load_tensors(d, wanted, torch.bfloat16, "cpu", fp16="refuse")
+    assert load_tensors(d, wanted, torch.float32, "cpu", fp16="refuse")["w"].dtype == torch.float32
+    with pytest.raises(ValueError, match="fp16"):
+        load_tensors(d, wanted, torch.bfloat16, "cpu", fp16="maybe")

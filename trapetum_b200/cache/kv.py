@@ -16,7 +16,7 @@ A sequence takes a slot when it starts and pages as it grows; :meth:`release`
 gives all of it back, and the next sequence reuses the numbers.  Stale keys in a
 reused page are never read: every reader is bounded by the sequence's own length.
 
-``StateNeed`` entries get ``[max_slots, *shape]`` float32 each, addressed by slot
+``StateNeed`` entries get ``[max_slots, *shape]`` of their dtype each, addressed by slot
 and zeroed when the slot is taken.  Gemma-2 has none; the area exists so that a
 mixer with a recurrent state has a place to keep it.
 """
@@ -66,7 +66,7 @@ class KVLineView:
 @dataclass
 class StateView:
     """Per-slot state of one schedule entry: ``data[slot]`` is the sequence's state."""
-    data: torch.Tensor                       # [max_slots, *shape] float32
+    data: torch.Tensor                       # [max_slots, *shape] of the need's dtype
     entry: int
 
 
@@ -93,7 +93,7 @@ class Cache:
             if isinstance(need, KVNeed):
                 by_key.setdefault((need.n_kv_heads, need.head_dim, need.window), []).append(e)
             elif isinstance(need, StateNeed):
-                self.states[e] = torch.zeros((self.max_slots,) + tuple(need.shape), dtype=torch.float32,
+                self.states[e] = torch.zeros((self.max_slots,) + tuple(need.shape), dtype=need.dtype,
                                              device=self.device)
             elif need is not None:
                 raise TypeError(f"schedule entry {e}: a cache need must be KVNeed, StateNeed or None, got {need!r}")

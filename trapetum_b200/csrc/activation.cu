@@ -49,3 +49,29 @@ extern "C" int tb_gated_act(const void* gu, int in_dtype, void* out, int out_dty
 #undef LAUNCH
     return tb_launch_status();
 }
+
+// x[r, c] += bias[c] in place, the sum in 32-bit (rows may be wider than `width`: row_stride elements apart).
+template <typename T, typename TB>
+__global__ void add_bias_kernel(T* __restrict__ x, long long row_stride, const TB* __restrict__ bias, int width) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= width) return;
+    T* p = x + (size_t)blockIdx.x * row_stride + c;
+    *p = from_f<T>(to_f<T>(*p) + to_f<TB>(bias[c]));
+}
+
+extern "C" int tb_add_bias(void* x, int x_dtype, long long row_stride, const void* bias, int bias_dtype, int rows,
+                           int width, cudaStream_t stream) {
+    if (rows <= 0 || width <= 0) return 0;
+    dim3 grid(rows, (width + 255) / 256);
+    if (grid.y > 65535) return tb_refuse("add_bias: width %d is too wide", width);
+#define LAUNCH(T, TB) tb_launch(add_bias_kernel<T, TB>, dim3(grid), dim3(256), 0, stream, (T*)x, row_stride, (const TB*)bias, width)
+    if (x_dtype == TB_F32 && bias_dtype == TB_F32) LAUNCH(float, float);
+    else if (x_dtype == TB_F32 && bias_dtype == TB_BF16) LAUNCH(float, bf16);
+    else if (x_dtype == TB_BF16 && bias_dtype == TB_BF16) LAUNCH(bf16, bf16);
+    else if (x_dtype == TB_BF16 && bias_dtype == TB_F32) LAUNCH(bf16, float);
+    else return tb_refuse("add_bias: unknown dtype codes %d %d", x_dtype, bias_dtype);
+#undef LAUNCH
+    return tb_launch_status();
+}

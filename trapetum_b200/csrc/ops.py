@@ -203,6 +203,18 @@ def gated_act(gu: torch.Tensor, activation: str, out_dtype: torch.dtype) -> torc
     return out
 
 
+def add_bias(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """x[r, :] += bias in place (x 2-D with contiguous rows, possibly a column slice of a wider matrix)."""
+    _cuda(x, bias)
+    _rows_contig(x, "add_bias: x")
+    if bias.dim() != 1 or bias.numel() != x.shape[1] or not bias.is_contiguous():
+        raise KernelError(f"add_bias: bias {tuple(bias.shape)} does not fit rows of width {x.shape[1]}")
+    lib = build.load("activation")
+    _check(lib, lib.tb_add_bias(_ptr(x), c_int(code(x.dtype)), c_longlong(x.stride(0)), _ptr(bias), c_int(code(bias.dtype)),
+                                c_int(x.shape[0]), c_int(x.shape[1]), _stream()), "add_bias")
+    return x
+
+
 # ---------------------------------------------------------------------------
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, softcap: float = 0.0,
               out: Optional[torch.Tensor] = None) -> torch.Tensor:

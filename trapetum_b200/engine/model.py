@@ -106,8 +106,11 @@ def parse_dtype(dtype) -> torch.dtype:
         raise ValueError(f"unknown dtype '{dtype}' (bfloat16 or float32)") from None
 
 
-def load_model(folder: str, dtype="bfloat16", device="cuda:0") -> Model:
-    """Read config.json, pick the model by its architecture name, load and bind the weights."""
+def load_model(folder: str, dtype="bfloat16", device="cuda:0", fp16: str = "widen") -> Model:
+    """Read config.json, pick the model by its architecture name, load and bind the weights.
+    ``fp16``: what happens to tensors stored in float16 when the engine computes in bfloat16: "widen" keeps
+    them exactly, as float32 (their products then take the 32-bit path), "round" rounds them to bfloat16,
+    "refuse" reports them (see :mod:`trapetum_b200.weights.loader`)."""
     import trapetum_b200.models  # noqa: F401  (registers the architectures)
     dt = parse_dtype(dtype)
     dev = torch.device(device)
@@ -118,7 +121,7 @@ def load_model(folder: str, dtype="bfloat16", device="cuda:0") -> Model:
     _, spec = load_config(folder)
     model = Model(spec, Runtime(dt, dev))
     build.require(model.kernel_files())
-    tensors = load_tensors(folder, model.tensor_specs(), dt, dev)
+    tensors = load_tensors(folder, model.tensor_specs(), dt, dev, fp16)
     model.bind(tensors)
     return model
 

@@ -55,9 +55,10 @@ class KVNeed:
 
 @dataclass(frozen=True)
 class StateNeed:
-    """Per-sequence state of fixed size: ``shape`` float32 numbers, zeroed when
-    a sequence starts."""
+    """Per-sequence state of fixed size: ``shape`` numbers of ``dtype`` (float32 unless
+    said otherwise; any torch dtype), zeroed when a sequence starts."""
     shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
 
 
 # ---------------------------------------------------------------------------

@@ -7,11 +7,15 @@ shapes that do not fit.  The reference's format is positional and has no such
 check (runtime/src/lib.rs:4564-4604: a short or mismatched file ends in a panic
 inside ``read_exact``).
 
-Storage rules: floating-point tensors stored in 16 bits are kept in bfloat16
-when the engine runs in bfloat16; a tensor stored in 32 bits stays in 32 bits;
-integer tables become int32; the float32 engine up-casts every float tensor to
-float32 (bfloat16 -> float32 is exact: the 16 bits become the upper half of the
-word, as model/export_safetensors.py:38-40 does on the host).
+Storage rules: tensors stored in bfloat16 are kept so when the engine runs in
+bfloat16; a tensor stored in 32 bits stays in 32 bits; integer tables become
+int32; the float32 engine up-casts every float tensor to float32 (bfloat16 ->
+float32 is exact: the 16 bits become the upper half of the word, as
+model/export_safetensors.py:38-40 does on the host).  float16 has three bits
+more than bfloat16, so a float16 tensor is never rounded in silence: by default
+(``fp16="widen"``) it is widened to float32, which is exact and sends its
+products down the 32-bit path; ``fp16="round"`` rounds it to bfloat16 on
+request; ``fp16="refuse"`` reports it as a wrong dtype.
 
 :func:`write_random_model` is the random-weights mode: it writes a model folder
 (config.json and model.safetensors) from a configuration and a seed.
@@ -67,7 +71,10 @@ def _is_float(dt: torch.dtype) -> bool:
     return dt in (torch.bfloat16, torch.float16, torch.float32, torch.float64)
 
 
-def storage_dtype(stored: torch.dtype, role: str, engine_dtype: torch.dtype) -> torch.dtype:
+FP16_POLICIES = ("widen", "round", "refuse")
+
+
+def storage_dtype(stored: torch.dtype, role: str, engine_dtype: torch.dtype, fp16: str = "widen") -> torch.dtype:
     """The dtype a tensor has on the device, given how the file stores it."""
     if role == "table":
         return torch.int32
@@ -75,11 +82,15 @@ def storage_dtype(stored: torch.dtype, role: str, engine_dtype: torch.dtype) -> 
         return torch.float32
     if stored in (torch.float32, torch.float64):
         return torch.float32          # stored in 32 bits: stays so
+    if stored == torch.float16 and fp16 != "round":
+        return torch.float32          # exact; bfloat16 would drop three bits of every value
     return torch.bfloat16
 
 
 def load_tensors(folder: str, wanted: Dict[str, TensorSpec], engine_dtype: torch.dtype,
-                 device) -> Dict[str, torch.Tensor]:
+                 device, fp16: str = "widen") -> Dict[str, torch.Tensor]:
+    if fp16 not in FP16_POLICIES:
+        raise ValueError(f"fp16 must be one of {FP16_POLICIES}, got {fp16!r}")
     files = open_model_files(folder)
     missing, unexpected, wrong_shape, wrong_kind = [], [], [], []
     for name, spec in wanted.items():
@@ -95,6 +106,9 @@ def load_tensors(folder: str, wanted: Dict[str, TensorSpec], engine_dtype: torch
             wrong_kind.append((name, str(stored).replace("torch.", ""), "an integer type"))
         if spec.role != "table" and not _is_float(stored):
             wrong_kind.append((name, str(stored).replace("torch.", ""), "a floating-point type"))
+        if spec.role != "table" and stored == torch.float16 and fp16 == "refuse" and engine_dtype != torch.float32:
+            wrong_kind.append((name, "float16", "bfloat16 or float32 (float16 does not fit bfloat16 without rounding; "
+                                                "load with fp16='widen' or fp16='round')"))
     for name in files:
         if name not in wanted:
             unexpected.append(name)
@@ -106,7 +120,7 @@ def load_tensors(folder: str, wanted: Dict[str, TensorSpec], engine_dtype: torch
         if name not in files:
             continue
         f = files[name]
-        dt = storage_dtype(f.dtype(name), spec.role, engine_dtype)
+        dt = storage_dtype(f.dtype(name), spec.role, engine_dtype, fp16)
         t = f.tensor(name)
         # .to() copies out of the memory map; the device copy owns its bytes
         out[name] = t.to(device=device, dtype=dt, copy=True).contiguous()
