@@ -141,6 +141,28 @@ class ModelSpec:
                                       f"which does not own a cache itself")
 
 
+def spec_to_json(spec: "ModelSpec") -> str:
+    """The spec as JSON text, for the native host: part specs become ``{"kind", "params"}`` objects (also where
+    they stand inside another part's parameters), tuples become lists."""
+    def enc(v):
+        if isinstance(v, PartSpec):
+            return {"kind": v.kind, "params": {k: enc(x) for k, x in v.params.items()}}
+        if isinstance(v, dict):
+            return {str(k): enc(x) for k, x in v.items()}
+        if isinstance(v, (list, tuple)):
+            return [enc(x) for x in v]
+        if isinstance(v, (str, int, float, bool)) or v is None:
+            return v
+        raise ConfigError(f"a spec value of type {type(v).__name__} cannot be handed to the native host: {v!r}")
+    return json.dumps({
+        "architecture": spec.architecture, "hidden_size": spec.hidden_size, "vocab_size": spec.vocab_size,
+        "embedding": enc(spec.embedding), "final_norm": enc(spec.final_norm), "head": enc(spec.head),
+        "layers": [{"prefix": l.prefix, "block": enc(l.block), "mixer": enc(l.mixer), "feed_forward": enc(l.feed_forward)}
+                   for l in spec.layers],
+        "schedule": [{"layer": e.layer, "cache_of": e.cache_of} for e in spec.schedule],
+        "max_positions": spec.max_positions, "stop_ids": list(spec.stop_ids)})
+
+
 # ----------------------------------------------------------------------------
 # Registry: architecture name -> (config class, spec function)
 # ----------------------------------------------------------------------------

@@ -149,6 +149,92 @@ def require(names: Iterable[str]) -> None:
         return
     with ThreadPoolExecutor(max_workers=min(len(todo), os.cpu_count() or 4)) as ex:
         list(ex.map(_compile, todo))
+    write_manifest()
+
+
+def write_manifest() -> str:
+    """``manifest.json`` in the build folder: kernel library name -> file, for every library that is built.
+    The native host finds the kernels through it (the file names carry source hashes)."""
+    import json
+    entries = {n: os.path.basename(library_path(n)) for n in SOURCES if os.path.exists(library_path(n))}
+    path = os.path.join(_build_dir(), "manifest.json")
+    tmp = f"{path}.{os.getpid()}.tmp"
+    with open(tmp, "w") as f:
+        json.dump(entries, f, indent=1, sort_keys=True)
+    os.replace(tmp, path)
+    return path
+
+
+# ---------------------------------------------------------------------------
+# The native host: libtrapetum_b200.so (C interface, see native/trapetum_b200.h) and the gemma_run binary
+# ---------------------------------------------------------------------------
+_NATIVE = os.path.join(os.path.dirname(_HERE), "native")
+HOST_FLAGS = ["-std=c++17", "-O2", "-fPIC", "-Wall", "-Wno-unused-function"]
+
+
+def _native_digest() -> str:
+    h = hashlib.sha256()
+    for fn in sorted(os.listdir(_NATIVE)):
+        if fn.endswith((".hpp", ".cpp", ".h")):
+            with open(os.path.join(_NATIVE, fn), "rb") as f:
+                h.update(fn.encode() + f.read())
+    with open(os.path.join(_HERE, "decode_args.h"), "rb") as f:
+        h.update(f.read())
+    h.update(" ".join(HOST_FLAGS).encode())
+    return h.hexdigest()[:16]
+
+
+def native_library_path() -> str:
+    return os.path.join(_build_dir(), f"libtrapetum_b200-{_native_digest()}.so")
+
+
+def native_binary_path() -> str:
+    return os.path.join(_build_dir(), f"gemma_run-{_native_digest()}")
+
+
+def _host_compiler() -> str:
+    cxx = os.environ.get("CXX") or shutil.which("g++") or shutil.which("c++")
+    if not cxx:
+        raise KernelBuildError("no C++ compiler (g++) was found; the native host cannot be built")
+    return cxx
+
+
+def _run(cmd, what: str) -> None:
+    _say(f"compiling {what} ...")
+    t0 = time.time()
+    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if proc.returncode != 0:
+        raise KernelBuildError(f"building {what} failed:\n{proc.stdout}")
+    _say(f"  built {what} in {time.time() - t0:.1f} s")
+
+
+def build_native() -> str:
+    """Compile the native host library and the ``gemma_run`` binary (once per source state); returns the
+    library's path.  Stable names (``libtrapetum_b200.so``, ``gemma_run``) point at the current builds."""
+    lib, exe = native_library_path(), native_binary_path()
+    cuda = os.path.dirname(os.path.dirname(_nvcc()))
+    with _lock:
+        if not os.path.exists(lib):
+            tmp = f"{lib}.{os.getpid()}.tmp"
+            _run([_host_compiler()] + HOST_FLAGS + ["-shared", "-I", os.path.join(cuda, "include"),
+                  os.path.join(_NATIVE, "c_api.cpp"), "-o", tmp, "-L", os.path.join(cuda, "lib64"),
+                  "-lcudart_static", "-ldl", "-lrt", "-lpthread"], "the native host library")
+            os.replace(tmp, lib)
+        if not os.path.exists(exe):
+            tmp = f"{exe}.{os.getpid()}.tmp"
+            _run([_host_compiler()] + HOST_FLAGS + [os.path.join(_NATIVE, "gemma_run.cpp"), "-o", tmp, lib,
+                  "-Wl,-rpath,$ORIGIN", "-ldl", "-lpthread"], "the gemma_run binary")
+            os.replace(tmp, exe)
+        for target, name in ((lib, "libtrapetum_b200.so"), (exe, "gemma_run")):
+            link = os.path.join(_build_dir(), name)
+            try:
+                if os.path.lexists(link):
+                    os.unlink(link)
+                os.symlink(os.path.basename(target), link)
+            except OSError:
+                pass
+    write_manifest()
+    return lib
 
 
 def load(name: str) -> ctypes.CDLL:
@@ -173,4 +259,5 @@ def loaded() -> List[str]:
 
 def build_all() -> List[str]:
     require(SOURCES)
-    return [library_path(n) for n in SOURCES]
+    write_manifest()
+    return [library_path(n) for n in SOURCES] + [build_native(), native_binary_path()]
