@@ -129,9 +129,20 @@ class ClockSampler:
                 "samples": len(self.rows)}
 
 
+HOST = None              # which host runs the models (None: the library's default, the native host for these models)
+
+
 def build_model(cfg, seed):
     import trapetum_b200 as tb
-    return tb.random_model(cfg, seed, 0.02, 0.1, "bfloat16", "cuda:0")
+    return tb.random_model(cfg, seed, 0.02, 0.1, "bfloat16", "cuda:0", host=HOST)
+
+
+def launches():
+    """Kernel launches of this process so far, on whichever host runs the steps."""
+    import sys as _sys
+    from trapetum_b200.csrc import ops
+    nat = _sys.modules.get("trapetum_b200.native")
+    return ops.launches() + (nat.launches() if nat is not None and nat._lib is not None else 0)
 
 
 def weight_bytes(cfg):
@@ -198,7 +209,7 @@ def time_decode(engine, torch, ctxs, steps, warmup, vocab, repeats=REPEATS, e2e=
             engine.step(slots, [[t] for t in next(it)], borrow=True)
         torch.cuda.synchronize()
         regions, done = [], warmup
-        n0 = ops.launches()
+        n0 = launches()
         for _ in range(repeats):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
@@ -211,7 +222,7 @@ def time_decode(engine, torch, ctxs, steps, warmup, vocab, repeats=REPEATS, e2e=
             t1 = time.perf_counter()
             regions.append({"ms": round(e0.elapsed_time(e1) / steps, 4),
                             "sm_mhz": clocks.mhz_between(t0, t1) if clocks is not None else None})
-        out["launches"] = (ops.launches() - n0) // (repeats * steps)
+        out["launches"] = (launches() - n0) // (repeats * steps)
         ms = sorted(r["ms"] for r in regions)
         out.update(ms=ms[len(ms) // 2], ms_min=ms[0], ms_max=ms[-1], regions=regions)
         # the context each timed step reads: the tokens before it, and its own
@@ -221,15 +232,14 @@ def time_decode(engine, torch, ctxs, steps, warmup, vocab, repeats=REPEATS, e2e=
             # end to end: host token lists in, chosen token ids out, each step feeding the next
             cur = next(it)
             for _ in range(warmup):
-                cur = engine.step(slots, [[t] for t in cur], borrow=True, greedy=True).cpu().tolist()
+                cur = engine.step_tokens(slots, [[t] for t in cur])
             torch.cuda.synchronize()
             t0 = time.perf_counter()
             for _ in range(steps):
-                cur = engine.step(slots, [[t] for t in cur], borrow=True, greedy=True).cpu().tolist()
+                cur = engine.step_tokens(slots, [[t] for t in cur])
             torch.cuda.synchronize()
             out["e2e_ms"] = (time.perf_counter() - t0) * 1e3 / steps
-            shape = next((d for key, d in engine._decode.items() if key[0] == batch), None)
-            out["h2d"] = shape.h2d_bytes if shape is not None else 0
+            out["h2d"] = engine.last_h2d_bytes
         return out
     finally:
         engine.release(slots)
@@ -289,7 +299,7 @@ def other_runs(torch, which, steps, warmup, hbm_gbs, bf16_tflops, have=None):
     """The measurements beside the headline: per model shape, decode at batch 1/8/64 with caches of 2,048 tokens
     (the 9B shape: its unequal batch of 8, prompts U[64, 2048], decode and the prompts' own step), and a
     2,048-token prompt.  ``have``: (name, model) already built.  Models are built and freed one after another."""
-    from trapetum_b200.engine import Engine
+    from trapetum_b200 import Engine
     runs = {}
     for name in which:
         cfg = MODELS[name]
@@ -392,6 +402,8 @@ def main() -> int:
     ap.add_argument("--runs", default="2b,9b,27b",
                     help="model shapes whose other measurements (caches of 2,048 tokens, prefill) are taken: a comma "
                          "list out of 2b, 9b, 27b, or 'none'")
+    ap.add_argument("--host", default=None, choices=["native", "python"],
+                    help="the host that runs the steps (default: the library's own choice, the native host)")
     ap.add_argument("--prefill-only", action="store_true",
                     help="instead of the bench line: time only the prompt of 2,048 tokens and print one line about it")
     ap.add_argument("--leave-out", action="store_true",
@@ -411,7 +423,9 @@ def main() -> int:
     warmup = max(3, args.warmup)
 
     import torch
-    from trapetum_b200.engine import Engine
+    from trapetum_b200 import Engine
+    global HOST
+    HOST = "python" if args.leave_out else args.host
     full = MODELS[args.model]
     args.layers = args.layers or full["num_hidden_layers"]
     cfg = dict(full, num_hidden_layers=args.layers)
@@ -453,7 +467,8 @@ def main() -> int:
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": V, "window": cfg["sliding_window"],
                    "prefill_tokens": PREFILL_TOKENS, "l2": "inputs larger than L2 (each step reads every weight)",
-                   "timed": "median of %d regions of %d steps" % (REPEATS, args.steps), "peaks": peak_src},
+                   "timed": "median of %d regions of %d steps" % (REPEATS, args.steps), "peaks": peak_src,
+                   "host": type(engine).__module__.split(".")[-1].replace("engine", "python")},
         "clocks": csum,
         "spread": {"ms_min": r["ms_min"], "ms_max": r["ms_max"], "regions": r["regions"],
                    "ms_x_ghz": round(dev_ms * mhz / 1e3, 4) if mhz else None},

@@ -164,7 +164,7 @@ def test_schedule_repeats_a_layer_and_shares_a_cache(tmp_path, dtype):
     pc, pw = plain.load_folder(d)
     model = tb.load_model(d, dtype)
     eng = tb.Engine(model, 64 * 8)
-    assert len(eng.cache.entry_group) == 3                         # entries 0, 1, 2 own lines; entry 3 reads entry 1's
+    assert sum(g.k.shape[0] for g in eng.cache.groups) == 3        # entries 0, 1, 2 own lines; entry 3 reads entry 1's
     prompts = make_prompts(256, [30, 12], seed=8)
     truth = [plain.forward(pc, pw, p, schedule=LOOPED) for p in prompts]
     tol = TOL[dtype] if dtype == "float32" else bf16_budget(pc, pw, prompts, LOOPED)
@@ -565,8 +565,9 @@ def _biased_plain(cfg, w, ids, rnd=lambda x: x):
     return (rnd(norm(h, w["out_norm.weight"])) @ w["head.weight"].T).float()
 
 
+@pytest.mark.parametrize("host", ["python", "native"])
 @pytest.mark.parametrize("dtype,hd", [("float32", 24), ("bfloat16", 64), ("bfloat16", 32)])
-def test_attention_with_biases_and_head_norms_is_a_matter_of_parameters(tmp_path, dtype, hd):
+def test_attention_with_biases_and_head_norms_is_a_matter_of_parameters(tmp_path, dtype, hd, host):
     """The library's attention part with a bias on each projection and an RMS norm on every query and key head:
     a model made of it is registered from here, built and stepped (prompts, then token by token, in a batch of
     unequal lengths) against a plain computation.  With a head size that the tensor-core decode kernel takes,
@@ -587,8 +588,8 @@ def test_attention_with_biases_and_head_norms_is_a_matter_of_parameters(tmp_path
             stored[k] = (stored[k].float() * 3.0).to(stored[k].dtype)
     save_file(stored, d + "/model.safetensors")
     pw = plain.load_folder(d)[1]
-    model = tb.load_model(d, dtype)
-    assert not any(b.mixer.fused_decode() for b in model.blocks)
+    assert not any(b.mixer.fused_decode() for b in tb.load_model(d, dtype, host="python").blocks)
+    model = tb.load_model(d, dtype, host=host)
     eng = tb.Engine(model, 64 * 6, max_slots=3)
     for g in eng.cache.groups:
         g.k.fill_(float("nan")); g.v.fill_(float("nan"))

@@ -25,18 +25,22 @@ __version__ = "0.2.0"
 HOSTS = ("python", "native")
 
 
-def _host(host):
-    """Which host runs a model: "native" (the C++ library, for models whose parts all have native classes) or
-    "python" (this package's own loop, which also runs parts written in Python).  None: $TRAPETUM_HOST, else python."""
-    host = host or _os.environ.get("TRAPETUM_HOST") or "python"
+def _host(host, config) -> str:
+    """Which host runs a model.  "native": the C++ library (``trapetum_b200.native``), for models whose parts all
+    have native classes; it refuses others.  "python": this package's own loop, which also runs parts written in
+    Python.  "auto" (the default; or $TRAPETUM_HOST): native where the model allows it, else python."""
+    host = host or _os.environ.get("TRAPETUM_HOST") or "auto"
+    if host == "auto":
+        from . import native
+        return "native" if native.is_native(load_config(config)[1]) else "python"
     if host not in HOSTS:
-        raise ValueError(f"host must be one of {HOSTS}, got {host!r}")
+        raise ValueError(f"host must be one of {HOSTS + ('auto',)}, got {host!r}")
     return host
 
 
 def load_model(folder, dtype="bfloat16", device="cuda:0", fp16="widen", host=None):
     """Read config.json, pick the model by its architecture name, load and bind the weights."""
-    if _host(host) == "native":
+    if _host(host, folder) == "native":
         from . import native
         return native.load_model(folder, dtype, device, fp16)
     return _python_load_model(folder, dtype, device, fp16)
@@ -44,7 +48,7 @@ def load_model(folder, dtype="bfloat16", device="cuda:0", fp16="widen", host=Non
 
 def random_model(config, seed=0, std=0.02, norm_std=0.1, dtype="bfloat16", device="cuda:0", host=None):
     """A model of ``config`` with random weights made on the device (the values that ``write_random_model`` stores)."""
-    if _host(host) == "native":
+    if _host(host, config) == "native":
         from . import native
         return native.random_model(config, seed, std, norm_std, dtype, device)
     return _python_random_model(config, seed, std, norm_std, dtype, device)

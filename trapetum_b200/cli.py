@@ -45,6 +45,9 @@ def main(argv=None) -> int:
                     help="stop token id (may be repeated; default: the model's eos_token_id)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--device", default="cuda:0")
+    ap.add_argument("--host", default=None, choices=["native", "python", "auto"],
+                    help="which host runs the model: the native library, this package's own loop, or (default) the "
+                         "native one where every part of the model has a native class")
     ap.add_argument("--max_batch", "--max-batch", type=int, default=64)
     ap.add_argument("--random-weights", "--random_weights", metavar="CONFIG_JSON",
                     help="seeded random weights for this config.json: written to --out, or, without --out, made on "
@@ -74,9 +77,9 @@ def main(argv=None) -> int:
     t0 = time.time()
     if args.random_weights:
         with open(args.random_weights) as f:
-            model = tb.random_model(json.load(f), args.seed, args.std, args.norm_std, args.dtype, args.device)
+            model = tb.random_model(json.load(f), args.seed, args.std, args.norm_std, args.dtype, args.device, host=args.host)
     else:
-        model = tb.load_model(args.model, args.dtype, args.device)
+        model = tb.load_model(args.model, args.dtype, args.device, host=args.host)
     print(f"loaded in {time.time() - t0:.1f}s vocab={model.vocab_size} "
           + " ".join(f"prompt={len(p)} tokens {p}" for p in prompts), flush=True)
     import torch

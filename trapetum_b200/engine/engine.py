@@ -125,6 +125,20 @@ class Engine:
             self.cache.shrink(growth)
             raise
 
+    def step_tokens(self, slots: Sequence[int], tokens: Sequence[Sequence[int]]) -> List[int]:
+        """One step of a generation loop: host token lists in, each sequence's greedy next token out (host ints)."""
+        return self.step(slots, tokens, borrow=True, greedy=True).cpu().tolist()
+
+    @property
+    def graphs_captured(self) -> int:
+        """How many decode-step shapes run as captured graphs by now."""
+        return sum(1 for d in self._decode.values() if d.graph is not None)
+
+    @property
+    def last_h2d_bytes(self) -> int:
+        """Bytes of the last decode step's one host-to-device copy (its integer inputs and page tables)."""
+        return max((d.h2d_bytes for d in self._decode.values()), default=0)
+
     def check_kernels(self) -> None:
         """Raise :class:`~trapetum_b200.csrc.ops.KernelError` if a kernel's bounded wait has run out since
         the last check (its results are then garbage).  Synchronises the device, so callers place it where they

@@ -12,13 +12,12 @@ from typing import Dict, Optional
 
 import numpy as np
 
-from .engine import Engine
-from .model import load_model
 
 
 class Replayer:
-    def __init__(self, model_dir: str, dtype: str, max_tokens: int, device: str = "cuda:0"):
-        self.engine = Engine(load_model(model_dir, dtype, device), max_tokens)
+    def __init__(self, model_dir: str, dtype: str, max_tokens: int, device: str = "cuda:0", host=None):
+        import trapetum_b200 as tb
+        self.engine = tb.Engine(tb.load_model(model_dir, dtype, device, host=host), max_tokens)
         self.slot_of: Dict[str, int] = {}
 
     def run_step(self, rec: dict) -> Optional[np.ndarray]:

@@ -329,6 +329,19 @@ class Engine:
             t = _tensor(logits.value, (rows.value, self.vocab_size), torch.float32, self.device)
         return t if borrow else t.clone()
 
+    def step_tokens(self, slots: Sequence[int], tokens: Sequence[Sequence[int]]) -> List[int]:
+        """One step of a generation loop: host token lists in, each sequence's greedy next token out (host ints)."""
+        self._on_torch_stream()
+        if len(tokens) != len(slots):
+            raise StepError(f"{len(slots)} slots but {len(tokens)} token lists")
+        n = len(slots)
+        sl, k0 = _ints(list(slots))
+        flat, k1 = _ints([int(t) for seq in tokens for t in seq])
+        n_new, k2 = _ints([len(seq) for seq in tokens])
+        out = (c_int * max(1, n))()
+        _ok(lib().tb_step_tokens(c_void_p(self._h), sl, c_int(n), flat, n_new, out), "step")
+        return list(out[:n])
+
     def check_kernels(self) -> None:
         err = lib().tb_kernel_errors(c_void_p(self._h)).decode()
         if err:

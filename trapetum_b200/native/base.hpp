@@ -86,6 +86,8 @@ class Arena {
 public:
     enum Region { STEP = 0, LAYER_A = 1, LAYER_B = 2 };
     void reserve(size_t step_bytes, size_t layer_bytes) {
+        step_bytes = (step_bytes + 255) & ~(size_t)255;         // every region starts on a 256-byte boundary
+        layer_bytes = (layer_bytes + 255) & ~(size_t)255;
         cap_[0] = step_bytes; cap_[1] = cap_[2] = layer_bytes;
         buf_.alloc(step_bytes + 2 * layer_bytes);
         base_[0] = 0; base_[1] = step_bytes; base_[2] = step_bytes + layer_bytes;

@@ -184,6 +184,14 @@ int tb_step_host(tb_engine* e, const int* slots, int n_seqs, const int* tokens, 
     TB_CATCH_STATUS
 }
 
+int tb_step_tokens(tb_engine* e, const int* slots, int n_seqs, const int* tokens, const int* n_new, int* out_ids) {
+    TB_TRY
+    StepResult r = do_step(e, slots, n_seqs, tokens, n_new, nullptr, nullptr, true);
+    e->e->read_ids(r.ids, r.rows, out_ids);
+    return TB_OK;
+    TB_CATCH_STATUS
+}
+
 int tb_generate(tb_engine* e, const int* prompts, const int* prompt_lens, int n_prompts, const tb_sampling* params,
                 const int* stop_ids, int n_stop, int max_batch, tb_on_token on_token, void* user, int* out_tokens,
                 int* out_lens, int out_capacity) {

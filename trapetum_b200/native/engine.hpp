@@ -160,6 +160,15 @@ public:
         }
     }
 
+    // Chosen ids from the device to the caller's memory, through a pinned buffer; returns when they have arrived.
+    void read_ids(const int* dev_ids, int n, int* out) {
+        if (n <= 0) return;
+        ids_host_.reserve((size_t)n);
+        cuda_ok(cudaMemcpyAsync(ids_host_.host, dev_ids, (size_t)n * 4, cudaMemcpyDeviceToHost, ops.stream), "reading the chosen tokens");
+        synchronize();
+        memcpy(out, ids_host_.host, (size_t)n * 4);
+    }
+
     // Error words of the kernels with bounded waits: "" when no wait ever ran out.  Synchronises and clears them.
     std::string kernel_errors() {
         synchronize();
@@ -473,7 +482,7 @@ private:
     }
 
     Arena arena_;
-    InputBuffer in_;
+    InputBuffer in_, ids_host_;
     DeviceBuffer tickets_;
     cudaStream_t own_stream_ = nullptr;
     bool graph_safe_ = true;
@@ -578,7 +587,7 @@ inline std::vector<std::vector<int>> generate(Engine& eng, const std::vector<std
                 const int rows = (int)live.size();
                 chosen.resize(rows);
                 if (greedy) {
-                    cuda_ok(cudaMemcpyAsync(chosen.data(), r.ids, rows * 4, cudaMemcpyDeviceToHost, eng.ops.stream), "reading the chosen tokens");
+                    eng.read_ids(r.ids, rows, chosen.data());
                 } else {
                     // per row: temperature, top_p, penalty, draw; and the recent tokens if there is a penalty
                     fhost.resize(4 * rows);
@@ -602,9 +611,8 @@ inline std::vector<std::vector<int>> generate(Engine& eng, const std::vector<std
                     int* ids = eng.sized_run(sample_arena, [&]() {
                         return eng.ops.sample(logits, f, f + rows, f + 2 * rows, f + 3 * rows, recent, REPETITION_WINDOW, p.top_p < 1.f);
                     });
-                    cuda_ok(cudaMemcpyAsync(chosen.data(), ids, rows * 4, cudaMemcpyDeviceToHost, eng.ops.stream), "reading the chosen tokens");
+                    eng.read_ids(ids, rows, chosen.data());
                 }
-                eng.synchronize();
                 std::vector<Seq> next;
                 for (int i = 0; i < rows; i++) {
                     Seq& s = live[i];

@@ -304,6 +304,9 @@ public:
         if (line.owner) {
             const bool plain = !b_qkv_ && !q_norm_ && !k_norm_;
             Mat qkv;
+            // keys and values that a later call of this step reads must outlive this layer's scratch
+            const Arena::Region region = ops.arena->current();
+            if (ctx.is_prefill && line.shared) ops.arena->use(Arena::STEP);
             if (plain && dt == BF16 && x.rows <= 128 && Ops::gemm_tc_takes(x, w_qkv_)) {
                 // few tokens: the product comes as split-K partial sums, which the rotation kernel adds up
                 Partials part = ops.gemm_tc_partials(x, w_qkv_);
@@ -322,6 +325,7 @@ public:
                 finish_projection(ops, qkv, n_heads_, n_kv_);
                 position_->rotate_and_store(ops, qkv, n_heads_, n_kv_, ctx, line, true, nullptr);
             }
+            ops.arena->use(region);
             q = qkv.cols_slice(0, qd_);
             k = qkv.cols_slice(qd_, kvd_);
             v = qkv.cols_slice(qd_ + kvd_, kvd_);

@@ -64,6 +64,10 @@ int tb_step(tb_engine* e, const int* slots, int n_seqs, const int* tokens, const
 int tb_step_host(tb_engine* e, const int* slots, int n_seqs, const int* tokens, const int* n_new, const int* want,
                  const int* n_want, float* out_logits, long long capacity, int* out_rows);
 
+/* One step of a generation loop: the tokens in, each sequence's greedy next token out (host memory, one id per
+ * sequence: the largest logit at its last token of this step).  Returns when the ids have arrived. */
+int tb_step_tokens(tb_engine* e, const int* slots, int n_seqs, const int* tokens, const int* n_new, int* out_ids);
+
 typedef struct tb_sampling {
     float temperature;              /* <= 0: greedy */
     float top_p;                    /* default 0.95 */
