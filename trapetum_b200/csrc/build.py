@@ -257,7 +257,25 @@ def loaded() -> List[str]:
     return list(_libs)
 
 
+def prune() -> int:
+    """Remove libraries of earlier source states from the build folder (their names carry other hashes)."""
+    keep = {os.path.basename(library_path(n)) for n in SOURCES}
+    keep |= {os.path.basename(native_library_path()), os.path.basename(native_binary_path()), "manifest.json",
+             "libtrapetum_b200.so", "gemma_run"}
+    n = 0
+    for fn in os.listdir(_build_dir()):
+        if fn not in keep and (fn.startswith(("tb_", "libtrapetum_b200-", "gemma_run-")) or fn.endswith(".tmp")):
+            try:
+                os.unlink(os.path.join(_build_dir(), fn))
+                n += 1
+            except OSError:
+                pass
+    return n
+
+
 def build_all() -> List[str]:
     require(SOURCES)
     write_manifest()
-    return [library_path(n) for n in SOURCES] + [build_native(), native_binary_path()]
+    out = [library_path(n) for n in SOURCES] + [build_native(), native_binary_path()]
+    prune()
+    return out
