@@ -63,6 +63,14 @@ struct InputBuffer {
     const int* d(size_t off) const { return (const int*)dev.p + off; }
 };
 
+// The ids of a step taken from the device: row i of the step gets ids[src_rows[i]] (the greedy choice of an
+// earlier step that the host has not read yet).
+struct DeviceIds {
+    const int* ids = nullptr;
+    int n_src = 0;
+    std::vector<int> src_rows;
+};
+
 struct StepResult {
     const float* logits = nullptr;       // device, [rows, vocab] (null when greedy or nothing wanted)
     const int* ids = nullptr;            // device, [rows] chosen ids (greedy steps)
@@ -124,7 +132,7 @@ public:
     // in the order of the sequences and of the lists (want null: each sequence's last token).  greedy: instead of
     // the logits, the ids of the largest logit at each wanted place (the smallest id on a tie).
     StepResult step(const std::vector<int>& slots, const std::vector<std::vector<int>>& tokens,
-                    const std::vector<std::vector<int>>* want_in, bool greedy) {
+                    const std::vector<std::vector<int>>* want_in, bool greedy, const DeviceIds* chained = nullptr) {
         const bool is_prefill = classify(slots, tokens);
         const int B = (int)slots.size(), V = model.vocab;
         std::vector<int> lens(B);
@@ -152,12 +160,21 @@ public:
         }
         cache->grow(slots, lens);                    // throws CacheFull before anything ran
         try {
-            if (!is_prefill && use_graphs && graph_safe_) return decode_step(slots, tokens, want, before, after, greedy);
+            if (!is_prefill && use_graphs && graph_safe_) return decode_step(slots, tokens, want, before, after, greedy, chained);
+            if (chained) throw StepError("a step that takes its ids from the device needs the captured decode path");
             return eager_step(slots, tokens, want, before, after, lens, is_prefill, greedy);
         } catch (...) {
             cache->shrink(slots, lens);              // the cache must not claim tokens whose keys were never written
             throw;
         }
+    }
+
+    // One token each for `slots`, the tokens being the greedy choice of an earlier step, still on the device (the host
+    // may read them later): the next step of a generation loop is queued before the last one's tokens have arrived.
+    bool can_chain() const { return use_graphs && graph_safe_; }
+    StepResult step_chained(const std::vector<int>& slots, const DeviceIds& from) {
+        std::vector<std::vector<int>> tokens(slots.size(), std::vector<int>{0});
+        return step(slots, tokens, nullptr, true, &from);
     }
 
     // Chosen ids from the device to the caller's memory, through a pinned buffer; returns when they have arrived.
@@ -226,7 +243,7 @@ private:
         Arena arena;
         std::vector<size_t> table_off;
         std::vector<int> widths;
-        size_t ints = 0, ids_off = 0, pos_off = 0, tseq_off = 0, start_off = 0, after_off = 0, slot_off = 0;
+        size_t ints = 0, ids_off = 0, pos_off = 0, tseq_off = 0, start_off = 0, after_off = 0, slot_off = 0, src_off = 0;
         std::vector<int> table_slots;
         long long table_epoch = -1;
         cudaGraphExec_t exec = nullptr;
@@ -344,7 +361,7 @@ private:
 
     StepResult decode_step(const std::vector<int>& slots, const std::vector<std::vector<int>>& tokens,
                            const std::vector<std::vector<int>>& want, const std::vector<int>& before, const std::vector<int>& after,
-                           bool greedy) {
+                           bool greedy, const DeviceIds* chained = nullptr) {
         const int B = (int)slots.size();
         int max_after = 0;
         for (int a : after) max_after = std::max(max_after, a);
@@ -369,8 +386,24 @@ private:
             d.table_slots = slots;
             for (size_t gi = 0; gi < d.widths.size(); gi++) fill_tables(h + d.table_off[gi], d.widths[gi], (int)gi, slots);
         }
+        bool same_rows = false;
+        if (chained) {
+            if ((int)chained->src_rows.size() != B) throw StepError("a chained step needs one source row per sequence");
+            same_rows = chained->n_src == B;
+            for (int i = 0; i < B; i++) {
+                if (chained->src_rows[i] < 0 || chained->src_rows[i] >= chained->n_src) throw StepError("a chained step's source row is out of range");
+                same_rows &= chained->src_rows[i] == i;
+                h[d.src_off + i] = chained->src_rows[i];
+            }
+        }
         d.in.upload(d.ints, ops.stream);
         h2d_bytes_last = (long long)d.ints * 4;
+        if (chained) {
+            // the ids come from the device, after the copy of the other inputs
+            int* dst = (int*)d.in.dev.p + d.ids_off;
+            if (same_rows) cuda_ok(cudaMemcpyAsync(dst, chained->ids, (size_t)B * 4, cudaMemcpyDeviceToDevice, ops.stream), "chaining ids");
+            else ops.gather_rows_into(chained->ids, d.in.d(d.src_off), dst, B, 1, chained->n_src);
+        }
         d.hits++;
 
         StepCtx ctx;
@@ -467,6 +500,7 @@ private:
         d->start_off = ints; ints += align4(B + 1);
         d->after_off = ints; ints += align4(B);
         d->slot_off = ints; ints += align4(B);
+        d->src_off = ints; ints += align4(B);
         for (size_t gi = 0; gi < cache->groups().size(); gi++) {
             d->widths.push_back(cache->table_width((int)gi, cap));
             d->table_off.push_back(ints);
@@ -544,6 +578,31 @@ inline std::vector<std::vector<int>> plan_batches(const std::vector<int>& prompt
     return batches;
 }
 
+// Chosen ids on their way from the device to the host: the copy is queued at once, the host waits for it later.
+struct IdsReader {
+    int* host = nullptr;
+    size_t cap = 0;
+    cudaEvent_t done = nullptr;
+    ~IdsReader() {
+        if (host) cudaFreeHost(host);
+        if (done) cudaEventDestroy(done);
+    }
+    void start(Engine& eng, const int* dev_ids, int n) {
+        if ((size_t)n > cap) {
+            if (host) cudaFreeHost(host);
+            cap = std::max<size_t>(256, (size_t)n * 2);
+            cuda_ok(cudaMallocHost((void**)&host, cap * 4), "pinned ids");
+        }
+        if (!done) cuda_ok(cudaEventCreateWithFlags(&done, cudaEventDisableTiming), "event");
+        cuda_ok(cudaMemcpyAsync(host, dev_ids, (size_t)n * 4, cudaMemcpyDeviceToHost, eng.ops.stream), "reading the chosen tokens");
+        cuda_ok(cudaEventRecord(done, eng.ops.stream), "event");
+    }
+    const int* wait() {
+        cuda_ok(cudaEventSynchronize(done), "waiting for the chosen tokens");
+        return host;
+    }
+};
+
 typedef int (*OnToken)(int request, int token, void* user);        // a non-zero return ends the generation
 
 // Generate up to params.max_tokens new ids for every prompt.  A sequence ends at a stop id (which is not emitted,
@@ -561,7 +620,7 @@ inline std::vector<std::vector<int>> generate(Engine& eng, const std::vector<std
     for (auto& q : prompts) lens.push_back((int)q.size());
     const bool greedy = !p.needs_sampler();
     const int max_pos = eng.model.max_positions;
-    struct Seq { int request, slot, length; std::deque<int> recent; int count = 0; std::vector<int> out; };
+    struct Seq { int request, slot, length; std::deque<int> recent; int count = 0; std::vector<int> out; int row = 0; bool queued = false; };
     DeviceBuffer fbuf, rbuf;
     Arena sample_arena;
     sample_arena.reserve(1 << 16, 256);
@@ -583,6 +642,61 @@ inline std::vector<std::vector<int>> generate(Engine& eng, const std::vector<std
             for (auto& s : live) toks.push_back(prompts[s.request]);
             StepResult r = eng.step(slots, toks, nullptr, greedy);
             int steps = 0;
+            if (greedy && eng.can_chain()) {
+                // Greedy decoding, pipelined: the next step is queued with its ids taken on the device (the choice that
+                // the step before it made) before the host has read those ids.  The host reads them one step behind,
+                // emits them and decides who goes on.  What it cannot know ahead is a stop id: a sequence that turns
+                // out to have stopped was stepped once too often, which costs one row of one step and nothing else
+                // (its slot and pages go back; that row's result is never read).
+                IdsReader readers[2];
+                int cur = 0;
+                for (size_t i = 0; i < live.size(); i++) live[i].row = (int)i;
+                readers[cur].start(eng, r.ids, r.rows);
+                while (!live.empty()) {
+                    // who goes on unless the pending token turns out to be a stop id
+                    std::vector<int> next_slots;
+                    DeviceIds from;
+                    from.ids = r.ids; from.n_src = r.rows;
+                    for (auto& s : live) {
+                        const bool known_last = (int)s.out.size() + 1 >= p.max_tokens || s.length + 1 > max_pos - 1;
+                        s.queued = !known_last && !stop_all;
+                        if (s.queued) { next_slots.push_back(s.slot); from.src_rows.push_back(s.row); }
+                    }
+                    StepResult r2;
+                    if (!next_slots.empty()) {
+                        r2 = eng.step_chained(next_slots, from);
+                        readers[cur ^ 1].start(eng, r2.ids, r2.rows);
+                    }
+                    const int* ids = readers[cur].wait();
+                    std::vector<Seq> next;
+                    int next_row = 0;
+                    for (auto& s : live) {
+                        const int tok = ids[s.row];
+                        const bool is_stop = stops.count(tok) != 0;
+                        if (!is_stop) {
+                            s.out.push_back(tok);
+                            if (on_token && on_token(s.request, tok, user)) stop_all = true;
+                        }
+                        const int row2 = s.queued ? next_row++ : -1;
+                        if (s.queued && !is_stop && !stop_all) {
+                            s.row = row2;
+                            s.length++;
+                            next.push_back(std::move(s));
+                        } else {
+                            outputs[s.request] = s.out;
+                            eng.release({s.slot});
+                        }
+                    }
+                    live = std::move(next);
+                    r = r2;
+                    cur ^= 1;
+                    steps++;
+                    if (live.empty() || steps % 64 == 0) {
+                        const std::string err = eng.kernel_errors();
+                        if (!err.empty()) throw Error("a kernel gave up waiting and its results are not valid: " + err);
+                    }
+                }
+            }
             while (!live.empty()) {
                 const int rows = (int)live.size();
                 chosen.resize(rows);

@@ -71,6 +71,14 @@ public:
         return out;
     }
 
+    // out[i] = in[rows[i]] for rows of `width` 32-bit words, into memory of the caller's
+    void gather_rows_into(const void* in, const int* rows, void* out, int n, int width, int n_rows) {
+        if (dry()) return;
+        auto& l = K().lib("embed");
+        static auto f = l.sym<int (*)(const float*, const int*, float*, int, int, int, cudaStream_t)>("tb_gather_rows");
+        launched(l, f((const float*)in, rows, (float*)out, n, width, n_rows, stream), "gather_rows");
+    }
+
     // ---- norms -----------------------------------------------------------------------------------------
     Mat rmsnorm(const Mat& x, const Mat& w, float eps, float offset, DType out_dt) {
         need(x.contiguous() && w.cols == x.cols, "rmsnorm: x and w do not fit");
