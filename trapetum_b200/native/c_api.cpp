@@ -272,6 +272,100 @@ int tb_cache_grow(tb_engine* e, const int* slots, const int* growth, int n) {
     TB_CATCH_STATUS
 }
 
+const char* tb_spec_from_config(const char* config_json) {
+    static thread_local std::string out;
+    try {
+        out = spec_for_config(Json::parse(config_json ? config_json : "")).dump();
+        return out.c_str();
+    } catch (const std::exception& ex) {
+        fail(ex);
+        return nullptr;
+    }
+}
+
+int tb_check_weights(const char* folder, const char* spec_json, const char* dtype, const char* fp16) {
+    TB_TRY
+    Model m(Json::parse(spec_json ? spec_json : ""), parse_dtype(dtype), 0);
+    check_tensors(folder ? folder : "", m.wanted(), m.rt.dt, fp16 && *fp16 ? fp16 : "widen");
+    return TB_OK;
+    TB_CATCH_STATUS
+}
+
+int tb_plan_batches(const int* prompt_lens, int n, int max_new, int max_batch, long long max_tokens, int max_positions, int* batch_of) {
+    try {
+        auto batches = plan_batches(std::vector<int>(prompt_lens, prompt_lens + n), max_new, max_batch, max_tokens, max_positions);
+        for (size_t b = 0; b < batches.size(); b++)
+            for (int i : batches[b]) batch_of[i] = (int)b;
+        return (int)batches.size();
+    } catch (const std::exception& ex) {
+        fail(ex);
+        return -1;
+    }
+}
+
+struct tb_sim_cache {
+    std::unique_ptr<Cache> c;
+};
+
+tb_sim_cache* tb_sim_cache_new(const char* needs_json, long long max_tokens, int max_slots) {
+    TB_TRY
+    Json j = Json::parse(needs_json ? needs_json : "[]");
+    std::map<int, CacheNeed> needs;
+    for (auto& e : j.arr) {
+        CacheNeed n;
+        if (e.has("state_bytes")) { n.kind = CacheNeed::STATE; n.state_bytes = (size_t)e.at("state_bytes").integer("state_bytes"); }
+        else {
+            n.kind = CacheNeed::KV;
+            n.n_kv_heads = (int)e.at("n_kv_heads").integer("n_kv_heads");
+            n.head_dim = (int)e.at("head_dim").integer("head_dim");
+            n.window = e.has("window") && !e.at("window").is_null() ? (int)e.at("window").integer("window") : 0;
+        }
+        needs[(int)e.at("entry").integer("entry")] = n;
+    }
+    std::unique_ptr<tb_sim_cache> h(new tb_sim_cache);
+    h->c.reset(new Cache(needs, {}, max_tokens, BF16, max_slots, false));
+    return h.release();
+    TB_CATCH_NULL
+}
+void tb_sim_cache_free(tb_sim_cache* c) { delete c; }
+int tb_sim_cache_claim(tb_sim_cache* c) {
+    try { return c->c->claim(); } catch (const std::exception& ex) { fail(ex); return -1; }
+}
+int tb_sim_cache_grow(tb_sim_cache* c, const int* slots, const int* growth, int n) {
+    TB_TRY
+    c->c->grow(std::vector<int>(slots, slots + n), std::vector<int>(growth, growth + n));
+    return TB_OK;
+    TB_CATCH_STATUS
+}
+int tb_sim_cache_shrink(tb_sim_cache* c, const int* slots, const int* growth, int n) {
+    TB_TRY
+    c->c->shrink(std::vector<int>(slots, slots + n), std::vector<int>(growth, growth + n));
+    return TB_OK;
+    TB_CATCH_STATUS
+}
+int tb_sim_cache_release(tb_sim_cache* c, int slot) {
+    TB_TRY
+    c->c->release(slot);
+    return TB_OK;
+    TB_CATCH_STATUS
+}
+int tb_sim_cache_check(tb_sim_cache* c) {
+    TB_TRY
+    c->c->check();
+    return TB_OK;
+    TB_CATCH_STATUS
+}
+long long tb_sim_cache_length(tb_sim_cache* c, int slot) { return c->c->slot_held(slot) ? c->c->length(slot) : -1; }
+int tb_sim_cache_pages(tb_sim_cache* c, int slot, int group, int* out, int capacity) {
+    try {
+        const auto& pg = c->c->pages(slot, group);
+        for (size_t i = 0; i < pg.size() && (int)i < capacity; i++) out[i] = pg[i];
+        return (int)pg.size();
+    } catch (const std::exception& ex) { fail(ex); return -1; }
+}
+int tb_sim_cache_groups(tb_sim_cache* c) { return (int)c->c->groups().size(); }
+long long tb_sim_cache_epoch(tb_sim_cache* c) { return c->c->epoch; }
+
 const char* tb_kernel_errors(tb_engine* e) {
     try {
         e->errors = e->e->kernel_errors();

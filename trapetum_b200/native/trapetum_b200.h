@@ -98,6 +98,31 @@ int tb_cache_live(tb_engine* e, int* out, int capacity);                /* retur
 int tb_cache_check(tb_engine* e);
 int tb_cache_grow(tb_engine* e, const int* slots, const int* growth, int n);     /* room without a step (measurements) */
 
+/* What needs no GPU (tools, tests).
+ * tb_spec_from_config: the spec this host builds from a config.json's text (NULL on error).
+ * tb_check_weights: holds a folder's weight files against a spec; TB_OK, or TB_ERROR with one message that lists
+ * everything that does not fit.
+ * tb_plan_batches: cuts requests into batches as tb_generate does; batch_of[i] is request i's batch; returns the
+ * number of batches, -1 on error.
+ * tb_sim_cache_*: the cache's bookkeeping without storage.  needs_json: [{"entry", "n_kv_heads", "head_dim",
+ * "window" (0: none)} or {"entry", "state_bytes"}, ...]. */
+const char* tb_spec_from_config(const char* config_json);
+int tb_check_weights(const char* folder, const char* spec_json, const char* dtype, const char* fp16);
+int tb_plan_batches(const int* prompt_lens, int n, int max_new, int max_batch, long long max_tokens, int max_positions,
+                    int* batch_of);
+typedef struct tb_sim_cache tb_sim_cache;
+tb_sim_cache* tb_sim_cache_new(const char* needs_json, long long max_tokens, int max_slots);
+void tb_sim_cache_free(tb_sim_cache* c);
+int tb_sim_cache_claim(tb_sim_cache* c);                                         /* the slot, -1 on error */
+int tb_sim_cache_grow(tb_sim_cache* c, const int* slots, const int* growth, int n);
+int tb_sim_cache_shrink(tb_sim_cache* c, const int* slots, const int* growth, int n);
+int tb_sim_cache_release(tb_sim_cache* c, int slot);
+int tb_sim_cache_check(tb_sim_cache* c);
+long long tb_sim_cache_length(tb_sim_cache* c, int slot);
+int tb_sim_cache_pages(tb_sim_cache* c, int slot, int group, int* out, int capacity);
+int tb_sim_cache_groups(tb_sim_cache* c);
+long long tb_sim_cache_epoch(tb_sim_cache* c);
+
 /* "" when no kernel's bounded wait has run out since the last call; synchronises. */
 const char* tb_kernel_errors(tb_engine* e);
 long long tb_kernel_launches(void);

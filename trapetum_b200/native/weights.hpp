@@ -164,11 +164,18 @@ inline DType storage_dtype(const std::string& stored, const std::string& role, D
     return BF16;
 }
 
-// Reads the wanted tensors of a model folder onto the device; every misfit goes into ONE error.
-inline TensorMap load_tensors(const std::string& folder, const WantedTensors& wanted, DType engine, const std::string& fp16 = "widen") {
-    if (fp16 != "widen" && fp16 != "round" && fp16 != "refuse") throw Error("fp16 must be widen, round or refuse, got " + fp16);
+struct OpenedWeights {
     std::vector<std::unique_ptr<SafetensorsFile>> files;
     std::map<std::string, SafetensorsFile*> by_name;
+};
+
+// Opens the weight files of a model folder and holds them against what the model wants; every misfit (missing,
+// unexpected, wrongly shaped, wrongly typed) goes into ONE error.  Needs no GPU.
+inline OpenedWeights check_tensors(const std::string& folder, const WantedTensors& wanted, DType engine, const std::string& fp16 = "widen") {
+    if (fp16 != "widen" && fp16 != "round" && fp16 != "refuse") throw Error("fp16 must be widen, round or refuse, got " + fp16);
+    OpenedWeights opened;
+    auto& files = opened.files;
+    auto& by_name = opened.by_name;
     const std::string idx = folder + "/model.safetensors.index.json", single = folder + "/model.safetensors";
     if (file_exists(idx)) {
         Json j = Json::parse(read_text(idx));
@@ -232,7 +239,13 @@ inline TensorMap load_tensors(const std::string& folder, const WantedTensors& wa
         if (!wrong_kind.empty()) msg += fmt("\n  wrong dtype (%zu): ", wrong_kind.size()) + join(wrong_kind);
         throw Error(msg);
     }
+    return opened;
+}
 
+// Reads the wanted tensors of a model folder onto the device.
+inline TensorMap load_tensors(const std::string& folder, const WantedTensors& wanted, DType engine, const std::string& fp16 = "widen") {
+    OpenedWeights opened = check_tensors(folder, wanted, engine, fp16);
+    auto& by_name = opened.by_name;
     TensorMap out;
     std::vector<unsigned char> stage;
     for (auto& name : wanted.order) {
