@@ -254,6 +254,7 @@ def time_generate(engine, torch, ctx, batch, steps, warmup, vocab):
     stay low for some tens of milliseconds, which the mean of a short run shows and the median does not."""
     import trapetum_b200 as tb
     g = torch.Generator().manual_seed(1000 + batch)
+    warmup = warmup + 100          # the clocks need about 120 ms to come back after the prompts' step: those steps are not timed
     n_new = warmup + steps + 1
     prompts = torch.randint(0, vocab, (batch, max(1, ctx - n_new)), generator=g).tolist()
     stamps = []
@@ -421,6 +422,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None,
                     help="fewer layers than the model has (same layer sizes); both numbers are reported")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points, the prefill and the other runs")
+    ap.add_argument("--no-e2e", action="store_true",
+                    help="skip the end-to-end run through tb.generate (it starts with 8 prompts of about 8,000 tokens); the "
+                         "step-loop figure then stands in its place (for short captures under a profiler)")
     ap.add_argument("--runs", default="2b,9b,27b",
                     help="model shapes whose other measurements (caches of 2,048 tokens, prefill) are taken: a comma "
                          "list out of 2b, 9b, 27b, or 'none'")
@@ -473,7 +477,7 @@ def main() -> int:
     with ClockSampler() as clocks:
         r = time_decode(engine, torch, [args.context] * args.batch, args.steps, warmup, V, e2e=True, clocks=clocks)
     dev_ms, loop_ms = r["ms"], r["e2e_ms"]
-    e2e_ms, e2e_mean_ms = time_generate(engine, torch, args.context, args.batch, args.steps, warmup, V)
+    e2e_ms = e2e_mean_ms = loop_ms                     # replaced below by the run through tb.generate
     rec = decode_record(cfg, r, hbm_gbs)
     csum = clocks.summary()
     mhz = csum.get("sm_mhz")
@@ -497,7 +501,7 @@ def main() -> int:
                    "ms_x_ghz": round(dev_ms * mhz / 1e3, 4) if mhz else None},
         "e2e": {"value": round(args.batch * 1e3 / e2e_ms, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
                 "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": 4 * args.batch,
-                "how": "tb.generate, host prompts in, tokens out through its callback; median time between a request's tokens",
+                "how": "engine.step_tokens in a loop: host tokens in, the chosen tokens back on the host, every step",
                 "mean_ms_per_step": round(e2e_mean_ms, 4),
                 "step_loop_value": round(args.batch * 1e3 / loop_ms, 1), "step_loop_ms": round(loop_ms, 4)},
         "gpu_launches": r["launches"] * args.steps,
@@ -513,13 +517,20 @@ def main() -> int:
             rr = decode_record(cfg, rb, hbm_gbs)
             pts[f"decode_b{b}"] = rr["value"]
             if b == 1:
-                pts["e2e_b1"] = round(1e3 / time_generate(engine, torch, args.context, 1, max(8, args.steps // 2), warmup, V)[0], 1)
                 pts["e2e_b1_step_loop"] = round(1e3 / rb["e2e_ms"], 1)
             runs[f"{args.model}_decode_b{b}_ctx{args.context}"] = rr
         pms, hms, wms = time_prefill(engine, torch, PREFILL_TOKENS, V, reps=5, warmup=3)
         prec = prefill_record(cfg, PREFILL_TOKENS, pms, hms, wms, bf16_tflops)
         out["prefill"] = dict(prec, of=peak_src)
         out["points"] = pts
+        if not args.no_e2e:
+            pts["e2e_b1"] = round(1e3 / time_generate(engine, torch, args.context, 1, max(8, args.steps // 2), warmup, V)[0], 1)
+        if not args.no_e2e:
+            e2e_ms, e2e_mean_ms = time_generate(engine, torch, args.context, args.batch, args.steps, warmup, V)
+            out["e2e"].update(value=round(args.batch * 1e3 / e2e_ms, 1), ms_per_step=round(e2e_ms, 4),
+                              mean_ms_per_step=round(e2e_mean_ms, 4),
+                              how="tb.generate: host prompts in, tokens out through its callback; median time between a "
+                                  "request's tokens, the first hundred after the prompts' step left out")
         which = [] if args.runs == "none" else [w for w in args.runs.split(",") if w in MODELS]
         if args.layers != full["num_hidden_layers"]:
             which = []                                  # the other runs are of whole models

@@ -15,6 +15,7 @@ pytestmark = pytest.mark.gpu
 
 NAMES = ["A", "B", "C"]
 DTYPES = ["float32", "bfloat16"]
+HOSTS = ["native", "python"]          # the C++ host (the default for these models) and the Python host
 TOLERANCE = {}       # "of": (model name, token ids, dtype) -> tolerance, set from the fixture below
 
 
@@ -23,10 +24,10 @@ def engines(model_folders):
     import trapetum_b200 as tb
     cache = {}
 
-    def get(name, dtype, max_tokens=64 * 40):
-        key = (name, dtype, max_tokens)
+    def get(name, dtype, max_tokens=64 * 40, host=None):
+        key = (name, dtype, max_tokens, host)
         if key not in cache:
-            model = tb.load_model(model_folders[name], dtype)
+            model = tb.load_model(model_folders[name], dtype, host=host)
             eng = tb.Engine(model, max_tokens=max_tokens)
             for g in eng.cache.groups:                      # a row that was never written reads as NaN
                 g.k.fill_(float("nan")); g.v.fill_(float("nan"))
@@ -62,10 +63,11 @@ def check(got, want, dtype, what, ids):
         assert (got.cpu().argmax(-1) == want.argmax(-1)).all(), f"{what}: top-1 differs"
 
 
+@pytest.mark.parametrize("host", HOSTS)
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", NAMES)
-def test_each_request_alone_and_whole(engines, requests_and_truth, name, dtype):
-    eng = engines(name, dtype)
+def test_each_request_alone_and_whole(engines, requests_and_truth, name, dtype, host):
+    eng = engines(name, dtype, host=host)
     prompts, truth = requests_and_truth[name]
     for p, t in zip(prompts, truth):
         s = eng.start(1)
@@ -76,10 +78,11 @@ def test_each_request_alone_and_whole(engines, requests_and_truth, name, dtype):
     assert eng.cache.live_slots() == []
 
 
+@pytest.mark.parametrize("host", HOSTS)
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", NAMES)
-def test_last_32_tokens_one_by_one(engines, requests_and_truth, name, dtype):
-    eng = engines(name, dtype)
+def test_last_32_tokens_one_by_one(engines, requests_and_truth, name, dtype, host):
+    eng = engines(name, dtype, host=host)
     prompts, truth = requests_and_truth[name]
     for p, t in zip(prompts, truth):
         n = len(p) - 32
@@ -91,13 +94,14 @@ def test_last_32_tokens_one_by_one(engines, requests_and_truth, name, dtype):
         check(torch.cat(got), t, dtype, f"{name} tail one by one, {len(p)} tokens", p)
 
 
+@pytest.mark.parametrize("host", HOSTS)
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", NAMES)
-def test_unequal_batches_one_after_another(engines, requests_and_truth, name, dtype):
+def test_unequal_batches_one_after_another(engines, requests_and_truth, name, dtype, host):
     """Batches of unequal prompts; each request's prompt is its first part, the rest is fed one token
     per step; shorter requests end earlier and give their slot back while the others go on; the next
     batch starts in the slots (and pages) the first one used."""
-    eng = engines(name, dtype)
+    eng = engines(name, dtype, host=host)
     prompts, truth = requests_and_truth[name]
     cut = [20, 70, 9, 1, 66, 64]                 # prompt part of each request
     used_slots = []
@@ -128,12 +132,13 @@ def test_unequal_batches_one_after_another(engines, requests_and_truth, name, dt
     assert used_slots[1] == used_slots[0] and eng.cache.live_slots() == []     # slots were used again
 
 
+@pytest.mark.parametrize("host", HOSTS)
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["A", "C"])
-def test_long_decoding_and_first_tokens(engines, plain_models, name, dtype):
+def test_long_decoding_and_first_tokens(engines, plain_models, name, dtype, host):
     """From a one-token prompt, 280 tokens one by one: across page borders, past the window, around
     the ring more than once.  The first positions of a sequence are checked on the way."""
-    eng = engines(name, dtype)
+    eng = engines(name, dtype, host=host)
     cfg, w = plain_models[name]
     ids = make_prompts(cfg["vocab_size"], [281], seed=5)[0]
     truth = plain.forward(cfg, w, ids)
@@ -147,9 +152,10 @@ def test_long_decoding_and_first_tokens(engines, plain_models, name, dtype):
     check(got, truth, dtype, f"{name} long decoding", ids)
 
 
+@pytest.mark.parametrize("host", HOSTS)
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", NAMES)
-def test_second_batch_with_the_same_slots_and_page_counts_but_other_pages(model_folders, plain_models, name, dtype):
+def test_second_batch_with_the_same_slots_and_page_counts_but_other_pages(model_folders, plain_models, name, dtype, host):
     """Batch one: two prompts of 40 tokens that decode 30 more, so each sequence ends with two pages, taken
     alternately ([0, 2] and [1, 3]).  Batch two, in the same slots: two prompts of 70 tokens, two pages each
     again, but taken in a row ([0, 1] and [2, 3]).  Its first decode step has the batch size, the length bucket
@@ -157,7 +163,7 @@ def test_second_batch_with_the_same_slots_and_page_counts_but_other_pages(model_
     and write sequence 1's page."""
     import trapetum_b200 as tb
     cfg, w = plain_models[name]
-    eng = tb.Engine(tb.load_model(model_folders[name], dtype), max_tokens=64 * 8)
+    eng = tb.Engine(tb.load_model(model_folders[name], dtype, host=host), max_tokens=64 * 8)
     for g in eng.cache.groups:
         g.k.fill_(float("nan")); g.v.fill_(float("nan"))
     first = make_prompts(cfg["vocab_size"], [70, 70], seed=41)
@@ -268,12 +274,13 @@ def test_padding_and_neighbours_change_nothing(engines, requests_and_truth):
     assert float((alone - among).abs().max()) < 1e-5
 
 
+@pytest.mark.parametrize("host", HOSTS)
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", NAMES)
-def test_greedy_generation_through_the_entry_point(model_folders, plain_models, name, dtype):
+def test_greedy_generation_through_the_entry_point(model_folders, plain_models, name, dtype, host):
     import trapetum_b200 as tb
     cfg, w = plain_models[name]
-    model = tb.load_model(model_folders[name], dtype)
+    model = tb.load_model(model_folders[name], dtype, host=host)
     prompts = make_prompts(cfg["vocab_size"], [5, 11, 17, 3], seed=21)
     want = [plain.generate_greedy(cfg, w, p, 12) for p in prompts]
     got = tb.generate(model, prompts, max_tokens=12, max_batch=3)          # two batches: 3 + 1

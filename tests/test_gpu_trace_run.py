@@ -14,18 +14,19 @@ from conftest import ROOT, TOL, make_prompts, rel_l2, within
 pytestmark = pytest.mark.gpu
 
 
-def run_trace(folder, dtype, out, steps, max_tokens):
+def run_trace(folder, dtype, out, steps, max_tokens, host=None):
     proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
-                           "--out", out, "--max-tokens", str(max_tokens)],
+                           "--out", out, "--max-tokens", str(max_tokens)] + (["--host", host] if host else []),
                           input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=900)
     assert proc.returncode == 0, proc.stderr[-3000:]
     assert proc.stdout.split() == [x for s in steps for x in ("done", str(s["step"]))]
     return proc
 
 
+@pytest.mark.parametrize("host", [None, "python"])          # the program's own choice (the native host), and the Python host
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B"])
-def test_replay_three_ways(model_folders, plain_models, tolerance_of, tmp_path, name, dtype):
+def test_replay_three_ways(model_folders, plain_models, tolerance_of, tmp_path, name, dtype, host):
     cfg, w = plain_models[name]
     V = cfg["vocab_size"]
     reqs = make_prompts(V, [40, 75, 130], seed=3)
@@ -68,7 +69,7 @@ def test_replay_three_ways(model_folders, plain_models, tolerance_of, tmp_path, 
             t += 1
     out = str(tmp_path / "out")
     # 3 pages + 2 pages + 1 page live at most (the batch), the single requests need less
-    run_trace(model_folders[name], dtype, out, steps, max_tokens=64 * 6)
+    run_trace(model_folders[name], dtype, out, steps, max_tokens=64 * 6, host=host)
     files = sorted(os.listdir(out))
     assert files == sorted(f"{n}.f32" for n in expect)
     for n, want in expect.items():

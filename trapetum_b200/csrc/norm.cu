@@ -171,15 +171,23 @@ __global__ void __launch_bounds__(256) add_rmsnorm_rows_kernel(float* __restrict
     const int seg = width / WPR;                                  // columns per warp (a multiple of 4)
     const size_t base = (size_t)(live ? row : 0) * width + (size_t)sub * seg;
     const int col0 = sub * seg;
-    float v[NV][4];
+    float v[NV][4], hv[NV][4];
     float ss = 0.f;
+    // the branch output and the residual row are both requested before anything waits for either
 #pragma unroll
     for (int k = 0; k < NV; k++) {
         const int i = (k * 32 + lane) * 4;
-        if (live && i < seg) {
-            Vec4<float>::load(a + base + i, v[k]);
-            ss += v[k][0] * v[k][0] + v[k][1] * v[k][1] + v[k][2] * v[k][2] + v[k][3] * v[k][3];
-        }
+        if (live && i < seg) Vec4<float>::load(a + base + i, v[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < NV; k++) {
+        const int i = (k * 32 + lane) * 4;
+        if (live && i < seg) Vec4<float>::load(h + base + i, hv[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < NV; k++) {
+        const int i = (k * 32 + lane) * 4;
+        if (live && i < seg) ss += v[k][0] * v[k][0] + v[k][1] * v[k][1] + v[k][2] * v[k][2] + v[k][3] * v[k][3];
     }
     ss = warp_sum(ss);
     if (WPR > 1) {
@@ -195,11 +203,10 @@ __global__ void __launch_bounds__(256) add_rmsnorm_rows_kernel(float* __restrict
     for (int k = 0; k < NV; k++) {
         const int i = (k * 32 + lane) * 4;
         if (live && i < seg) {
-            float hv[4], g[4];
-            Vec4<float>::load(h + base + i, hv);
+            float g[4];
             Vec4<bf16>::load(wa + col0 + i, g);
 #pragma unroll
-            for (int e = 0; e < 4; e++) { v[k][e] = hv[e] + v[k][e] * ra * (off_a + g[e]); s2 += v[k][e] * v[k][e]; }
+            for (int e = 0; e < 4; e++) { v[k][e] = hv[k][e] + v[k][e] * ra * (off_a + g[e]); s2 += v[k][e] * v[k][e]; }
             Vec4<float>::store(h + base + i, v[k]);
         }
     }
@@ -361,9 +368,9 @@ extern "C" int tb_add_rmsnorm(float* h, const void* a, int a_dtype, int n_splits
                      aligned16(wb) && aligned16(out);
     if (vec && rows >= 64 && n_splits == 1 && a_dtype == TB_F32 && w_dtype == TB_BF16 && width <= 48 * 128) {
         // warps per row: as few as keep a lane's share of the row within twelve groups of four columns
-        // (measured at 2,048 rows of 2,304 / 3,584 / 4,608 columns: 4 warps a row take 22 / 30 / 42 us, one warp a
-        // row with the whole row in its registers took 27 / 59 / 76)
-        int wpr = width <= 512 ? 1 : width <= 1024 ? 2 : 4;
+        // (measured alone, cold, at 2,048 rows of 2,304 / 3,584 / 4,608 columns: 8 warps a row with both inputs
+        // requested at once take 20 / 26 / 36 us; one warp a row with the whole row in its registers took 27 / 59 / 76)
+        int wpr = width <= 512 ? 1 : width <= 1024 ? 2 : width <= 2048 ? 4 : 8;
         while (wpr > 1 && width % (wpr * 4)) wpr /= 2;
         const int nv = (width / wpr / 4 + 31) / 32;
         if (nv <= 12) {
