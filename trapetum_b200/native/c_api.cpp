@@ -1,6 +1,7 @@
 // The C interface of the native host (see trapetum_b200.h): every function catches what the C++ below it throws
 // and turns it into a status and a message.
 #include "trapetum_b200.h"
+#include "plugin.h"
 
 #include "engine.hpp"
 
@@ -268,6 +269,17 @@ int tb_cache_check(tb_engine* e) {
 int tb_cache_grow(tb_engine* e, const int* slots, const int* growth, int n) {
     TB_TRY
     e->e->cache->grow(std::vector<int>(slots, slots + n), std::vector<int>(growth, growth + n));
+    return TB_OK;
+    TB_CATCH_STATUS
+}
+
+int tb_register_mixer(const char* kind, const tb_mixer_plugin* plugin) {
+    TB_TRY
+    if (!kind || !*kind || !plugin || !plugin->create || !plugin->forward) throw Error("tb_register_mixer: a kind, create and forward are needed");
+    register_builtin_parts();
+    Registry<MixerPart>::add(kind, [plugin](const PartSpec& s, const std::string& prefix, Runtime rt) {
+        return std::unique_ptr<MixerPart>(new PluginMixer(plugin, s, prefix, rt));
+    });
     return TB_OK;
     TB_CATCH_STATUS
 }

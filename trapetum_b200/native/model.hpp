@@ -8,6 +8,7 @@
 #include <functional>
 
 #include "cache.hpp"
+#include "plugin.h"
 #include "weights.hpp"
 
 namespace tb {
@@ -384,6 +385,83 @@ private:
     DeviceBuffer w_qkv_buf_, b_qkv_buf_, b_o_buf_;
     Mat w_qkv_, w_o_, b_qkv_, b_o_;
     std::shared_ptr<DeviceTensor> keep_;
+};
+
+// ---- a mixer from outside the library (plugin.h) -------------------------------------------------------------------
+class PluginMixer : public MixerPart {
+public:
+    PluginMixer(const tb_mixer_plugin* p, const PartSpec& s, const std::string& prefix, Runtime rt) : p_(p), rt_(rt) {
+        const char* err = nullptr;
+        self_ = p->create(s.params.dump().c_str(), prefix.c_str(), (int)rt.dt, &err);
+        if (!self_) throw Error("mixer '" + s.kind + "' could not be made: " + (err ? err : "no reason given"));
+        kind_ = s.kind;
+    }
+    ~PluginMixer() override {
+        if (self_ && p_->destroy) p_->destroy(self_);
+    }
+    void tensor_specs(WantedTensors& w) const override {
+        const int n = p_->tensor_count ? p_->tensor_count(self_) : 0;
+        for (int i = 0; i < n; i++) {
+            tb_tensor_decl d;
+            memset(&d, 0, sizeof d);
+            if (p_->tensor_decl(self_, i, &d)) throw Error("mixer '" + kind_ + "': tensor_decl failed");
+            TensorSpec ts;
+            ts.shape.assign(d.shape, d.shape + d.ndim);
+            ts.role = d.role[0] ? d.role : "matrix";
+            ts.optional = d.optional != 0;
+            w.add(d.name, ts);
+        }
+    }
+    void bind(const TensorMap& t, Ops&) override {
+        const int n = p_->tensor_count ? p_->tensor_count(self_) : 0;
+        for (int i = 0; i < n; i++) {
+            tb_tensor_decl d;
+            memset(&d, 0, sizeof d);
+            p_->tensor_decl(self_, i, &d);
+            auto it = t.find(d.name);
+            if (it == t.end()) continue;
+            keep_.push_back(it->second);
+            const char* err = nullptr;
+            if (p_->bind(self_, d.name, it->second->buf.p, (int)it->second->dt, &err))
+                throw Error("mixer '" + kind_ + "' refused tensor " + d.name + ": " + (err ? err : "no reason given"));
+        }
+    }
+    bool graph_safe() const override { return p_->graph_safe != 0; }
+    CacheNeed cache_need() const override {
+        CacheNeed n;
+        tb_cache_need c;
+        memset(&c, 0, sizeof c);
+        if (p_->cache_need && p_->cache_need(self_, &c)) throw Error("mixer '" + kind_ + "': cache_need failed");
+        n.kind = c.kind == TB_NEED_KV ? CacheNeed::KV : c.kind == TB_NEED_STATE ? CacheNeed::STATE : CacheNeed::NONE;
+        n.n_kv_heads = c.n_kv_heads; n.head_dim = c.head_dim; n.window = c.window; n.state_bytes = (size_t)c.state_bytes;
+        return n;
+    }
+    Partials forward(Ops& ops, const Mat& x, StepCtx& ctx, const CacheLine& line) override {
+        Mat out = ops.arena->mat(F32, x.rows, x.cols);
+        tb_part_ctx c;
+        memset(&c, 0, sizeof c);
+        c.stream = ops.stream; c.dry = ops.dry() ? 1 : 0; c.is_prefill = ctx.is_prefill; c.n_tokens = ctx.n_tokens; c.batch = ctx.batch;
+        c.positions = ctx.positions; c.token_seq = ctx.token_seq; c.seq_start = ctx.seq_start; c.len_after = ctx.len_after;
+        c.slot_ids = ctx.slot_ids; c.host_slots = ctx.slots.data(); c.host_seq_lens = ctx.seq_lens.data();
+        c.state = line.state; c.state_bytes = (long long)line.state_bytes;
+        c.k = line.k; c.v = line.v; c.page_table = line.page_table; c.pt_stride = line.pt_stride; c.ring_rows = line.ring_rows;
+        c.line_owner = line.owner ? 1 : 0;
+        c.alloc = [](void* a, size_t bytes) { return ((Arena*)a)->alloc(bytes); };
+        c.arena = ops.arena;
+        const char* err = nullptr;
+        if (p_->forward(self_, &c, x.p, (int)x.dt, x.rows, x.cols, (float*)out.p, &err))
+            throw Error("mixer '" + kind_ + "' failed: " + (err ? err : "no reason given"));
+        Partials r;
+        r.p = (float*)out.p; r.rows = out.rows; r.cols = out.cols; r.split_stride = out.rows * out.cols;
+        return r;
+    }
+
+private:
+    const tb_mixer_plugin* p_;
+    Runtime rt_;
+    void* self_ = nullptr;
+    std::string kind_;
+    std::vector<std::shared_ptr<DeviceTensor>> keep_;
 };
 
 // ---- gated dense feed-forward: down(act(gate(x)) * up(x)) ---------------------------------------------------------
