@@ -459,8 +459,9 @@ def main() -> int:
     model = build_model(cfg, SEEDS[args.model])
     V = cfg["vocab_size"]
     max_batch = args.batch if args.no_points else max(args.batch, 64)
-    if args.model == "27b":
-        max_batch = min(max_batch, 16)                    # 27B weights and 64 caches of 8,192 tokens do not fit
+    per_token = 4 * cfg["num_key_value_heads"] * cfg["head_dim"] * cfg["num_hidden_layers"]      # key and value bytes
+    if max_batch > args.batch and max_batch * args.context * per_token + weight_bytes(cfg) > 150e9:
+        max_batch = args.batch                            # the batch-64 point does not fit beside these weights
     engine = Engine(model, max_tokens=max_batch * args.context, max_slots=max(max_batch, args.batch))
     random_cache(engine)
 
