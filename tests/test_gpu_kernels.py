@@ -603,3 +603,14 @@ def test_refusals(ops):
     with pytest.raises(ops.KernelError, match="float32 and bfloat16"):
         ops.rmsnorm(torch.zeros(2, 4, device="cuda", dtype=torch.float16), torch.zeros(4, device="cuda"), 1e-6, 1.0,
                     torch.float32)
+
+
+def test_attn_decode_ctas_per_sm(ops):
+    """The tensor-core decode kernel's stream partition is budgeted (shared memory to the byte, registers by its
+    launch bounds) for two CTAs an SM at heads narrower than 256: if a change breaks the budget the kernel still
+    computes the same, only slower, so the fit is checked here."""
+    from trapetum_b200.csrc import build
+    lib = build.load("attention_decode")
+    for hd in (64, 128, 256):
+        assert lib.tb_attn_decode_occupancy(hd, 0) == 1, hd
+        assert lib.tb_attn_decode_occupancy(hd, 1) == (2 if hd <= 128 else 1), hd

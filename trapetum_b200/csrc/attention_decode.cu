@@ -348,19 +348,24 @@ __global__ void __launch_bounds__(DCfg<HD>::NWARP * 32, 1) attn_decode_kernel(De
 #define TW 8                                       // warps that compute: 0..3 the scores, 4..7 the outputs
 #define NTHREADS ((TW + 1) * 32)                   // and one warp that issues the page copies
 #define SROW 72                                    // floats between heads in the score arrays (64 keys + 8: no bank conflicts)
-template <int HD> struct MCfg {
+template <int HD, bool STREAM> struct MCfg {
     static constexpr int BOXES = HD / 64;                            // 64-dim column boxes per page
     static constexpr int BOX_BYTES = PAGE * 128;                     // 64 keys x 128 bytes, swizzled
     static constexpr int TILE_BYTES = BOXES * BOX_BYTES;             // one page of K (or V)
     static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
-    static constexpr int STAGES_RAW = (192 * 1024) / STAGE_BYTES;
+    // One CTA an SM with the whole shared memory as stages; but the stream partition at heads narrower than 256 takes
+    // half, so that two CTAs share an SM: a page of narrow heads is copied faster than its chain of dependent steps
+    // runs through the two warp groups, and a second CTA's pages fill that time (27B shape, batch 64: 0.63 -> 0.77 of
+    // the memory's speed).  The split partition serves small batches, where one CTA with six stages was faster.
+    static constexpr int CTAS_PER_SM = (STREAM && HD <= 128) ? 2 : 1;
+    static constexpr int STAGES_RAW = ((192 / CTAS_PER_SM) * 1024) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 6 ? 6 : STAGES_RAW;
     static constexpr int KS = HD / 16;                               // k-steps of S^T = K Q^T
     static constexpr int MT_W = HD / 64;                             // 16-dim tiles of O^T per output warp (head_dim / 4 dims)
     static constexpr int SCORE_FLOATS = 2 * 8 * SROW + 2 * 8 * 4;    // two pages' scores, and their maxima per score warp
-    static constexpr int SMEM = STAGES * STAGE_BYTES + SCORE_FLOATS * 4 + 256 /* barriers */ + (1024 + 4) * 4 /* stream: page prefix */
+    static constexpr int SMEM = STAGES * STAGE_BYTES + SCORE_FLOATS * 4 + 192 /* barriers */ + (1024 + 4) * 4 /* stream: page prefix */
                                 + 8 * HD * 2 /* rotated queries */ + 10 * HD * 4 /* this step's q, k, v, summed */
-                                + 1024 /* alignment */;
+                                + 32 /* fold job, abort flag */ + 1024 /* alignment */;
 };
 // byte offset of (key row r, 16-byte chunk c of the head dim) inside a swizzled page
 __device__ __forceinline__ int sw_off(int r, int c) {
@@ -413,11 +418,11 @@ struct PageCursor {
 };
 
 template <int HD, bool STREAM>
-__global__ void __launch_bounds__(NTHREADS, 1)
+__global__ void __launch_bounds__(NTHREADS, MCfg<HD, STREAM>::CTAS_PER_SM)
 attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, DecodeArgs a,
                        int batch) {
     pdl_launch_dependents();
-    using C = MCfg<HD>;
+    using C = MCfg<HD, STREAM>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     float* sf = (float*)(smem + C::STAGES * C::STAGE_BYTES);         // [page parity][8 heads][SROW] scores: scaled, capped, masked
@@ -427,11 +432,18 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     uint64_t* s_full = empty + C::STAGES;                            // [2] the four score warps have written a page's scores
     uint64_t* s_empty = s_full + 2;                                  // [2] the four output warps have read them
     uint64_t* grp = s_empty + 2;                                     // [3] meeting points of the score warps, of the output warps, of all eight
-    int* pref = (int*)(full + 32);                                   // stream: [batch + 1] pages before each sequence
+    int* pref = (int*)(full + 24);                                   // stream: [batch + 1] pages before each sequence
     bf16* q_s = (bf16*)(pref + 1024 + 4);                            // [8 heads][HD] this run's queries, rotated (fused rotation)
     float* fold_s = (float*)(q_s + 8 * HD);                          // [G heads of q, then k, then v][HD]: the partial sums added up
-    __shared__ int s_last, s_job[3];                // split: the pair to fold (sequence, kv head, parts)
-    __shared__ volatile int s_abort;
+    // (no static shared memory: two CTAs of this kernel fill an SM's shared memory to the last kilobyte)
+    int* misc = (int*)(fold_s + 10 * HD);
+    int& s_last = misc[0];                          // split: this CTA folds the pair below
+    int* s_job = misc + 1;                          // the pair to fold (sequence, kv head, parts)
+    volatile int& s_abort = *(volatile int*)(misc + 4);
+    if ((uint8_t*)(misc + 8) > smem_raw + C::SMEM) {                 // the block began less aligned than the budget assumes
+        if (threadIdx.x == 0) atomicExch(&g_attn_error, 2);
+        return;
+    }
 
     const int G = a.n_heads / a.n_kv_heads;                         // 1..8 query heads on columns 0..G-1
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -1116,7 +1128,7 @@ static int pool_map(CUtensorMap* m, const void* pool, long long rows, int hd) {
 
 template <int HD, bool STREAM>
 static int launch_mma(const DecodeArgs& a, int batch, int n_ctas, cudaStream_t stream) {
-    using C = MCfg<HD>;
+    using C = MCfg<HD, STREAM>;
     static bool attr_set = false;
     auto kern = attn_decode_mma_kernel<HD, STREAM>;
     if (!attr_set) {
@@ -1257,6 +1269,26 @@ static int run_decode(const DecodeArgs* args, int dtype, int batch, bool tensor_
 // piece count to choose, every SM equally loaded whatever the lengths are.  `args->n_splits` is ignored;
 // `args->partial` must hold tb_attn_decode_stream_scratch_floats() floats and `args->tickets` batch * n_kv_heads
 // zeroed counters, which the launch leaves at zero.
+// CTAs of the tensor-core kernel that fit an SM together (the stream partition's shared memory and registers are
+// budgeted for two at heads narrower than 256; one everywhere else); -1 on error.
+template <int HD, bool STREAM> static int mma_occupancy() {
+    using C = MCfg<HD, STREAM>;
+    int n = 0;
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HD, STREAM>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+    if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attn_decode_mma_kernel<HD, STREAM>, NTHREADS, C::SMEM);
+    return e == cudaSuccess ? n : -1;
+}
+extern "C" int tb_attn_decode_occupancy(int hd, int stream_partition) {
+    switch (hd) {
+    case 64: return stream_partition ? mma_occupancy<64, true>() : mma_occupancy<64, false>();
+    case 128: return stream_partition ? mma_occupancy<128, true>() : mma_occupancy<128, false>();
+    case 256: return stream_partition ? mma_occupancy<256, true>() : mma_occupancy<256, false>();
+    default: return -1;
+    }
+}
+
+// How many CTAs a stream launch should use on a GPU of `sms` SMs (two an SM for heads narrower than 256).
+extern "C" int tb_attn_decode_stream_ctas(int sms, int hd) { return sms * (hd <= 128 ? 2 : 1); }
 extern "C" long long tb_attn_decode_stream_scratch_floats(int n_ctas, int n_heads, int n_kv_heads, int hd) {
     return (long long)n_ctas * 2 * (n_heads / (n_kv_heads > 0 ? n_kv_heads : 1)) * (hd + 2);
 }

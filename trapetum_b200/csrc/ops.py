@@ -759,9 +759,9 @@ def attn_decode_stream(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tens
     if tuple(k_pool.shape[1:]) != (n_kv_heads, PAGE_ROWS, head_dim) or k_pool.shape != v_pool.shape \
             or not k_pool.is_contiguous() or not v_pool.is_contiguous() or k_pool.dtype != q.dtype:
         raise KernelError("attention: pools must be contiguous [pages, n_kv_heads, PAGE_ROWS, head_dim] of q's dtype")
-    if n_ctas is None:
-        n_ctas = sm_count(q.device)
     lib = build.load("attention_decode")
+    if n_ctas is None:
+        n_ctas = int(lib.tb_attn_decode_stream_ctas(c_int(sm_count(q.device)), c_int(head_dim)))
     lib.tb_attn_decode_stream_scratch_floats.restype = c_longlong
     need = int(lib.tb_attn_decode_stream_scratch_floats(c_int(n_ctas), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim)))
     out = torch.empty((B, n_heads * head_dim), dtype=q.dtype, device=q.device)

@@ -323,10 +323,12 @@ public:
             auto& l = K().lib("attention_decode");
             static auto nf = l.sym<long long (*)(int, int, int, int)>("tb_attn_decode_stream_scratch_floats");
             static auto f = l.sym<int (*)(const DecodeArgs*, int, int, int, cudaStream_t)>("tb_attn_decode_stream");
-            a.partial = (float*)arena->alloc((size_t)nf(sms, n_heads, n_kv, hd) * 4);
+            static auto nc = l.sym<int (*)(int, int)>("tb_attn_decode_stream_ctas");
+            const int n_ctas = nc(sms, hd);
+            a.partial = (float*)arena->alloc((size_t)nf(n_ctas, n_heads, n_kv, hd) * 4);
             a.n_splits = 0; a.tickets = tickets;
             if (dry()) return out;
-            launched(l, f(&a, dt, B, sms, stream), "attn_decode_stream");
+            launched(l, f(&a, dt, B, n_ctas, stream), "attn_decode_stream");
             return out;
         }
         if (attn_decode_takes(dt, n_heads, n_kv, hd)) {
