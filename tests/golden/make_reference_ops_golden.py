@@ -10,7 +10,8 @@ float16 cases of reference_ops_cases.py on a GPU and stores their outputs.  test
 the plain implementation's functions with them on the CPU; tests/test_gpu_reference_ops.py repeats the
 comparison live where the compiled library is present.
 
-    python tests/golden/make_reference_ops_golden.py [/path/to/reference]        (needs a CUDA device)
+    python tests/golden/make_reference_ops_golden.py /path/to/reference        (needs a CUDA device; without
+    the path, or $TRAPETUM_REFERENCE, an already compiled baseline/_ref/libcodebook_gemv.so is used)
 """
 import ctypes
 import json
@@ -96,7 +97,7 @@ def run_all(lib):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("TRAPETUM_REFERENCE", "")
     lib = load(build(ref))
     if not torch.cuda.is_available():
         print(f"built {LIB}; run this script again on a machine with a GPU to write the outputs")
