@@ -61,15 +61,25 @@ __device__ __forceinline__ float gated(float g, float u, int act) {
 }
 
 // Shared-memory budget.  Many tokens (tiles are reused, the tensor cores are the limit): as many stages as an SM
-// holds.  Few tokens (swapped tiles, a stream of weights): half of an SM, so that the next product's CTAs already
-// sit beside this one's, fetch their tensor maps and fill their stages with weights while this one drains; the
-// two kernels together keep as many bytes in flight as one with the whole SM.
+// holds.  Few tokens (swapped tiles, a stream of weights) and a short stream: half of an SM, so that the next
+// product's CTAs already sit beside this one's, fetch their tensor maps and fill their stages with weights while this
+// one drains; the two kernels together keep as many bytes in flight as one with the whole SM.  A long stream (WIDE:
+// the host asks for it from TB_WIDE_FROM_BYTES of weights on) takes the whole SM: its own bytes in flight count for
+// more than the overlap with its neighbours.  Measured, decode steps at context 2,048 with every small product on
+// the whole SM against half: 2B shape 2.5 % slower at batch 8, 9B shape 2 % faster, 27B shape 5 % faster; with 32 to
+// 128 tokens the whole SM is never slower (9B shape at batch 64: 4 % faster).
 #ifndef TB_SWAP_KB
 #define TB_SWAP_KB 108
 #endif
+#ifndef TB_WIDE_FROM_BYTES
+#define TB_WIDE_FROM_BYTES (128 << 20)
+#endif
+#ifndef TB_SWAP_HALF_UPTO
+#define TB_SWAP_HALF_UPTO 16
+#endif
 template <int BN, bool SWAP, bool WIDE = false> struct Cfg {
     static constexpr int STAGE_BYTES = BM * BK * 2 + BN * BK * 2;
-    static constexpr int BUDGET = ((SWAP && !WIDE) ? TB_SWAP_KB : 200) * 1024;
+    static constexpr int BUDGET = ((SWAP && !WIDE && BN <= TB_SWAP_HALF_UPTO) ? TB_SWAP_KB : 200) * 1024;
     static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 10 ? 10 : STAGES_RAW;
     static constexpr int ACC_COLS = BN < 32 ? 32 : BN;               // columns of one accumulator stage
@@ -449,6 +459,7 @@ extern "C" int tb_gemm_tc(const void* A, const void* W, void* C, int c_dtype, in
     }
 
     const bool swap = M <= BM;
+    const bool wide = (long long)N * K * 2 >= (long long)TB_WIDE_FROM_BYTES;
     int bn;
     if (swap) bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
     else bn = N >= 256 ? 256 : 128;
@@ -472,16 +483,16 @@ extern "C" int tb_gemm_tc(const void* A, const void* W, void* C, int c_dtype, in
 #define GO(BN_, SW_) (c_dtype == TB_BF16 ? launch<BN_, SW_, bf16>(mp, mq, p, stream) : launch<BN_, SW_, float>(mp, mq, p, stream))
     if (gated) {
 #define GG(BN_, SW_) launch<BN_, SW_, bf16, true>(mp, mq, p, stream)
-        if (swap) st = bn == 16 ? GG(16, true) : bn == 32 ? GG(32, true) : bn == 64 ? GG(64, true) : GG(128, true);
+        if (swap) st = bn == 16 ? (wide ? launch<16, true, bf16, true, true>(mp, mq, p, stream) : GG(16, true))
+                     : bn == 32 ? GG(32, true) : bn == 64 ? GG(64, true) : GG(128, true);
         else st = bn == 256 ? GG(256, false) : GG(128, false);
 #undef GG
     } else if (swap) {
         switch (bn) {
         case 16:
-            // a long stream (several tiles per CTA: an output head): the kernel's own bytes in flight count for more
-            // than the overlap with its neighbours, so it takes the whole SM
-            if (c_dtype == TB_F32 && (long long)p.tiles_p * p.tiles_q * p.splits >= 4LL * g_sms)
-                st = launch<16, true, float, false, true>(mp, mq, p, stream);
+            // a long stream of weights: the kernel's own bytes in flight count for more than the overlap with its
+            // neighbours, so it takes the whole SM
+            if (c_dtype == TB_F32 && wide) st = launch<16, true, float, false, true>(mp, mq, p, stream);
             else st = GO(16, true);
             break;
         case 32: st = GO(32, true); break;
