@@ -151,12 +151,20 @@ def test_gemm_simt_row_does_not_depend_on_the_batch(ops):
 @pytest.mark.parametrize("odt", DT)
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (3, 40, 72), (16, 384, 96), (17, 130, 64), (64, 2304, 2048),
                                    (100, 512, 520), (128, 256, 64), (129, 256, 64), (300, 520, 200),
-                                   (1000, 301 * 8, 1032), (2048, 1024, 2304)])
-def test_gemm_tc(ops, odt, M, N, K):
+                                   (1000, 301 * 8, 1032), (2048, 1024, 2304), (2048, 10240, 128)])
+@pytest.mark.parametrize("pair", [0, 1])
+def test_gemm_tc(ops, odt, M, N, K, pair):
+    """Few tokens (swapped tiles), many tokens on single SMs and on pairs of SMs (one tile a pair, and several)."""
+    if pair and (M <= 128 or N < 256):
+        pytest.skip("the pair kernel takes more than 128 tokens and at least 256 weight rows")
     a, w = rnd(M, K, dt=torch.bfloat16, s=0.5), rnd(N, K, dt=torch.bfloat16, s=0.5, seed=1)
     assert ops.gemm_tc_takes(a, w)
     want = a.double() @ w.double().T
-    got = ops.gemm_tc(a, w, odt)
+    was = ops.gemm_tc_set_pair(pair)
+    try:
+        got = ops.gemm_tc(a, w, odt)
+    finally:
+        ops.gemm_tc_set_pair(was)
     torch.cuda.synchronize()
     assert ops.gemm_tc_error() == 0
     if odt == torch.float32:
@@ -181,15 +189,52 @@ def test_gemm_tc_split_k(ops, M, N, K, splits):
 @pytest.mark.parametrize("act", ["gelu_tanh", "silu"])
 @pytest.mark.parametrize("M,I,K", [(1, 160, 96), (8, 9216, 2304), (40, 128, 64), (64, 1024, 512), (128, 176, 72),
                                    (129, 160, 96), (700, 1296, 520), (2048, 2048, 256)])
-def test_gemm_tc_gated_epilogue(ops, act, M, I, K):
-    """act(x Wg^T) * (x Wu^T) in the product's epilogue, swapped tiles (few tokens) and token-major ones."""
+@pytest.mark.parametrize("pair", [0, 1])
+def test_gemm_tc_gated_epilogue(ops, act, M, I, K, pair):
+    """act(x Wg^T) * (x Wu^T) in the product's epilogue, swapped tiles (few tokens) and token-major ones, these on
+    single SMs and on pairs."""
+    if pair and M <= 128:
+        pytest.skip("the pair kernel takes more than 128 tokens")
     x = rnd(M, K, dt=torch.bfloat16, s=1.0)
     wg, wu = rnd(I, K, dt=torch.bfloat16, s=0.1, seed=1), rnd(I, K, dt=torch.bfloat16, s=0.1, seed=2)
     g, u = x.double() @ wg.double().T, x.double() @ wu.double().T
     want = (plain.gelu_tanh(g) if act == "gelu_tanh" else g * torch.sigmoid(g)) * u
-    got = ops.gemm_tc(x, ops.interleave_gate_up(wg, wu), torch.bfloat16, gated_act=act)
+    was = ops.gemm_tc_set_pair(pair)
+    try:
+        got = ops.gemm_tc(x, ops.interleave_gate_up(wg, wu), torch.bfloat16, gated_act=act)
+    finally:
+        ops.gemm_tc_set_pair(was)
     assert got.shape == (M, I) and got.dtype == torch.bfloat16
     assert float((got.double() - want).norm() / want.norm()) < 4e-3
+    assert ops.gemm_tc_error() == 0
+
+
+def test_gemm_tc_pair_policy_and_cap(ops):
+    """The default policy sends a long product to pairs of SMs and a short one to single SMs; either way the result
+    is the same up to the order of additions inside an instruction, with a soft cap and through a row-strided view."""
+    big = rnd(300, 2 * 8192, dt=torch.bfloat16, s=0.5)
+    a = big[:, 8192:]                                                # row stride 16384
+    w = rnd(520, 8192, dt=torch.bfloat16, s=0.05, seed=1)
+    want = 5 * torch.tanh(a.double() @ w.double().T / 5)
+    outs = []
+    for mode in (0, 1, 2):
+        was = ops.gemm_tc_set_pair(mode)
+        try:
+            outs.append(ops.gemm_tc(a, w, torch.float32, 5.0))
+        finally:
+            ops.gemm_tc_set_pair(was)
+    assert was == 2                                                  # the default
+    for got in outs:
+        assert float((got.double() - want).abs().max()) < 1e-4
+    assert torch.equal(outs[2], outs[1])                             # K of 8,192: where the pair pays
+    short = rnd(520, 64, dt=torch.bfloat16, s=0.5, seed=2)
+    x = rnd(300, 64, dt=torch.bfloat16, s=0.5, seed=3)
+    ops.gemm_tc_set_pair(0)
+    try:
+        single = ops.gemm_tc(x, short, torch.float32)
+    finally:
+        ops.gemm_tc_set_pair(2)
+    assert torch.equal(ops.gemm_tc(x, short, torch.float32), single)  # a short product stays on single SMs
     assert ops.gemm_tc_error() == 0
 
 

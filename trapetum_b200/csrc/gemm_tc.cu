@@ -1,8 +1,10 @@
 // C[M,N] = A[M,K] * W[N,K]^T in bfloat16 on the 5th-generation tensor cores.
 //
-// tcgen05.mma (cta_group::1, kind::f16, 128 x BN x 16 per instruction) issued by one
-// thread, operands staged in shared memory by TMA (128-byte swizzle, K-major),
-// accumulators in tensor memory, read back with tcgen05.ld for the epilogue.
+// tcgen05.mma (kind::f16; cta_group::1 with 128 x BN x 16 per instruction, and for long
+// products of many tokens cta_group::2 with 256 x 256 x 16 over a pair of SMs, see
+// gemm_tc_pair_kernel) issued by one thread, operands staged in shared memory by TMA
+// (128-byte swizzle, K-major), accumulators in tensor memory, read back with tcgen05.ld
+// for the epilogue.
 // The reference has no dense tensor-core product: its linears are 4-bit codebook
 // GEMVs (runtime/cuda/codebook_gemv.cu:86-114) with a fixed-order second stage
 // for determinism (:178-184); the same rule holds here (no atomics anywhere).
@@ -30,6 +32,7 @@
 // anything else is refused and the caller falls back to the FMA kernel.
 #include "common.cuh"
 #include "tcgen05.cuh"
+#include <stdlib.h>
 
 TB_EXPORT_ERROR()
 
@@ -86,6 +89,75 @@ template <int BN, bool SWAP, bool WIDE = false> struct Cfg {
     static constexpr int TMEM_COLS = 2 * ACC_COLS;                   // a power of two >= 32
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
 };
+
+// Epilogue of token-major tiles: the thread holds CH consecutive columns (weight rows q0 .. q0 + CH - 1) of token prow.
+template <typename TOut, bool GATED, int CH>
+__device__ __forceinline__ void store_token_major(const uint32_t* r, int prow, int q0, int sp, const GemmParams& p) {
+    static_assert(!GATED || CH == 32, "a gate and its up value lie 16 columns apart");
+    if (GATED) {
+        // 32 columns = 16 gates then their 16 ups: 16 outputs at column q0 / 2
+        if (prow < p.rows_p && q0 < p.rows_q) {
+            bf16* dst = (bf16*)p.out + (size_t)prow * p.ld_out + (q0 >> 1);
+            uint32_t w[8];
+#pragma unroll
+            for (int j = 0; j < 16; j += 2) {
+                const float v0 = gated(__uint_as_float(r[j]), __uint_as_float(r[j + 16]), p.act);
+                const float v1 = gated(__uint_as_float(r[j + 1]), __uint_as_float(r[j + 17]), p.act);
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(v0, v1);
+                w[j >> 1] = *(uint32_t*)&h2;
+            }
+            if ((((uintptr_t)dst) & 15) == 0) {
+                *(uint4*)dst = make_uint4(w[0], w[1], w[2], w[3]);
+                *(uint4*)(dst + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; j++) *(uint32_t*)(dst + 2 * j) = w[j];
+            }
+        }
+    } else {
+        // tokens on lanes (prow), weight rows on columns (q0 + j): a thread writes a row segment
+        if (prow < p.rows_p) {
+            if (p.splits > 1) {
+                float* dst = p.partial + ((size_t)sp * p.rows_p + prow) * p.rows_q + q0;
+#pragma unroll
+                for (int j = 0; j < CH; j++) if (q0 + j < p.rows_q) dst[j] = __uint_as_float(r[j]);
+            } else {
+                TOut* dst = (TOut*)p.out + (size_t)prow * p.ld_out + q0;
+                const bool vec = (q0 + CH <= p.rows_q) && ((((uintptr_t)dst) & 15) == 0);
+                if (vec && sizeof(TOut) == 2) {
+#pragma unroll
+                    for (int j = 0; j < CH; j += 8) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            float v0 = __uint_as_float(r[j + 2 * e]), v1 = __uint_as_float(r[j + 2 * e + 1]);
+                            if (p.cap > 0.f) { v0 = softcap_f(v0, p.cap); v1 = softcap_f(v1, p.cap); }
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(v0, v1);
+                            w[e] = *(uint32_t*)&h2;
+                        }
+                        *(uint4*)((bf16*)dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                } else if (vec) {
+#pragma unroll
+                    for (int j = 0; j < CH; j += 4) {
+                        float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                               __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                        if (p.cap > 0.f) { v.x = softcap_f(v.x, p.cap); v.y = softcap_f(v.y, p.cap);
+                                           v.z = softcap_f(v.z, p.cap); v.w = softcap_f(v.w, p.cap); }
+                        *(float4*)((float*)dst + j) = v;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < CH; j++) if (q0 + j < p.rows_q) {
+                        float v = __uint_as_float(r[j]);
+                        if (p.cap > 0.f) v = softcap_f(v, p.cap);
+                        dst[j] = from_f<TOut>(v);
+                    }
+                }
+            }
+        }
+    }
+}
 
 template <int BN, bool SWAP, typename TOut, bool GATED, bool WIDE>
 __global__ void __launch_bounds__(192, 1)
@@ -224,26 +296,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 if (CH == 32) tmem_ld32(t_addr + c0, r); else tmem_ld16(t_addr + c0, r);
                 tmem_ld_wait();
                 const int q0 = tq * BN + c0;                           // first row of Q in this chunk
-                if (GATED && !SWAP) {
-                    // 32 columns = 16 gates then their 16 ups: 16 outputs at column q0 / 2
-                    if (prow < p.rows_p && q0 < p.rows_q) {
-                        bf16* dst = (bf16*)p.out + (size_t)prow * p.ld_out + (q0 >> 1);
-                        uint32_t w[8];
-#pragma unroll
-                        for (int j = 0; j < 16; j += 2) {
-                            const float v0 = gated(__uint_as_float(r[j]), __uint_as_float(r[j + 16]), p.act);
-                            const float v1 = gated(__uint_as_float(r[j + 1]), __uint_as_float(r[j + 17]), p.act);
-                            __nv_bfloat162 h2 = __floats2bfloat162_rn(v0, v1);
-                            w[j >> 1] = *(uint32_t*)&h2;
-                        }
-                        if ((((uintptr_t)dst) & 15) == 0) {
-                            *(uint4*)dst = make_uint4(w[0], w[1], w[2], w[3]);
-                            *(uint4*)(dst + 8) = make_uint4(w[4], w[5], w[6], w[7]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 8; j++) *(uint32_t*)(dst + 2 * j) = w[j];
-                        }
-                    }
+                if constexpr (!SWAP) {
+                    store_token_major<TOut, GATED, CH>(r, prow, q0, sp, p);
                 } else if (GATED && SWAP) {
                     // lanes 0..15 hold gates, lanes 16..31 the ups of the same 16 features
 #pragma unroll
@@ -254,48 +308,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                         if (lane < 16 && tok < p.rows_q && prow < p.rows_p)
                             ((bf16*)p.out)[(size_t)tok * p.ld_out + ((prow >> 5) << 4) + lane] =
                                 __float2bfloat16_rn(gated(mine, other, p.act));
-                    }
-                } else if (!SWAP) {
-                    // tokens on lanes (prow), weight rows on columns (q0 + j): a thread writes a row segment
-                    if (prow < p.rows_p) {
-                        if (p.splits > 1) {
-                            float* dst = p.partial + ((size_t)sp * p.rows_p + prow) * p.rows_q + q0;
-#pragma unroll
-                            for (int j = 0; j < CH; j++) if (q0 + j < p.rows_q) dst[j] = __uint_as_float(r[j]);
-                        } else {
-                            TOut* dst = (TOut*)p.out + (size_t)prow * p.ld_out + q0;
-                            const bool vec = (q0 + CH <= p.rows_q) && ((((uintptr_t)dst) & 15) == 0);
-                            if (vec && sizeof(TOut) == 2) {
-#pragma unroll
-                                for (int j = 0; j < CH; j += 8) {
-                                    uint32_t w[4];
-#pragma unroll
-                                    for (int e = 0; e < 4; e++) {
-                                        float v0 = __uint_as_float(r[j + 2 * e]), v1 = __uint_as_float(r[j + 2 * e + 1]);
-                                        if (p.cap > 0.f) { v0 = softcap_f(v0, p.cap); v1 = softcap_f(v1, p.cap); }
-                                        __nv_bfloat162 h2 = __floats2bfloat162_rn(v0, v1);
-                                        w[e] = *(uint32_t*)&h2;
-                                    }
-                                    *(uint4*)((bf16*)dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
-                                }
-                            } else if (vec) {
-#pragma unroll
-                                for (int j = 0; j < CH; j += 4) {
-                                    float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                           __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                                    if (p.cap > 0.f) { v.x = softcap_f(v.x, p.cap); v.y = softcap_f(v.y, p.cap);
-                                                       v.z = softcap_f(v.z, p.cap); v.w = softcap_f(v.w, p.cap); }
-                                    *(float4*)((float*)dst + j) = v;
-                                }
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < CH; j++) if (q0 + j < p.rows_q) {
-                                    float v = __uint_as_float(r[j]);
-                                    if (p.cap > 0.f) v = softcap_f(v, p.cap);
-                                    dst[j] = from_f<TOut>(v);
-                                }
-                            }
-                        }
                     }
                 } else {
                     // weight rows on lanes (prow), tokens on columns (q0 + j): lanes write neighbours
@@ -326,6 +338,174 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------
+// The same product for many tokens on a pair of SMs (cta_group::2): a cluster of two CTAs owns a tile of 256 tokens
+// by 256 weight rows.  Each CTA copies its 128 tokens of A and its 128 of the tile's weight rows into its own shared
+// memory; one thread of the even CTA issues MMAs of 256 x 256 x 16 that read A and half of B from each CTA and leave
+// each CTA's 128 tokens of the result in its own tensor memory.  A k-block of 64 then costs an SM 32 KB of shared
+// memory and of copies instead of 48 KB: on one SM a 128 x 256 tile reads and refills its operands faster than the
+// shared memory delivers them, which is what bounds the single-CTA kernel above.
+//
+// Barriers: both CTAs' copies count their bytes on the leader's `full` barrier (the leader expects both shares);
+// a commit arrives on `empty` and `acc_full` at the same offset in both CTAs; the epilogue warps of both CTAs arrive
+// on the leader's `acc_empty`.  All waits on these are bounded as above.  The two cluster barriers (after set-up,
+// before the tensor memory is given back) are not: every path reaches them, since every loop before them ends.
+// ---------------------------------------------------------------------------
+struct PairCfg {
+    static constexpr int BN = 256, HALF = 128;
+    static constexpr int STAGE_BYTES = BM * BK * 2 + HALF * BK * 2;       // per CTA
+    static constexpr int STAGES = (227 * 1024 - 1024 - 256) / STAGE_BYTES;   // 7: all of an SM's shared memory
+    static constexpr int TMEM_COLS = 2 * BN;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
+};
+
+template <typename TOut, bool GATED>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, GemmParams p) {
+    pdl_launch_dependents();
+    using C = PairCfg;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(smem + C::STAGES * C::STAGE_BYTES);
+    uint64_t* full = bars;                       // [STAGES], the leader's is used
+    uint64_t* empty = bars + C::STAGES;          // [STAGES], each CTA's own
+    uint64_t* acc_full = bars + 2 * C::STAGES;   // [2], each CTA's own
+    uint64_t* acc_empty = acc_full + 2;          // [2], the leader's is used
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();     // 0: the leader
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 32) { tma_prefetch_map(&map_p); tma_prefetch_map(&map_q); }
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
+        *abort_flag = 0;
+        mbar_init_fence();
+    }
+    if (warp == 1) tmem_alloc_pair(tmem_slot, C::TMEM_COLS);
+    tc_fence_before();
+    cluster_sync();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int n_items = p.tiles_p * p.tiles_q * p.splits;
+    auto decode = [&](int item, int& tp, int& tq, int& sp) {
+        sp = item % p.splits; item /= p.splits;
+        tp = item % p.tiles_p; tq = item / p.tiles_p;
+    };
+    constexpr int A_OFF = 0, W_OFF = BM * BK * 2;
+
+    if (warp == 0) {
+        // ---------------- TMA producer, in both CTAs ----------------
+        if (lane == 0) {
+            const uint32_t lead_full = cluster_addr(&full[0], 0);
+            uint32_t it = 0;
+            bool ok = true, waited = false;
+            for (int item = pair; item < n_items && ok; item += n_pairs) {
+                int tp, tq, sp; decode(item, tp, tq, sp);
+                const int kb0 = sp * p.kb_per_split, kb1 = min(p.kblocks, kb0 + p.kb_per_split);
+                const int a_row = tp * 256 + (int)rank * BM, w_row = tq * C::BN + (int)rank * C::HALF;
+                int kb = kb0;
+                if (!waited) {
+                    // weights first, then the wait for the kernel before this one, then its output
+                    const int pre = min(kb1 - kb0, C::STAGES);
+                    for (int j = 0; j < pre; j++) {
+                        if (rank == 0) mbar_expect_tx(&full[j], 2 * C::STAGE_BYTES);
+                        tma_load_2d_pair(smem + j * C::STAGE_BYTES + W_OFF, &map_q, lead_full + 8 * j, (kb0 + j) * BK, w_row);
+                    }
+                    pdl_wait();
+                    waited = true;
+                    for (int j = 0; j < pre; j++)
+                        tma_load_2d_pair(smem + j * C::STAGE_BYTES + A_OFF, &map_p, lead_full + 8 * j, (kb0 + j) * BK, a_row);
+                    it = pre; kb = kb0 + pre;
+                }
+                for (; kb < kb1; kb++, it++) {
+                    const int s = it % C::STAGES; const uint32_t ph = (it / C::STAGES) & 1;
+                    if (*abort_flag || !mbar_wait(&empty[s], ph ^ 1)) { ok = false; break; }
+                    uint8_t* st = smem + s * C::STAGE_BYTES;
+                    if (rank == 0) mbar_expect_tx(&full[s], 2 * C::STAGE_BYTES);
+                    tma_load_2d_pair(st + W_OFF, &map_q, lead_full + 8 * s, kb * BK, w_row);
+                    tma_load_2d_pair(st + A_OFF, &map_p, lead_full + 8 * s, kb * BK, a_row);
+                }
+            }
+            if (!ok) {
+                if (!*abort_flag) { atomicExch(&g_gemm_error, 4); *abort_flag = 1; }
+                // the leader's barriers count both CTAs' copies: wait for those already issued
+                if (rank == 0)
+                    for (uint32_t back = 1; back <= (uint32_t)C::STAGES && back <= it; back++) {
+                        const uint32_t j = it - back;
+                        mbar_wait(&full[j % C::STAGES], (j / C::STAGES) & 1);
+                    }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer, in the leader ----------------
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = instr_desc_pair(C::BN);
+            uint32_t it = 0, tile_it = 0;
+            bool ok = true;
+            for (int item = pair; item < n_items && ok; item += n_pairs, tile_it++) {
+                int tp, tq, sp; decode(item, tp, tq, sp);
+                const int kb0 = sp * p.kb_per_split, kb1 = min(p.kblocks, kb0 + p.kb_per_split);
+                const int a = tile_it & 1; const uint32_t aph = (tile_it >> 1) & 1;
+                if (*abort_flag || !mbar_wait(&acc_empty[a], aph ^ 1)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_addr = tmem_base + a * C::BN;
+                for (int kb = kb0; kb < kb1; kb++, it++) {
+                    const int s = it % C::STAGES; const uint32_t ph = (it / C::STAGES) & 1;
+                    if (*abort_flag || !mbar_wait(&full[s], ph)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + s * C::STAGE_BYTES);
+                    const uint32_t sb = sa + W_OFF;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; k++) {
+                        umma_bf16_pair(d_addr, smem_desc(sa + k * UMMA_K * 2), smem_desc(sb + k * UMMA_K * 2), idesc,
+                                       (kb > kb0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit_pair(&empty[s]);           // frees the stage in both CTAs
+                }
+                if (ok) umma_commit_pair(&acc_full[a]);    // the accumulator is complete in both CTAs
+            }
+            if (!ok && !*abort_flag) { atomicExch(&g_gemm_error, 5); *abort_flag = 1; }
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5 of both CTAs ----------------
+        const int quarter = warp & 3;
+        const uint32_t lead_acc_empty = cluster_addr(&acc_empty[0], 0);
+        pdl_wait();
+        uint32_t tile_it = 0;
+        bool ok = true;
+        for (int item = pair; item < n_items && ok; item += n_pairs, tile_it++) {
+            int tp, tq, sp; decode(item, tp, tq, sp);
+            const int a = tile_it & 1; const uint32_t aph = (tile_it >> 1) & 1;
+            const bool mine = !*abort_flag && mbar_wait(&acc_full[a], aph);
+            if (!__all_sync(0xffffffffu, mine)) { ok = false; break; }
+            tc_fence_after();
+            const int prow = tp * 256 + (int)rank * BM + quarter * 32 + lane;
+            const uint32_t t_addr = tmem_base + a * C::BN + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+            for (int c0 = 0; c0 < C::BN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(t_addr + c0, r);
+                tmem_ld_wait();
+                store_token_major<TOut, GATED, 32>(r, prow, tq * C::BN + c0, sp, p);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(lead_acc_empty + 8 * a);
+        }
+        if (!ok && !*abort_flag && lane == 0) { atomicExch(&g_gemm_error, 6); *abort_flag = 1; }
+    }
+
+    tc_fence_before();
+    cluster_sync();
+    tc_fence_after();
+    if (warp == 1) tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
 }
 
 // partial[splits][rows][cols] summed in split order, then cap and conversion.
@@ -395,6 +575,52 @@ static int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmParams
     return tb_launch_status();
 }
 
+// Many-token products on pairs of SMs: 0 never, 1 whenever the shape allows, 2 where it pays.  The environment
+// variable TRAPETUM_GEMM_PAIR sets the start value (for profiling one kernel on every shape).
+static int pair_policy_from_env() {
+    const char* e = getenv("TRAPETUM_GEMM_PAIR");
+    return (e && e[0] >= '0' && e[0] <= '2' && !e[1]) ? e[0] - '0' : 2;
+}
+static int g_pair = pair_policy_from_env();
+static int g_pair_clusters = 0;
+
+// Sets that policy (for comparisons and tests); returns the previous setting.
+extern "C" int tb_gemm_tc_set_pair(int mode) { const int was = g_pair; g_pair = mode < 0 ? 0 : mode > 2 ? 2 : mode; return was; }
+
+// Where the pair kernel pays.  Its launch costs about a microsecond more (a cluster is placed, two cluster barriers),
+// its main loop runs 5 to 10 % faster.  Measured against the single-SM kernel with weights from memory, 512 to 8,192
+// tokens on the 2B, 9B and 27B shapes: from about 300 k-blocks of work per pair on, or with K of 8,192 and more, the
+// pair is 3 to 12 % faster; below, equal or up to 7 % slower.
+static bool pair_pays(int M, int N, int K) {
+    const long long tiles = (long long)((M + 255) / 256) * ((N + 255) / 256);
+    const long long kblocks = (K + BK - 1) / BK;
+    return K >= 8192 || tiles * kblocks >= 300LL * (g_sms / 2);
+}
+
+template <typename TOut, bool GATED>
+static int launch_pair(const CUtensorMap& mp, const CUtensorMap& mq, const GemmParams& p, cudaStream_t stream) {
+    using C = PairCfg;
+    static bool attr_set = false;
+    auto kern = gemm_tc_pair_kernel<TOut, GATED>;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    if (!g_pair_clusters) {
+        // how many pairs the device runs at once (an SM without a free neighbour takes none)
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * (g_sms / 2)); cfg.blockDim = dim3(192); cfg.dynamicSmemBytes = C::SMEM;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) { cudaGetLastError(); n = g_sms / 2; }
+        g_pair_clusters = n < g_sms / 2 ? n : g_sms / 2;
+    }
+    const int items = p.tiles_p * p.tiles_q * p.splits;
+    const int pairs = items < g_pair_clusters ? items : g_pair_clusters;
+    tb_launch(kern, dim3(2 * pairs), dim3(192), C::SMEM, stream, mp, mq, p);
+    return tb_launch_status();
+}
+
 extern "C" int tb_gemm_tc_takes(const void* A, const void* W, int M, int N, int K, long long lda, long long ldw) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if (K % 8 || lda % 8 || ldw % 8) return 0;
@@ -459,6 +685,7 @@ extern "C" int tb_gemm_tc(const void* A, const void* W, void* C, int c_dtype, in
     }
 
     const bool swap = M <= BM;
+    const bool pair = !swap && N >= 256 && (g_pair == 1 || (g_pair == 2 && pair_pays(M, N, K)));
     const bool wide = (long long)N * K * 2 >= (long long)TB_WIDE_FROM_BYTES;
     int bn;
     if (swap) bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
@@ -474,9 +701,9 @@ extern "C" int tb_gemm_tc(const void* A, const void* W, void* C, int c_dtype, in
         if (make_map(&mp, W, N, K, ldw, BM) || make_map(&mq, A, M, K, lda, bn)) return -1;
     } else {
         p.rows_p = M; p.rows_q = N;
-        if (make_map(&mp, A, M, K, lda, BM) || make_map(&mq, W, N, K, ldw, bn)) return -1;
+        if (make_map(&mp, A, M, K, lda, BM) || make_map(&mq, W, N, K, ldw, pair ? PairCfg::HALF : bn)) return -1;
     }
-    p.tiles_p = (p.rows_p + BM - 1) / BM;
+    p.tiles_p = (p.rows_p + (pair ? 256 : BM) - 1) / (pair ? 256 : BM);
     p.tiles_q = (p.rows_q + bn - 1) / bn;
 
     int st;
@@ -485,6 +712,7 @@ extern "C" int tb_gemm_tc(const void* A, const void* W, void* C, int c_dtype, in
 #define GG(BN_, SW_) launch<BN_, SW_, bf16, true>(mp, mq, p, stream)
         if (swap) st = bn == 16 ? (wide ? launch<16, true, bf16, true, true>(mp, mq, p, stream) : GG(16, true))
                      : bn == 32 ? GG(32, true) : bn == 64 ? GG(64, true) : GG(128, true);
+        else if (pair) st = launch_pair<bf16, true>(mp, mq, p, stream);
         else st = bn == 256 ? GG(256, false) : GG(128, false);
 #undef GG
     } else if (swap) {
@@ -499,6 +727,8 @@ extern "C" int tb_gemm_tc(const void* A, const void* W, void* C, int c_dtype, in
         case 64: st = GO(64, true); break;
         default: st = GO(128, true); break;
         }
+    } else if (pair) {
+        st = c_dtype == TB_BF16 ? launch_pair<bf16, false>(mp, mq, p, stream) : launch_pair<float, false>(mp, mq, p, stream);
     } else {
         st = bn == 256 ? GO(256, false) : GO(128, false);
     }

@@ -546,9 +546,15 @@ def kernel_errors() -> dict:
     return out
 
 
+def gemm_tc_set_pair(mode: int) -> int:
+    """Many-token products on pairs of SMs: 0 never, 1 whenever the shape allows, 2 where it pays (the default);
+    returns the previous setting."""
+    return int(build.load("gemm_tc").tb_gemm_tc_set_pair(c_int(int(mode))))
+
+
 def gemm_tc_error() -> int:
     """Reads and clears the tensor-core GEMM's error word (synchronises): 0, or the role whose
-    bounded wait ran out (1 loader, 2 MMA issuer, 3 epilogue)."""
+    bounded wait ran out (1 loader, 2 MMA issuer, 3 epilogue; 4 to 6 the same roles of the kernel on pairs of SMs)."""
     return int(build.load("gemm_tc").tb_gemm_tc_error())
 
 
