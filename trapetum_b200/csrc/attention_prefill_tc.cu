@@ -97,9 +97,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int b = blockIdx.z, h = blockIdx.y;
+    const int b = blockIdx.y, h = blockIdx.x;
     const int s0 = a.seq_start[b], len = a.seq_start[b + 1] - s0;
-    const int qb = (int)gridDim.x - 1 - (int)blockIdx.x;             // longest blocks first
+    // Blocks are placed in the order of their index, x fastest: the heads of one query block side by side (those of a
+    // kv head read the same keys), then the sequences; the longest query blocks of every head and sequence first.
+    const int qb = (int)gridDim.z - 1 - (int)blockIdx.z;
     const int m0 = qb * BM;
     if (m0 >= len) return;                                           // uniform for the CTA
     const int kvh = h / (a.n_heads / a.n_kv_heads);
@@ -438,7 +440,8 @@ extern "C" int tb_attn_prefill_tc(const void* q, const void* k, const void* v, l
         return tb_refuse("attn_prefill_tc: %d heads cannot share %d kv heads", n_heads, n_kv_heads);
     if (((uintptr_t)q & 15) || ((uintptr_t)k & 15) || ((uintptr_t)v & 15) || (q_stride % 8) || (kv_stride % 8))
         return tb_refuse("attn_prefill_tc: q, k, v rows must be 16-byte aligned");
-    if (n_heads > 65535 || batch > 65535) return tb_refuse("attn_prefill_tc: %d heads x %d sequences exceed one launch", n_heads, batch);
+    if ((max_seq_len + BM - 1) / BM > 65535 || batch > 65535)
+        return tb_refuse("attn_prefill_tc: %d query blocks x %d sequences exceed one launch", (max_seq_len + BM - 1) / BM, batch);
     const int kvw = n_kv_heads * HD;
     CUtensorMap mk, mv;
     if (make_map(&mk, k, n_tokens, kvw, kv_stride, BN) || make_map(&mv, v, n_tokens, kvw, kv_stride, BN)) return -1;
@@ -452,7 +455,7 @@ extern "C" int tb_attn_prefill_tc(const void* q, const void* k, const void* v, l
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
     }
-    dim3 grid((max_seq_len + BM - 1) / BM, n_heads, batch);
+    dim3 grid(n_heads, batch, (max_seq_len + BM - 1) / BM);
     tb_launch(attn_prefill_tc_kernel, grid, dim3(320), SMEM_BYTES, stream, mk, mv, a);
     return tb_launch_status();
 }

@@ -153,83 +153,104 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TA* __restrict__
     }
 }
 
-// Many rows (prefill): WPR warps per row (1, 2, 4 or 8, so that a lane holds at most NV groups of four columns in
-// registers), eight warps a block.  A row's warps meet twice, for the two sums of squares, through shared memory;
-// nothing else is shared.  32-bit branch input (one partial sum), bfloat16 weights: the engine's hot case.
+// Many rows (prefill): WPR warps per row (1 to 16, so that a lane holds at most NV groups of four columns of a row in
+// registers), eight warps a block (sixteen with WPR 16).  A row's warps meet twice, for the two sums of squares,
+// through shared memory; nothing else is shared.  The grid is as many blocks as the device holds at once; a block
+// walks its rows and has the next row's loads under way while it works on this one (the kernel is bound by the
+// latency of its loads, not by bandwidth).  32-bit branch input (one partial sum), bfloat16 weights: the engine's
+// hot case.
 template <typename TO, int NV, int WPR>
-__global__ void __launch_bounds__(256) add_rmsnorm_rows_kernel(float* __restrict__ h, const float* __restrict__ a,
-                                                               const bf16* __restrict__ wa, float eps_a, float off_a,
-                                                               const bf16* __restrict__ wb, float eps_b, float off_b,
-                                                               TO* __restrict__ out, int rows, int width) {
+__global__ void __launch_bounds__(32 * (WPR > 8 ? WPR : 8))
+add_rmsnorm_rows_kernel(float* __restrict__ h, const float* __restrict__ a,
+                        const bf16* __restrict__ wa, float eps_a, float off_a,
+                        const bf16* __restrict__ wb, float eps_b, float off_b,
+                        TO* __restrict__ out, int rows, int width) {
+    constexpr int WARPS = WPR > 8 ? WPR : 8;                      // warps of a block
+    constexpr int RPB = WARPS / WPR;                              // rows a block holds at a time
     pdl_launch_dependents();
     pdl_wait();
-    __shared__ float part[2][8];
+    __shared__ float part[2][2][WARPS];                           // [row parity][which norm][warp]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int sub = warp % WPR;                                   // which piece of the row this warp holds
-    const int row = blockIdx.x * (8 / WPR) + warp / WPR;
-    const bool live = row < rows;
     const int seg = width / WPR;                                  // columns per warp (a multiple of 4)
-    const size_t base = (size_t)(live ? row : 0) * width + (size_t)sub * seg;
     const int col0 = sub * seg;
-    float v[NV][4], hv[NV][4];
-    float ss = 0.f;
-    // the branch output and the residual row are both requested before anything waits for either
+    const int stride = gridDim.x * RPB;
+    int row = blockIdx.x * RPB + warp / WPR;
+    float v[NV][4], hv[NV][4], nv[NV][4], nhv[NV][4];
+    // a block walks its rows; the next row's branch output and residual are requested before this row's are
+    // waited for, so that a block always has loads under way
+    auto fetch = [&](int r, float (*va)[4], float (*vh)[4]) {
+        const size_t base = (size_t)r * width + col0;
 #pragma unroll
-    for (int k = 0; k < NV; k++) {
-        const int i = (k * 32 + lane) * 4;
-        if (live && i < seg) Vec4<float>::load(a + base + i, v[k]);
-    }
-#pragma unroll
-    for (int k = 0; k < NV; k++) {
-        const int i = (k * 32 + lane) * 4;
-        if (live && i < seg) Vec4<float>::load(h + base + i, hv[k]);
-    }
-#pragma unroll
-    for (int k = 0; k < NV; k++) {
-        const int i = (k * 32 + lane) * 4;
-        if (live && i < seg) ss += v[k][0] * v[k][0] + v[k][1] * v[k][1] + v[k][2] * v[k][2] + v[k][3] * v[k][3];
-    }
-    ss = warp_sum(ss);
-    if (WPR > 1) {
-        if (lane == 0) part[0][warp] = ss;
-        __syncthreads();
-        ss = 0.f;
-#pragma unroll
-        for (int w = 0; w < WPR; w++) ss += part[0][warp - sub + w];           // the same order in every warp of the row
-    }
-    const float ra = rsqrtf(ss / (float)width + eps_a);
-    float s2 = 0.f;
-#pragma unroll
-    for (int k = 0; k < NV; k++) {
-        const int i = (k * 32 + lane) * 4;
-        if (live && i < seg) {
-            float g[4];
-            Vec4<bf16>::load(wa + col0 + i, g);
-#pragma unroll
-            for (int e = 0; e < 4; e++) { v[k][e] = hv[k][e] + v[k][e] * ra * (off_a + g[e]); s2 += v[k][e] * v[k][e]; }
-            Vec4<float>::store(h + base + i, v[k]);
+        for (int k = 0; k < NV; k++) {
+            const int i = (k * 32 + lane) * 4;
+            if (r < rows && i < seg) Vec4<float>::load(a + base + i, va[k]);
         }
-    }
-    if (out == nullptr) return;                                   // the same in every thread of the launch
-    s2 = warp_sum(s2);
-    if (WPR > 1) {
-        if (lane == 0) part[1][warp] = s2;
-        __syncthreads();
-        s2 = 0.f;
 #pragma unroll
-        for (int w = 0; w < WPR; w++) s2 += part[1][warp - sub + w];
-    }
-    const float rb = rsqrtf(s2 / (float)width + eps_b);
-#pragma unroll
-    for (int k = 0; k < NV; k++) {
-        const int i = (k * 32 + lane) * 4;
-        if (live && i < seg) {
-            float g[4], y[4];
-            Vec4<bf16>::load(wb + col0 + i, g);
-#pragma unroll
-            for (int e = 0; e < 4; e++) y[e] = v[k][e] * rb * (off_b + g[e]);
-            Vec4<TO>::store(out + base + i, y);
+        for (int k = 0; k < NV; k++) {
+            const int i = (k * 32 + lane) * 4;
+            if (r < rows && i < seg) Vec4<float>::load(h + base + i, vh[k]);
         }
+    };
+    fetch(row, v, hv);
+    for (int it = 0; row - warp / WPR < rows; row += stride, it++) {        // the same trip count in every warp
+        const bool live = row < rows;
+        const size_t base = (size_t)(live ? row : 0) * width + col0;
+        fetch(row + stride, nv, nhv);
+        float (*pt)[WARPS] = part[it & 1];
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < NV; k++) {
+            const int i = (k * 32 + lane) * 4;
+            if (live && i < seg) ss += v[k][0] * v[k][0] + v[k][1] * v[k][1] + v[k][2] * v[k][2] + v[k][3] * v[k][3];
+        }
+        ss = warp_sum(ss);
+        if (WPR > 1) {
+            if (lane == 0) pt[0][warp] = ss;
+            __syncthreads();
+            ss = 0.f;
+#pragma unroll
+            for (int w = 0; w < WPR; w++) ss += pt[0][warp - sub + w];        // the same order in every warp of the row
+        }
+        const float ra = rsqrtf(ss / (float)width + eps_a);
+        float s2 = 0.f;
+#pragma unroll
+        for (int k = 0; k < NV; k++) {
+            const int i = (k * 32 + lane) * 4;
+            if (live && i < seg) {
+                float g[4];
+                Vec4<bf16>::load(wa + col0 + i, g);
+#pragma unroll
+                for (int e = 0; e < 4; e++) { v[k][e] = hv[k][e] + v[k][e] * ra * (off_a + g[e]); s2 += v[k][e] * v[k][e]; }
+                Vec4<float>::store(h + base + i, v[k]);
+            }
+        }
+        if (out != nullptr) {                                     // the same in every thread of the launch
+            s2 = warp_sum(s2);
+            if (WPR > 1) {
+                if (lane == 0) pt[1][warp] = s2;
+                __syncthreads();
+                s2 = 0.f;
+#pragma unroll
+                for (int w = 0; w < WPR; w++) s2 += pt[1][warp - sub + w];
+            }
+            const float rb = rsqrtf(s2 / (float)width + eps_b);
+#pragma unroll
+            for (int k = 0; k < NV; k++) {
+                const int i = (k * 32 + lane) * 4;
+                if (live && i < seg) {
+                    float g[4], y[4];
+                    Vec4<bf16>::load(wb + col0 + i, g);
+#pragma unroll
+                    for (int e = 0; e < 4; e++) y[e] = v[k][e] * rb * (off_b + g[e]);
+                    Vec4<TO>::store(out + base + i, y);
+                }
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < NV; k++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) { v[k][e] = nv[k][e]; hv[k][e] = nhv[k][e]; }
     }
 }
 
@@ -366,24 +387,41 @@ extern "C" int tb_add_rmsnorm(float* h, const void* a, int a_dtype, int n_splits
     const size_t smem = row_cache ? (size_t)width * sizeof(float) : 0;
     const bool vec = width % 4 == 0 && split_stride % 4 == 0 && aligned16(h) && aligned16(a) && aligned16(wa) &&
                      aligned16(wb) && aligned16(out);
-    if (vec && rows >= 64 && n_splits == 1 && a_dtype == TB_F32 && w_dtype == TB_BF16 && width <= 48 * 128) {
-        // warps per row: as few as keep a lane's share of the row within twelve groups of four columns
-        // (measured alone, cold, at 2,048 rows of 2,304 / 3,584 / 4,608 columns: 8 warps a row with both inputs
-        // requested at once take 20 / 26 / 36 us; one warp a row with the whole row in its registers took 27 / 59 / 76)
-        int wpr = width <= 512 ? 1 : width <= 1024 ? 2 : width <= 2048 ? 4 : 8;
+    if (vec && rows >= 64 && n_splits == 1 && a_dtype == TB_F32 && w_dtype == TB_BF16 && width <= 16 * 512) {
+        // warps per row: as few as keep a lane's share of the row within four groups of four columns (it holds two
+        // rows at a time: the one it works on and the one it has requested)
+        int wpr = width <= 512 ? 1 : width <= 1024 ? 2 : width <= 2048 ? 4 : width <= 4096 ? 8 : 16;
         while (wpr > 1 && width % (wpr * 4)) wpr /= 2;
         const int nv = (width / wpr / 4 + 31) / 32;
-        if (nv <= 12) {
-            const unsigned blocks = (unsigned)((rows + 8 / wpr - 1) / (8 / wpr));
+        if (nv <= 4) {
+            static int sms = 0;
+            if (!sms) {
+                int dev = 0; cudaGetDevice(&dev);
+                cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+                if (sms <= 0) sms = 148;
+            }
+            const int rpb = (wpr > 8 ? wpr : 8) / wpr;
+            const unsigned need = (unsigned)((rows + rpb - 1) / rpb);
+            const unsigned threads = 32 * (wpr > 8 ? wpr : 8);
+            unsigned blocks = 0;
 #define ROWS(NV_, WPR_)                                                                                            \
             do {                                                                                                   \
-                if (out_dtype == TB_BF16) tb_launch(add_rmsnorm_rows_kernel<bf16, NV_, WPR_>, dim3(blocks), dim3(256), 0, stream, \
+                static int per_sm = 0;                        /* blocks of this kernel that an SM holds at once */   \
+                if (!per_sm) {                                                                                     \
+                    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, add_rmsnorm_rows_kernel<bf16, NV_, WPR_>, \
+                                                                      (int)threads, 0) != cudaSuccess || per_sm < 1) { \
+                        cudaGetLastError(); per_sm = 1;                                                            \
+                    }                                                                                              \
+                }                                                                                                  \
+                blocks = need < (unsigned)(sms * per_sm) ? need : (unsigned)(sms * per_sm);                        \
+                if (out_dtype == TB_BF16) tb_launch(add_rmsnorm_rows_kernel<bf16, NV_, WPR_>, dim3(blocks), dim3(threads), 0, stream, \
                     h, (const float*)a, (const bf16*)wa, eps_a, off_a, (const bf16*)wb, eps_b, off_b, (bf16*)out, rows, width); \
-                else tb_launch(add_rmsnorm_rows_kernel<float, NV_, WPR_>, dim3(blocks), dim3(256), 0, stream,        \
+                else tb_launch(add_rmsnorm_rows_kernel<float, NV_, WPR_>, dim3(blocks), dim3(threads), 0, stream,    \
                     h, (const float*)a, (const bf16*)wa, eps_a, off_a, (const bf16*)wb, eps_b, off_b, (float*)out, rows, width); \
             } while (0)
-#define ROWS_W(NV_) do { if (wpr == 1) ROWS(NV_, 1); else if (wpr == 2) ROWS(NV_, 2); else if (wpr == 4) ROWS(NV_, 4); else ROWS(NV_, 8); } while (0)
-            if (nv <= 2) ROWS_W(2); else if (nv <= 4) ROWS_W(4); else if (nv <= 8) ROWS_W(8); else ROWS_W(12);
+#define ROWS_W(NV_) do { if (wpr == 1) ROWS(NV_, 1); else if (wpr == 2) ROWS(NV_, 2); else if (wpr == 4) ROWS(NV_, 4); \
+                         else if (wpr == 8) ROWS(NV_, 8); else ROWS(NV_, 16); } while (0)
+            if (nv <= 2) ROWS_W(2); else if (nv == 3) ROWS_W(3); else ROWS_W(4);
 #undef ROWS_W
 #undef ROWS
             return tb_launch_status();
