@@ -17,9 +17,10 @@
 // and optional split-K (small N, large K): each split writes 32-bit partials to
 // scratch and tb_splitk_reduce adds them in split order.
 //
-// Roles per CTA (192 threads): warp 0 issues TMA loads, warp 1 owns tensor memory
-// and issues the MMAs, warps 2..5 are the epilogue (a warp reads the 32 lanes of
-// tensor memory that its index modulo 4 selects).  The kernel is persistent: a
+// Roles per CTA (320 threads): warp 0 issues TMA loads, warp 1 owns tensor memory
+// and issues the MMAs, warps 2..9 are the epilogue (a warp reads the 32 lanes of
+// tensor memory that its index modulo 4 selects; the two warps of a quarter take
+// the chunks of columns in turn).  The kernel is persistent: a
 // CTA walks its share of the work items; two accumulator stages let the epilogue
 // of one item overlap the MMAs of the next.
 //
@@ -38,6 +39,8 @@ TB_EXPORT_ERROR()
 
 #define BM 128
 #define BK 64
+#define EPI_WARPS 8                      // two warps for each quarter of the tensor memory's lanes
+#define GEMM_THREADS (64 + 32 * EPI_WARPS)
 
 __device__ int g_gemm_error = 0;
 
@@ -160,7 +163,7 @@ __device__ __forceinline__ void store_token_major(const uint32_t* r, int prow, i
 }
 
 template <int BN, bool SWAP, typename TOut, bool GATED, bool WIDE>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, GemmParams p) {
     pdl_launch_dependents();
     using C = Cfg<BN, SWAP, WIDE>;
@@ -179,7 +182,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     if (threadIdx.x == 32) { tma_prefetch_map(&map_p); tma_prefetch_map(&map_q); }
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int a = 0; a < 2; a++) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+        for (int a = 0; a < 2; a++) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], EPI_WARPS); }
         *abort_flag = 0;
         mbar_init_fence();
     }
@@ -275,8 +278,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             if (!ok && !*abort_flag) { atomicExch(&g_gemm_error, 2); *abort_flag = 1; }
         }
     } else {
-        // ---------------- epilogue: warps 2..5 ----------------
+        // ---------------- epilogue: warps 2..9 ----------------
         const int quarter = warp & 3;                  // the TMEM lanes this warp may read
+        const int turn = (warp - 2) >> 2;              // the two warps of a quarter take the chunks of columns in turn
         pdl_wait();                                    // the output may still be read by the kernel before
         uint32_t tile_it = 0;
         bool ok = true;
@@ -291,7 +295,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             const uint32_t t_addr = tmem_base + a * C::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
             constexpr int CH = BN >= 32 ? 32 : 16;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += CH) {
+            for (int c0 = turn * CH; c0 < BN; c0 += (EPI_WARPS / 4) * CH) {
                 uint32_t r[CH];
                 if (CH == 32) tmem_ld32(t_addr + c0, r); else tmem_ld16(t_addr + c0, r);
                 tmem_ld_wait();
@@ -299,15 +303,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 if constexpr (!SWAP) {
                     store_token_major<TOut, GATED, CH>(r, prow, q0, sp, p);
                 } else if (GATED && SWAP) {
-                    // lanes 0..15 hold gates, lanes 16..31 the ups of the same 16 features
+                    // Lanes 0..15 hold gates, lanes 16..31 the ups of the same 16 features.  Two tokens a round: the
+                    // lower lanes hand over their gates of the second token and get the ups of the first, so that each
+                    // half of the warp computes and stores one token.
+                    const bool low = lane < 16;
+                    const int feat = ((prow >> 5) << 4) + (lane & 15);
 #pragma unroll
-                    for (int j = 0; j < CH; j++) {
-                        const float mine = __uint_as_float(r[j]);
-                        const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
-                        const int tok = q0 + j;
-                        if (lane < 16 && tok < p.rows_q && prow < p.rows_p)
-                            ((bf16*)p.out)[(size_t)tok * p.ld_out + ((prow >> 5) << 4) + lane] =
-                                __float2bfloat16_rn(gated(mine, other, p.act));
+                    for (int j = 0; j < CH; j += 2) {
+                        const float got = __shfl_xor_sync(0xffffffffu, __uint_as_float(low ? r[j + 1] : r[j]), 16);
+                        const float g = low ? __uint_as_float(r[j]) : got;
+                        const float u = low ? got : __uint_as_float(r[j + 1]);
+                        const int tok = q0 + j + (low ? 0 : 1);
+                        if (tok < p.rows_q && prow < p.rows_p)
+                            ((bf16*)p.out)[(size_t)tok * p.ld_out + feat] = __float2bfloat16_rn(gated(g, u, p.act));
                     }
                 } else {
                     // weight rows on lanes (prow), tokens on columns (q0 + j): lanes write neighbours
@@ -362,7 +370,7 @@ struct PairCfg {
 };
 
 template <typename TOut, bool GATED>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, GemmParams p) {
     pdl_launch_dependents();
     using C = PairCfg;
@@ -383,7 +391,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     if (threadIdx.x == 32) { tma_prefetch_map(&map_p); tma_prefetch_map(&map_q); }
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int a = 0; a < 2; a++) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
+        for (int a = 0; a < 2; a++) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 2 * EPI_WARPS); }
         *abort_flag = 0;
         mbar_init_fence();
     }
@@ -474,8 +482,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             if (!ok && !*abort_flag) { atomicExch(&g_gemm_error, 5); *abort_flag = 1; }
         }
     } else {
-        // ---------------- epilogue: warps 2..5 of both CTAs ----------------
+        // ---------------- epilogue: warps 2..9 of both CTAs ----------------
         const int quarter = warp & 3;
+        const int turn = (warp - 2) >> 2;
         const uint32_t lead_acc_empty = cluster_addr(&acc_empty[0], 0);
         pdl_wait();
         uint32_t tile_it = 0;
@@ -489,7 +498,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             const int prow = tp * 256 + (int)rank * BM + quarter * 32 + lane;
             const uint32_t t_addr = tmem_base + a * C::BN + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll 1
-            for (int c0 = 0; c0 < C::BN; c0 += 32) {
+            for (int c0 = turn * 32; c0 < C::BN; c0 += (EPI_WARPS / 4) * 32) {
                 uint32_t r[32];
                 tmem_ld32(t_addr + c0, r);
                 tmem_ld_wait();
@@ -571,7 +580,7 @@ static int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmParams
     }
     const int items = p.tiles_p * p.tiles_q * p.splits;
     const int grid = items < g_sms ? items : g_sms;
-    tb_launch(kern, dim3(grid), dim3(192), C::SMEM, stream, mp, mq, p);
+    tb_launch(kern, dim3(grid), dim3(GEMM_THREADS), C::SMEM, stream, mp, mq, p);
     return tb_launch_status();
 }
 
@@ -610,14 +619,14 @@ static int launch_pair(const CUtensorMap& mp, const CUtensorMap& mq, const GemmP
     if (!g_pair_clusters) {
         // how many pairs the device runs at once (an SM without a free neighbour takes none)
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(2 * (g_sms / 2)); cfg.blockDim = dim3(192); cfg.dynamicSmemBytes = C::SMEM;
+        cfg.gridDim = dim3(2 * (g_sms / 2)); cfg.blockDim = dim3(GEMM_THREADS); cfg.dynamicSmemBytes = C::SMEM;
         int n = 0;
         if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) { cudaGetLastError(); n = g_sms / 2; }
         g_pair_clusters = n < g_sms / 2 ? n : g_sms / 2;
     }
     const int items = p.tiles_p * p.tiles_q * p.splits;
     const int pairs = items < g_pair_clusters ? items : g_pair_clusters;
-    tb_launch(kern, dim3(2 * pairs), dim3(192), C::SMEM, stream, mp, mq, p);
+    tb_launch(kern, dim3(2 * pairs), dim3(GEMM_THREADS), C::SMEM, stream, mp, mq, p);
     return tb_launch_status();
 }
 
