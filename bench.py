@@ -410,6 +410,48 @@ def leave_out_report(engine, model, cfg, torch, args, warmup) -> int:
     return 0
 
 
+def gemm_compare(cfg, torch, tokens, bf16_tflops):
+    """The four products of a layer at ``tokens`` tokens, this library's tensor-core kernel beside torch.matmul
+    (cuBLAS), as a comparison only: neither result feeds a bench number.  Each launch gets another of three weight
+    matrices, so the weights come from memory; 12 launches are captured in a CUDA graph and timed as one."""
+    from trapetum_b200.csrc import ops
+    H, I = cfg["hidden_size"], cfg["intermediate_size"]
+    qd, kvd = cfg["num_attention_heads"] * cfg["head_dim"], cfg["num_key_value_heads"] * cfg["head_dim"]
+    shapes = [("qkv", qd + 2 * kvd, H), ("o", H, qd), ("gate_up", 2 * I, H), ("down", H, I)]
+    g0 = torch.Generator(device="cuda").manual_seed(1)
+
+    def timed(fn, reps=12):
+        for i in range(3):
+            fn(i)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(reps):
+                fn(i)
+        best = None
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); graph.replay(); e1.record()
+            torch.cuda.synchronize()
+            t = e0.elapsed_time(e1) / reps
+            best = t if best is None else min(best, t)
+        return best
+
+    for name, N, K in shapes:
+        a = (torch.randn(tokens, K, device="cuda", generator=g0) * 0.5).to(torch.bfloat16)
+        ws = [(torch.randn(N, K, device="cuda", generator=g0) * 0.05).to(torch.bfloat16) for _ in range(3)]
+        outs = [torch.empty(tokens, N, dtype=torch.bfloat16, device="cuda") for _ in range(3)]
+        ours = timed(lambda i: ops.gemm_tc(a, ws[i % 3], torch.bfloat16))
+        lib = timed(lambda i: torch.matmul(a, ws[i % 3].t(), out=outs[i % 3]))
+        fl = 2.0 * tokens * N * K
+        print(json.dumps({"product": name, "tokens": tokens, "weight_rows": N, "k": K,
+                          "ours_us": round(ours * 1e3, 1), "ours_tflops": round(fl / ours / 1e9, 1),
+                          "torch_matmul_us": round(lib * 1e3, 1), "torch_matmul_tflops": round(fl / lib / 1e9, 1),
+                          "ours_over_torch": round(lib / ours, 3),
+                          "ours_frac_of_peak": round(fl / (ours * 1e-3) / (bf16_tflops * 1e12), 3)}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -435,6 +477,9 @@ def main() -> int:
     ap.add_argument("--leave-out", action="store_true",
                     help="instead of the bench line: the decode step re-timed with one kind of launch left out at a "
                          "time (its results are then wrong; only its time is of interest), one line per kind")
+    ap.add_argument("--gemm-compare", type=int, default=0, metavar="TOKENS",
+                    help="instead of the bench line: the four products of a layer of --model at TOKENS tokens, this "
+                         "library's kernel beside torch.matmul, one line per product (a comparison only)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -449,6 +494,8 @@ def main() -> int:
     warmup = max(3, args.warmup)
 
     import torch
+    if args.gemm_compare:
+        return gemm_compare(MODELS[args.model], torch, args.gemm_compare, peaks()[1])
     from trapetum_b200 import Engine
     global HOST
     HOST = "python" if args.leave_out else args.host
