@@ -284,6 +284,18 @@ int tb_register_mixer(const char* kind, const tb_mixer_plugin* plugin) {
     TB_CATCH_STATUS
 }
 
+int tb_register_feed_forward(const char* kind, const tb_mixer_plugin* plugin) {
+    TB_TRY
+    if (!kind || !*kind || !plugin || !plugin->create || !plugin->forward)
+        throw Error("tb_register_feed_forward: a kind, create and forward are needed");
+    register_builtin_parts();
+    Registry<FeedForwardPart>::add(kind, [plugin](const PartSpec& s, const std::string& prefix, Runtime rt) {
+        return std::unique_ptr<FeedForwardPart>(new PluginFeedForward(plugin, s, prefix, rt));
+    });
+    return TB_OK;
+    TB_CATCH_STATUS
+}
+
 const char* tb_spec_from_config(const char* config_json) {
     static thread_local std::string out;
     try {

@@ -387,24 +387,27 @@ private:
     std::shared_ptr<DeviceTensor> keep_;
 };
 
-// ---- a mixer from outside the library (plugin.h) -------------------------------------------------------------------
-class PluginMixer : public MixerPart {
+// ---- parts from outside the library (plugin.h): a mixer or a feed-forward described by a table of functions -----------
+class PluginCore {
 public:
-    PluginMixer(const tb_mixer_plugin* p, const PartSpec& s, const std::string& prefix, Runtime rt) : p_(p), rt_(rt) {
+    PluginCore(const char* what, const tb_mixer_plugin* p, const PartSpec& s, const std::string& prefix, Runtime rt)
+        : p_(p), what_(std::string(what) + " '" + s.kind + "'") {
         const char* err = nullptr;
         self_ = p->create(s.params.dump().c_str(), prefix.c_str(), (int)rt.dt, &err);
-        if (!self_) throw Error("mixer '" + s.kind + "' could not be made: " + (err ? err : "no reason given"));
-        kind_ = s.kind;
+        if (!self_) throw Error(what_ + " could not be made: " + (err ? err : "no reason given"));
     }
-    ~PluginMixer() override {
+    ~PluginCore() {
         if (self_ && p_->destroy) p_->destroy(self_);
     }
-    void tensor_specs(WantedTensors& w) const override {
+    PluginCore(const PluginCore&) = delete;
+    PluginCore& operator=(const PluginCore&) = delete;
+
+    void tensor_specs(WantedTensors& w) const {
         const int n = p_->tensor_count ? p_->tensor_count(self_) : 0;
         for (int i = 0; i < n; i++) {
             tb_tensor_decl d;
             memset(&d, 0, sizeof d);
-            if (p_->tensor_decl(self_, i, &d)) throw Error("mixer '" + kind_ + "': tensor_decl failed");
+            if (p_->tensor_decl(self_, i, &d)) throw Error(what_ + ": tensor_decl failed");
             TensorSpec ts;
             ts.shape.assign(d.shape, d.shape + d.ndim);
             ts.role = d.role[0] ? d.role : "matrix";
@@ -412,7 +415,7 @@ public:
             w.add(d.name, ts);
         }
     }
-    void bind(const TensorMap& t, Ops&) override {
+    void bind(const TensorMap& t) {
         const int n = p_->tensor_count ? p_->tensor_count(self_) : 0;
         for (int i = 0; i < n; i++) {
             tb_tensor_decl d;
@@ -423,34 +426,37 @@ public:
             keep_.push_back(it->second);
             const char* err = nullptr;
             if (p_->bind(self_, d.name, it->second->buf.p, (int)it->second->dt, &err))
-                throw Error("mixer '" + kind_ + "' refused tensor " + d.name + ": " + (err ? err : "no reason given"));
+                throw Error(what_ + " refused tensor " + d.name + ": " + (err ? err : "no reason given"));
         }
     }
-    bool graph_safe() const override { return p_->graph_safe != 0; }
-    CacheNeed cache_need() const override {
+    bool graph_safe() const { return p_->graph_safe != 0; }
+    CacheNeed cache_need() const {
         CacheNeed n;
         tb_cache_need c;
         memset(&c, 0, sizeof c);
-        if (p_->cache_need && p_->cache_need(self_, &c)) throw Error("mixer '" + kind_ + "': cache_need failed");
+        if (p_->cache_need && p_->cache_need(self_, &c)) throw Error(what_ + ": cache_need failed");
         n.kind = c.kind == TB_NEED_KV ? CacheNeed::KV : c.kind == TB_NEED_STATE ? CacheNeed::STATE : CacheNeed::NONE;
         n.n_kv_heads = c.n_kv_heads; n.head_dim = c.head_dim; n.window = c.window; n.state_bytes = (size_t)c.state_bytes;
         return n;
     }
-    Partials forward(Ops& ops, const Mat& x, StepCtx& ctx, const CacheLine& line) override {
+    // line: the mixer's cache line; a feed-forward has none
+    Partials forward(Ops& ops, const Mat& x, StepCtx& ctx, const CacheLine* line) {
         Mat out = ops.arena->mat(F32, x.rows, x.cols);
         tb_part_ctx c;
         memset(&c, 0, sizeof c);
         c.stream = ops.stream; c.dry = ops.dry() ? 1 : 0; c.is_prefill = ctx.is_prefill; c.n_tokens = ctx.n_tokens; c.batch = ctx.batch;
         c.positions = ctx.positions; c.token_seq = ctx.token_seq; c.seq_start = ctx.seq_start; c.len_after = ctx.len_after;
         c.slot_ids = ctx.slot_ids; c.host_slots = ctx.slots.data(); c.host_seq_lens = ctx.seq_lens.data();
-        c.state = line.state; c.state_bytes = (long long)line.state_bytes;
-        c.k = line.k; c.v = line.v; c.page_table = line.page_table; c.pt_stride = line.pt_stride; c.ring_rows = line.ring_rows;
-        c.line_owner = line.owner ? 1 : 0;
+        if (line) {
+            c.state = line->state; c.state_bytes = (long long)line->state_bytes;
+            c.k = line->k; c.v = line->v; c.page_table = line->page_table; c.pt_stride = line->pt_stride; c.ring_rows = line->ring_rows;
+            c.line_owner = line->owner ? 1 : 0;
+        }
         c.alloc = [](void* a, size_t bytes) { return ((Arena*)a)->alloc(bytes); };
         c.arena = ops.arena;
         const char* err = nullptr;
         if (p_->forward(self_, &c, x.p, (int)x.dt, x.rows, x.cols, (float*)out.p, &err))
-            throw Error("mixer '" + kind_ + "' failed: " + (err ? err : "no reason given"));
+            throw Error(what_ + " failed: " + (err ? err : "no reason given"));
         Partials r;
         r.p = (float*)out.p; r.rows = out.rows; r.cols = out.cols; r.split_stride = out.rows * out.cols;
         return r;
@@ -458,10 +464,36 @@ public:
 
 private:
     const tb_mixer_plugin* p_;
-    Runtime rt_;
     void* self_ = nullptr;
-    std::string kind_;
+    std::string what_;
     std::vector<std::shared_ptr<DeviceTensor>> keep_;
+};
+
+class PluginMixer : public MixerPart {
+public:
+    PluginMixer(const tb_mixer_plugin* p, const PartSpec& s, const std::string& prefix, Runtime rt) : core_("mixer", p, s, prefix, rt) {}
+    void tensor_specs(WantedTensors& w) const override { core_.tensor_specs(w); }
+    void bind(const TensorMap& t, Ops&) override { core_.bind(t); }
+    bool graph_safe() const override { return core_.graph_safe(); }
+    CacheNeed cache_need() const override { return core_.cache_need(); }
+    Partials forward(Ops& ops, const Mat& x, StepCtx& ctx, const CacheLine& line) override { return core_.forward(ops, x, ctx, &line); }
+
+private:
+    PluginCore core_;
+};
+
+// The same table describes a feed-forward: it has no cache (cache_need is not asked) and gets no cache line.
+class PluginFeedForward : public FeedForwardPart {
+public:
+    PluginFeedForward(const tb_mixer_plugin* p, const PartSpec& s, const std::string& prefix, Runtime rt)
+        : core_("feed-forward", p, s, prefix, rt) {}
+    void tensor_specs(WantedTensors& w) const override { core_.tensor_specs(w); }
+    void bind(const TensorMap& t, Ops&) override { core_.bind(t); }
+    bool graph_safe() const override { return core_.graph_safe(); }
+    Partials forward(Ops& ops, const Mat& x, StepCtx& ctx) override { return core_.forward(ops, x, ctx, nullptr); }
+
+private:
+    PluginCore core_;
 };
 
 // ---- gated dense feed-forward: down(act(gate(x)) * up(x)) ---------------------------------------------------------

@@ -1,5 +1,5 @@
-/* Parts from outside the library, for the native host: a mixer written in C, C++ or CUDA is described by a
- * table of functions and registered under a kind name; a model spec that names that kind is then built, bound
+/* Parts from outside the library, for the native host: a mixer or a feed-forward written in C, C++ or CUDA is
+ * described by a table of functions and registered under a kind name; a model spec that names that kind is then built, bound
  * and stepped like any other, with no change to the library.  (The Python host takes parts written in Python
  * the same way, trapetum_b200.parts.register_part.)
  *
@@ -74,6 +74,10 @@ typedef struct tb_mixer_plugin {
 
 /* Makes `kind` a mixer that model specs can name.  The table must outlive the process's models. */
 int tb_register_mixer(const char* kind, const tb_mixer_plugin* plugin);
+
+/* Makes `kind` a feed-forward.  The table is the same; cache_need is not asked (a feed-forward keeps nothing
+ * between steps), and the cache fields of tb_part_ctx (state, k, v, page_table) are null in its calls. */
+int tb_register_feed_forward(const char* kind, const tb_mixer_plugin* plugin);
 
 #ifdef __cplusplus
 }
