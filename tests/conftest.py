@@ -156,3 +156,21 @@ def tolerance_of(plain_models):
 def make_prompts(vocab: int, lengths, seed: int):
     g = torch.Generator().manual_seed(seed)
     return [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lengths]
+
+
+import contextlib
+
+
+@contextlib.contextmanager
+def decode_partition(mode):
+    """Decode attention's partition forced on both hosts ("split", "stream"; None leaves the choice to the library)
+    for engines made inside the block."""
+    from trapetum_b200 import native
+    from trapetum_b200.csrc import ops
+    was_py = ops.set_decode_partition(mode)
+    was_native = native.set_decode_partition(mode)
+    try:
+        yield
+    finally:
+        ops.set_decode_partition(was_py)
+        native.set_decode_partition(was_native)

@@ -7,7 +7,7 @@ import pytest
 import torch
 
 import plain_gemma2 as plain
-from conftest import TOL, bf16_budget, make_prompts, rel_l2, sharpen, within
+from conftest import decode_partition, TOL, bf16_budget, make_prompts, rel_l2, sharpen, within
 
 pytestmark = pytest.mark.gpu
 
@@ -54,9 +54,19 @@ def models(tmp_path_factory):
     return get
 
 
+@pytest.mark.parametrize("partition", [None, "stream"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("shape", ["2b", "9b", "27b"])
-def test_logits_at_real_layer_sizes(models, shape, dtype):
+def test_logits_at_real_layer_sizes(models, shape, dtype, partition):
+    """Three unequal prompts, then one token each.  Contexts this short are cut into pieces whatever their
+    lengths; the second run deals their pages out as one stream, as the library does for long uneven batches."""
+    if partition and dtype == "float32":
+        pytest.skip("the 32-bit path has one attention kernel")
+    with decode_partition(partition):
+        _logits_at_real_layer_sizes(models, shape, dtype)
+
+
+def _logits_at_real_layer_sizes(models, shape, dtype):
     import trapetum_b200 as tb
     from trapetum_b200.csrc import ops
     folder, cfg, w, prompts, want = models(shape)

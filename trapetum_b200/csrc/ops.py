@@ -828,21 +828,46 @@ def choose_decode_splits(batch: int, n_kv_heads: int, pages: int, sms: int) -> i
     return best
 
 
+_DECODE_PARTITION = None          # None: chosen per launch; "split" or "stream": forced (tests, comparisons)
+
+
+def set_decode_partition(mode: Optional[str]) -> Optional[str]:
+    """Forces decode attention's partition ("split", "stream") or gives the choice back (None); returns the
+    previous setting.  Set it before an engine captures its decode graphs."""
+    global _DECODE_PARTITION
+    if mode not in (None, "split", "stream"):
+        raise KernelError(f"decode partition {mode!r}: None, 'split' or 'stream'")
+    was, _DECODE_PARTITION = _DECODE_PARTITION, mode
+    return was
+
+
+def decode_partition_is_stream(batch: int, n_kv_heads: int, pages: int, splits: int, uneven: int, sms: int) -> bool:
+    """Whether decode attention deals its pages out as one stream (else every sequence is cut into ``splits``
+    pieces).  A streaming launch costs about ten pages' time more (its CTAs walk several sequences: page prefix,
+    a rotation and a fold per run), so it is taken when the pieces of the longest sequence are at least that much
+    longer than an even share: ``uneven`` quarters of a piece's pages are saved at least.  And when cutting
+    every sequence would take more than two rounds of CTAs: each round pays its start-up again."""
+    per = (pages + splits - 1) // splits
+    return uneven * per >= 4 * 10 or batch * n_kv_heads * splits > 2 * sms
+
+
 def attn_decode(q, k_pool, v_pool, page_table, len_after, n_heads, n_kv_heads, head_dim, scale, softcap, window,
-                ring_rows, len_bucket: int, uneven: bool = False, rotate=None) -> torch.Tensor:
+                ring_rows, len_bucket: int, uneven: int = 0, rotate=None) -> torch.Tensor:
     """Decode attention, kernel and partition chosen here.  ``len_bucket``: an upper bound of the longest
     context of the batch (the engine passes a power of two so that the choice is stable across steps).
-    ``uneven``: the batch's contexts differ much in length; the pages are then dealt out to the CTAs as one
-    stream, so that the launch's time follows the sum of the lengths and not the longest one."""
+    ``uneven``: how much the batch's contexts differ in length (``engine.unevenness``, 0..3); if enough, the pages
+    are dealt out to the CTAs as one stream, so that the launch's time follows the sum of the lengths and not
+    the longest one."""
     B = q.shape[0] if rotate is None else q.shape[1]
     dt = q.dtype if rotate is None else torch.bfloat16
     rows = min(len_bucket, ring_rows) if ring_rows else len_bucket
     pages = max(1, (rows + PAGE_ROWS - 1) // PAGE_ROWS)
     sms = sm_count(q.device)
     splits = choose_decode_splits(B, n_kv_heads, pages, sms)
-    # One stream of pages over one CTA per SM when the lengths differ much, and when cutting every sequence would
-    # take several rounds of CTAs: each CTA of a round pays its start-up again, a streaming CTA pays it once.
-    if (uneven or B * n_kv_heads * splits > 2 * sms) and attn_decode_stream_takes(dt, n_heads, n_kv_heads, head_dim, B):
+    stream = decode_partition_is_stream(B, n_kv_heads, pages, splits, int(uneven), sms)
+    if _DECODE_PARTITION is not None:
+        stream = _DECODE_PARTITION == "stream"
+    if stream and attn_decode_stream_takes(dt, n_heads, n_kv_heads, head_dim, B):
         return attn_decode_stream(q, k_pool, v_pool, page_table, len_after, n_heads, n_kv_heads, head_dim, scale,
                                   softcap, window, ring_rows, rotate=rotate)
     if attn_decode_takes(dt, n_heads, n_kv_heads, head_dim):

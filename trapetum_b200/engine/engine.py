@@ -34,10 +34,20 @@ def _sm_count(device) -> int:
     return _SM_COUNT[idx]
 
 
+def unevenness(lens: Sequence[int]) -> int:
+    """How much a batch's context lengths differ, in quarters: 0 if their sum is at least three quarters of
+    batch x longest, 1 from a half on, 2 from a quarter on, else 3.  Work dealt out by the longest sequence
+    leaves that share of the GPU idle; decode attention weighs it against what dealing the pages out as one
+    stream costs (``ops.attn_decode``).  Launch shapes depend on the lengths only through this and the bucket."""
+    if len(lens) <= 1:
+        return 0
+    full = len(lens) * max(lens)
+    return max(0, min(3, 3 - (4 * sum(lens)) // full)) if full > 0 else 0
+
+
 def uneven_lengths(lens: Sequence[int]) -> bool:
-    """Whether a batch's context lengths differ so much that work dealt out by the longest one would leave
-    most of the GPU idle: the sum is under three quarters of batch x longest."""
-    return len(lens) > 1 and 4 * sum(lens) < 3 * len(lens) * max(lens)
+    """Whether the lengths differ at all in the sense of :func:`unevenness`."""
+    return unevenness(lens) > 0
 
 
 def len_bucket(max_len: int) -> int:
@@ -175,7 +185,7 @@ class Engine:
                           token_seq=dev["token_seq"], seq_start=dev["seq_start"], len_after=dev["len_after"],
                           slot_ids=dev["slot_ids"], slots=slots, seq_lens=lens, max_seq_len=max(lens),
                           max_len_after=max_after, len_bucket=len_bucket(max_after),
-                          uneven=(not is_prefill) and uneven_lengths(after))
+                          uneven=0 if is_prefill else unevenness(after))
         n_want = arrays["want"].size
         if n_want == 0:
             # nothing is asked for: the layers still run (they fill the cache), the head does not
@@ -201,7 +211,7 @@ class Engine:
         B = len(slots)
         max_after = max(after)
         bucket = len_bucket(max_after)
-        uneven = uneven_lengths(after)
+        uneven = unevenness(after)
         key = (B, bucket, uneven)
         dg = self._decode.get(key)
         if dg is None:
@@ -239,7 +249,7 @@ class Engine:
 class _DecodeShape:
     """The fixed-layout inputs, and later the graph, of decode steps of one batch size and length bucket."""
 
-    def __init__(self, B: int, bucket: int, engine: "Engine", uneven: bool = False):
+    def __init__(self, B: int, bucket: int, engine: "Engine", uneven: int = 0):
         self.B, self.bucket, self.uneven = B, bucket, uneven
         self.graph = None
         self.logits = None

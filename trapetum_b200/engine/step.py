@@ -40,7 +40,7 @@ class StepContext:
     max_seq_len: int                 # the longest of them
     max_len_after: int
     len_bucket: int = 0              # a power of two >= max_len_after: what launch shapes may depend on
-    uneven: bool = False             # decode: the contexts differ much in length (launch shapes may depend on it)
+    uneven: int = 0                  # decode: how much the contexts differ in length, 0..3 (launch shapes may depend on it)
     step_kv: Dict[int, tuple] = field(default_factory=dict)   # prefill: entry -> (k, v) of this step
     memo: Dict[str, object] = field(default_factory=dict)     # small per-step values that kernels share across layers
 

@@ -359,6 +359,15 @@ class Engine:
         return int(lib().tb_last_h2d_bytes(c_void_p(self._h)))
 
 
+def set_decode_partition(mode: Optional[str]) -> Optional[str]:
+    """As ``csrc.ops.set_decode_partition``, for the native host: "split", "stream" or None (chosen per launch)."""
+    codes = {None: 0, "split": 1, "stream": 2}
+    if mode not in codes:
+        raise ValueError(f"decode partition {mode!r}: None, 'split' or 'stream'")
+    was = int(lib().tb_set_decode_partition(ctypes.c_int(codes[mode])))
+    return {0: None, 1: "split", 2: "stream"}[was]
+
+
 def launches() -> int:
     """Kernels launched by the native host in this process (graph replays count their kernels)."""
     return int(lib().tb_kernel_launches())

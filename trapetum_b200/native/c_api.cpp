@@ -284,6 +284,12 @@ int tb_register_mixer(const char* kind, const tb_mixer_plugin* plugin) {
     TB_CATCH_STATUS
 }
 
+int tb_set_decode_partition(int mode) {
+    const int was = Ops::decode_partition_override();
+    Ops::decode_partition_override() = (mode == 1 || mode == 2) ? mode : 0;
+    return was;
+}
+
 int tb_register_feed_forward(const char* kind, const tb_mixer_plugin* plugin) {
     TB_TRY
     if (!kind || !*kind || !plugin || !plugin->create || !plugin->forward)

@@ -18,12 +18,18 @@ struct StepError : Error {
     using Error::Error;
 };
 
-inline bool uneven_lengths(const std::vector<int>& lens) {
-    if (lens.size() <= 1) return false;
+// How much a batch's context lengths differ, in quarters: 0 if their sum is at least three quarters of
+// batch x longest, 1 from a half on, 2 from a quarter on, else 3 (what share of the GPU stays idle if work is dealt
+// out by the longest sequence).  Launch shapes depend on the lengths only through this and the bucket.
+inline int unevenness(const std::vector<int>& lens) {
+    if (lens.size() <= 1) return 0;
     long long sum = 0;
     int mx = 0;
     for (int l : lens) { sum += l; mx = std::max(mx, l); }
-    return 4 * sum < 3 * (long long)lens.size() * mx;
+    const long long full = (long long)lens.size() * mx;
+    if (full <= 0) return 0;
+    const long long q = (4 * sum) / full;                        // quarters that are filled, rounded down (0..4)
+    return (int)std::max(0LL, std::min(3LL, 3 - q));
 }
 
 inline int len_bucket(int max_len) {
@@ -237,7 +243,7 @@ public:
 private:
     struct DecodeShape {
         int B = 0, bucket = 0;
-        bool uneven = false;
+        int uneven = 0;
         int hits = 0;
         InputBuffer in;
         Arena arena;
@@ -331,7 +337,7 @@ private:
         ctx.positions = in_.d(pos_off); ctx.token_seq = in_.d(tseq_off); ctx.seq_start = in_.d(start_off);
         ctx.len_after = in_.d(after_off); ctx.slot_ids = in_.d(slot_off);
         ctx.slots = slots; ctx.seq_lens = lens; ctx.max_seq_len = max_len; ctx.max_len_after = max_after;
-        ctx.len_bucket = len_bucket(max_after); ctx.uneven = !is_prefill && uneven_lengths(after);
+        ctx.len_bucket = len_bucket(max_after); ctx.uneven = is_prefill ? 0 : unevenness(after);
         std::vector<const int*> tables(G);
         for (size_t gi = 0; gi < G; gi++) tables[gi] = in_.d(table_off[gi]);
         std::vector<CacheLine> lines = lines_for(tables, widths);
@@ -366,7 +372,7 @@ private:
         int max_after = 0;
         for (int a : after) max_after = std::max(max_after, a);
         const int bucket = len_bucket(max_after);
-        const bool uneven = uneven_lengths(after);
+        const int uneven = unevenness(after);
         auto key = std::make_tuple(B, bucket, uneven);
         auto it = decode_.find(key);
         if (it == decode_.end()) it = decode_.emplace(key, make_shape(B, bucket, uneven)).first;
@@ -489,7 +495,7 @@ private:
         });
     }
 
-    std::unique_ptr<DecodeShape> make_shape(int B, int bucket, bool uneven) {
+    std::unique_ptr<DecodeShape> make_shape(int B, int bucket, int uneven) {
         std::unique_ptr<DecodeShape> d(new DecodeShape);
         d->B = B; d->bucket = bucket; d->uneven = uneven;
         const long long cap = std::min<long long>(model.max_positions, cache->max_tokens());
@@ -521,7 +527,7 @@ private:
     cudaStream_t own_stream_ = nullptr;
     bool graph_safe_ = true;
     std::set<std::tuple<bool, int, int, int, bool>> sized_shapes_;
-    std::map<std::tuple<int, int, bool>, std::unique_ptr<DecodeShape>> decode_;
+    std::map<std::tuple<int, int, int>, std::unique_ptr<DecodeShape>> decode_;
 };
 
 // ---- sampling options and the generation loop ------------------------------------------------------------------------

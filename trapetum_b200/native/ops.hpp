@@ -31,7 +31,7 @@ struct StepCtx {                         // what the parts may know about the ru
     const int* slot_ids = nullptr;       // [batch]
     std::vector<int> slots, seq_lens;    // host copies
     int max_seq_len = 0, max_len_after = 0, len_bucket = 0;
-    bool uneven = false;
+    int uneven = 0;                  // decode: how much the contexts differ in length, 0..3
     std::map<int, std::pair<Mat, Mat>> step_kv;      // prefill: entry -> (k, v) of this step
 };
 
@@ -281,6 +281,17 @@ public:
     static bool attn_decode_stream_takes(DType dt, int n_heads, int n_kv, int hd, int batch) {
         return attn_decode_takes(dt, n_heads, n_kv, hd) && hd >= 64 && batch <= 1024 && batch * n_kv <= TICKET_SLOTS;
     }
+    // Whether decode attention deals its pages out as one stream (see csrc/ops.py: decode_partition_is_stream).
+    static bool decode_partition_is_stream(int batch, int n_kv, int pages, int splits, int uneven, int sms) {
+        const int per = (pages + splits - 1) / splits;
+        return uneven * per >= 4 * 10 || batch * n_kv * splits > 2 * sms;
+    }
+    // 0: chosen per launch; 1: the split partition, 2: the stream partition (tests, comparisons)
+    static int& decode_partition_override() {
+        static int mode = 0;
+        return mode;
+    }
+
     // In how many pieces decode attention cuts a sequence's pages (see csrc/ops.py: choose_decode_splits).
     static int choose_decode_splits(int batch, int n_kv, int pages, int sms) {
         const int items = std::max(1, batch * n_kv);
@@ -319,7 +330,9 @@ public:
             a.qkv_part = part->p; a.qkv_splits = part->splits; a.qkv_split_stride = part->split_stride;
             a.qkv_row_stride = part->cols; a.inv_freq = inv_freq; a.rotary_dim = inv_freq ? rotary_dim : 0;
         }
-        if ((ctx.uneven || B * n_kv * splits > 2 * sms) && attn_decode_stream_takes(dt, n_heads, n_kv, hd, B)) {
+        bool one_stream = decode_partition_is_stream(B, n_kv, pages, splits, ctx.uneven, sms);
+        if (decode_partition_override()) one_stream = decode_partition_override() == 2;
+        if (one_stream && attn_decode_stream_takes(dt, n_heads, n_kv, hd, B)) {
             auto& l = K().lib("attention_decode");
             static auto nf = l.sym<long long (*)(int, int, int, int)>("tb_attn_decode_stream_scratch_floats");
             static auto f = l.sym<int (*)(const DecodeArgs*, int, int, int, cudaStream_t)>("tb_attn_decode_stream");

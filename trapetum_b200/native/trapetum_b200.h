@@ -28,6 +28,11 @@ const char* tb_last_error(void);
 /* Where the kernel libraries and their manifest.json lie (default: $TRAPETUM_KERNEL_DIR, else this library's folder). */
 int tb_set_kernel_dir(const char* dir);
 
+/* Decode attention's partition: 0 chosen per launch (the default), 1 every sequence cut into pieces, 2 all pages dealt
+ * out as one stream.  For tests and comparisons; set it before an engine captures its decode graphs.  Returns the
+ * previous setting. */
+int tb_set_decode_partition(int mode);
+
 /* A model from a folder.  spec_json: the model spec as the Python side serialises it, or NULL to build it here from
  * config.json (architectures this host knows by itself: Gemma2ForCausalLM).  dtype: "bfloat16" or "float32" (a true
  * 32-bit path).  fp16: what happens to float16 tensors in a bfloat16 engine: "widen" (NULL), "round" or "refuse". */
