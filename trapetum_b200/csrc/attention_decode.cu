@@ -30,7 +30,7 @@ TB_EXPORT_ERROR()
 
 #define PAGE 64
 
-__device__ int g_attn_error = 0;
+__device__ int g_attn_error = 0;          // 0, or: 1 a bounded wait ran out, 2 shared memory less aligned than budgeted, 3 too many runs in a CTA
 
 #include "decode_args.h"
 
@@ -408,6 +408,7 @@ __device__ __forceinline__ float softcap_fast(float x, float cap, float inv_cap)
 //           sequences.  A run that covers only part of a (sequence, kv head) leaves a partial: in the
 //           CTA's slot 1 if it begins the pair, in slot 0 if it continues one.
 #define STREAM_MAX_BATCH 1024
+#define HOT_RUNS_MAX ((2 * 8 * SROW - 1) / 2)        // runs of one CTA that hold a new token's page: their list lies in the scores' place
 
 // Walks pages in (sequence, kv head, page) order.  The same code runs in every thread (consumer side)
 // and, ahead of it, in the thread that issues the copies.
@@ -548,100 +549,83 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     // ---- fused rotation: this step's q, k, v come as partial sums of their product
     const bool fused = a.qkv_part != nullptr;
     const int half = (a.inv_freq != nullptr) ? (a.rotary_dim >> 1) : 0;      // rotated pairs per head
+    const int per = HD - half;                                               // items of a head: rotated pairs, then dims beyond them
     const int k_off = a.n_heads * HD, v_off = (a.n_heads + a.n_kv_heads) * HD;
-    auto qkv_val = [&](int b, int col) -> float {   // column `col` of sequence b's row: the splits added in order
-        const float* p = a.qkv_part + (size_t)b * a.qkv_row_stride + col;
-        float v = p[0];
-        for (int s0 = 1; s0 < a.qkv_splits; s0 += 4) {              // four independent loads at a time
-            float t4[4];
+    // Adds up partial sums into fold_s: segment g (HD columns) is the piece of sequence seg_b(g)'s row that begins at
+    // column seg_col(g).  Every partial sum that is needed is requested at once, four columns a thread and eight
+    // splits each, and added in the splits' order: one wait for memory.  For the nthr threads t0 = 0 .. nthr - 1.
+    auto bulk_sum = [&](int n_seg, auto seg_b, auto seg_col, int t0, int nthr) {
+        const int n_cols = n_seg * HD;
+        for (int c0 = t0; c0 < n_cols; c0 += 4 * nthr) {
+            float sum[4] = {0.f, 0.f, 0.f, 0.f};
+            const float* src[4];
 #pragma unroll
-            for (int k = 0; k < 4; k++) t4[k] = (s0 + k < a.qkv_splits) ? p[(size_t)(s0 + k) * a.qkv_split_stride] : 0.f;
+            for (int e = 0; e < 4; e++) {
+                const int c = min(c0 + e * nthr, n_cols - 1), g = c / HD;
+                src[e] = a.qkv_part + (size_t)seg_b(g) * a.qkv_row_stride + seg_col(g) + (c - g * HD);
+            }
+            for (int s0 = 0; s0 < a.qkv_splits; s0 += 8) {
+                float t8[4][8];
 #pragma unroll
-            for (int k = 0; k < 4; k++) if (s0 + k < a.qkv_splits) v += t4[k];
+                for (int e = 0; e < 4; e++)
+#pragma unroll
+                    for (int k = 0; k < 8; k++)
+                        if (c0 + e * nthr < n_cols && s0 + k < a.qkv_splits) t8[e][k] = src[e][(size_t)(s0 + k) * a.qkv_split_stride];
+#pragma unroll
+                for (int e = 0; e < 4; e++)
+#pragma unroll
+                    for (int k = 0; k < 8; k++)
+                        if (c0 + e * nthr < n_cols && s0 + k < a.qkv_splits) sum[e] = (s0 + k == 0) ? t8[e][k] : sum[e] + t8[e][k];
+            }
+#pragma unroll
+            for (int e = 0; e < 4; e++) if (c0 + e * nthr < n_cols) fold_s[c0 + e * nthr] = sum[e];
         }
-        return v;
     };
-    // head `col0` (first column) of sequence b, rotated at `pos`, rounded, to dst[0..HD) (and dst2 if set)
-    auto rotate_head = [&](int b, int col0, int pos, bf16* dst, bf16* dst2, int x) {
-        // x in [0, HD - half): a rotated pair, or a dim beyond the rotary part that passes through
+    // a head (its 32-bit values at hsrc) rotated at `pos` and rounded: item x is a rotated pair or a dim beyond the rotary part
+    auto rotate_from = [&](const float* hsrc, bf16* dst, int x, int pos) {
         if (x < half) {
             float sn, cs;
             sincosf((float)pos * a.inv_freq[x], &sn, &cs);
-            const float x0 = qkv_val(b, col0 + x), x1 = qkv_val(b, col0 + x + half);
-            const bf16 y0 = __float2bfloat16_rn(x0 * cs - x1 * sn), y1 = __float2bfloat16_rn(x1 * cs + x0 * sn);
-            dst[x] = y0; dst[x + half] = y1;
-            if (dst2) { dst2[x] = y0; dst2[x + half] = y1; }
+            const float x0 = hsrc[x], x1 = hsrc[x + half];
+            dst[x] = __float2bfloat16_rn(x0 * cs - x1 * sn);
+            dst[x + half] = __float2bfloat16_rn(x1 * cs + x0 * sn);
         } else {
-            const int d = x + half;
-            const bf16 y = __float2bfloat16_rn(qkv_val(b, col0 + d));
-            dst[d] = y;
-            if (dst2) dst2[d] = y;
+            dst[x + half] = __float2bfloat16_rn(hsrc[x + half]);
+        }
+    };
+    // where the new token's k and v rows of (sequence b, kv head kvh) lie in the pools
+    auto new_row = [&](int b, int kvh) -> size_t {
+        const int pos = a.len_after[b] - 1;
+        const int r = (a.ring_rows > 0) ? pos % a.ring_rows : pos;
+        const int page = a.page_table[(size_t)b * a.pt_stride + r / PAGE];
+        return ((size_t)(page * a.n_kv_heads + kvh) * PAGE + (r % PAGE)) * HD;
+    };
+    // k (32-bit at ksrc) rotated and v (at vsrc) rounded into the new token's rows, by the nthr threads t0 = 0 .. nthr - 1
+    auto append_kv = [&](int b, int kvh, const float* ksrc, const float* vsrc, int t0, int nthr) {
+        const size_t off = new_row(b, kvh);
+        bf16* kd = (bf16*)a.k_pool + off;
+        bf16* vd = (bf16*)a.v_pool + off;
+        const int pos = a.len_after[b] - 1;
+        for (int x = t0; x < per + HD; x += nthr) {
+            if (x < per) rotate_from(ksrc, kd, x, pos);
+            else vd[x - per] = __float2bfloat16_rn(vsrc[x - per]);
         }
     };
     if (fused && !STREAM) {
-        // Split: the CTA has one run.  Every partial sum that it needs (its G query heads; k and v too if its run holds
-        // the page of the new token, which this CTA and no other reads) is requested at once, four columns a thread
-        // and eight splits each, added in the splits' order and left in shared memory: one wait for memory.  Then
-        // the rotation works from there.
-        const int len0 = a.len_after[cur.b], pos = len0 - 1;
+        // Split: the CTA has one run.  It needs its G query heads; k and v too if its run holds the page of the new
+        // token, which this CTA and no other reads.
+        const int pos = a.len_after[cur.b] - 1;
         const int hot_rel = cur.hot - cur.first_page;
         const bool hot_here = cur.left > 0 && hot_rel >= cur.pg && hot_rel < cur.pg + cur.left;
-        const int n_cols = (G + (hot_here ? 2 : 0)) * HD;
-        const float* row = a.qkv_part + (size_t)cur.b * a.qkv_row_stride;
-        if (warp < TW) {
-            for (int c0 = tid; c0 < n_cols; c0 += 4 * TW * 32) {
-                float sum[4] = {0.f, 0.f, 0.f, 0.f};
-                const float* src[4];
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const int c = c0 + e * TW * 32;
-                    const int col = c < G * HD ? cur.kvh * G * HD + c
-                                  : c < (G + 1) * HD ? k_off + cur.kvh * HD + (c - G * HD) : v_off + cur.kvh * HD + (c - (G + 1) * HD);
-                    src[e] = row + col;
-                }
-                for (int s0 = 0; s0 < a.qkv_splits; s0 += 8) {
-                    float t8[4][8];
-#pragma unroll
-                    for (int e = 0; e < 4; e++)
-#pragma unroll
-                        for (int k = 0; k < 8; k++)
-                            if (c0 + e * TW * 32 < n_cols && s0 + k < a.qkv_splits) t8[e][k] = src[e][(size_t)(s0 + k) * a.qkv_split_stride];
-#pragma unroll
-                    for (int e = 0; e < 4; e++)
-#pragma unroll
-                        for (int k = 0; k < 8; k++)
-                            if (c0 + e * TW * 32 < n_cols && s0 + k < a.qkv_splits) sum[e] = (s0 + k == 0) ? t8[e][k] : sum[e] + t8[e][k];
-                }
-#pragma unroll
-                for (int e = 0; e < 4; e++) if (c0 + e * TW * 32 < n_cols) fold_s[c0 + e * TW * 32] = sum[e];
-            }
-        }
+        if (warp < TW)
+            bulk_sum(G + (hot_here ? 2 : 0), [&](int) { return cur.b; },
+                     [&](int g) { return g < G ? (cur.kvh * G + g) * HD : g == G ? k_off + cur.kvh * HD : v_off + cur.kvh * HD; },
+                     tid, TW * 32);
         __syncthreads();
         if (warp < TW) {
-            // head (first value fold_s[c0]) rotated at `pos` and rounded: item x is a rotated pair or a dim beyond the rotary part
-            auto rotate_from = [&](const float* hsrc, bf16* dst, int x) {
-                if (x < half) {
-                    float sn, cs;
-                    sincosf((float)pos * a.inv_freq[x], &sn, &cs);
-                    const float x0 = hsrc[x], x1 = hsrc[x + half];
-                    dst[x] = __float2bfloat16_rn(x0 * cs - x1 * sn);
-                    dst[x + half] = __float2bfloat16_rn(x1 * cs + x0 * sn);
-                } else {
-                    dst[x + half] = __float2bfloat16_rn(hsrc[x + half]);
-                }
-            };
-            const int per = HD - half;
-            for (int x = tid; x < G * per; x += TW * 32) rotate_from(fold_s + (x / per) * HD, q_s + (x / per) * HD, x % per);
+            for (int x = tid; x < G * per; x += TW * 32) rotate_from(fold_s + (x / per) * HD, q_s + (x / per) * HD, x % per, pos);
             if (hot_here) {
-                const int r = (a.ring_rows > 0) ? pos % a.ring_rows : pos;
-                const int page = a.page_table[(size_t)cur.b * a.pt_stride + r / PAGE];
-                const size_t off = ((size_t)(page * a.n_kv_heads + cur.kvh) * PAGE + (r % PAGE)) * HD;
-                bf16* kd = (bf16*)a.k_pool + off;
-                bf16* vd = (bf16*)a.v_pool + off;
-                for (int x = tid; x < per + HD; x += TW * 32) {
-                    if (x < per) rotate_from(fold_s + G * HD, kd, x);
-                    else vd[x - per] = __float2bfloat16_rn(fold_s[(G + 1) * HD + x - per]);
-                }
+                append_kv(cur.b, cur.kvh, fold_s + G * HD, fold_s + (G + 1) * HD, tid, TW * 32);
                 // the rows were written by ordinary stores and are read by the copy engine next
                 __threadfence();
                 asm volatile("fence.proxy.async;" ::: "memory");
@@ -649,35 +633,55 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         }
         __syncthreads();
     } else if (fused) {
-        if (warp >= TW / 2 && warp < TW) {
-            // the upper half of the warps rotates the first run's query heads into shared memory meanwhile
-            const int len0 = a.len_after[cur.b], per = HD - half;
-            for (int x = tid - (TW / 2) * 32; x < G * per; x += (TW / 2) * 32)
-                rotate_head(cur.b, (cur.kvh * G + x / per) * HD, len0 - 1, q_s + (x / per) * HD, nullptr, x % per);
-        }
-        // The runs of this CTA that hold the page of their sequence's new token: this CTA, and no other, reads
-        // that page, so it (the lower half of its warps) writes the token's k and v rows there first.
-        PageCursor w = cur;
-        while (w.left > 0 && warp < TW / 2) {
-            const int n = min(w.left, w.np - w.pg), hot_rel = w.hot - w.first_page;
-            if (hot_rel >= w.pg && hot_rel < w.pg + n) {
-                const int len = a.len_after[w.b], pos = len - 1;
-                const int r = (a.ring_rows > 0) ? pos % a.ring_rows : pos;
-                const int page = a.page_table[(size_t)w.b * a.pt_stride + r / PAGE];
-                const size_t off = ((size_t)(page * a.n_kv_heads + w.kvh) * PAGE + (r % PAGE)) * HD;
-                bf16* kd = (bf16*)a.k_pool + off;
-                bf16* vd = (bf16*)a.v_pool + off;
-                for (int x = tid; x < (HD - half) + HD; x += (TW / 2) * 32) {
-                    if (x < HD - half) rotate_head(w.b, k_off + w.kvh * HD, pos, kd, nullptr, x);
-                    else vd[x - (HD - half)] = __float2bfloat16_rn(qkv_val(w.b, v_off + w.kvh * HD + x - (HD - half)));
+        // Stream: the CTA has one run or several.  Those that hold the page of their sequence's new token (this CTA,
+        // and no other, reads that page) get the token's k and v rows written first; the first run's query heads go
+        // to shared memory.  In passes of up to ten heads' worth of partial sums (what fold_s holds): the first pass
+        // takes the G query heads and as many (k, v) pairs as fit beside them, the later ones five pairs each.
+        int* hot_runs = (int*)sf;                                   // [0] how many, then (sequence, kv head) each; scores come later
+        if (tid == 0) {
+            int n = 0;
+            PageCursor w = cur;
+            while (w.left > 0) {
+                const int nrun = min(w.left, w.np - w.pg), hot_rel = w.hot - w.first_page;
+                if (hot_rel >= w.pg && hot_rel < w.pg + nrun) {
+                    if (n == HOT_RUNS_MAX) { atomicExch(&g_attn_error, 3); s_abort = 1; break; }      // (the host refuses such launches)
+                    hot_runs[1 + 2 * n] = w.b; hot_runs[2 + 2 * n] = w.kvh; n++;
+                }
+                w.left -= nrun;
+                w.pg += nrun;
+                if (w.pg == w.np && w.left > 0) {
+                    w.pg = 0;
+                    if (++w.kvh == a.n_kv_heads) { w.kvh = 0; w.b++; w.np = seq_pages(w.b, w.first_page, w.hot); }
                 }
             }
-            w.left -= n;
-            w.pg += n;
-            if (w.pg == w.np && w.left > 0) {
-                w.pg = 0;
-                if (++w.kvh == a.n_kv_heads) { w.kvh = 0; w.b++; w.np = seq_pages(w.b, w.first_page, w.hot); }
+            hot_runs[0] = n;
+        }
+        __syncthreads();
+        const int n_hot = hot_runs[0];
+        const int q_b = cur.b, q_kvh = cur.kvh, q_pos = a.len_after[cur.b] - 1;
+        int done = 0;                                               // hot runs written so far
+        for (int pass = 0; pass == 0 || done < n_hot; pass++) {
+            const int nq = pass == 0 ? G : 0;                       // query heads in this pass
+            const int take = min(n_hot - done, (10 - nq) / 2);
+            if (warp < TW)
+                bulk_sum(nq + 2 * take,
+                         [&](int g) { return g < nq ? q_b : hot_runs[1 + 2 * (done + (g - nq) / 2)]; },
+                         [&](int g) {
+                             if (g < nq) return (q_kvh * G + g) * HD;
+                             const int kvh = hot_runs[2 + 2 * (done + (g - nq) / 2)];
+                             return ((g - nq) & 1) ? v_off + kvh * HD : k_off + kvh * HD;
+                         },
+                         tid, TW * 32);
+            __syncthreads();
+            if (warp < TW) {
+                for (int x = tid; x < nq * per; x += TW * 32) rotate_from(fold_s + (x / per) * HD, q_s + (x / per) * HD, x % per, q_pos);
+                // a pair of warps (64 threads) takes a hot run; four runs at a time
+                for (int r = warp / 2; r < take; r += TW / 2)
+                    append_kv(hot_runs[1 + 2 * (done + r)], hot_runs[2 + 2 * (done + r)], fold_s + (nq + 2 * r) * HD,
+                              fold_s + (nq + 2 * r + 1) * HD, tid & 63, 64);
             }
+            done += take;
+            __syncthreads();                                        // fold_s is free for the next pass; q_s is written
         }
         // the rows were written by ordinary stores and are read by the copy engine next
         __threadfence();
@@ -779,11 +783,11 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             if (fused) {
                 // the pair's query heads, rotated, go through shared memory (the first run's are there already)
                 if (!first_run) {
-                    if (!meet(0, meet_phase)) break;                // nobody reads the run before's queries any more
-                    for (int x = tid; x < G * (HD - half); x += (TW / 2) * 32) {
-                        const int g = x / (HD - half);
-                        rotate_head(b, (kvh * G + g) * HD, len - 1, q_s + g * HD, nullptr, x % (HD - half));
-                    }
+                    // the run's partial sums are requested at once and added up in fold_s (nothing else uses it now)
+                    bulk_sum(G, [&](int) { return b; }, [&](int g) { return (kvh * G + g) * HD; }, tid, (TW / 2) * 32);
+                    if (!meet(0, meet_phase)) break;                // the sums are there; nobody reads the run before's queries any more
+                    for (int x = tid; x < G * per; x += (TW / 2) * 32)
+                        rotate_from(fold_s + (x / per) * HD, q_s + (x / per) * HD, x % per, len - 1);
                     if (!meet(0, meet_phase)) break;
                 }
                 qp = q_s + quad * HD;
@@ -1301,6 +1305,10 @@ extern "C" int tb_attn_decode_stream(const DecodeArgs* args, int dtype, int batc
     if (a.page_rows != PAGE) return tb_refuse("attn_decode: pages of %d rows, this kernel is built for %d", a.page_rows, PAGE);
     if (batch > STREAM_MAX_BATCH) return tb_refuse("attn_decode_stream: batch %d, takes up to %d", batch, STREAM_MAX_BATCH);
     if (n_ctas < 1 || n_ctas > 65535) return tb_refuse("attn_decode_stream: n_ctas=%d", n_ctas);
+    // a CTA's runs are at most its share of the (sequence, kv head) pairs and one more
+    if (a.qkv_part != nullptr && ((long long)batch * a.n_kv_heads + n_ctas - 1) / n_ctas + 1 > HOT_RUNS_MAX)
+        return tb_refuse("attn_decode_stream: %d sequences x %d kv heads on %d CTAs are more runs per CTA than the fused rotation takes (%d)",
+                         batch, a.n_kv_heads, n_ctas, HOT_RUNS_MAX);
     if (a.partial == nullptr || a.tickets == nullptr) return tb_refuse("attn_decode_stream: needs scratch and ticket counters");
     if (a.qkv_part != nullptr) { if (int r = check_rotation(a)) return r; }
     else if (a.q == nullptr) return tb_refuse("attn_decode_stream: q is missing");

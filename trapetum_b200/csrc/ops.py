@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import ctypes
 from ctypes import c_float, c_int, c_longlong, c_void_p
-from typing import Optional
+from typing import Tuple, Optional
 
 import torch
 
@@ -799,8 +799,10 @@ def attn_decode_stream_takes(dtype: torch.dtype, n_heads: int, n_kv_heads: int, 
 
 
 def attn_decode_error() -> int:
-    """Reads and clears the decode attention's error word (synchronises); 0 = no wait ran out.  After an
-    error the ticket counters are zeroed again (a launch that gave up may have left them half counted)."""
+    """Reads and clears the decode attention's error word (synchronises): 0, or 1 a bounded wait ran out, 2 the
+    shared-memory block began less aligned than budgeted, 3 a CTA of the stream partition had more runs than its
+    list holds.  After an error the ticket counters are zeroed again (a launch that gave up may have left them
+    half counted)."""
     v = int(build.load("attention_decode").tb_attn_decode_error())
     if v:
         for t in _TICKETS.values():
@@ -851,6 +853,19 @@ def decode_partition_is_stream(batch: int, n_kv_heads: int, pages: int, splits: 
     return uneven * per >= 4 * 10 or batch * n_kv_heads * splits > 2 * sms
 
 
+def attn_decode_plan(batch: int, n_kv_heads: int, len_bucket: int, ring_rows: int, uneven: int, device) -> Tuple[bool, int]:
+    """(whether the pages of a decode launch are dealt out as one stream, else in how many pieces every sequence
+    is cut), from what a captured step may depend on."""
+    rows = min(len_bucket, ring_rows) if ring_rows else len_bucket
+    pages = max(1, (rows + PAGE_ROWS - 1) // PAGE_ROWS)
+    sms = sm_count(device)
+    splits = choose_decode_splits(batch, n_kv_heads, pages, sms)
+    stream = decode_partition_is_stream(batch, n_kv_heads, pages, splits, int(uneven), sms)
+    if _DECODE_PARTITION is not None:
+        stream = _DECODE_PARTITION == "stream"
+    return stream, splits
+
+
 def attn_decode(q, k_pool, v_pool, page_table, len_after, n_heads, n_kv_heads, head_dim, scale, softcap, window,
                 ring_rows, len_bucket: int, uneven: int = 0, rotate=None) -> torch.Tensor:
     """Decode attention, kernel and partition chosen here.  ``len_bucket``: an upper bound of the longest
@@ -860,13 +875,7 @@ def attn_decode(q, k_pool, v_pool, page_table, len_after, n_heads, n_kv_heads, h
     the longest one."""
     B = q.shape[0] if rotate is None else q.shape[1]
     dt = q.dtype if rotate is None else torch.bfloat16
-    rows = min(len_bucket, ring_rows) if ring_rows else len_bucket
-    pages = max(1, (rows + PAGE_ROWS - 1) // PAGE_ROWS)
-    sms = sm_count(q.device)
-    splits = choose_decode_splits(B, n_kv_heads, pages, sms)
-    stream = decode_partition_is_stream(B, n_kv_heads, pages, splits, int(uneven), sms)
-    if _DECODE_PARTITION is not None:
-        stream = _DECODE_PARTITION == "stream"
+    stream, splits = attn_decode_plan(B, n_kv_heads, len_bucket, ring_rows, uneven, q.device)
     if stream and attn_decode_stream_takes(dt, n_heads, n_kv_heads, head_dim, B):
         return attn_decode_stream(q, k_pool, v_pool, page_table, len_after, n_heads, n_kv_heads, head_dim, scale,
                                   softcap, window, ring_rows, rotate=rotate)
