@@ -212,9 +212,9 @@ def test_gemm_tc_gated_epilogue(ops, act, M, I, K, pair):
 def test_gemm_tc_pair_policy_and_cap(ops):
     """The default policy sends a long product to pairs of SMs and a short one to single SMs; either way the result
     is the same up to the order of additions inside an instruction, with a soft cap and through a row-strided view."""
-    big = rnd(300, 2 * 8192, dt=torch.bfloat16, s=0.5)
-    a = big[:, 8192:]                                                # row stride 16384
-    w = rnd(520, 8192, dt=torch.bfloat16, s=0.05, seed=1)
+    big = rnd(2048, 2 * 4096, dt=torch.bfloat16, s=0.5)
+    a = big[:, 4096:]                                                # row stride 8192
+    w = rnd(16384 + 8, 4096, dt=torch.bfloat16, s=0.05, seed=1)      # 8 x 65 tiles of 64 k-blocks: long enough for the pair
     want = 5 * torch.tanh(a.double() @ w.double().T / 5)
     outs = []
     for mode in (0, 1, 2):
@@ -226,7 +226,7 @@ def test_gemm_tc_pair_policy_and_cap(ops):
     assert was == 2                                                  # the default
     for got in outs:
         assert float((got.double() - want).abs().max()) < 1e-4
-    assert torch.equal(outs[2], outs[1])                             # K of 8,192: where the pair pays
+    assert torch.equal(outs[2], outs[1])                             # where the pair pays
     short = rnd(520, 64, dt=torch.bfloat16, s=0.5, seed=2)
     x = rnd(300, 64, dt=torch.bfloat16, s=0.5, seed=3)
     ops.gemm_tc_set_pair(0)

@@ -598,12 +598,14 @@ extern "C" int tb_gemm_tc_set_pair(int mode) { const int was = g_pair; g_pair = 
 
 // Where the pair kernel pays.  Its launch costs about a microsecond more (a cluster is placed, two cluster barriers),
 // its main loop runs 5 to 10 % faster.  Measured against the single-SM kernel with weights from memory, 512 to 8,192
-// tokens on the 2B, 9B and 27B shapes: from about 300 k-blocks of work per pair on, or with K of 8,192 and more, the
-// pair is 3 to 12 % faster; below, equal or up to 7 % slower.
+// tokens on the 2B, 9B and 27B shapes: from about 300 k-blocks of work per pair on the pair is 3 to 12 % faster;
+// below, equal or up to 7 % slower.  Whole prompts under sustained load (blocks of twelve repetitions, alternating):
+// 27B shape at 2,048 tokens 98.8 -> 95.0 ms, 2B shape at 8,192 tokens 42.2 -> 41.3 ms, 9B shape at 2,048 equal; the 2B
+// shape at 2,048 tokens has no product that long and does not use it.
 static bool pair_pays(int M, int N, int K) {
     const long long tiles = (long long)((M + 255) / 256) * ((N + 255) / 256);
     const long long kblocks = (K + BK - 1) / BK;
-    return K >= 8192 || tiles * kblocks >= 300LL * (g_sms / 2);
+    return tiles * kblocks >= 300LL * (g_sms / 2);
 }
 
 template <typename TOut, bool GATED>
