@@ -54,16 +54,22 @@ def models(tmp_path_factory):
     return get
 
 
-@pytest.mark.parametrize("partition", [None, "stream"])
+@pytest.mark.parametrize("variant", ["as chosen", "stream and pairs"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("shape", ["2b", "9b", "27b"])
-def test_logits_at_real_layer_sizes(models, shape, dtype, partition):
+def test_logits_at_real_layer_sizes(models, shape, dtype, variant):
     """Three unequal prompts, then one token each.  Contexts this short are cut into pieces whatever their
-    lengths; the second run deals their pages out as one stream, as the library does for long uneven batches."""
-    if partition and dtype == "float32":
-        pytest.skip("the 32-bit path has one attention kernel")
-    with decode_partition(partition):
-        _logits_at_real_layer_sizes(models, shape, dtype)
+    lengths, and prompts this short run their products on single SMs; the second run deals the pages out as one
+    stream and sends the products to pairs of SMs, as the library does for long uneven batches and long prompts."""
+    from trapetum_b200.csrc import ops
+    if variant != "as chosen" and dtype == "float32":
+        pytest.skip("the 32-bit path has one attention kernel and one product kernel")
+    was = ops.gemm_tc_set_pair(1 if variant != "as chosen" else 2)
+    try:
+        with decode_partition("stream" if variant != "as chosen" else None):
+            _logits_at_real_layer_sizes(models, shape, dtype)
+    finally:
+        ops.gemm_tc_set_pair(was)
 
 
 def _logits_at_real_layer_sizes(models, shape, dtype):
