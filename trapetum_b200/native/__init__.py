@@ -131,7 +131,7 @@ class Model:
         self.vocab_size = lib().tb_model_vocab(c_void_p(handle))
 
     def __del__(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and _graveyard is not None:         # (None while the interpreter shuts down)
             _graveyard.append(("model", self._h))
             self._h = None
 
@@ -286,7 +286,8 @@ class Engine:
 
     def __del__(self):
         if getattr(self, "_h", None):
-            _graveyard.insert(0, ("engine", self._h))          # engines go before their models
+            if _graveyard is not None:                        # (None while the interpreter shuts down)
+                _graveyard.insert(0, ("engine", self._h))      # engines go before their models
             self._h = None
 
     def _on_torch_stream(self) -> None:
