@@ -141,7 +141,7 @@ __global__ void rope_kv_kernel(RopeKvArgs a) {
 // rotary_dim a multiple of 16: one warp per token, 16-byte accesses.  A lane owns eight neighbouring pairs
 // (dims i..i+7 and i+half..i+half+7) of every second head slot; their sines and cosines are computed once and
 // reused for all the heads the lane visits.
-__global__ void __launch_bounds__(256) rope_kv_rows_kernel(RopeKvArgs a, int n_tokens) {
+__global__ void __launch_bounds__(256, 2) rope_kv_rows_kernel(RopeKvArgs a, int n_tokens) {
     pdl_launch_dependents();
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -176,19 +176,33 @@ __global__ void __launch_bounds__(256) rope_kv_rows_kernel(RopeKvArgs a, int n_t
         return make_uint4(u[0], u[1], u[2], u[3]);
     };
     const int qk_slots = a.n_heads + a.n_kv_heads;
+    // ---- what is only copied to the cache (k dims beyond the rotary part, and v): requested first, stored last, so
+    // that the token's row is on its way while the sines and cosines are made
+    const int k_tail = chunks - 2 * groups;             // chunks per k head that pass through
+    const int n_copy = store ? a.n_kv_heads * (k_tail + chunks) : 0;
+    auto copy_src = [&](int x) -> const bf16* {
+        const int kvh = x / (k_tail + chunks), c = x % (k_tail + chunks);
+        return c < k_tail ? row + a.k_off + kvh * hd + 2 * half + c * 8 : row + a.v_off + kvh * hd + (c - k_tail) * 8;
+    };
+    auto copy_dst = [&](int x) -> bf16* {
+        const int kvh = x / (k_tail + chunks), c = x % (k_tail + chunks);
+        return c < k_tail ? (bf16*)a.k_pool + cache_off + (size_t)kvh * a.page_rows * hd + 2 * half + c * 8
+                          : (bf16*)a.v_pool + cache_off + (size_t)kvh * a.page_rows * hd + (c - k_tail) * 8;
+    };
+    constexpr int HELD = 4;                             // copied chunks a lane holds in registers (more go round a loop at the end)
+    uint4 held[HELD];
+#pragma unroll
+    for (int i = 0; i < HELD; i++)
+        if (lane + 32 * i < n_copy) held[i] = *(const uint4*)copy_src(lane + 32 * i);
     // ---- rotated part of q and k heads: work items (head slot, group of eight pairs)
     if (groups > 0) {
         const int lanes_per_head = groups < 32 ? groups : 32;          // groups <= 16 for head_dim <= 256
         const int heads_at_once = 32 / lanes_per_head;
         const int g = lane % lanes_per_head, h0 = lane / lanes_per_head;
-        float sn[8], cs[8];
         if (h0 < heads_at_once) {
-#pragma unroll
-            for (int e = 0; e < 8; e++) sincosf((float)pos * a.inv_freq[g * 8 + e], &sn[e], &cs[e]);
-            // four head slots at a time: their loads are requested together, so that a warp waits for memory
-            // once per four heads and not once per head
-            for (int hs0 = h0; hs0 < qk_slots; hs0 += 4 * heads_at_once) {
-                uint4 wlo[4], whi[4];
+            // four head slots at a time: their loads are requested together, and the next four before these are
+            // worked on, so that a warp waits for memory once and not once per head
+            auto fetch = [&](int hs0, uint4* wlo, uint4* whi) {
 #pragma unroll
                 for (int u = 0; u < 4; u++) {
                     const int hs = hs0 + u * heads_at_once;
@@ -198,6 +212,14 @@ __global__ void __launch_bounds__(256) rope_kv_rows_kernel(RopeKvArgs a, int n_t
                         whi[u] = *(const uint4*)(row + col0 + half + g * 8);
                     }
                 }
+            };
+            uint4 wlo[4], whi[4], nlo[4], nhi[4];
+            fetch(h0, wlo, whi);
+            float sn[8], cs[8];
+#pragma unroll
+            for (int e = 0; e < 8; e++) sincosf((float)pos * a.inv_freq[g * 8 + e], &sn[e], &cs[e]);
+            for (int hs0 = h0; hs0 < qk_slots; hs0 += 4 * heads_at_once) {
+                fetch(hs0 + 4 * heads_at_once, nlo, nhi);
 #pragma unroll
                 for (int u = 0; u < 4; u++) {
                     const int hs = hs0 + u * heads_at_once;
@@ -218,24 +240,15 @@ __global__ void __launch_bounds__(256) rope_kv_rows_kernel(RopeKvArgs a, int n_t
                         }
                     }
                 }
+#pragma unroll
+                for (int u = 0; u < 4; u++) { wlo[u] = nlo[u]; whi[u] = nhi[u]; }
             }
         }
     }
-    if (!store) return;
-    // ---- what is only copied to the cache: k dims beyond the rotary part, and v
-    const int k_tail = chunks - 2 * groups;             // chunks per k head that pass through
-    for (int x = lane; x < a.n_kv_heads * (k_tail + chunks); x += 32) {
-        const int kvh = x / (k_tail + chunks), c = x % (k_tail + chunks);
-        if (c < k_tail) {
-            const int d = 2 * half + c * 8;
-            *(uint4*)((bf16*)a.k_pool + cache_off + (size_t)kvh * a.page_rows * hd + d) =
-                *(const uint4*)(row + a.k_off + kvh * hd + d);
-        } else {
-            const int d = (c - k_tail) * 8;
-            *(uint4*)((bf16*)a.v_pool + cache_off + (size_t)kvh * a.page_rows * hd + d) =
-                *(const uint4*)(row + a.v_off + kvh * hd + d);
-        }
-    }
+#pragma unroll
+    for (int i = 0; i < HELD; i++)
+        if (lane + 32 * i < n_copy) *(uint4*)copy_dst(lane + 32 * i) = held[i];
+    for (int x = lane + 32 * HELD; x < n_copy; x += 32) *(uint4*)copy_dst(x) = *(const uint4*)copy_src(x);
 }
 
 extern "C" int tb_rope_kv(const RopeKvArgs* args, int dtype, int n_tokens, cudaStream_t stream) {
