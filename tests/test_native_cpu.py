@@ -174,3 +174,27 @@ def test_native_batch_planning_is_the_python_side_s(L):
             continue
         n = L.tb_plan_batches((I * len(lens))(*lens), len(lens), max_new, max_batch, ctypes.c_longlong(max_tokens), max_pos, out)
         assert n == len(want) and [[i for i in range(len(lens)) if out[i] == b] for b in range(n)] == want
+
+
+def test_native_decode_launch_shapes_are_the_python_side_s(L):
+    """Bucket, unevenness, pieces and partition of a decode step: both hosts must choose alike, or their steps would
+    not give the same bits."""
+    from trapetum_b200.csrc.ops import PAGE_ROWS, choose_decode_splits, decode_partition_is_stream
+    from trapetum_b200.engine.engine import len_bucket, unevenness
+    rng = random.Random(2)
+    I = ctypes.c_int
+    for _ in range(300):
+        n = rng.choice([1, 2, 3, 8, 17, 64])
+        top = rng.choice([5, 70, 600, 3000, 8192])
+        lens = [rng.randint(1, top) for _ in range(n)]
+        if rng.random() < 0.3:
+            lens = [top] * n
+        n_kv, ring, sms = rng.choice([1, 2, 4, 8, 16]), rng.choice([0, 0, 128, 4096]), rng.choice([148, 132, 64])
+        out = (I * 3)()
+        stream = L.tb_decode_launch_shape((I * n)(*lens), n, n_kv, ring, sms, out)
+        bucket = len_bucket(max(lens))
+        rows = min(bucket, ring) if ring else bucket
+        pages = max(1, (rows + PAGE_ROWS - 1) // PAGE_ROWS)
+        splits = choose_decode_splits(n, n_kv, pages, sms)
+        assert [out[0], out[1], out[2]] == [bucket, unevenness(lens), splits], (lens, n_kv, ring, sms)
+        assert stream == int(decode_partition_is_stream(n, n_kv, pages, splits, unevenness(lens), sms))

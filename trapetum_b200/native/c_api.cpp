@@ -333,6 +333,23 @@ int tb_plan_batches(const int* prompt_lens, int n, int max_new, int max_batch, l
     }
 }
 
+int tb_decode_launch_shape(const int* lens_after, int n, int n_kv_heads, int ring_rows, int sms, int* out3) {
+    try {
+        if (n <= 0 || n_kv_heads <= 0 || sms <= 0) throw Error("tb_decode_launch_shape: a batch, kv heads and SMs are needed");
+        std::vector<int> lens(lens_after, lens_after + n);
+        const int bucket = len_bucket(*std::max_element(lens.begin(), lens.end()));
+        const int rows = ring_rows ? std::min(bucket, ring_rows) : bucket;
+        const int pages = std::max(1, (rows + PAGE_ROWS - 1) / PAGE_ROWS);
+        const int uneven = unevenness(lens);
+        const int splits = Ops::choose_decode_splits(n, n_kv_heads, pages, sms);
+        out3[0] = bucket; out3[1] = uneven; out3[2] = splits;
+        return Ops::decode_partition_is_stream(n, n_kv_heads, pages, splits, uneven, sms) ? 1 : 0;
+    } catch (const std::exception& ex) {
+        fail(ex);
+        return -1;
+    }
+}
+
 struct tb_sim_cache {
     std::unique_ptr<Cache> c;
 };

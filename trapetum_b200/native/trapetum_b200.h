@@ -109,12 +109,16 @@ int tb_cache_grow(tb_engine* e, const int* slots, const int* growth, int n);    
  * everything that does not fit.
  * tb_plan_batches: cuts requests into batches as tb_generate does; batch_of[i] is request i's batch; returns the
  * number of batches, -1 on error.
+ * tb_decode_launch_shape: what a decode step's launches depend on, for a batch with these lengths after the step:
+ * out3 = {length bucket, unevenness of the lengths (0..3), pieces a sequence's pages are cut into}; returns 1 if the
+ * pages are dealt out as one stream instead, 0 if not, -1 on error.
  * tb_sim_cache_*: the cache's bookkeeping without storage.  needs_json: [{"entry", "n_kv_heads", "head_dim",
  * "window" (0: none)} or {"entry", "state_bytes"}, ...]. */
 const char* tb_spec_from_config(const char* config_json);
 int tb_check_weights(const char* folder, const char* spec_json, const char* dtype, const char* fp16);
 int tb_plan_batches(const int* prompt_lens, int n, int max_new, int max_batch, long long max_tokens, int max_positions,
                     int* batch_of);
+int tb_decode_launch_shape(const int* lens_after, int n, int n_kv_heads, int ring_rows, int sms, int* out3);
 typedef struct tb_sim_cache tb_sim_cache;
 tb_sim_cache* tb_sim_cache_new(const char* needs_json, long long max_tokens, int max_slots);
 void tb_sim_cache_free(tb_sim_cache* c);
